@@ -1,0 +1,383 @@
+// Candidate tabulation: the ordered action list of a logical Spec, reduced to the
+// limits-independent facts the combine kernel needs.
+//
+// The action list of a Spec depends only on its logical part; memory limits decide
+// applicability at evaluation time (morello/src/spec.rs:4551-4553). For every action
+// that can apply at SOME limits this emits one Candidate: its ActionNum (index in the
+// reference's enumeration order, counting inapplicable actions too,
+// morello/src/search/spectask.rs:66), a combine kind, integer immediates, the memory
+// it consumes and its sub-Specs in request order.
+//
+// Restates: morello/src/target/cpu.rs:455-823 (Target::actions), :896-1879 (kernel
+// applicability), :1881-1998 (kernel memory), :2000-2380 (kernel cost), :2719-2808
+// (broadcastvecmult_side); morello/src/target/common_actions.rs:37-121 (tile-outs),
+// :123-249 (splits), :301-376 (moves); morello/src/scheduling/tiling.rs:132-228,478-541
+// (TileOut/Split solvers); morello/src/scheduling/moves.rs:118-138,275-381,383-528
+// (Move solver); morello/src/scheduling/to_accum.rs:12-62; morello/src/scheduling/select.rs:13-56.
+#pragma once
+#include "spec.hpp"
+
+namespace mrl {
+
+// How a candidate's Cost is combined from its children (morello/src/scheduling/mod.rs:286-368).
+enum CombineKind : u8 {
+  CK_LEAF = 0,   // Select(kernel): no children; cost and allocation are constants
+  CK_LOOP = 1,   // TileOut / Split without boundary: main = child.main * iters (saturating),
+                 //   peaks = child's, depth = 1
+  CK_MOVE = 2,   // Move: main = base + sum(children) (saturating), peaks fold own + child,
+                 //   depth = max + 1; children see limits lowered by `units` in `level`
+  CK_BLOCK = 3,  // ToAccum: main = sum(children) (saturating), peaks = fold with no own
+                 //   allocation, depth = max + 1; same limits
+};
+
+struct Candidate {
+  u16 action = 0;
+  u8 kind = CK_LEAF;
+  u8 nchild = 0;
+  u32 imm = 0;    // LEAF: kernel main cost; LOOP: iteration count; MOVE: base main cost
+  u8 level = 0;   // memory index that `units` refers to
+  u32 units = 0;  // MOVE: units consumed in `level`; LEAF: kernel allocation in `level`
+  LogicalSpec child[3];
+};
+
+// ---- leaf kernels ----
+inline bool is_rf_or_l1(Mem m) { return m == RF || m == L1; }
+
+// broadcastvecmult_side(..).is_some() (cpu.rs:2719-2808)
+inline bool broadcastvecmult_applies(const TensorSpec* op) {
+  const TensorSpec& out = op[2];
+  if (out.aux.mem != VRF || !out.is_contiguous()) return false;
+  if (!op[0].is_contiguous() || !op[1].is_contiguous()) return false;
+  if (op[0].shape[0] != out.shape[0] || op[1].shape[0] != out.shape[0]) return false;
+  u32 ovs = out.aux.vector_size;
+  if (ovs == 0) return false;
+  if (out.volume() % ovs != 0) return false;
+  const int pairs[2][2] = {{0, 1}, {1, 0}};
+  for (auto& pr : pairs) {
+    const TensorSpec& scalar = op[pr[0]];
+    const TensorSpec& bcast = op[pr[1]];
+    if (!is_rf_or_l1(scalar.aux.mem) || !scalar.is_contiguous() || bcast.aux.mem != VRF || !bcast.is_contiguous()) continue;
+    if (!scalar.shape.all_ones()) continue;
+    if (bcast.aux.vector_size != ovs || bcast.volume() % ovs != 0) continue;
+    u32 b1 = bcast.shape[1], b2 = bcast.shape[2], s1 = scalar.shape[1], s2 = scalar.shape[2];
+    u32 o1 = out.shape[1], o2 = out.shape[2];
+    if (s1 == o1 && s2 == 1 && b1 == 1 && b2 == o2) return true;
+    if (s1 == 1 && s2 == o2 && b1 == o1 && b2 == 1) return true;
+  }
+  return false;
+}
+
+struct LeafInfo { bool applies = false; u32 main = 0; u8 level = 0; u32 units = 0; };
+
+enum LeafKernel : u8 { LK_MULTADD, LK_BCAST_VEC_MULTADD, LK_DOT_PRODUCT_LOOP, LK_ASSIGN, LK_MEMSET_ZERO, LK_VALUE_ZERO, LK_VECTOR_ZERO };
+
+inline LeafInfo leaf_kernel_info(LeafKernel k, const LogicalSpec& spec) {
+  LeafInfo r;
+  TensorSpec op[MAX_OPS];
+  for (int i = 0; i < spec.nops(); i++) op[i] = spec.operand(i);
+  u32 io = 0;
+  for (int i = 0; i < spec.nops(); i++) io += move_cost(op[i]);
+  switch (k) {
+    case LK_MULTADD: {  // cpu.rs:914-921, 2315-2340
+      if (spec.kind != K_MATMUL_ACCUM) return r;
+      for (int i = 0; i < 3; i++) if (!is_rf_or_l1(op[i].aux.mem) || !op[i].shape.all_ones()) return r;
+      r.applies = true;
+      r.main = (spec.dtype == DT_F32 ? 1 : (spec.dtype == DT_BF16 ? 30 : 2)) + io;
+      return r;
+    }
+    case LK_BCAST_VEC_MULTADD: {  // cpu.rs:922-943, 1884-1897, 2010-2036
+      if (spec.kind != K_MATMUL_ACCUM) return r;
+      if (spec.dtype == DT_BF16) return r;
+      if (!broadcastvecmult_applies(op)) return r;
+      r.applies = true;
+      u32 vcount = (u32)op[2].volume() / op[2].aux.vector_size;
+      r.main = vcount * 2 + 1;
+      r.level = VRF; r.units = 1;
+      return r;
+    }
+    case LK_DOT_PRODUCT_LOOP: {  // cpu.rs:988-1031, 1910-1923, 2037-2042
+      if (spec.kind != K_MATMUL_ACCUM || spec.dtype != DT_F32) return r;
+      const TensorSpec &lhs = op[0], &rhs = op[1], &out = op[2];
+      if (lhs.shape[0] != 1 || lhs.shape[1] != 1) return r;
+      if (lhs.shape[2] % 8 != 0) return r;  // vector_accum_count(k, 8).is_some()
+      if (!out.shape.all_ones()) return r;
+      if (!lhs.aux.layout.is_row_major() || !rhs.aux.layout.is_col_major()) return r;
+      if (!lhs.is_contiguous() || !rhs.is_contiguous()) return r;
+      if (lhs.aux.vector_size != 0 && lhs.aux.vector_size != 8) return r;
+      if (rhs.aux.vector_size != 0 && rhs.aux.vector_size != 8) return r;
+      if (!(lhs.aux.mem == L1 || (lhs.aux.mem == VRF && lhs.aux.vector_size == 8))) return r;
+      if (rhs.aux.mem != L1 || !is_rf_or_l1(out.aux.mem)) return r;
+      r.applies = true;
+      r.main = 8 * lhs.shape[2] / 32 + move_cost(out);
+      r.level = VRF; r.units = 1;
+      return r;
+    }
+    case LK_ASSIGN: {  // cpu.rs:1694-1745, 2351-2370
+      if (spec.kind != K_MOVE) return r;
+      bool scalar = op[0].shape.all_ones() && op[1].shape.all_ones();
+      if (scalar) {
+        if (op[0].aux.layout != op[1].aux.layout) return r;
+        if (!is_rf_or_l1(op[0].aux.mem) || !is_rf_or_l1(op[1].aux.mem)) return r;
+        r.applies = true;
+        r.main = io + 1;
+        return r;
+      }
+      if (!op[0].is_contiguous() || !op[1].is_contiguous()) return r;
+      if (op[0].aux.layout != op[1].aux.layout) return r;
+      bool has_vrf = false;
+      for (int i = 0; i < 2; i++) {
+        if (mem_is_vector(op[i].aux.mem)) {
+          has_vrf = true;
+          if (op[i].volume() % op[i].aux.vector_size != 0) return r;
+        }
+      }
+      if (!has_vrf) return r;
+      r.applies = true;
+      u32 vs = op[0].aux.vector_size ? op[0].aux.vector_size : op[1].aux.vector_size;
+      r.main = (u32)op[0].volume() / vs;
+      return r;
+    }
+    case LK_MEMSET_ZERO: {  // cpu.rs:1812-1821, 2371
+      if (spec.kind != K_FILL_ZERO) return r;
+      if (op[0].aux.mem == RF || op[0].aux.mem == VRF || !op[0].is_contiguous()) return r;
+      r.applies = true; r.main = 1;
+      return r;
+    }
+    case LK_VALUE_ZERO: {  // cpu.rs:1822-1831, 2057-2069
+      if (spec.kind != K_FILL_ZERO) return r;
+      if (op[0].volume() != 1 || !is_rf_or_l1(op[0].aux.mem)) return r;
+      r.applies = true; r.main = io + 1;
+      return r;
+    }
+    case LK_VECTOR_ZERO: {  // cpu.rs:1832-1856, 2372-2378
+      if (spec.kind != K_FILL_ZERO) return r;
+      if (!op[0].is_contiguous() || op[0].aux.mem != VRF) return r;
+      if (op[0].aux.vector_size == 0 || op[0].aux.vector_size != op[0].volume()) return r;
+      r.applies = true; r.main = 1;
+      return r;
+    }
+  }
+  return r;
+}
+
+// ---- Move planning (scheduling/moves.rs:275-381 plan_alloc_shared, :383-528) ----
+struct MovePlan {
+  bool applies = false;
+  TensorSpec new_spec;
+  bool cache_miss = false;
+  u64 units = 0;
+};
+
+inline MovePlan plan_move(const TensorSpec& src, Mem dest, const Layout& dest_layout, u32 dest_vs) {
+  MovePlan p;
+  Layout lay;
+  bool miss = false;
+  if (!mem_has_layout(dest)) {
+    lay = Layout();
+    miss = false;  // RF is addressed: never a cache miss
+  } else if (!mem_is_addressed(dest)) {
+    if (!layout_canonicalize(dest_layout, src.shape, lay))
+      throw ModelError("destination layout does not apply to the moved tensor");
+    miss = (src.aux.layout == lay);
+    if (!miss) lay.contig = lay.n;
+  } else {
+    lay = dest_layout;
+    lay.contig = lay.n;
+  }
+  p.new_spec.shape = src.shape;
+  p.new_spec.dtype = src.dtype;
+  p.new_spec.aux.mem = dest;
+  p.new_spec.aux.layout = lay;
+  p.new_spec.aux.vector_size = (u8)dest_vs;
+  if (!miss) {
+    if (tensorspec_canonicalize(p.new_spec) != CANON_OK) return p;
+  }
+  if (src == p.new_spec) return p;  // SelfMove
+  p.cache_miss = miss;
+  p.units = tensorspec_memory_units(p.new_spec);
+  p.applies = true;
+  return p;
+}
+
+inline LogicalSpec make_move_spec(const TensorSpec& left, const TensorSpec& right, bool serial_only) {
+  LogicalSpec l;
+  l.kind = K_MOVE;
+  l.dtype = left.dtype;
+  l.serial_only = serial_only;
+  l.spec_shape = left.shape;
+  l.aux[0] = left.aux;
+  l.aux[1] = right.aux;
+  canonicalize_matching_contiguous_move_auxes(l);
+  return l;
+}
+
+// ---- the enumeration ----
+// Returns the total number of enumerated actions (applicable or not).
+inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& out) {
+  if (!spec.serial_only) throw ModelError("only serial-only Specs are tabulated");
+  u32 action = 0;
+  const int nops = spec.nops();
+  TensorSpec ops[MAX_OPS];
+  for (int i = 0; i < nops; i++) ops[i] = spec.operand(i);
+
+  // 1. Moves (common_actions.rs:301-376)
+  auto emit_move = [&](int i, Mem mem, const Layout& layout, u32 vs) {
+    u32 this_action = action++;
+    MovePlan p = plan_move(ops[i], mem, layout, vs);
+    if (!p.applies) return;
+    Candidate c;
+    c.action = (u16)this_action;
+    c.kind = CK_MOVE;
+    c.level = (u8)mem;
+    c.units = (u32)p.units;
+    c.imm = move_cost(ops[i]) + move_cost(p.new_spec);
+    Direction dir = kind_direction(spec.kind, i);
+    bool prologue = !p.cache_miss && (dir == DIR_IN || dir == DIR_INOUT);
+    bool epilogue = !p.cache_miss && (dir == DIR_OUT || dir == DIR_INOUT);
+    int n = 0;
+    if (prologue) c.child[n++] = make_move_spec(ops[i], p.new_spec, spec.serial_only);
+    LogicalSpec body = spec;
+    body.aux[i] = p.new_spec.aux;
+    if (body.kind == K_MOVE) canonicalize_matching_contiguous_move_auxes(body);
+    c.child[n++] = body;
+    if (epilogue) c.child[n++] = make_move_spec(p.new_spec, ops[i], spec.serial_only);
+    c.nchild = (u8)n;
+    out.push_back(c);
+  };
+  for (int i = 0; i < nops; i++) {
+    std::vector<Layout> dest_layouts = move_destination_layouts(ops[i].shape, ops[i].dtype);
+    std::vector<Mem> dest_mems = possible_destination_memories(ops[i].aux.mem);
+    bool contains_source_layout = false;
+    for (const Layout& layout : dest_layouts) {
+      if (!contains_source_layout && layout == ops[i].aux.layout) contains_source_layout = true;
+      for (Mem mem : dest_mems) {
+        const std::vector<u32>& vb = mem_vector_bytes(mem);
+        if (vb.empty()) emit_move(i, mem, layout, 0);
+        else for (u32 b : vb) emit_move(i, mem, layout, b / dtype_size(ops[i].dtype));
+      }
+    }
+    if (!contains_source_layout) {
+      for (Mem mem : dest_mems) {
+        if (mem_is_addressed(mem)) continue;
+        emit_move(i, mem, ops[i].aux.layout, 0);  // caches have no vector sizes
+      }
+    }
+  }
+
+  // 2. Serial single-loop tile-outs (common_actions.rs:37-121; tiling.rs:132-228)
+  {
+    const int oi = kind_output_index(spec.kind);
+    const Shape out_shape = ops[oi].shape;
+    u32 max_dim = 0;
+    for (int d = 0; d < out_shape.n; d++) if (out_shape[d] > max_dim) max_dim = out_shape[d];
+    for (u32 size : dim_range_pow2(max_dim, true)) {
+      for (int dim = 0; dim < out_shape.n; dim++) {
+        u32 this_action = action++;
+        if (out_shape[dim] == size) continue;  // TileShapeMatchesOriginal
+        if (size > out_shape[dim]) continue;   // TileShapeIsLarger
+        Shape tile = out_shape;
+        tile[dim] = size;
+        if (!tensorspec_valid_tile_shape(ops[oi], tile)) continue;
+        if (out_shape[dim] % size != 0) throw ModelError("boundary tile-outs are outside the tabulated space");
+        LogicalSpec body = spec;
+        if (spec.kind == K_MATMUL || spec.kind == K_MATMUL_ACCUM) {
+          body.spec_shape[0] = tile[0]; body.spec_shape[1] = tile[1]; body.spec_shape[3] = tile[2];
+        } else {
+          body.spec_shape = tile;
+        }
+        bool ok = true;
+        for (int j = 0; j < nops && ok; j++) {
+          if (!mem_has_layout(ops[j].aux.mem)) continue;
+          Layout nl;
+          if (!layout_update_for_tiling(ops[j].aux.layout, ops[j].shape, body.operand_shape(j), nl)) ok = false;
+          else body.aux[j].layout = nl;
+        }
+        if (!ok) continue;
+        if (logicalspec_canonicalize(body) != CANON_OK) continue;
+        Candidate c;
+        c.action = (u16)this_action;
+        c.kind = CK_LOOP;
+        c.nchild = 1;
+        u64 iters = 1;
+        for (int d = 0; d < spec.spec_shape.n; d++) iters *= spec.spec_shape[d] / body.spec_shape[d];
+        if (iters > 0xFFFFFFFFull) throw ModelError("loop iteration count overflows u32");
+        c.imm = (u32)iters;
+        c.child[0] = body;
+        out.push_back(c);
+      }
+    }
+  }
+
+  // 3. Leaf kernels in per-kind order; inapplicable kernels take no action number
+  //    (cpu.rs:477-611).
+  {
+    std::vector<LeafKernel> ks;
+    switch (spec.kind) {
+      case K_MATMUL_ACCUM: ks = {LK_MULTADD, LK_BCAST_VEC_MULTADD, LK_DOT_PRODUCT_LOOP}; break;
+      case K_MOVE: ks = {LK_ASSIGN}; break;
+      case K_FILL_ZERO: ks = {LK_MEMSET_ZERO, LK_VALUE_ZERO, LK_VECTOR_ZERO}; break;
+      default: break;
+    }
+    for (LeafKernel k : ks) {
+      LeafInfo li = leaf_kernel_info(k, spec);
+      if (!li.applies) continue;
+      Candidate c;
+      c.action = (u16)action++;
+      c.kind = CK_LEAF;
+      c.nchild = 0;
+      c.imm = li.main;
+      c.level = li.level;
+      c.units = li.units;
+      out.push_back(c);
+    }
+  }
+
+  // 4. Kind-specific tail (cpu.rs:685-699)
+  if (spec.kind == K_MATMUL) {  // ToAccum (to_accum.rs:12-62; mod.rs:526-546)
+    Candidate c;
+    c.action = (u16)action++;
+    c.kind = CK_BLOCK;
+    c.nchild = 2;
+    LogicalSpec fill;
+    fill.kind = K_FILL_ZERO;
+    fill.dtype = spec.dtype;
+    fill.serial_only = spec.serial_only;
+    fill.spec_shape = ops[2].shape;
+    fill.aux[0] = ops[2].aux;
+    if (logicalspec_canonicalize(fill) != CANON_OK) throw ModelError("ToAccum: Fill is not canonicalizable");
+    LogicalSpec acc = spec;
+    acc.kind = K_MATMUL_ACCUM;
+    if (logicalspec_canonicalize(acc) != CANON_OK) throw ModelError("ToAccum: accumulating Spec is not canonicalizable");
+    c.child[0] = fill;
+    c.child[1] = acc;
+    out.push_back(c);
+  } else if (spec.kind == K_MATMUL_ACCUM) {  // Split (common_actions.rs:123-197; tiling.rs:478-541)
+    const u32 b = spec.spec_shape[0], m = spec.spec_shape[1], K = spec.spec_shape[2], n = spec.spec_shape[3];
+    for (u32 k : dim_range_pow2(K, false)) {
+      if (!tensorspec_valid_tile_shape(ops[0], Shape{b, m, k}) || !tensorspec_valid_tile_shape(ops[1], Shape{b, k, n})) continue;
+      u32 this_action = action++;
+      if (K % k != 0) throw ModelError("boundary splits are outside the tabulated space");
+      LogicalSpec body = spec;
+      body.spec_shape[2] = k;
+      bool ok = true;
+      for (int j = 0; j < nops && ok; j++) {
+        if (!mem_has_layout(ops[j].aux.mem)) continue;
+        Layout nl;
+        if (!layout_update_for_tiling(ops[j].aux.layout, ops[j].shape, body.operand_shape(j), nl)) ok = false;
+        else body.aux[j].layout = nl;
+      }
+      if (!ok) continue;
+      if (logicalspec_canonicalize(body) != CANON_OK) continue;
+      Candidate c;
+      c.action = (u16)this_action;
+      c.kind = CK_LOOP;
+      c.nchild = 1;
+      c.imm = K / k;
+      c.child[0] = body;
+      out.push_back(c);
+    }
+  }
+  return action;
+}
+
+}  // namespace mrl
