@@ -1,0 +1,114 @@
+/*
+ * morello_b200 — C ABI of the B200 synthesis-database fill.
+ *
+ * Drop-in boundary for ONE path of Morello: the search/database calls its `precompute`
+ * binary and `top_down` make. Plain pointers and sizes only; the library owns every device
+ * allocation; no call throws or aborts across this boundary (int status, 0 = success,
+ * negative = error, text from mrl_last_error).
+ *
+ * Spec blobs. A logical Spec crosses the boundary as the byte string produced by
+ * mrl_spec_* helpers (or built by hand): kind, dtype, serial flag, rank, dims (u16 LE each),
+ * then per operand: memory, vector size, physical-dim count, contiguous count and 4 bytes per
+ * physical dim (logical dim, kind, size u16 LE). Memory limits are four u64 in the order
+ * RF, VRF, L1, GL: registers, and cache lines (powers of two), exactly the decoded MemVec of
+ * morello/src/memorylimits.rs:51.
+ */
+#ifndef MORELLO_B200_H
+#define MORELLO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mrl_ctx mrl_ctx;
+
+/* One ActionCostVec with k = 1 (morello/src/db/mod.rs:54,171): found = 1 with the optimal
+ * (ActionNum, Cost{main, peaks, depth}) (morello/src/cost.rs:13-17), found = 0 when the Spec
+ * has no implementation under its limits, found = -1 for a Spec the tables do not hold. */
+typedef struct mrl_decision {
+  int32_t found;
+  uint32_t action;
+  uint32_t main_cost;
+  uint32_t depth;
+  uint64_t peaks[4]; /* decoded: RF, VRF registers; L1, GL cache lines */
+} mrl_decision;
+
+typedef struct mrl_stats {
+  uint64_t n_specs;           /* logical Specs in the tables (goals and their closure) */
+  uint64_t n_goal_specs;
+  uint64_t n_candidates;      /* candidate records */
+  uint64_t n_rows;            /* (logical Spec, limits cell) rows = Specs resolved per fill */
+  uint64_t n_launches;        /* kernel launches of the last fill */
+  uint64_t algorithmic_bytes; /* bytes one fill must move (rows out, candidate headers, child rows in) */
+  uint64_t h2d_bytes;         /* bytes copied host->device by the last upload */
+  uint64_t d2h_bytes;         /* bytes copied device->host by the last query */
+  double plan_seconds;        /* host: closure, candidate tabulation, lattice masks, schedule */
+  double upload_seconds;
+  double fill_ms;             /* device time of the last fill (CUDA events on the launch stream) */
+} mrl_stats;
+
+enum { MRL_KIND_MOVE = 0, MRL_KIND_FILL_ZERO = 1, MRL_KIND_MATMUL_ACCUM = 2, MRL_KIND_MATMUL = 3 };
+enum { MRL_DTYPE_U32 = 4, MRL_DTYPE_F32 = 6 };
+enum { MRL_MEM_RF = 0, MRL_MEM_VRF = 1, MRL_MEM_L1 = 2, MRL_MEM_GL = 3 };
+enum { MRL_THROUGH_MOVE = 0, MRL_THROUGH_ZERO = 1, MRL_THROUGH_MATMUL = 2 };
+
+/* Replaces FilesDatabase::new (morello/src/db/mod.rs:350-380): one context = one in-memory
+ * database on one GPU. n_threads = host threads for planning (0 = all cores). */
+int mrl_ctx_create(int device, int n_threads, mrl_ctx** out);
+/* Replaces Drop for FilesDatabase (morello/src/db/mod.rs:1154-1167); frees device memory. */
+void mrl_ctx_destroy(mrl_ctx* ctx);
+const char* mrl_last_error(const mrl_ctx* ctx);
+
+/* Builds the blob of a Spec whose operands are all row-major in one memory: the goal Specs of
+ * frontend/src/main.rs:192-204 and the bound Specs of precompute/src/main.rs:651-736.
+ * Returns the blob length, or a negative status. */
+int mrl_spec_simple(int kind, int dtype, const uint32_t* spec_shape, int rank, int memory, uint8_t* out,
+                    size_t cap);
+/* Spec::canonicalize (morello/src/spec.rs:1704-1747). Returns the new blob length. */
+int mrl_spec_canonicalize(const uint8_t* blob, size_t len, uint8_t* out, size_t cap);
+/* Display form of a Spec blob (debugging aid). Returns the string length. */
+int mrl_spec_describe(const uint8_t* blob, size_t len, char* out, size_t cap);
+/* Avx2Target::max_mem() (morello/src/target/avx2.rs:59-65). */
+void mrl_max_mem(uint64_t limits[4]);
+
+/* Replaces search::top_down_many (morello/src/search/mod.rs:21-42) as called from
+ * precompute/src/main.rs:419 and frontend/src/main.rs:296: canonicalises each goal, fills the
+ * tables for the goals' whole dependency closure on the GPU and returns each goal's decision
+ * at its limits. Host buffers in, host buffers out. blob_off has n+1 entries. */
+int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
+                      mrl_decision* out);
+
+/* Replaces the precompute driver (precompute/src/main.rs:172-386) for the Move, Zero and Matmul
+ * phases: fills the tables of every canonical Spec up to `size` (and their closure).
+ * dtype_mask: bit 0 = u32, bit 1 = f32 (DTYPES, precompute/src/main.rs:55). */
+int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask);
+
+/* The three stages of the two calls above, exposed separately for measurement: plan on the
+ * host, copy the plan to the device, run the launch schedule (may be repeated). */
+int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask);
+int mrl_plan_goals(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n);
+int mrl_upload(mrl_ctx* ctx);
+int mrl_fill(mrl_ctx* ctx);
+
+/* Replaces FilesDatabase::get (morello/src/db/mod.rs:481-503, 538-573): point lookups in the
+ * filled tables; found = -1 for Specs outside the tables. */
+int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
+                 mrl_decision* out);
+
+int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out);
+
+/* Table export (the data a FilesDatabase::put stream would have produced,
+ * morello/src/db/mod.rs:637-766): number of Specs, a Spec's blob, its lattice breakpoint masks
+ * and its dense cell block (n0*n1*n2*n3 decisions, RF index fastest). */
+uint64_t mrl_num_specs(const mrl_ctx* ctx);
+int mrl_spec_blob(const mrl_ctx* ctx, uint64_t spec_id, uint8_t* out, size_t cap);
+int mrl_spec_grid(const mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells);
+int mrl_export_rows(mrl_ctx* ctx, uint64_t spec_id, mrl_decision* out, size_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MORELLO_B200_H */

@@ -1,0 +1,61 @@
+"""ctypes binding of the C ABI declared in include/morello_b200.h."""
+import ctypes as C
+import os
+
+from .build import LIB_PATH
+
+
+class Decision(C.Structure):
+    _fields_ = [("found", C.c_int32), ("action", C.c_uint32), ("main_cost", C.c_uint32), ("depth", C.c_uint32),
+                ("peaks", C.c_uint64 * 4)]
+
+
+class Stats(C.Structure):
+    _fields_ = [("n_specs", C.c_uint64), ("n_goal_specs", C.c_uint64), ("n_candidates", C.c_uint64),
+                ("n_rows", C.c_uint64), ("n_launches", C.c_uint64), ("algorithmic_bytes", C.c_uint64),
+                ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("plan_seconds", C.c_double),
+                ("upload_seconds", C.c_double), ("fill_ms", C.c_double)]
+
+
+EXPORTS = {
+    "mrl_ctx_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "mrl_ctx_destroy": (None, [C.c_void_p]),
+    "mrl_last_error": (C.c_char_p, [C.c_void_p]),
+    "mrl_spec_simple": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_char_p, C.c_size_t]),
+    "mrl_spec_canonicalize": (C.c_int, [C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t]),
+    "mrl_spec_describe": (C.c_int, [C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t]),
+    "mrl_max_mem": (None, [C.POINTER(C.c_uint64)]),
+    "mrl_top_down_many": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_uint64),
+                                    C.POINTER(Decision)]),
+    "mrl_precompute": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_int]),
+    "mrl_plan_precompute": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_int]),
+    "mrl_plan_goals": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t]),
+    "mrl_upload": (C.c_int, [C.c_void_p]),
+    "mrl_fill": (C.c_int, [C.c_void_p]),
+    "mrl_get_many": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_uint64),
+                               C.POINTER(Decision)]),
+    "mrl_get_stats": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),
+    "mrl_num_specs": (C.c_uint64, [C.c_void_p]),
+    "mrl_spec_blob": (C.c_int, [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t]),
+    "mrl_spec_grid": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
+    "mrl_export_rows": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(Decision), C.c_size_t]),
+}
+
+_lib = None
+
+
+def load():
+    """Loads the CUDA extension. There is no fallback: a missing library is an error."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build the CUDA extension first (python -c 'import __graft_entry__ as g; g.build()')")
+    lib = C.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in EXPORTS.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib

@@ -1,0 +1,287 @@
+// C ABI of the B200 synthesis-database fill (declared in include/morello_b200.h).
+#include "../../include/morello_b200.h"
+#include "fill.hpp"
+#include <chrono>
+#include <thread>
+
+using namespace mrl;
+
+struct mrl_ctx {
+  int device = 0;
+  int n_threads = 1;
+  Plan plan;
+  bool planned = false, uploaded = false, filled = false;
+  DeviceFill dev;
+  mrl_stats stats;
+  std::string err;
+};
+
+namespace {
+
+double now_s() {
+  return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+int fail(mrl_ctx* ctx, int code, const std::string& msg) {
+  if (ctx) ctx->err = msg;
+  return code;
+}
+
+void decode_row(const MrlRow& r, mrl_decision* d) {
+  memset(d, 0, sizeof(*d));
+  if (r.tail == MRL_UNSAT) { d->found = 0; return; }
+  d->found = 1;
+  d->action = r.tail & 0xFFFFu;
+  d->depth = r.tail >> 16;
+  d->main_cost = r.main;
+  d->peaks[0] = limit_value(0, (r.peaks >> 24) & 0xFF);
+  d->peaks[1] = limit_value(1, (r.peaks >> 16) & 0xFF);
+  d->peaks[2] = limit_value(2, (r.peaks >> 8) & 0xFF);
+  d->peaks[3] = limit_value(3, r.peaks & 0xFF);
+}
+
+std::vector<Dtype> dtypes_of(int mask) {
+  std::vector<Dtype> d;
+  if (mask & 1) d.push_back(DT_U32);
+  if (mask & 2) d.push_back(DT_F32);
+  return d;
+}
+
+int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
+  double t0 = now_s();
+  ctx->plan = build_plan(goals, ctx->n_threads);
+  ctx->planned = true;
+  ctx->uploaded = ctx->filled = false;
+  const PlanStats& ps = ctx->plan.stats;
+  ctx->stats.n_specs = ps.n_specs;
+  ctx->stats.n_goal_specs = ps.n_goal_specs;
+  ctx->stats.n_candidates = ps.n_cands;
+  ctx->stats.n_rows = ps.n_rows;
+  ctx->stats.algorithmic_bytes = ps.algorithmic_bytes;
+  ctx->stats.plan_seconds = now_s() - t0;
+  return 0;
+}
+
+int parse_goals(const uint8_t* blobs, const uint64_t* off, size_t n, std::vector<LogicalSpec>& out) {
+  for (size_t i = 0; i < n; i++) {
+    LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)blobs + off[i], off[i + 1] - off[i]));
+    if (logicalspec_canonicalize(ls) != CANON_OK) return -1;
+    out.push_back(ls);
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mrl_ctx_create(int device, int n_threads, mrl_ctx** out) {
+  if (!out) return -1;
+  mrl_ctx* ctx = new mrl_ctx();
+  ctx->device = device;
+  if (n_threads <= 0) n_threads = (int)std::thread::hardware_concurrency();
+  if (n_threads <= 0) n_threads = 1;
+  ctx->n_threads = n_threads;
+  memset(&ctx->stats, 0, sizeof(ctx->stats));
+  *out = ctx;
+  // No silent CPU path: a context without a usable GPU is an error.
+  if (ctx->dev.init(device) != 0) {
+    ctx->err = std::string("no usable CUDA device: ") + ctx->dev.error();
+    return -2;
+  }
+  return 0;
+}
+
+void mrl_ctx_destroy(mrl_ctx* ctx) { delete ctx; }
+
+const char* mrl_last_error(const mrl_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+int mrl_spec_simple(int kind, int dtype, const uint32_t* spec_shape, int rank, int memory, uint8_t* out, size_t cap) {
+  try {
+    if (kind < 0 || kind > K_MATMUL || rank < 1 || rank > MAX_RANK || memory < 0 || memory > GL) return -1;
+    LogicalSpec l;
+    l.kind = (SpecKind)kind;
+    l.dtype = (Dtype)dtype;
+    l.serial_only = true;
+    l.spec_shape.n = (u8)rank;
+    for (int i = 0; i < rank; i++) l.spec_shape.d[i] = spec_shape[i];
+    if ((l.kind == K_MATMUL || l.kind == K_MATMUL_ACCUM) && rank != 4) return -1;
+    for (int i = 0; i < l.nops(); i++) {
+      l.aux[i].mem = (Mem)memory;
+      l.aux[i].vector_size = 0;
+      if (mem_is_vector((Mem)memory)) return -1;
+      l.aux[i].layout = mem_has_layout((Mem)memory) ? layout_row_major(l.operand_shape(i)) : Layout();
+    }
+    if (logicalspec_canonicalize(l) != CANON_OK) return -2;
+    std::string k = l.key();
+    if (k.size() > cap) return -3;
+    memcpy(out, k.data(), k.size());
+    return (int)k.size();
+  } catch (const std::exception&) {
+    return -1;
+  }
+}
+
+int mrl_spec_canonicalize(const uint8_t* blob, size_t len, uint8_t* out, size_t cap) {
+  try {
+    LogicalSpec l = LogicalSpec::from_key(std::string((const char*)blob, len));
+    if (logicalspec_canonicalize(l) != CANON_OK) return -2;
+    std::string k = l.key();
+    if (k.size() > cap) return -3;
+    memcpy(out, k.data(), k.size());
+    return (int)k.size();
+  } catch (const std::exception&) {
+    return -1;
+  }
+}
+
+int mrl_spec_describe(const uint8_t* blob, size_t len, char* out, size_t cap) {
+  try {
+    std::string s = LogicalSpec::from_key(std::string((const char*)blob, len)).str();
+    if (s.size() + 1 > cap) return -3;
+    memcpy(out, s.c_str(), s.size() + 1);
+    return (int)s.size();
+  } catch (const std::exception&) {
+    return -1;
+  }
+}
+
+void mrl_max_mem(uint64_t limits[4]) { for (int i = 0; i < 4; i++) limits[i] = AVX2_MAX_MEM[i]; }
+
+int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
+  if (!ctx) return -1;
+  try {
+    if (size == 0 || !is_pow2(size)) return fail(ctx, -1, "size must be a power of two");
+    if (through < 0 || through > THROUGH_MATMUL) return fail(ctx, -1, "bad `through`");
+    std::vector<Dtype> dts = dtypes_of(dtype_mask);
+    if (dts.empty()) return fail(ctx, -1, "empty dtype mask");
+    double t0 = now_s();
+    std::vector<LogicalSpec> goals = precompute_goals(size, (Through)through, dts);
+    int rc = set_plan(ctx, goals);
+    ctx->stats.plan_seconds = now_s() - t0;
+    return rc;
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
+}
+
+int mrl_plan_goals(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n) {
+  if (!ctx) return -1;
+  try {
+    std::vector<LogicalSpec> goals;
+    if (parse_goals(blobs, blob_off, n, goals) != 0) return fail(ctx, -4, "goal Spec is not canonicalizable");
+    return set_plan(ctx, goals);
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
+}
+
+int mrl_upload(mrl_ctx* ctx) {
+  if (!ctx) return -1;
+  if (!ctx->planned) return fail(ctx, -1, "nothing planned");
+  double t0 = now_s();
+  if (ctx->dev.upload(ctx->plan) != 0) return fail(ctx, -2, ctx->dev.error());
+  ctx->uploaded = true;
+  ctx->filled = false;
+  ctx->stats.upload_seconds = now_s() - t0;
+  ctx->stats.h2d_bytes = ctx->dev.h2d_bytes();
+  return 0;
+}
+
+int mrl_fill(mrl_ctx* ctx) {
+  if (!ctx) return -1;
+  if (!ctx->uploaded) return fail(ctx, -1, "plan not uploaded");
+  float ms = 0;
+  uint64_t launches = 0;
+  if (ctx->dev.run(ctx->plan, &ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
+  ctx->filled = true;
+  ctx->stats.fill_ms = ms;
+  ctx->stats.n_launches = launches;
+  return 0;
+}
+
+int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
+                 mrl_decision* out) {
+  if (!ctx) return -1;
+  if (!ctx->filled) return fail(ctx, -1, "tables are not filled");
+  try {
+    std::vector<uint64_t> idx;
+    std::vector<size_t> where;
+    for (size_t i = 0; i < n; i++) {
+      memset(&out[i], 0, sizeof(out[i]));
+      out[i].found = -1;
+      LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)blobs + blob_off[i], blob_off[i + 1] - blob_off[i]));
+      if (logicalspec_canonicalize(ls) != CANON_OK) continue;
+      long id = ctx->plan.find(ls);
+      if (id < 0) continue;
+      long row = ctx->plan.row_of((u32)id, limits + 4 * i);
+      if (row < 0) continue;
+      idx.push_back((uint64_t)row);
+      where.push_back(i);
+    }
+    std::vector<MrlRow> rows(idx.size());
+    if (ctx->dev.read_rows(idx.data(), idx.size(), rows.data()) != 0) return fail(ctx, -2, ctx->dev.error());
+    for (size_t j = 0; j < idx.size(); j++) decode_row(rows[j], &out[where[j]]);
+    ctx->stats.d2h_bytes = idx.size() * sizeof(MrlRow);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
+}
+
+int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
+                      mrl_decision* out) {
+  int rc = mrl_plan_goals(ctx, blobs, blob_off, n);
+  if (rc) return rc;
+  if ((rc = mrl_upload(ctx))) return rc;
+  if ((rc = mrl_fill(ctx))) return rc;
+  return mrl_get_many(ctx, blobs, blob_off, n, limits, out);
+}
+
+int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
+  int rc = mrl_plan_precompute(ctx, size, through, dtype_mask);
+  if (rc) return rc;
+  if ((rc = mrl_upload(ctx))) return rc;
+  return mrl_fill(ctx);
+}
+
+int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out) {
+  if (!ctx || !out) return -1;
+  *out = ctx->stats;
+  return 0;
+}
+
+uint64_t mrl_num_specs(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.specs.size() : 0; }
+
+int mrl_spec_blob(const mrl_ctx* ctx, uint64_t spec_id, uint8_t* out, size_t cap) {
+  if (!ctx || !ctx->planned || spec_id >= ctx->plan.specs.size()) return -1;
+  std::string k = ctx->plan.specs[spec_id].key();
+  if (k.size() > cap) return -3;
+  memcpy(out, k.data(), k.size());
+  return (int)k.size();
+}
+
+int mrl_spec_grid(const mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells) {
+  if (!ctx || !ctx->planned || spec_id >= ctx->plan.specs.size()) return -1;
+  const SpecHdr& h = ctx->plan.hdrs[spec_id];
+  uint64_t n = 1;
+  for (int k = 0; k < 4; k++) { masks[k] = h.mask[k]; n *= (uint64_t)__builtin_popcount(h.mask[k]); }
+  if (n_cells) *n_cells = n;
+  return 0;
+}
+
+int mrl_export_rows(mrl_ctx* ctx, uint64_t spec_id, mrl_decision* out, size_t cap) {
+  if (!ctx || !ctx->filled || spec_id >= ctx->plan.specs.size()) return -1;
+  const SpecHdr& h = ctx->plan.hdrs[spec_id];
+  uint64_t n = 1;
+  for (int k = 0; k < 4; k++) n *= (uint64_t)__builtin_popcount(h.mask[k]);
+  if (n > cap) return fail(ctx, -3, "export buffer too small");
+  std::vector<uint64_t> idx(n);
+  for (uint64_t i = 0; i < n; i++) idx[i] = h.row_base + i;
+  std::vector<MrlRow> rows(n);
+  if (ctx->dev.read_rows(idx.data(), n, rows.data()) != 0) return fail(ctx, -2, ctx->dev.error());
+  for (uint64_t i = 0; i < n; i++) decode_row(rows[i], &out[i]);
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,313 @@
+// combine_argmin: the CUDA side of the synthesis-database fill (sm_100a).
+//
+// One launch evaluates, for one group of logical Specs (same phase and log-shape sum, so no
+// dependencies among them), every table cell that lies on one diagonal of the memory-limits
+// lattice. A thread owns one "column" of a Spec's cell grid (RF, VRF and L1 indices fixed;
+// the GL index is whatever puts the cell on the launch's diagonal), loops over the Spec's
+// candidate records, gathers the child rows each candidate needs at the child's limits,
+// combines them into a Cost and keeps the lexicographic minimum. Lanes of a warp hold
+// neighbouring RF indices of the same Spec, so the rows they gather from one child are
+// neighbours in memory.
+//
+// What it replaces in the reference (paths inside the Morello repository):
+//   morello/src/scheduling/mod.rs:286-368     ActionSolver::compute_cost
+//   morello/src/imp/loops.rs:207-242          loop main cost (serial, no boundary regions)
+//   morello/src/memorylimits.rs:159-224,409-470  peak propagation, limit subtraction
+//   morello/src/scheduling/select.rs:34-47    kernel-allocation feasibility
+//   morello/src/search/reducer.rs:40-99       argmin on (Cost, ActionNum)
+//   morello/src/db/pagecontents.rs:103-123    child lookup (here: an index computation)
+// Integer-only work bounded by HBM/L2 bandwidth; no tensor cores.
+#include "device_types.h"
+#include "fill.hpp"
+#include <cuda_runtime.h>
+#include <stdio.h>
+
+namespace {
+
+__device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
+  uint32_t s = a + b;
+  return s < a ? 0xFFFFFFFFu : s;
+}
+__device__ __forceinline__ uint32_t sat_mul(uint32_t a, uint32_t b) {
+  unsigned long long p = (unsigned long long)a * b;
+  return p > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)p;
+}
+// cpack: limit codes packed one per byte, RF in byte 0 .. GL in byte 3.
+__device__ __forceinline__ uint32_t code_of(uint32_t cpack, uint32_t level) { return (cpack >> (8 * level)) & 0xFFu; }
+__device__ __forceinline__ uint32_t with_code(uint32_t cpack, uint32_t level, uint32_t code) {
+  return (cpack & ~(0xFFu << (8 * level))) | (code << (8 * level));
+}
+// peaks word: RF in byte 3 .. GL in byte 0 (so that a plain u32 compare is lexicographic).
+__device__ __forceinline__ uint32_t peak_shift(uint32_t level) { return 8 * (3 - level); }
+
+// Code of the power-of-two-rounded line count x (0 -> 0, 1 -> 1, 2 -> 2, 3..4 -> 3, ...).
+__device__ __forceinline__ uint32_t cache_code_ceil(uint32_t x) {
+  if (x == 0) return 0;
+  if (x == 1) return 1;
+  return (32 - __clz(x - 1)) + 1;
+}
+__device__ __forceinline__ uint32_t cache_value(uint32_t code) { return code ? (1u << (code - 1)) : 0u; }
+
+struct Key {
+  uint32_t main, peaks, tail;
+};
+__device__ __forceinline__ bool key_less(const Key& a, const Key& b) {
+  if (a.main != b.main) return a.main < b.main;
+  if (a.peaks != b.peaks) return a.peaks < b.peaks;
+  return a.tail < b.tail;
+}
+
+// Row of (child Spec, limits cpack): the cell whose breakpoints are the largest ones not above
+// the limits. 32 bytes of header, then 12 bytes of row.
+__device__ __forceinline__ MrlRow lookup(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
+                                         uint32_t child, uint32_t cpack) {
+  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[child]));
+  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[child].row_base));
+  const uint32_t c0 = cpack & 0xFF, c1 = (cpack >> 8) & 0xFF, c2 = (cpack >> 16) & 0xFF, c3 = cpack >> 24;
+  const uint32_t i0 = __popc(m.x & ((2u << c0) - 1u)) - 1;
+  const uint32_t i1 = __popc(m.y & ((2u << c1) - 1u)) - 1;
+  const uint32_t i2 = __popc(m.z & ((2u << c2) - 1u)) - 1;
+  const uint32_t i3 = __popc(m.w & ((2u << c3) - 1u)) - 1;
+  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+  const unsigned long long idx = base + ((unsigned long long)(i3 * n2 + i2) * n1 + i1) * n0 + i0;
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(rows + idx);
+  MrlRow r;
+  // Plain loads: rows of earlier launches are final, but this buffer is written by this
+  // kernel too, so the read-only path is not used for them.
+  r.main = p[0];
+  r.peaks = p[1];
+  r.tail = p[2];
+  return r;
+}
+
+__global__ void __launch_bounds__(128)
+combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
+                      const Chunk* __restrict__ chunks, uint32_t n_chunks, uint32_t diag,
+                      MrlRow* __restrict__ rows, uint32_t n_specs, int* __restrict__ error_flag) {
+  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (warp >= n_chunks) return;
+  const Chunk ch = chunks[warp];
+  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch.spec]));
+  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+  const uint32_t col = ch.col_start + lane;
+  if (col >= n0 * n1 * n2) return;
+  const uint32_t i0 = col % n0, i1 = (col / n0) % n1, i2 = col / (n0 * n1);
+  const uint32_t c0 = __fns(m.x, 0, i0 + 1), c1 = __fns(m.y, 0, i1 + 1), c2 = __fns(m.z, 0, i2 + 1);
+  const int c3s = (int)diag - (int)(c0 + c1 + c2);
+  if (c3s < 0 || c3s > 31 || !((m.w >> c3s) & 1u)) return;
+  const uint32_t c3 = (uint32_t)c3s;
+  const uint32_t i3 = __popc(m.w & ((1u << c3) - 1u));
+  const uint32_t cpack = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+
+  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ch.spec].row_base));
+  const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[ch.spec].cand_off));
+  const uint32_t cand_off = cl.x, ncand = cl.y;
+
+  Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+  for (uint32_t ci = 0; ci < ncand; ci++) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]));
+    const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+    const uint32_t imm = a.y;
+    const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, pcode = (a.z >> 16) & 0xFFu;
+    const uint32_t units = a.w;
+    const uint32_t lv = code_of(cpack, level);
+    Key k;
+    if (kind == MRL_CK_LEAF) {
+      if (lv < thr) continue;
+      k.main = imm;
+      k.peaks = pcode << peak_shift(level);
+      k.tail = (1u << 16) | action;
+    } else {
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]) + 1);
+      const uint32_t kid[3] = {b.x, b.y, b.z};
+      uint32_t ccpack = cpack;
+      if (kind == MRL_CK_MOVE) {
+        if (lv < thr) continue;
+        uint32_t ccode;
+        if (level < 2) ccode = lv - units;                      // registers: exact
+        else ccode = 32 - __clz(cache_value(lv) - units);       // caches: snap down to 2^k
+        ccpack = with_code(cpack, level, ccode);
+      }
+      uint32_t main = (kind == MRL_CK_MOVE) ? imm : 0u;
+      uint32_t peaks = 0, depth = 0;
+      bool ok = true;
+      for (uint32_t j = 0; j < nchild; j++) {
+        if (kid[j] >= n_specs) { atomicExch(error_flag, 1); ok = false; break; }
+        const MrlRow r = lookup(hdrs, rows, kid[j], ccpack);
+        if (r.tail == MRL_UNSAT) { ok = false; break; }
+        uint32_t cp = r.peaks;
+        if (kind == MRL_CK_MOVE) {
+          // own allocation sits on top of the child's peak in `level`
+          const uint32_t sh = peak_shift(level);
+          const uint32_t child_code = (cp >> sh) & 0xFFu;
+          uint32_t ncode;
+          if (level < 2) ncode = units + child_code;
+          else ncode = cache_code_ceil(units + cache_value(child_code));
+          cp = (cp & ~(0xFFu << sh)) | (ncode << sh);
+          main = sat_add(main, r.main);
+        } else if (kind == MRL_CK_LOOP) {
+          main = sat_mul(r.main, imm);
+        } else {
+          main = (j == 0) ? r.main : sat_add(main, r.main);
+        }
+        peaks = __vmaxu4(peaks, cp);
+        depth = max(depth, r.tail >> 16);
+      }
+      if (!ok) continue;
+      // depth: a single-body tile loop is 1; Move and Block are 1 + deepest child (Block saturates)
+      uint32_t d = (kind == MRL_CK_LOOP) ? 1u : min(depth + 1u, 255u);
+      k.main = main;
+      k.peaks = peaks;
+      k.tail = (d << 16) | action;
+    }
+    if (key_less(k, best)) best = k;
+  }
+  const unsigned long long out = base + ((unsigned long long)(i3 * n2 + i2) * n1 + i1) * n0 + i0;
+  uint32_t* q = reinterpret_cast<uint32_t*>(rows + out);
+  q[0] = best.main;
+  q[1] = best.peaks;
+  q[2] = best.tail;
+}
+
+// Point lookups for get: copies the rows at the given indices into a dense buffer.
+__global__ void gather_rows_kernel(const MrlRow* __restrict__ rows, const unsigned long long* __restrict__ idx,
+                                   unsigned long long n, MrlRow* __restrict__ out) {
+  unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(rows + idx[i]);
+  uint32_t* q = reinterpret_cast<uint32_t*>(out + i);
+  q[0] = p[0];
+  q[1] = p[1];
+  q[2] = p[2];
+}
+
+}  // namespace
+
+namespace mrl {
+
+#define CK(x)                                                                              \
+  do {                                                                                     \
+    cudaError_t e_ = (x);                                                                  \
+    if (e_ != cudaSuccess) {                                                               \
+      snprintf(err_, sizeof(err_), "%s failed: %s", #x, cudaGetErrorString(e_));           \
+      return -1;                                                                           \
+    }                                                                                      \
+  } while (0)
+
+DeviceFill::~DeviceFill() { release(); }
+
+void DeviceFill::release() {
+  if (d_hdrs_) cudaFree(d_hdrs_);
+  if (d_cands_) cudaFree(d_cands_);
+  if (d_chunks_) cudaFree(d_chunks_);
+  if (d_rows_) cudaFree(d_rows_);
+  if (d_err_) cudaFree(d_err_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_chunks_ = nullptr; d_rows_ = nullptr; d_err_ = nullptr;
+  if (ev0_) cudaEventDestroy(ev0_);
+  if (ev1_) cudaEventDestroy(ev1_);
+  ev0_ = ev1_ = nullptr;
+  if (own_stream_ && stream_) cudaStreamDestroy(stream_);
+  stream_ = nullptr;
+  own_stream_ = false;
+}
+
+int DeviceFill::init(int device) {
+  device_ = device;
+  CK(cudaSetDevice(device));
+  if (!stream_) {
+    CK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    own_stream_ = true;
+  }
+  if (!ev0_) CK(cudaEventCreate(&ev0_));
+  if (!ev1_) CK(cudaEventCreate(&ev1_));
+  return 0;
+}
+
+int DeviceFill::upload(const Plan& plan) {
+  CK(cudaSetDevice(device_));
+  if (d_hdrs_) { cudaFree(d_hdrs_); d_hdrs_ = nullptr; }
+  if (d_cands_) { cudaFree(d_cands_); d_cands_ = nullptr; }
+  if (d_chunks_) { cudaFree(d_chunks_); d_chunks_ = nullptr; }
+  if (d_rows_) { cudaFree(d_rows_); d_rows_ = nullptr; }
+  if (!d_err_) CK(cudaMalloc(&d_err_, sizeof(int)));
+  n_specs_ = (uint32_t)plan.hdrs.size();
+  n_rows_ = plan.stats.n_rows;
+  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) + plan.chunks.size() * sizeof(Chunk);
+  CK(cudaMalloc(&d_hdrs_, std::max<size_t>(plan.hdrs.size(), 1) * sizeof(SpecHdr)));
+  CK(cudaMalloc(&d_cands_, std::max<size_t>(plan.cands.size(), 1) * sizeof(CandRec)));
+  CK(cudaMalloc(&d_chunks_, std::max<size_t>(plan.chunks.size(), 1) * sizeof(Chunk)));
+  CK(cudaMalloc(&d_rows_, std::max<uint64_t>(n_rows_, 1) * sizeof(MrlRow)));
+  CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
+  CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), plan.cands.size() * sizeof(CandRec), cudaMemcpyHostToDevice, stream_));
+  CK(cudaMemcpyAsync(d_chunks_, plan.chunks.data(), plan.chunks.size() * sizeof(Chunk), cudaMemcpyHostToDevice, stream_));
+  CK(cudaMemsetAsync(d_err_, 0, sizeof(int), stream_));
+  CK(cudaStreamSynchronize(stream_));
+  return 0;
+}
+
+int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
+  CK(cudaSetDevice(device_));
+  // Every row starts as "no implementation": a cell that is never written stays unsat.
+  CK(cudaEventRecord(ev0_, stream_));
+  CK(cudaMemsetAsync(d_rows_, 0xFF, n_rows_ * sizeof(MrlRow), stream_));
+  uint64_t launches = 0;
+  for (const Step& st : plan.steps) {
+    const Group& g = plan.groups[st.group];
+    const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
+    const uint32_t blocks = (n_chunks + 3) / 4;
+    combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, st.diag,
+                                                       d_rows_, n_specs_, d_err_);
+    launches++;
+  }
+  CK(cudaGetLastError());
+  CK(cudaEventRecord(ev1_, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  float ms = 0;
+  CK(cudaEventElapsedTime(&ms, ev0_, ev1_));
+  int flag = 0;
+  CK(cudaMemcpy(&flag, d_err_, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag) {
+    snprintf(err_, sizeof(err_), "combine kernel reported a bad child index");
+    return -2;
+  }
+  if (ms_out) *ms_out = ms;
+  if (launches_out) *launches_out = launches;
+  return 0;
+}
+
+int DeviceFill::read_rows(const uint64_t* row_idx, size_t n, MrlRow* out) {
+  CK(cudaSetDevice(device_));
+  if (n == 0) return 0;
+  for (size_t i = 0; i < n; i++)
+    if (row_idx[i] >= n_rows_) { snprintf(err_, sizeof(err_), "row index out of range"); return -3; }
+  unsigned long long* d_idx = nullptr;
+  MrlRow* d_out = nullptr;
+  CK(cudaMalloc(&d_idx, n * sizeof(unsigned long long)));
+  if (cudaMalloc(&d_out, n * sizeof(MrlRow)) != cudaSuccess) {
+    cudaFree(d_idx);
+    snprintf(err_, sizeof(err_), "cudaMalloc failed in read_rows");
+    return -1;
+  }
+  cudaError_t e = cudaMemcpyAsync(d_idx, row_idx, n * sizeof(unsigned long long), cudaMemcpyHostToDevice, stream_);
+  if (e == cudaSuccess) {
+    gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream_>>>(d_rows_, d_idx, n, d_out);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, n * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+  cudaFree(d_idx);
+  cudaFree(d_out);
+  if (e != cudaSuccess) { snprintf(err_, sizeof(err_), "read_rows failed: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+int DeviceFill::download(std::vector<MrlRow>& out) {
+  CK(cudaSetDevice(device_));
+  out.resize(n_rows_);
+  CK(cudaMemcpyAsync(out.data(), d_rows_, n_rows_ * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  return 0;
+}
+
+}  // namespace mrl

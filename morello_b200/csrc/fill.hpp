@@ -1,0 +1,44 @@
+// Device side of the fill: owns the device copies of a Plan and the row table, and runs
+// the launch schedule. All device memory is allocated here with cudaMalloc; callers hand
+// in host data only.
+#pragma once
+#include "plan.hpp"
+#include <cuda_runtime.h>
+
+namespace mrl {
+
+class DeviceFill {
+ public:
+  ~DeviceFill();
+  int init(int device);
+  // Copies headers, candidate records and chunk lists to the device and allocates the rows.
+  int upload(const Plan& plan);
+  // Runs every (group, diagonal) step. ms_out: device time of the whole schedule, measured
+  // with CUDA events on the launching stream.
+  int run(const Plan& plan, float* ms_out, uint64_t* launches_out);
+  int read_rows(const uint64_t* row_idx, size_t n, MrlRow* out);
+  int download(std::vector<MrlRow>& out);
+  void release();
+  const char* error() const { return err_; }
+  uint64_t n_rows() const { return n_rows_; }
+  uint64_t h2d_bytes() const { return h2d_bytes_; }
+  MrlRow* device_rows() const { return d_rows_; }
+  cudaStream_t stream() const { return stream_; }
+
+ private:
+  int device_ = 0;
+  SpecHdr* d_hdrs_ = nullptr;
+  CandRec* d_cands_ = nullptr;
+  Chunk* d_chunks_ = nullptr;
+  MrlRow* d_rows_ = nullptr;
+  int* d_err_ = nullptr;
+  uint32_t n_specs_ = 0;
+  uint64_t n_rows_ = 0;
+  uint64_t h2d_bytes_ = 0;
+  cudaStream_t stream_ = nullptr;
+  bool own_stream_ = false;
+  cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+  char err_[256] = {0};
+};
+
+}  // namespace mrl

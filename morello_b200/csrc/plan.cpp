@@ -1,0 +1,358 @@
+// Host-side planner of the database fill. See plan.hpp.
+#include "plan.hpp"
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <mutex>
+#include <thread>
+#include <unordered_map>
+
+namespace mrl {
+
+namespace {
+
+constexpr int NSHARD = 512;
+
+struct Shard {
+  std::mutex mu;
+  std::unordered_map<std::string, u32> map;
+};
+
+struct TempSpec {
+  LogicalSpec ls;
+  std::string key;
+  std::vector<CandRec> cands;  // child[] holds temporary ids
+};
+
+double now_s() {
+  return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+template <class F>
+void parallel_for(size_t n, int n_threads, F f) {
+  if (n_threads <= 1 || n < 64) {
+    for (size_t i = 0; i < n; i++) f(i, 0);
+    return;
+  }
+  std::atomic<size_t> next{0};
+  std::vector<std::thread> pool;
+  std::vector<std::string> errors(n_threads);
+  for (int t = 0; t < n_threads; t++) {
+    pool.emplace_back([&, t]() {
+      try {
+        while (true) {
+          size_t lo = next.fetch_add(64);
+          if (lo >= n) break;
+          size_t hi = std::min(n, lo + 64);
+          for (size_t i = lo; i < hi; i++) f(i, t);
+        }
+      } catch (const std::exception& e) {
+        errors[t] = e.what();
+      }
+    });
+  }
+  for (auto& th : pool) th.join();
+  for (auto& e : errors) if (!e.empty()) throw ModelError(e);
+}
+
+u32 shape_log_sum(const LogicalSpec& ls) {
+  u32 s = 0;
+  for (int i = 0; i < ls.spec_shape.n; i++) s += bit_length(ls.spec_shape[i]) - 1;
+  return s;
+}
+
+// Smallest limit code whose value is >= units, and the code of the peak `units` itself
+// leaves behind (registers: raw; caches: rounded to a power of two,
+// morello/src/memorylimits.rs:159-170,458-470).
+u32 code_ceil(int mem, u64 units) {
+  if (mem_counts_registers((Mem)mem)) return (u32)units;
+  return bit_length(next_binary_power(units));
+}
+
+}  // namespace
+
+std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes) {
+  std::vector<LogicalSpec> goals;
+  for (auto& phase : goal_phases(size, through, dtypes))
+    for (const Bound& b : phase)
+      for (auto& stage : diagonals(bound_point(b)))
+        for (auto& pt : stage) {
+          std::vector<LogicalSpec> v = task_point_specs(b, pt);
+          goals.insert(goals.end(), v.begin(), v.end());
+        }
+  return goals;
+}
+
+long Plan::find(const LogicalSpec& ls) const {
+  std::string k = ls.key();
+  auto it = std::lower_bound(sorted_keys_.begin(), sorted_keys_.end(), k,
+                             [](const std::pair<std::string, u32>& a, const std::string& b) { return a.first < b; });
+  if (it == sorted_keys_.end() || it->first != k) return -1;
+  return it->second;
+}
+
+long Plan::row_of(u32 id, const u64 limits[NMEM]) const {
+  const SpecHdr& h = hdrs[id];
+  u64 idx = 0, stride = 1;
+  for (int k = 0; k < NMEM; k++) {
+    u32 code = limit_code(k, limits[k]);
+    if (code > top_code[k]) return -1;  // beyond the limits this table was filled for
+    u32 below = h.mask[k] & (code >= 31 ? 0xFFFFFFFFu : ((2u << code) - 1u));
+    u32 i = (u32)__builtin_popcount(below) - 1;
+    idx += stride * i;
+    stride *= (u32)__builtin_popcount(h.mask[k]);
+  }
+  return (long)(h.row_base + idx);
+}
+
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits) {
+  if (n_threads < 1) n_threads = 1;
+  Plan plan;
+  u32 top_code[NMEM];
+  for (int k = 0; k < NMEM; k++) {
+    u64 v = top_limits ? top_limits[k] : AVX2_MAX_MEM[k];
+    if (!mem_counts_registers((Mem)k) && v != 0 && !is_pow2(v)) throw ModelError("cache limits must be powers of two");
+    top_code[k] = limit_code(k, v);
+    if (top_code[k] > 30) throw ModelError("memory limit too large for the lattice masks");
+    plan.top_code[k] = top_code[k];
+  }
+
+  // ---- 1. discovery: closure of the goals under "is a sub-Spec of some candidate" ----
+  double t0 = now_s();
+  std::vector<Shard> shards(NSHARD);
+  std::vector<TempSpec> temp;
+  std::atomic<u32> next_id{0};
+  auto shard_of = [&](const std::string& k) -> Shard& { return shards[std::hash<std::string>()(k) % NSHARD]; };
+
+  std::vector<u32> frontier;
+  {
+    for (const LogicalSpec& g0 : goals) {
+      LogicalSpec g = g0;
+      if (logicalspec_canonicalize(g) != CANON_OK) throw ModelError("goal Spec cannot be canonicalized: " + g0.str());
+      std::string k = g.key();
+      Shard& sh = shard_of(k);
+      auto it = sh.map.find(k);
+      if (it == sh.map.end()) {
+        u32 id = next_id++;
+        sh.map.emplace(k, id);
+        TempSpec ts;
+        ts.ls = g;
+        ts.key = k;
+        temp.push_back(std::move(ts));
+        frontier.push_back(id);
+        plan.goal_ids.push_back(id);
+      } else {
+        plan.goal_ids.push_back(it->second);
+      }
+    }
+  }
+  plan.stats.n_goal_specs = frontier.size();
+
+  while (!frontier.empty()) {
+    struct NewSpec { u32 id; LogicalSpec ls; std::string key; };
+    std::vector<std::vector<NewSpec>> fresh(n_threads);
+    parallel_for(frontier.size(), n_threads, [&](size_t fi, int tid) {
+      TempSpec& ts = temp[frontier[fi]];
+      std::vector<Candidate> cs;
+      tabulate_candidates(ts.ls, cs);
+      ts.cands.reserve(cs.size());
+      for (const Candidate& c : cs) {
+        CandRec r;
+        memset(&r, 0, sizeof(r));
+        r.action = c.action;
+        r.kind = c.kind;
+        r.nchild = c.nchild;
+        r.imm = c.imm;
+        r.level = c.level;
+        r.units = c.units;
+        u32 thr = (c.kind == CK_MOVE || c.kind == CK_LEAF) ? code_ceil(c.level, c.units) : 0;
+        if (thr > top_code[c.level]) continue;  // never fits, at any limits in the lattice
+        r.thr_code = (u8)thr;
+        r.peak_code = (c.kind == CK_LEAF) ? (u8)code_ceil(c.level, c.units) : 0;
+        for (int j = 0; j < c.nchild; j++) {
+          std::string k = c.child[j].key();
+          Shard& sh = shard_of(k);
+          u32 id;
+          {
+            std::lock_guard<std::mutex> g(sh.mu);
+            auto it = sh.map.find(k);
+            if (it != sh.map.end()) id = it->second;
+            else {
+              id = next_id++;
+              sh.map.emplace(k, id);
+              fresh[tid].push_back(NewSpec{id, c.child[j], k});
+            }
+          }
+          r.child[j] = id;
+        }
+        ts.cands.push_back(r);
+      }
+    });
+    frontier.clear();
+    temp.resize(next_id.load());
+    for (auto& v : fresh)
+      for (auto& ns : v) {
+        temp[ns.id].ls = ns.ls;
+        temp[ns.id].key = std::move(ns.key);
+        frontier.push_back(ns.id);
+      }
+    std::sort(frontier.begin(), frontier.end());
+  }
+  const u32 n = (u32)temp.size();
+  plan.stats.seconds_discover = now_s() - t0;
+
+  // ---- 2. final ids: group-major (phase, log-shape sum), then key order ----
+  double t1 = now_s();
+  std::vector<u32> order(n);
+  for (u32 i = 0; i < n; i++) order[i] = i;
+  std::vector<u32> gkey(n);
+  for (u32 i = 0; i < n; i++) gkey[i] = ((u32)temp[i].ls.kind << 8) | shape_log_sum(temp[i].ls);
+  std::sort(order.begin(), order.end(), [&](u32 a, u32 b) {
+    if (gkey[a] != gkey[b]) return gkey[a] < gkey[b];
+    return temp[a].key < temp[b].key;
+  });
+  std::vector<u32> new_id(n);
+  for (u32 i = 0; i < n; i++) new_id[order[i]] = i;
+  for (u32& g : plan.goal_ids) g = new_id[g];
+
+  plan.specs.resize(n);
+  plan.hdrs.resize(n);
+  u64 ncand = 0;
+  for (u32 i = 0; i < n; i++) ncand += temp[order[i]].cands.size();
+  if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
+  plan.cands.resize(ncand);
+  {
+    u64 off = 0;
+    for (u32 i = 0; i < n; i++) {
+      TempSpec& ts = temp[order[i]];
+      plan.specs[i] = ts.ls;
+      SpecHdr& h = plan.hdrs[i];
+      memset(&h, 0, sizeof(h));
+      h.cand_off = (u32)off;
+      h.ncand = (u32)ts.cands.size();
+      for (CandRec r : ts.cands) {
+        for (int j = 0; j < r.nchild; j++) r.child[j] = new_id[r.child[j]];
+        plan.stats.n_children += r.nchild;
+        plan.cands[off++] = r;
+      }
+      plan.sorted_keys_.push_back({std::move(ts.key), i});
+      std::vector<CandRec>().swap(ts.cands);
+    }
+  }
+  std::vector<TempSpec>().swap(temp);
+  std::sort(plan.sorted_keys_.begin(), plan.sorted_keys_.end());
+
+  // groups
+  for (u32 i = 0; i < n;) {
+    u32 gk = ((u32)plan.specs[i].kind << 8) | shape_log_sum(plan.specs[i]);
+    u32 j = i;
+    while (j < n && ((((u32)plan.specs[j].kind << 8) | shape_log_sum(plan.specs[j])) == gk)) j++;
+    Group g;
+    g.spec_lo = i;
+    g.spec_hi = j;
+    g.phase = (u8)(gk >> 8);
+    g.shape_sum = (u8)(gk & 0xff);
+    plan.groups.push_back(g);
+    i = j;
+  }
+  plan.stats.seconds_layout = now_s() - t1;
+
+  // ---- 3. breakpoint masks: least fixpoint of "a parent's result can change wherever one
+  //         of its candidates becomes feasible or one of its children's results changes" ----
+  double t2 = now_s();
+  for (u32 i = 0; i < n; i++) for (int k = 0; k < NMEM; k++) plan.hdrs[i].mask[k] = 1u;
+  u32 all_mask[NMEM];
+  for (int k = 0; k < NMEM; k++) all_mask[k] = (top_code[k] >= 31) ? 0xFFFFFFFFu : ((2u << top_code[k]) - 1u);
+  bool changed = true;
+  while (changed) {
+    changed = false;
+    plan.stats.mask_sweeps++;
+    for (u32 i = 0; i < n; i++) {
+      SpecHdr& h = plan.hdrs[i];
+      u32 m[NMEM] = {h.mask[0], h.mask[1], h.mask[2], h.mask[3]};
+      for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
+        const CandRec& r = plan.cands[c];
+        if (r.kind == MRL_CK_LEAF) {
+          m[r.level] |= 1u << r.thr_code;
+          continue;
+        }
+        for (int j = 0; j < r.nchild; j++) {
+          const SpecHdr& ch = plan.hdrs[r.child[j]];
+          for (int k = 0; k < NMEM; k++) {
+            if (r.kind != MRL_CK_MOVE || k != r.level) { m[k] |= ch.mask[k]; continue; }
+            if (mem_counts_registers((Mem)k)) {
+              m[k] |= (r.units >= 32 ? 0u : (ch.mask[k] << r.units)) & all_mask[k];
+            } else {
+              u32 cm = ch.mask[k];
+              while (cm) {
+                u32 b = (u32)__builtin_ctz(cm);
+                cm &= cm - 1;
+                u32 code = bit_length(next_binary_power(bit_length_inverse(b) + r.units));
+                if (code <= top_code[k]) m[k] |= 1u << code;
+              }
+            }
+          }
+        }
+      }
+      for (int k = 0; k < NMEM; k++)
+        if (m[k] != h.mask[k]) { h.mask[k] = m[k]; changed = true; }
+    }
+  }
+  plan.stats.seconds_masks = now_s() - t2;
+
+  // ---- 4. rows, chunks, schedule, byte accounting ----
+  double t3 = now_s();
+  u64 row = 0, cols_total = 0, bytes = 0;
+  for (Group& g : plan.groups) {
+    g.chunk_lo = (u32)plan.chunks.size();
+    g.max_diag = 0;
+    for (u32 i = g.spec_lo; i < g.spec_hi; i++) {
+      SpecHdr& h = plan.hdrs[i];
+      u32 nk[NMEM];
+      u32 top_sum = 0;
+      for (int k = 0; k < NMEM; k++) {
+        nk[k] = (u32)__builtin_popcount(h.mask[k]);
+        top_sum += 31 - (u32)__builtin_clz(h.mask[k]);
+      }
+      g.max_diag = std::max(g.max_diag, top_sum);
+      u64 ncells = (u64)nk[0] * nk[1] * nk[2] * nk[3];
+      u32 ncols = nk[0] * nk[1] * nk[2];  // the GL index is fixed by the launch's diagonal
+      h.row_base = row;
+      row += ncells;
+      cols_total += ncols;
+      for (u32 c0 = 0; c0 < ncols; c0 += 32) plan.chunks.push_back(Chunk{i, c0});
+      // algorithmic bytes: one 12-byte row out; per candidate a 16-byte header; per child
+      // of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in.
+      bytes += ncells * 12;
+      for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
+        const CandRec& r = plan.cands[c];
+        bytes += ncells * 16;
+        if (r.nchild) {
+          u32 feasible_k = (u32)__builtin_popcount(h.mask[r.level] >> r.thr_code);
+          u64 feasible = ncells / nk[r.level] * feasible_k;
+          bytes += feasible * r.nchild * 16;
+        }
+      }
+    }
+    g.chunk_hi = (u32)plan.chunks.size();
+  }
+  u32 max_diag = 0;
+  for (const Group& g : plan.groups) max_diag = std::max(max_diag, g.max_diag);
+  for (u32 d = 0; d <= max_diag; d++)
+    for (u32 gi = 0; gi < plan.groups.size(); gi++)
+      if (plan.groups[gi].max_diag >= d && plan.groups[gi].chunk_hi > plan.groups[gi].chunk_lo)
+        plan.steps.push_back(Step{gi, d});
+
+  plan.stats.n_specs = n;
+  plan.stats.n_cands = ncand;
+  plan.stats.n_rows = row;
+  plan.stats.n_columns = cols_total;
+  plan.stats.n_groups = plan.groups.size();
+  plan.stats.n_steps = plan.steps.size();
+  plan.stats.max_diag = max_diag;
+  plan.stats.algorithmic_bytes = bytes;
+  plan.stats.seconds_layout += now_s() - t3;
+  return plan;
+}
+
+}  // namespace mrl

@@ -1,0 +1,83 @@
+// Host-side planner of the database fill.
+//
+// Turns a set of goal logical Specs into the flat arrays the combine kernel walks:
+//   * the dependency closure of the goals (every sub-Spec any candidate action can ask for),
+//   * per Spec its candidate records (action number, combine kind, immediates, child ids),
+//   * per Spec the breakpoints of its memory-limits lattice (one bit mask per memory), which
+//     give the Spec a dense 4-D grid of cells; one table row per cell,
+//   * the schedule: groups of Specs ordered by (phase, log-shape sum) crossed with limits
+//     diagonals, a total order in which every child row precedes its parent row.
+//
+// This replaces, for the path built here, the reference's on-demand recursion
+// (morello/src/search/algo.rs:61-95) and its paged R-tree tables
+// (morello/src/db/mod.rs:538-573,650-766): every (logical Spec, limits) point gets its own
+// direct solve, so a point lookup is an index computation instead of a rectangle search.
+#pragma once
+#include "model/actions.hpp"
+#include "model/space.hpp"
+#include "device_types.h"
+#include <string>
+#include <vector>
+
+namespace mrl {
+
+struct PlanStats {
+  u64 n_specs = 0;
+  u64 n_goal_specs = 0;
+  u64 n_cands = 0;
+  u64 n_children = 0;
+  u64 n_rows = 0;
+  u64 n_columns = 0;
+  u64 n_groups = 0;
+  u64 n_steps = 0;
+  u64 max_diag = 0;
+  u64 algorithmic_bytes = 0;  // per full fill
+  u64 mask_sweeps = 0;
+  double seconds_discover = 0, seconds_masks = 0, seconds_layout = 0;
+};
+
+struct Group {          // Specs with the same phase and log-shape sum: no dependencies inside
+  u32 spec_lo = 0, spec_hi = 0;  // id range
+  u32 chunk_lo = 0, chunk_hi = 0;
+  u32 max_diag = 0;     // largest limits diagonal any member has a cell on
+  u8 phase = 0;
+  u8 shape_sum = 0;
+};
+
+struct Step {           // one kernel launch
+  u32 group;
+  u32 diag;
+};
+
+struct Plan {
+  std::vector<LogicalSpec> specs;        // by id
+  std::vector<SpecHdr> hdrs;             // by id
+  std::vector<CandRec> cands;
+  std::vector<Chunk> chunks;
+  std::vector<Group> groups;
+  std::vector<Step> steps;
+  std::vector<u32> goal_ids;
+  u32 top_code[NMEM] = {0, 0, 0, 0};   // lattice codes of the top limits the plan covers
+  PlanStats stats;
+
+  // id of a logical Spec (canonical form), or -1.
+  long find(const LogicalSpec& ls) const;
+  // Row index of (spec id, limits) or -1 when limits exceed the planned top.
+  long row_of(u32 id, const u64 limits[NMEM]) const;
+
+ private:
+  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*);
+  std::vector<std::pair<std::string, u32>> sorted_keys_;  // (key, id), sorted by key
+};
+
+// Top limits are Avx2Target::max_mem() unless overridden.
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr);
+
+// Goal sets.
+std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes);
+
+// Lattice code <-> value helpers shared by planner and lookups.
+inline u32 limit_code(int mem, u64 value) { return mem_counts_registers((Mem)mem) ? (u32)value : bit_length(value); }
+inline u64 limit_value(int mem, u32 code) { return mem_counts_registers((Mem)mem) ? code : bit_length_inverse(code); }
+
+}  // namespace mrl

@@ -1,0 +1,180 @@
+"""Host-side mirror of the reference's search / database interface for the fill path."""
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+from . import _lib as L
+
+KIND_MOVE, KIND_FILL_ZERO, KIND_MATMUL_ACCUM, KIND_MATMUL = 0, 1, 2, 3
+DTYPE_U32, DTYPE_F32 = 4, 6
+RF, VRF, L1, GL = 0, 1, 2, 3
+THROUGH_MOVE, THROUGH_ZERO, THROUGH_MATMUL = 0, 1, 2
+# Avx2Target::max_mem() (morello/src/target/avx2.rs:59-65): RF, VRF registers; L1, GL lines.
+MAX_MEM = (16, 16, 1024, 33554432)
+
+
+@dataclass(frozen=True)
+class Decision:
+    """One ActionCostVec entry with k = 1 (morello/src/db/mod.rs:54,171)."""
+    found: int            # 1 optimum, 0 unsatisfiable, -1 not in the tables
+    action: int = 0
+    main_cost: int = 0
+    depth: int = 0
+    peaks: Tuple[int, int, int, int] = (0, 0, 0, 0)
+
+    @staticmethod
+    def from_c(d) -> "Decision":
+        if d.found != 1:
+            return Decision(found=int(d.found))
+        return Decision(1, int(d.action), int(d.main_cost), int(d.depth), tuple(int(x) for x in d.peaks))
+
+
+def simple_spec(kind: int, dtype: int, spec_shape: Sequence[int], memory: int = GL) -> bytes:
+    """Blob of a serial Spec with every operand row-major in `memory` (the goal Specs of
+    frontend/src/main.rs:192-204 and the bounds of precompute/src/main.rs:651-736)."""
+    lib = L.load()
+    shape = (C.c_uint32 * len(spec_shape))(*spec_shape)
+    buf = C.create_string_buffer(256)
+    n = lib.mrl_spec_simple(kind, dtype, shape, len(spec_shape), memory, buf, 256)
+    if n < 0:
+        raise ValueError(f"cannot build Spec (status {n})")
+    return buf.raw[:n]
+
+
+def describe_spec(blob: bytes) -> str:
+    lib = L.load()
+    buf = C.create_string_buffer(512)
+    n = lib.mrl_spec_describe(blob, len(blob), buf, 512)
+    if n < 0:
+        raise ValueError("bad Spec blob")
+    return buf.value.decode()
+
+
+def _pack(blobs: Sequence[bytes], limits: Optional[Sequence[Sequence[int]]]):
+    off = (C.c_uint64 * (len(blobs) + 1))()
+    pos = 0
+    for i, b in enumerate(blobs):
+        off[i] = pos
+        pos += len(b)
+    off[len(blobs)] = pos
+    data = b"".join(blobs)
+    lim = None
+    if limits is not None:
+        lim = (C.c_uint64 * (4 * len(blobs)))()
+        for i, l in enumerate(limits):
+            for k in range(4):
+                lim[4 * i + k] = l[k]
+    return data, off, lim
+
+
+class SynthesisDatabase:
+    """An in-memory synthesis database living on one GPU.
+
+    Mirrors, for the fill path, FilesDatabase (morello/src/db/mod.rs:350-380, 481-503) together
+    with search::top_down_many (morello/src/search/mod.rs:21-42) and the precompute driver
+    (precompute/src/main.rs:172-386). Everything is computed by the CUDA extension; there is
+    no CPU path, and construction fails when no GPU or no built extension is present.
+    """
+
+    def __init__(self, device: int = 0, threads: int = 0):
+        self._lib = L.load()
+        self._ctx = C.c_void_p()
+        rc = self._lib.mrl_ctx_create(device, threads, C.byref(self._ctx))
+        if rc != 0:
+            msg = self._lib.mrl_last_error(self._ctx).decode() if self._ctx else "context creation failed"
+            if self._ctx:
+                self._lib.mrl_ctx_destroy(self._ctx)
+                self._ctx = None
+            raise RuntimeError(msg)
+
+    def close(self):
+        if getattr(self, "_ctx", None):
+            self._lib.mrl_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != 0:
+            raise RuntimeError(self._lib.mrl_last_error(self._ctx).decode() or f"status {rc}")
+
+    # --- search::top_down_many / top_down ---
+    def top_down_many(self, goals: Sequence[bytes], limits: Optional[Sequence[Sequence[int]]] = None) -> List[Decision]:
+        if limits is None:
+            limits = [MAX_MEM] * len(goals)
+        data, off, lim = _pack(goals, limits)
+        out = (L.Decision * len(goals))()
+        self._check(self._lib.mrl_top_down_many(self._ctx, data, off, len(goals), lim, out))
+        return [Decision.from_c(d) for d in out]
+
+    def top_down(self, goal: bytes, limits: Sequence[int] = MAX_MEM) -> Decision:
+        return self.top_down_many([goal], [limits])[0]
+
+    # --- the precompute driver ---
+    def precompute(self, size: int, through: int = THROUGH_MATMUL, dtypes: Sequence[int] = (DTYPE_U32, DTYPE_F32)):
+        self._check(self._lib.mrl_precompute(self._ctx, size, through, self._dtype_mask(dtypes)))
+        return self.stats()
+
+    # --- the stages, for measurement ---
+    def plan_precompute(self, size: int, through: int = THROUGH_MATMUL, dtypes: Sequence[int] = (DTYPE_U32, DTYPE_F32)):
+        self._check(self._lib.mrl_plan_precompute(self._ctx, size, through, self._dtype_mask(dtypes)))
+
+    def plan_goals(self, goals: Sequence[bytes]):
+        data, off, _ = _pack(goals, None)
+        self._check(self._lib.mrl_plan_goals(self._ctx, data, off, len(goals)))
+
+    def upload(self):
+        self._check(self._lib.mrl_upload(self._ctx))
+
+    def fill(self):
+        self._check(self._lib.mrl_fill(self._ctx))
+
+    # --- FilesDatabase::get ---
+    def get_many(self, specs: Sequence[bytes], limits: Sequence[Sequence[int]]) -> List[Decision]:
+        data, off, lim = _pack(specs, limits)
+        out = (L.Decision * len(specs))()
+        self._check(self._lib.mrl_get_many(self._ctx, data, off, len(specs), lim, out))
+        return [Decision.from_c(d) for d in out]
+
+    def get(self, spec: bytes, limits: Sequence[int] = MAX_MEM) -> Decision:
+        return self.get_many([spec], [limits])[0]
+
+    # --- export / stats ---
+    def stats(self) -> dict:
+        s = L.Stats()
+        self._check(self._lib.mrl_get_stats(self._ctx, C.byref(s)))
+        return {name: getattr(s, name) for name, _ in L.Stats._fields_}
+
+    def num_specs(self) -> int:
+        return int(self._lib.mrl_num_specs(self._ctx))
+
+    def spec_blob(self, spec_id: int) -> bytes:
+        buf = C.create_string_buffer(256)
+        n = self._lib.mrl_spec_blob(self._ctx, spec_id, buf, 256)
+        if n < 0:
+            raise IndexError(spec_id)
+        return buf.raw[:n]
+
+    def spec_grid(self, spec_id: int):
+        masks = (C.c_uint32 * 4)()
+        n = C.c_uint64()
+        if self._lib.mrl_spec_grid(self._ctx, spec_id, masks, C.byref(n)) != 0:
+            raise IndexError(spec_id)
+        return [int(m) for m in masks], int(n.value)
+
+    def export_rows(self, spec_id: int) -> List[Decision]:
+        _, n = self.spec_grid(spec_id)
+        out = (L.Decision * n)()
+        self._check(self._lib.mrl_export_rows(self._ctx, spec_id, out, n))
+        return [Decision.from_c(d) for d in out]
+
+    @staticmethod
+    def _dtype_mask(dtypes):
+        mask = 0
+        for d in dtypes:
+            mask |= {DTYPE_U32: 1, DTYPE_F32: 2}[d]
+        return mask
