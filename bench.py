@@ -1,0 +1,249 @@
+#!/usr/bin/env python
+"""Benchmark of the synthesis-database fill.
+
+  python bench.py --gpus N --steps K --warmup W            # the CUDA path
+  python bench.py --impl reference --gpus N --steps K ...  # the reference algorithm on host cores
+
+One step = one complete fill of the workload's database. The workload is the precompute of
+every canonical Move / Zero / Matmul Spec up to size 2 over {u32, f32} on the Avx2 target with
+default memory limits (`precompute --target avx2 --through matmul 2`): the dependency closure of
+`morello matmul 2` and its f32 twin. All inputs are synthetic by construction: the Spec space is
+generated from the size alone.
+
+Unit of work ("Spec resolved"): one (logical Spec, memory limits) entry of the database made
+answerable. Both arms cover the same entries - every logical Spec of the workload over the
+whole 17 x 17 x 12 x 27 limits lattice of the target - so the figure is the same numerator
+divided by each arm's time. The CUDA arm also reports how many rows it actually computed and
+the reference arm how many solves (`put`s) it needed.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LATTICE_POINTS = 17 * 17 * 12 * 27  # RF 0..16, VRF 0..16, L1 and GL as bit lengths (avx2.rs:59-65)
+WORKLOAD = "precompute --target avx2 --through matmul 2 (Move+Zero+Matmul, u32+f32, serial)"
+SIZE = 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index=0):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                                         text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_oracle(threads, steps, warmup):
+    """The reference's algorithm (top-down memoised search with a range-filling memo table and
+    the precompute driver) restated in C++ under oracle/, on the host cores."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_lib
+    fac = oracle_lib.load()
+    times, puts, lspecs = [], 0, 0
+    for i in range(warmup + steps):
+        o = fac.new()
+        r = o.precompute(SIZE, through=2, dtype_mask=3, threads=threads)
+        o.close()
+        if i >= warmup:
+            times.append(r["seconds"])
+        puts, lspecs = r["puts"], r["logical_specs"]
+    return times, puts, lspecs
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    times, puts, lspecs = run_oracle(cores, args.steps, args.warmup)
+    per_step = sum(times) / len(times)
+    value = lspecs * LATTICE_POINTS / per_step
+    line = {
+        "impl": "reference", "metric": "specs_resolved_per_s", "value": value, "unit": "specs/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
+                   "reference_puts": puts},
+        "wall_s_full_db": per_step,
+        "cpu_baseline": {"value": value, "unit": "specs/s", "cores": cores, "kind": "port",
+                         "sample": "the whole workload, once per step (C++ restatement of the reference algorithm; "
+                                   "the Rust reference cannot be built here)",
+                         "puts_per_s": puts / per_step},
+        "e2e": {"value": value, "unit": "specs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def cuda_arm(args):
+    import torch
+    import torch.distributed as dist
+    import morello_b200 as m
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device: the fill has no CPU path")
+
+    # Replicas only at N > 1 for now: every rank fills the same database (weak scaling of
+    # independent jobs); the table rows are not exchanged.
+    db = m.SynthesisDatabase(device=local_rank)
+    db.plan_precompute(SIZE)
+    db.upload()
+    for _ in range(max(args.warmup, 3)):
+        db.fill()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    fill_ms = []
+    for _ in range(args.steps):
+        db.fill()  # device time measured inside with CUDA events on the launching stream
+        fill_ms.append(db.stats()["fill_ms"])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    st = db.stats()
+    total_ms = sum(fill_ms)
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+
+    # End to end through the public call: host planning, host->device copy of the plan, the fill,
+    # and a device->host read of every goal Spec's decision at the top limits.
+    goal_blobs = [db.spec_blob(i) for i in range(0, db.num_specs(), max(1, db.num_specs() // 512))]
+    e2e_s = []
+    for i in range(1 + max(1, min(args.steps, 3))):
+        t0 = time.perf_counter()
+        db.precompute(SIZE)
+        got = db.get_many(goal_blobs, [m.MAX_MEM] * len(goal_blobs))
+        dt = time.perf_counter() - t0
+        if i > 0:
+            e2e_s.append(dt)
+    assert all(g.found in (0, 1) for g in got)
+    st2 = db.stats()
+    e2e_step = sum(e2e_s) / len(e2e_s)
+    if world > 1:
+        t = torch.tensor([e2e_step], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_step = float(t.item())
+
+    lspecs = st["n_specs"]
+    units = lspecs * LATTICE_POINTS * world
+    hbm_gbs, peak_kind = measured_peaks()
+    achieved = st["algorithmic_bytes"] / (ms_per_step * 1e-3) / 1e9
+    line = {
+        "metric": "specs_resolved_per_s", "value": units / (ms_per_step * 1e-3), "unit": "specs/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
+                   "rows_computed_per_step": st["n_rows"], "candidate_records": st["n_candidates"],
+                   "l2": "row table (%.1f GB) is larger than L2" % (st["n_rows"] * 12 / 1e9),
+                   "multi_gpu": "replicas only" if world > 1 else "single"},
+        "wall_s_full_db": e2e_step,
+        "rows_per_s": st["n_rows"] * world / (ms_per_step * 1e-3),
+        "e2e": {"value": units / e2e_step, "unit": "specs/s", "h2d_bytes_per_step": st2["h2d_bytes"],
+                "d2h_bytes_per_step": st2["d2h_bytes"], "plan_s": st2["plan_seconds"],
+                "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "wall_s": e2e_step},
+        "gpu_launches": int(st["n_launches"]) * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "combine_argmin_kernel",
+                     "algorithmic_bytes_per_step": st["algorithmic_bytes"]},
+        "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            times, puts, _ = run_oracle(cores, 1, 0)
+            line["cpu_baseline"] = {
+                "value": lspecs * LATTICE_POINTS / times[0], "unit": "specs/s", "cores": cores, "kind": "port",
+                "sample": "the whole workload once (C++ restatement of the reference algorithm, all host cores)",
+                "wall_s": times[0], "reference_puts": puts, "puts_per_s": puts / times[0]}
+        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(traffic_path):
+            with open(traffic_path) as f:
+                line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_step")
+        print(json.dumps(line))
+    db.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        cuda_arm(args)
+
+
+if __name__ == "__main__":
+    main()

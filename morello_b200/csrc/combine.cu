@@ -248,9 +248,9 @@ int DeviceFill::upload(const Plan& plan) {
 
 int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
   CK(cudaSetDevice(device_));
-  // Every row starts as "no implementation": a cell that is never written stays unsat.
+  // No clearing pass: every cell lies on exactly one (group, diagonal) step and is written
+  // there, and no cell is read before its step.
   CK(cudaEventRecord(ev0_, stream_));
-  CK(cudaMemsetAsync(d_rows_, 0xFF, n_rows_ * sizeof(MrlRow), stream_));
   uint64_t launches = 0;
   for (const Step& st : plan.steps) {
     const Group& g = plan.groups[st.group];

@@ -1,12 +1,12 @@
-"""ctypes access to the CPU oracle (oracle/): TEST INFRASTRUCTURE only."""
+"""ctypes access to the CPU oracle. TEST INFRASTRUCTURE: used by tests/, the smoke check and
+the CPU-baseline legs of bench.py only; never by the product path."""
 import ctypes as C
 import os
 import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(ORACLE_DIR, "_build", "liboracle.so")
 KAT = os.path.join(ORACLE_DIR, "_build", "kat")
 CLI = os.path.join(ORACLE_DIR, "_build", "oracle_cli")

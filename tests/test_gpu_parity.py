@@ -44,3 +44,19 @@ def test_matmul2_top_down_closure_matches_oracle(m, oracle, dtype_name):
     assert not bad, "\n".join(bad)
     db.close()
     o.close()
+
+
+def test_precompute_size2_matches_oracle_everywhere(m, oracle):
+    """The bench workload at full size: every put of the oracle's size-2 precompute (u32 + f32),
+    checked at both corners of its rectangle."""
+    o = oracle.new()
+    rep = o.precompute(2)
+    assert rep["finished"] and o.dominance_conflicts() == 0
+    keys, off, rect, dec = o.dump()
+    db = m.SynthesisDatabase()
+    st = db.precompute(2)
+    assert st["n_specs"] == rep["logical_specs"] == 10454
+    bad = parity_util.compare_puts(db, keys, off, rect, dec)
+    assert not bad, "\n".join(bad)
+    db.close()
+    o.close()
