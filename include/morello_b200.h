@@ -81,6 +81,21 @@ void mrl_max_mem(uint64_t limits[4]);
 int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
                       mrl_decision* out);
 
+/* No counterpart in the reference. Same inputs, outputs and results as mrl_top_down_many, for
+ * callers that must not allocate device memory: a process that handed all of HBM to its tables
+ * at start-up has none left to give, and worker threads that call in concurrently would be
+ * serialised by the device-wide synchronisation of every cudaMalloc / cudaFree. This call makes
+ * neither; the device working set of the fill (plan arrays, row table, lookup staging) lives in
+ * one fixed array of MRL_NOALLOC_MAX_BYTES that each GPU loading the library holds until the
+ * process exits. A goal set whose fill needs more is refused with status -4 and a message; use
+ * mrl_top_down_many for it. The context's own tables are not touched.
+ * The first call on a device resolves the array's device address; make that call before any
+ * stream capture. All calls share the array, so calls that overlap on one GPU race - issue them
+ * one at a time per device. */
+#define MRL_NOALLOC_MAX_BYTES (32u << 20)
+int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n,
+                              const uint64_t* limits, mrl_decision* out);
+
 /* Replaces the precompute driver (precompute/src/main.rs:172-386) for the Move, Zero and Matmul
  * phases: fills the tables of every canonical Spec up to `size` (and their closure).
  * dtype_mask: bit 0 = u32, bit 1 = f32 (DTYPES, precompute/src/main.rs:55). */

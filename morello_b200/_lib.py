@@ -27,6 +27,8 @@ EXPORTS = {
     "mrl_max_mem": (None, [C.POINTER(C.c_uint64)]),
     "mrl_top_down_many": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_uint64),
                                     C.POINTER(Decision)]),
+    "mrl_top_down_many_noalloc": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t,
+                                            C.POINTER(C.c_uint64), C.POINTER(Decision)]),
     "mrl_precompute": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_int]),
     "mrl_plan_precompute": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_int]),
     "mrl_plan_goals": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t]),

@@ -238,6 +238,37 @@ int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_o
   return mrl_get_many(ctx, blobs, blob_off, n, limits, out);
 }
 
+int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n,
+                              const uint64_t* limits, mrl_decision* out) {
+  if (!ctx) return -1;
+  try {
+    std::vector<LogicalSpec> goals;
+    if (parse_goals(blobs, blob_off, n, goals) != 0) return fail(ctx, -4, "goal Spec is not canonicalizable");
+    // A plan of its own: the context's tables (and their device memory) are left as they are.
+    Plan plan = build_plan(goals, ctx->n_threads);
+    std::vector<uint64_t> idx;
+    std::vector<size_t> where;
+    for (size_t i = 0; i < n; i++) {
+      memset(&out[i], 0, sizeof(out[i]));
+      out[i].found = -1;
+      long id = plan.find(goals[i]);
+      if (id < 0) continue;
+      long row = plan.row_of((u32)id, limits + 4 * i);
+      if (row < 0) continue;
+      idx.push_back((uint64_t)row);
+      where.push_back(i);
+    }
+    std::vector<MrlRow> rows(idx.size());
+    char err[256] = {0};
+    int rc = fill_static(ctx->dev.device(), ctx->dev.stream(), plan, idx.data(), idx.size(), rows.data(), err, sizeof(err));
+    if (rc != 0) return fail(ctx, rc, err);
+    for (size_t j = 0; j < idx.size(); j++) decode_row(rows[j], &out[where[j]]);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
+}
+
 int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
   int rc = mrl_plan_precompute(ctx, size, through, dtype_mask);
   if (rc) return rc;

@@ -21,6 +21,7 @@
 #include "fill.hpp"
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <mutex>
 
 namespace {
 
@@ -308,6 +309,120 @@ int DeviceFill::download(std::vector<MrlRow>& out) {
   CK(cudaMemcpyAsync(out.data(), d_rows_, n_rows_ * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
   CK(cudaStreamSynchronize(stream_));
   return 0;
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Fill without device allocation.
+//
+// Some callers of this library must not allocate device memory while they run: a host that
+// reserved all of HBM for its replicated tables at start-up has nothing left to hand out, and
+// a worker pool that calls top_down_many from many threads would be serialised by the
+// device-wide synchronisation every cudaMalloc / cudaFree implies. For them the whole device
+// working set of one small fill - plan arrays, row table, lookup staging - is carved out of
+// the fixed array below instead of being allocated per call. Every GPU that loads this
+// library holds the array until the process exits.
+//
+// In host code `g_static_scratch` is only a stand-in for the device array, not a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, asked once per
+// device with that device current (static_scratch_address).
+namespace {
+__device__ __align__(256) unsigned char g_static_scratch[MRL_STATIC_SCRATCH_BYTES];
+}
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mu;
+
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+// Device address of the static array on `device`, resolved on first use.
+cudaError_t static_scratch_address(int device, void** out) {
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> g(g_scratch_mu);
+  if (!g_scratch_addr[device]) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return e;
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_scratch_addr[device] = p;
+  }
+  *out = g_scratch_addr[device];
+  return cudaSuccess;
+}
+}  // namespace
+
+// Runs `plan` entirely inside the static array and copies the rows at `row_idx` to `out`
+// (host). No cudaMalloc / cudaFree. Returns -4 with a message when the plan does not fit.
+int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_t* row_idx, size_t n,
+                MrlRow* out, char* err, size_t err_len) {
+#define CKS(x)                                                                        \
+  do {                                                                                \
+    cudaError_t e_ = (x);                                                             \
+    if (e_ != cudaSuccess) {                                                          \
+      snprintf(err, err_len, "%s failed: %s", #x, cudaGetErrorString(e_));            \
+      return -1;                                                                      \
+    }                                                                                 \
+  } while (0)
+  const size_t hdr_b = plan.hdrs.size() * sizeof(SpecHdr);
+  const size_t cand_b = plan.cands.size() * sizeof(CandRec);
+  const size_t chunk_b = plan.chunks.size() * sizeof(Chunk);
+  const size_t row_b = (size_t)plan.stats.n_rows * sizeof(MrlRow);
+  const size_t idx_b = n * sizeof(unsigned long long);
+  const size_t out_b = n * sizeof(MrlRow);
+  size_t off = 256;  // first 256 bytes: the error flag
+  const size_t o_hdr = off; off = align256(off + hdr_b);
+  const size_t o_cand = off; off = align256(off + cand_b);
+  const size_t o_chunk = off; off = align256(off + chunk_b);
+  const size_t o_rows = off; off = align256(off + row_b);
+  const size_t o_idx = off; off = align256(off + idx_b);
+  const size_t o_out = off; off = align256(off + out_b);
+  if (off > (size_t)MRL_STATIC_SCRATCH_BYTES) {
+    snprintf(err, err_len,
+             "this fill needs %zu bytes of device memory but the no-allocation entry point has a fixed %zu; "
+             "use mrl_top_down_many for it", off, (size_t)MRL_STATIC_SCRATCH_BYTES);
+    return -4;
+  }
+  for (size_t i = 0; i < n; i++)
+    if (row_idx[i] >= plan.stats.n_rows) { snprintf(err, err_len, "row index out of range"); return -3; }
+
+  void* base_v = nullptr;
+  CKS(static_scratch_address(device, &base_v));
+  CKS(cudaSetDevice(device));
+  unsigned char* base = static_cast<unsigned char*>(base_v);
+  int* d_err = reinterpret_cast<int*>(base);
+  SpecHdr* d_hdrs = reinterpret_cast<SpecHdr*>(base + o_hdr);
+  CandRec* d_cands = reinterpret_cast<CandRec*>(base + o_cand);
+  Chunk* d_chunks = reinterpret_cast<Chunk*>(base + o_chunk);
+  MrlRow* d_rows = reinterpret_cast<MrlRow*>(base + o_rows);
+  unsigned long long* d_idx = reinterpret_cast<unsigned long long*>(base + o_idx);
+  MrlRow* d_out = reinterpret_cast<MrlRow*>(base + o_out);
+
+  // The array keeps whatever the previous call left. Only the error flag has to start at
+  // zero; every table cell is written by its own step before anything reads it.
+  CKS(cudaMemsetAsync(d_err, 0, 256, stream));
+  if (hdr_b) CKS(cudaMemcpyAsync(d_hdrs, plan.hdrs.data(), hdr_b, cudaMemcpyHostToDevice, stream));
+  if (cand_b) CKS(cudaMemcpyAsync(d_cands, plan.cands.data(), cand_b, cudaMemcpyHostToDevice, stream));
+  if (chunk_b) CKS(cudaMemcpyAsync(d_chunks, plan.chunks.data(), chunk_b, cudaMemcpyHostToDevice, stream));
+  if (idx_b) CKS(cudaMemcpyAsync(d_idx, row_idx, idx_b, cudaMemcpyHostToDevice, stream));
+  const uint32_t n_specs = (uint32_t)plan.hdrs.size();
+  for (const Step& st : plan.steps) {
+    const Group& g = plan.groups[st.group];
+    const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
+    combine_argmin_kernel<<<(n_chunks + 3) / 4, 128, 0, stream>>>(d_hdrs, d_cands, d_chunks + g.chunk_lo, n_chunks,
+                                                                  st.diag, d_rows, n_specs, d_err);
+  }
+  if (n) gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(d_rows, d_idx, n, d_out);
+  CKS(cudaGetLastError());
+  int flag = 0;
+  if (out_b) CKS(cudaMemcpyAsync(out, d_out, out_b, cudaMemcpyDeviceToHost, stream));
+  CKS(cudaMemcpyAsync(&flag, d_err, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  CKS(cudaStreamSynchronize(stream));
+  if (flag) { snprintf(err, err_len, "combine kernel reported a bad child index"); return -2; }
+  return 0;
+#undef CKS
 }
 
 }  // namespace mrl

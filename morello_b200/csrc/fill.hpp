@@ -24,6 +24,7 @@ class DeviceFill {
   uint64_t h2d_bytes() const { return h2d_bytes_; }
   MrlRow* device_rows() const { return d_rows_; }
   cudaStream_t stream() const { return stream_; }
+  int device() const { return device_; }
 
  private:
   int device_ = 0;
@@ -40,5 +41,13 @@ class DeviceFill {
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
   char err_[256] = {0};
 };
+
+// Size of the fixed device array behind the no-allocation entry point (32 MiB per GPU).
+#define MRL_STATIC_SCRATCH_BYTES (32u << 20)
+
+// One whole small fill inside the fixed device array: plan arrays, row table and lookup
+// staging; no device allocation. See combine.cu.
+int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_t* row_idx, size_t n, MrlRow* out,
+                char* err, size_t err_len);
 
 }  // namespace mrl

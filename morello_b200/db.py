@@ -111,6 +111,18 @@ class SynthesisDatabase:
         self._check(self._lib.mrl_top_down_many(self._ctx, data, off, len(goals), lim, out))
         return [Decision.from_c(d) for d in out]
 
+    def top_down_many_noalloc(self, goals: Sequence[bytes],
+                              limits: Optional[Sequence[Sequence[int]]] = None) -> List[Decision]:
+        """top_down_many for callers that must not allocate device memory: the fill runs inside a
+        fixed 32 MiB device array and is refused (RuntimeError) when it needs more. One call at a
+        time per GPU; make the first call before any stream capture."""
+        if limits is None:
+            limits = [MAX_MEM] * len(goals)
+        data, off, lim = _pack(goals, limits)
+        out = (L.Decision * len(goals))()
+        self._check(self._lib.mrl_top_down_many_noalloc(self._ctx, data, off, len(goals), lim, out))
+        return [Decision.from_c(d) for d in out]
+
     def top_down(self, goal: bytes, limits: Sequence[int] = MAX_MEM) -> Decision:
         return self.top_down_many([goal], [limits])[0]
 
