@@ -145,8 +145,7 @@ def cuda_arm(args):
     # Replicas only at N > 1 for now: every rank fills the same database (weak scaling of
     # independent jobs); the table rows are not exchanged.
     db = m.SynthesisDatabase(device=local_rank)
-    db.plan_precompute(SIZE)
-    db.upload()
+    db.precompute(SIZE)  # plans, finds lattice caps that lose nothing, leaves plan and tables on the device
     for _ in range(max(args.warmup, 3)):
         db.fill()
     if world > 1:
@@ -155,8 +154,11 @@ def cuda_arm(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
     fill_ms = []
     for _ in range(args.steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
         db.fill()  # device time measured inside with CUDA events on the launching stream
         fill_ms.append(db.stats()["fill_ms"])
     torch.cuda.synchronize()
@@ -176,14 +178,16 @@ def cuda_arm(args):
     goal_blobs = [db.spec_blob(i) for i in range(0, db.num_specs(), max(1, db.num_specs() // 512))]
     e2e_s = []
     for i in range(1 + max(1, min(args.steps, 3))):
+        fresh = m.SynthesisDatabase(device=local_rank)  # a new database: nothing carried over
         t0 = time.perf_counter()
-        db.precompute(SIZE)
-        got = db.get_many(goal_blobs, [m.MAX_MEM] * len(goal_blobs))
+        fresh.precompute(SIZE)
+        got = fresh.get_many(goal_blobs, [m.MAX_MEM] * len(goal_blobs))
         dt = time.perf_counter() - t0
         if i > 0:
             e2e_s.append(dt)
+        st2 = fresh.stats()
+        fresh.close()
     assert all(g.found in (0, 1) for g in got)
-    st2 = db.stats()
     e2e_step = sum(e2e_s) / len(e2e_s)
     if world > 1:
         t = torch.tensor([e2e_step], device="cuda", dtype=torch.float64)
@@ -200,13 +204,15 @@ def cuda_arm(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
                    "rows_computed_per_step": st["n_rows"], "candidate_records": st["n_candidates"],
-                   "l2": "row table (%.1f GB) is larger than L2" % (st["n_rows"] * 12 / 1e9),
+                   "lattice_caps": st["lattice_caps"],
+                   "l2": ("row table %.0f MB; L2 flushed between fills" % (st["n_rows"] * 12 / 1e6)),
                    "multi_gpu": "replicas only" if world > 1 else "single"},
         "wall_s_full_db": e2e_step,
         "rows_per_s": st["n_rows"] * world / (ms_per_step * 1e-3),
         "e2e": {"value": units / e2e_step, "unit": "specs/s", "h2d_bytes_per_step": st2["h2d_bytes"],
                 "d2h_bytes_per_step": st2["d2h_bytes"], "plan_s": st2["plan_seconds"],
-                "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "wall_s": e2e_step},
+                "upload_s": st2["upload_seconds"], "fill_ms_all_attempts": st2["fill_ms_total"],
+                "fill_attempts": st2["fill_attempts"], "wall_s": e2e_step},
         "gpu_launches": int(st["n_launches"]) * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "combine_argmin_kernel",

@@ -48,6 +48,10 @@ typedef struct mrl_stats {
   double plan_seconds;        /* host: closure, candidate tabulation, lattice masks, schedule */
   double upload_seconds;
   double fill_ms;             /* device time of the last fill (CUDA events on the launch stream) */
+  double fill_ms_total;       /* device time of all fill attempts of the last precompute / top_down_many */
+  uint64_t n_launches_total;
+  uint32_t fill_attempts;     /* fills run until the lattice caps were large enough (>= 1) */
+  int32_t lattice_caps[4];    /* caps of the current tables, as lattice codes; -1 = memory not compressed */
 } mrl_stats;
 
 enum { MRL_KIND_MOVE = 0, MRL_KIND_FILL_ZERO = 1, MRL_KIND_MATMUL_ACCUM = 2, MRL_KIND_MATMUL = 3 };
@@ -107,6 +111,14 @@ int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask
 int mrl_plan_goals(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n);
 int mrl_upload(mrl_ctx* ctx);
 int mrl_fill(mrl_ctx* ctx);
+
+/* The limits lattice the tables keep per memory: the codes 0..caps[k] and the top limit
+ * (codes: registers raw, caches bit length; negative = keep all codes). Limits in between read
+ * the cap entry, which is exact while no optimal peak exceeds the cap; every fill checks that.
+ * With auto_raise (the default) mrl_precompute and mrl_top_down_many raise the caps and refill
+ * until the check passes; without it they return -5. No counterpart in the reference, whose
+ * R-tree rectangles need no such bound (morello/src/db/pagecontents.rs:125-184). */
+int mrl_set_lattice_caps(mrl_ctx* ctx, const int32_t caps[4], int auto_raise);
 
 /* Replaces FilesDatabase::get (morello/src/db/mod.rs:481-503, 538-573): point lookups in the
  * filled tables; found = -1 for Specs outside the tables. */

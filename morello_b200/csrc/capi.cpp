@@ -14,6 +14,10 @@ struct mrl_ctx {
   DeviceFill dev;
   mrl_stats stats;
   std::string err;
+  // Lattice caps per memory (lattice codes; negative = keep every code). Start low: a fill at
+  // low caps is cheap, and fill_verified raises them until no optimal peak exceeds its cap.
+  int caps[4] = {4, 2, 4, 0};
+  bool auto_raise = true;
 };
 
 namespace {
@@ -47,11 +51,74 @@ std::vector<Dtype> dtypes_of(int mask) {
   return d;
 }
 
+void copy_plan_stats(mrl_ctx* ctx) {
+  const PlanStats& ps = ctx->plan.stats;
+  ctx->stats.n_specs = ps.n_specs;
+  ctx->stats.n_goal_specs = ps.n_goal_specs;
+  ctx->stats.n_candidates = ps.n_cands;
+  ctx->stats.n_rows = ps.n_rows;
+  ctx->stats.algorithmic_bytes = ps.algorithmic_bytes;
+  for (int k = 0; k < 4; k++)
+    ctx->stats.lattice_caps[k] = ctx->plan.compressed(k) ? (int32_t)ctx->plan.cap_code[k] : -1;
+}
+
+// One upload + fill + check of the lattice compression. Returns 1 when some optimal peak
+// exceeded its cap (caps in ctx->caps have then been raised), 0 when the tables are exact.
+int fill_once(mrl_ctx* ctx) {
+  double t0 = now_s();
+  if (ctx->dev.upload(ctx->plan) != 0) return fail(ctx, -2, ctx->dev.error());
+  ctx->uploaded = true;
+  ctx->stats.upload_seconds += now_s() - t0;
+  ctx->stats.h2d_bytes += ctx->dev.h2d_bytes();
+  float ms = 0;
+  uint64_t launches = 0;
+  if (ctx->dev.run(ctx->plan, &ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
+  ctx->stats.fill_ms_total += ms;
+  ctx->stats.fill_ms = ms;
+  ctx->stats.n_launches = launches;
+  ctx->stats.n_launches_total += launches;
+  ctx->stats.fill_attempts++;
+  uint32_t pk[4];
+  if (ctx->dev.max_peaks(pk) != 0) return fail(ctx, -2, ctx->dev.error());
+  bool violated = false;
+  for (int k = 0; k < 4; k++)
+    if (ctx->plan.compressed(k) && pk[k] > ctx->plan.cap_code[k]) {
+      violated = true;
+      ctx->caps[k] = (int)pk[k];
+    }
+  return violated ? 1 : 0;
+}
+
+// Fills the planned tables, raising the lattice caps until the compression is exact.
+int fill_verified(mrl_ctx* ctx) {
+  ctx->stats.upload_seconds = 0;
+  ctx->stats.h2d_bytes = 0;
+  ctx->stats.fill_ms_total = 0;
+  ctx->stats.n_launches_total = 0;
+  ctx->stats.fill_attempts = 0;
+  ctx->filled = false;
+  for (int attempt = 0; attempt < 16; attempt++) {
+    int rc = fill_once(ctx);
+    if (rc < 0) return rc;
+    if (rc == 0) {
+      ctx->filled = true;
+      return 0;
+    }
+    if (!ctx->auto_raise) return fail(ctx, -5, "an optimal peak exceeds the lattice caps; raise them (mrl_set_lattice_caps)");
+    double t0 = now_s();
+    relayout_plan(ctx->plan, ctx->caps);
+    copy_plan_stats(ctx);
+    ctx->stats.plan_seconds += now_s() - t0;
+  }
+  return fail(ctx, -5, "lattice caps did not converge");
+}
+
 int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
   double t0 = now_s();
-  ctx->plan = build_plan(goals, ctx->n_threads);
+  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->caps);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
+  copy_plan_stats(ctx);
   const PlanStats& ps = ctx->plan.stats;
   ctx->stats.n_specs = ps.n_specs;
   ctx->stats.n_goal_specs = ps.n_goal_specs;
@@ -194,9 +261,29 @@ int mrl_fill(mrl_ctx* ctx) {
   float ms = 0;
   uint64_t launches = 0;
   if (ctx->dev.run(ctx->plan, &ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
-  ctx->filled = true;
   ctx->stats.fill_ms = ms;
   ctx->stats.n_launches = launches;
+  uint32_t pk[4];
+  if (ctx->dev.max_peaks(pk) != 0) return fail(ctx, -2, ctx->dev.error());
+  for (int k = 0; k < 4; k++)
+    if (ctx->plan.compressed(k) && pk[k] > ctx->plan.cap_code[k]) {
+      ctx->filled = false;
+      return fail(ctx, -5, "an optimal peak exceeds the lattice caps of this plan; use mrl_precompute / "
+                           "mrl_top_down_many (they raise the caps) or mrl_set_lattice_caps");
+    }
+  ctx->filled = true;
+  return 0;
+}
+
+int mrl_set_lattice_caps(mrl_ctx* ctx, const int32_t caps[4], int auto_raise) {
+  if (!ctx || !caps) return -1;
+  for (int k = 0; k < 4; k++) ctx->caps[k] = caps[k];
+  ctx->auto_raise = auto_raise != 0;
+  if (ctx->planned) {
+    relayout_plan(ctx->plan, ctx->caps);
+    copy_plan_stats(ctx);
+    ctx->uploaded = ctx->filled = false;
+  }
   return 0;
 }
 
@@ -233,8 +320,7 @@ int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_o
                       mrl_decision* out) {
   int rc = mrl_plan_goals(ctx, blobs, blob_off, n);
   if (rc) return rc;
-  if ((rc = mrl_upload(ctx))) return rc;
-  if ((rc = mrl_fill(ctx))) return rc;
+  if ((rc = fill_verified(ctx))) return rc;
   return mrl_get_many(ctx, blobs, blob_off, n, limits, out);
 }
 
@@ -245,7 +331,10 @@ int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t
     std::vector<LogicalSpec> goals;
     if (parse_goals(blobs, blob_off, n, goals) != 0) return fail(ctx, -4, "goal Spec is not canonicalizable");
     // A plan of its own: the context's tables (and their device memory) are left as they are.
-    Plan plan = build_plan(goals, ctx->n_threads);
+    // Every lattice code is kept here (no caps): the fill is small by construction and one
+    // pass must be final.
+    const int no_caps[4] = {-1, -1, -1, -1};
+    Plan plan = build_plan(goals, ctx->n_threads, nullptr, no_caps);
     std::vector<uint64_t> idx;
     std::vector<size_t> where;
     for (size_t i = 0; i < n; i++) {
@@ -272,8 +361,7 @@ int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t
 int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
   int rc = mrl_plan_precompute(ctx, size, through, dtype_mask);
   if (rc) return rc;
-  if ((rc = mrl_upload(ctx))) return rc;
-  return mrl_fill(ctx);
+  return fill_verified(ctx);
 }
 
 int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out) {

@@ -84,7 +84,8 @@ __device__ __forceinline__ MrlRow lookup(const SpecHdr* __restrict__ hdrs, const
 __global__ void __launch_bounds__(128)
 combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
                       const Chunk* __restrict__ chunks, uint32_t n_chunks, uint32_t diag,
-                      MrlRow* __restrict__ rows, uint32_t n_specs, int* __restrict__ error_flag) {
+                      MrlRow* __restrict__ rows, uint32_t n_specs, uint32_t cap_pack, uint32_t top_pack,
+                      int* __restrict__ error_flag) {
   const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
   if (warp >= n_chunks) return;
@@ -112,7 +113,11 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     const uint32_t imm = a.y;
     const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, pcode = (a.z >> 16) & 0xFFu;
     const uint32_t units = a.w;
-    const uint32_t lv = code_of(cpack, level);
+    // The cell's limit in `level` as a lattice code. In a compressed memory the grid keeps the
+    // codes 0..cap and, as slot cap+1, the top code.
+    const uint32_t cap = code_of(cap_pack, level);
+    const uint32_t lv_slot = code_of(cpack, level);
+    const uint32_t lv = (lv_slot == cap + 1u) ? code_of(top_pack, level) : lv_slot;
     Key k;
     if (kind == MRL_CK_LEAF) {
       if (lv < thr) continue;
@@ -128,7 +133,9 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
         uint32_t ccode;
         if (level < 2) ccode = lv - units;                      // registers: exact
         else ccode = 32 - __clz(cache_value(lv) - units);       // caches: snap down to 2^k
-        ccpack = with_code(cpack, level, ccode);
+        // The child's limit is below the top; codes above the cap read the cap slot (nothing
+        // changes between cap and top while no optimal peak exceeds the cap).
+        ccpack = with_code(cpack, level, min(ccode, cap));
       }
       uint32_t main = (kind == MRL_CK_MOVE) ? imm : 0u;
       uint32_t peaks = 0, depth = 0;
@@ -171,6 +178,23 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   q[2] = best.tail;
 }
 
+// Largest peak code per memory over all satisfiable rows (checks the lattice compression).
+__global__ void max_peaks_kernel(const MrlRow* __restrict__ rows, unsigned long long n, uint32_t* __restrict__ out4) {
+  uint32_t mx = 0;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (unsigned long long)gridDim.x * blockDim.x) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(rows + i);
+    if (p[2] != MRL_UNSAT) mx = __vmaxu4(mx, p[1]);
+  }
+  for (int o = 16; o > 0; o >>= 1) mx = __vmaxu4(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+  if ((threadIdx.x & 31) == 0) {
+    atomicMax(&out4[0], (mx >> 24) & 0xFFu);
+    atomicMax(&out4[1], (mx >> 16) & 0xFFu);
+    atomicMax(&out4[2], (mx >> 8) & 0xFFu);
+    atomicMax(&out4[3], mx & 0xFFu);
+  }
+}
+
 // Point lookups for get: copies the rows at the given indices into a dense buffer.
 __global__ void gather_rows_kernel(const MrlRow* __restrict__ rows, const unsigned long long* __restrict__ idx,
                                    unsigned long long n, MrlRow* __restrict__ out) {
@@ -204,6 +228,8 @@ void DeviceFill::release() {
   if (d_chunks_) cudaFree(d_chunks_);
   if (d_rows_) cudaFree(d_rows_);
   if (d_err_) cudaFree(d_err_);
+  if (d_peaks_) cudaFree(d_peaks_);
+  d_peaks_ = nullptr;
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_chunks_ = nullptr; d_rows_ = nullptr; d_err_ = nullptr;
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
@@ -258,7 +284,7 @@ int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
     const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
     const uint32_t blocks = (n_chunks + 3) / 4;
     combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, st.diag,
-                                                       d_rows_, n_specs_, d_err_);
+                                                       d_rows_, n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
     launches++;
   }
   CK(cudaGetLastError());
@@ -274,6 +300,17 @@ int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
   }
   if (ms_out) *ms_out = ms;
   if (launches_out) *launches_out = launches;
+  return 0;
+}
+
+int DeviceFill::max_peaks(uint32_t out[4]) {
+  CK(cudaSetDevice(device_));
+  if (!d_peaks_) CK(cudaMalloc(&d_peaks_, 4 * sizeof(uint32_t)));
+  CK(cudaMemsetAsync(d_peaks_, 0, 4 * sizeof(uint32_t), stream_));
+  if (n_rows_) max_peaks_kernel<<<148 * 8, 256, 0, stream_>>>(d_rows_, n_rows_, d_peaks_);
+  CK(cudaGetLastError());
+  CK(cudaMemcpyAsync(out, d_peaks_, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
   return 0;
 }
 
@@ -412,7 +449,8 @@ int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_
     const Group& g = plan.groups[st.group];
     const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
     combine_argmin_kernel<<<(n_chunks + 3) / 4, 128, 0, stream>>>(d_hdrs, d_cands, d_chunks + g.chunk_lo, n_chunks,
-                                                                  st.diag, d_rows, n_specs, d_err);
+                                                                  st.diag, d_rows, n_specs, plan.cap_pack(),
+                                                                  plan.top_pack(), d_err);
   }
   if (n) gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(d_rows, d_idx, n, d_out);
   CKS(cudaGetLastError());

@@ -16,6 +16,9 @@ class DeviceFill {
   // Runs every (group, diagonal) step. ms_out: device time of the whole schedule, measured
   // with CUDA events on the launching stream.
   int run(const Plan& plan, float* ms_out, uint64_t* launches_out);
+  // Largest peak (lattice code) per memory over the filled table: the check that a compressed
+  // lattice lost nothing (every peak must stay at or below its memory's cap).
+  int max_peaks(uint32_t out[4]);
   int read_rows(const uint64_t* row_idx, size_t n, MrlRow* out);
   int download(std::vector<MrlRow>& out);
   void release();
@@ -33,6 +36,7 @@ class DeviceFill {
   Chunk* d_chunks_ = nullptr;
   MrlRow* d_rows_ = nullptr;
   int* d_err_ = nullptr;
+  uint32_t* d_peaks_ = nullptr;
   uint32_t n_specs_ = 0;
   uint64_t n_rows_ = 0;
   uint64_t h2d_bytes_ = 0;

@@ -97,6 +97,7 @@ long Plan::row_of(u32 id, const u64 limits[NMEM]) const {
   for (int k = 0; k < NMEM; k++) {
     u32 code = limit_code(k, limits[k]);
     if (code > top_code[k]) return -1;  // beyond the limits this table was filled for
+    code = slot_of_code(k, code);
     u32 below = h.mask[k] & (code >= 31 ? 0xFFFFFFFFu : ((2u << code) - 1u));
     u32 i = (u32)__builtin_popcount(below) - 1;
     idx += stride * i;
@@ -105,7 +106,7 @@ long Plan::row_of(u32 id, const u64 limits[NMEM]) const {
   return (long)(h.row_base + idx);
 }
 
-Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits) {
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, const int* caps) {
   if (n_threads < 1) n_threads = 1;
   Plan plan;
   u32 top_code[NMEM];
@@ -115,6 +116,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     top_code[k] = limit_code(k, v);
     if (top_code[k] > 30) throw ModelError("memory limit too large for the lattice masks");
     plan.top_code[k] = top_code[k];
+    plan.cap_code[k] = (caps && caps[k] >= 0 && (u32)caps[k] < top_code[k]) ? (u32)caps[k] : top_code[k];
   }
 
   // ---- 1. discovery: closure of the goals under "is a sub-Spec of some candidate" ----
@@ -257,12 +259,33 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   }
   plan.stats.seconds_layout = now_s() - t1;
 
+  plan.stats.n_specs = n;
+  plan.stats.n_cands = ncand;
+  relayout_plan(plan, caps);
+  return plan;
+}
+
+void relayout_plan(Plan& plan, const int* caps) {
+  const u32 n = (u32)plan.hdrs.size();
+  const u32* top_code = plan.top_code;
+  for (int k = 0; k < NMEM; k++)
+    plan.cap_code[k] = (caps && caps[k] >= 0 && (u32)caps[k] < top_code[k]) ? (u32)caps[k] : top_code[k];
+  plan.chunks.clear();
+  plan.steps.clear();
+  plan.stats.mask_sweeps = 0;
+
   // ---- 3. breakpoint masks: least fixpoint of "a parent's result can change wherever one
   //         of its candidates becomes feasible or one of its children's results changes" ----
   double t2 = now_s();
   for (u32 i = 0; i < n; i++) for (int k = 0; k < NMEM; k++) plan.hdrs[i].mask[k] = 1u;
-  u32 all_mask[NMEM];
-  for (int k = 0; k < NMEM; k++) all_mask[k] = (top_code[k] >= 31) ? 0xFFFFFFFFu : ((2u << top_code[k]) - 1u);
+  // Masks live in slot space (Plan::cap_code). A threshold at limit code t sets slot_ceil(t).
+  // A Move lowers its children's limit in the destination memory, so their code there is always
+  // below the top: only the child's slots 0..cap (real codes) feed the parent's thresholds.
+  u32 real_slots[NMEM];   // mask of slots that are plain codes (0..cap, or 0..top when not compressed)
+  for (int k = 0; k < NMEM; k++) {
+    u32 hi = plan.compressed(k) ? plan.cap_code[k] : top_code[k];
+    real_slots[k] = (hi >= 31) ? 0xFFFFFFFFu : ((2u << hi) - 1u);
+  }
   bool changed = true;
   while (changed) {
     changed = false;
@@ -273,23 +296,20 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
         if (r.kind == MRL_CK_LEAF) {
-          m[r.level] |= 1u << r.thr_code;
+          m[r.level] |= 1u << plan.slot_ceil(r.level, r.thr_code);
           continue;
         }
         for (int j = 0; j < r.nchild; j++) {
           const SpecHdr& ch = plan.hdrs[r.child[j]];
           for (int k = 0; k < NMEM; k++) {
             if (r.kind != MRL_CK_MOVE || k != r.level) { m[k] |= ch.mask[k]; continue; }
-            if (mem_counts_registers((Mem)k)) {
-              m[k] |= (r.units >= 32 ? 0u : (ch.mask[k] << r.units)) & all_mask[k];
-            } else {
-              u32 cm = ch.mask[k];
-              while (cm) {
-                u32 b = (u32)__builtin_ctz(cm);
-                cm &= cm - 1;
-                u32 code = bit_length(next_binary_power(bit_length_inverse(b) + r.units));
-                if (code <= top_code[k]) m[k] |= 1u << code;
-              }
+            u32 cm = ch.mask[k] & real_slots[k];
+            while (cm) {
+              u32 b = (u32)__builtin_ctz(cm);
+              cm &= cm - 1;
+              u32 code = mem_counts_registers((Mem)k) ? b + r.units
+                                                      : bit_length(next_binary_power(bit_length_inverse(b) + r.units));
+              if (code <= top_code[k]) m[k] |= 1u << plan.slot_ceil(k, code);
             }
           }
         }
@@ -328,7 +348,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         const CandRec& r = plan.cands[c];
         bytes += ncells * 16;
         if (r.nchild) {
-          u32 feasible_k = (u32)__builtin_popcount(h.mask[r.level] >> r.thr_code);
+          u32 feasible_k = (u32)__builtin_popcount(h.mask[r.level] >> plan.slot_ceil(r.level, r.thr_code));
           u64 feasible = ncells / nk[r.level] * feasible_k;
           bytes += feasible * r.nchild * 16;
         }
@@ -338,13 +358,14 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   }
   u32 max_diag = 0;
   for (const Group& g : plan.groups) max_diag = std::max(max_diag, g.max_diag);
-  for (u32 d = 0; d <= max_diag; d++)
-    for (u32 gi = 0; gi < plan.groups.size(); gi++)
-      if (plan.groups[gi].max_diag >= d && plan.groups[gi].chunk_hi > plan.groups[gi].chunk_lo)
-        plan.steps.push_back(Step{gi, d});
+  // Group-major: a group only needs earlier groups (any limits) and, inside itself, cells on
+  // lower diagonals. Moves keep kind, dtype and shape, so they never leave their group;
+  // tile-outs and splits go to a smaller log-shape sum; ToAccum and Move prologues/epilogues
+  // go to an earlier phase.
+  for (u32 gi = 0; gi < plan.groups.size(); gi++)
+    if (plan.groups[gi].chunk_hi > plan.groups[gi].chunk_lo)
+      for (u32 d = 0; d <= plan.groups[gi].max_diag; d++) plan.steps.push_back(Step{gi, d});
 
-  plan.stats.n_specs = n;
-  plan.stats.n_cands = ncand;
   plan.stats.n_rows = row;
   plan.stats.n_columns = cols_total;
   plan.stats.n_groups = plan.groups.size();
@@ -352,7 +373,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   plan.stats.max_diag = max_diag;
   plan.stats.algorithmic_bytes = bytes;
   plan.stats.seconds_layout += now_s() - t3;
-  return plan;
 }
 
 }  // namespace mrl

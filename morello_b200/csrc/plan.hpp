@@ -46,7 +46,7 @@ struct Group {          // Specs with the same phase and log-shape sum: no depen
 
 struct Step {           // one kernel launch
   u32 group;
-  u32 diag;
+  u32 diag;             // sum of the four limit slots of the cells this launch evaluates
 };
 
 struct Plan {
@@ -58,6 +58,33 @@ struct Plan {
   std::vector<Step> steps;
   std::vector<u32> goal_ids;
   u32 top_code[NMEM] = {0, 0, 0, 0};   // lattice codes of the top limits the plan covers
+  // Lattice compression. In a compressed memory k the table keeps the codes 0..cap_code[k] and
+  // the top code only ("slots" 0..cap and cap+1); limits strictly between map to the cap slot.
+  // That is exact as long as no optimal peak exceeds the cap (checked after every fill): a
+  // result whose peak fits under the cap is already available at the cap, so nothing changes
+  // between cap and top. cap_code[k] == top_code[k] means memory k is not compressed.
+  u32 cap_code[NMEM] = {0, 0, 0, 0};
+  bool compressed(int k) const { return cap_code[k] + 1 < top_code[k]; }
+  u32 slot_of_code(int k, u32 code) const {
+    if (!compressed(k)) return code;
+    if (code == top_code[k]) return cap_code[k] + 1;
+    return code < cap_code[k] ? code : cap_code[k];
+  }
+  // Smallest slot whose limit is >= the limit `code` (for feasibility thresholds).
+  u32 slot_ceil(int k, u32 code) const {
+    if (!compressed(k) || code <= cap_code[k]) return code;
+    return cap_code[k] + 1;
+  }
+  u32 cap_pack() const {   // one byte per memory, 255 = not compressed
+    u32 r = 0;
+    for (int k = 0; k < NMEM; k++) r |= (compressed(k) ? cap_code[k] : 255u) << (8 * k);
+    return r;
+  }
+  u32 top_pack() const {
+    u32 r = 0;
+    for (int k = 0; k < NMEM; k++) r |= top_code[k] << (8 * k);
+    return r;
+  }
   PlanStats stats;
 
   // id of a logical Spec (canonical form), or -1.
@@ -66,12 +93,18 @@ struct Plan {
   long row_of(u32 id, const u64 limits[NMEM]) const;
 
  private:
-  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*);
+  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, const int*);
   std::vector<std::pair<std::string, u32>> sorted_keys_;  // (key, id), sorted by key
 };
 
-// Top limits are Avx2Target::max_mem() unless overridden.
-Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr);
+// Top limits are Avx2Target::max_mem() unless overridden. caps: per memory the largest lattice
+// code kept below the top (negative or >= top: no compression), see Plan::cap_code.
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr,
+                const int* caps = nullptr);
+
+// Recomputes everything that depends on the lattice caps (breakpoint masks, row offsets, chunk
+// lists, schedule, byte accounting) and leaves Specs and candidate records alone.
+void relayout_plan(Plan& plan, const int* caps);
 
 // Goal sets.
 std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes);

@@ -145,6 +145,11 @@ class SynthesisDatabase:
     def fill(self):
         self._check(self._lib.mrl_fill(self._ctx))
 
+    def set_lattice_caps(self, caps: Sequence[int], auto_raise: bool = True):
+        """Per memory (RF, VRF, L1, GL) the largest limit code kept below the top; -1 keeps all."""
+        arr = (C.c_int32 * 4)(*caps)
+        self._check(self._lib.mrl_set_lattice_caps(self._ctx, arr, int(auto_raise)))
+
     # --- FilesDatabase::get ---
     def get_many(self, specs: Sequence[bytes], limits: Sequence[Sequence[int]]) -> List[Decision]:
         data, off, lim = _pack(specs, limits)
@@ -159,7 +164,9 @@ class SynthesisDatabase:
     def stats(self) -> dict:
         s = L.Stats()
         self._check(self._lib.mrl_get_stats(self._ctx, C.byref(s)))
-        return {name: getattr(s, name) for name, _ in L.Stats._fields_}
+        out = {name: getattr(s, name) for name, _ in L.Stats._fields_}
+        out["lattice_caps"] = [int(x) for x in s.lattice_caps]
+        return out
 
     def num_specs(self) -> int:
         return int(self._lib.mrl_num_specs(self._ctx))

@@ -14,20 +14,31 @@ import morello_b200 as m
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["matmul1", "matmul2", "matmul2_f32", "precompute1", "precompute2", "precompute2_u32"])
+    ap.add_argument("case", choices=["matmul1", "matmul2", "matmul2_f32", "precompute1", "precompute2", "precompute2_u32",
+                                     "precompute4", "precompute4_u32"])
     ap.add_argument("--fills", type=int, default=1)
+    ap.add_argument("--caps", type=str, default=None, help="lattice caps RF,VRF,L1,GL (codes; -1 = all)")
     args = ap.parse_args()
     db = m.SynthesisDatabase(device=0)
+    if args.caps:
+        db.set_lattice_caps([int(x) for x in args.caps.split(",")])
     if args.case.startswith("matmul"):
         size = int(args.case[6])
         dtype = m.DTYPE_F32 if args.case.endswith("f32") else m.DTYPE_U32
-        db.plan_goals([m.simple_spec(m.KIND_MATMUL, dtype, [1, size, size, size], m.GL)])
+        goal = m.simple_spec(m.KIND_MATMUL, dtype, [1, size, size, size], m.GL)
+        db.plan_goals([goal])
     else:
-        if args.case.endswith("_u32"):
-            db.plan_precompute(int(args.case[10]), dtypes=(m.DTYPE_U32,))
-        else:
-            db.plan_precompute(int(args.case[-1]))
+        dtypes = (m.DTYPE_U32,) if args.case.endswith("_u32") else (m.DTYPE_U32, m.DTYPE_F32)
+        db.plan_precompute(int(args.case[10]), dtypes=dtypes)
     db.upload()
+    try:
+        db.fill()
+    except RuntimeError:
+        # the first fill found the starting lattice caps too small: let the library raise them
+        if args.case.startswith("matmul"):
+            db.top_down(goal)
+        else:
+            db.precompute(int(args.case[10]), dtypes=dtypes)
     for _ in range(args.fills):
         db.fill()
     st = db.stats()

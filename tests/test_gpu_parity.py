@@ -60,3 +60,48 @@ def test_precompute_size2_matches_oracle_everywhere(m, oracle):
     assert not bad, "\n".join(bad)
     db.close()
     o.close()
+
+
+@pytest.mark.parametrize("name", ["precompute_1", "matmul2_u32", "matmul2_f32"])
+def test_gpu_tables_match_committed_golden_fixtures(m, name):
+    """Same checks without the oracle in the loop: the committed fixtures of tests/golden."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name + ".npz"))
+    db = m.SynthesisDatabase()
+    if name == "precompute_1":
+        db.precompute(1)
+    else:
+        got = db.top_down(g["goal"].tobytes())
+        assert [got.found, got.action, got.main_cost, got.depth] + list(got.peaks) == list(g["goal_decision"])
+    bad = parity_util.compare_puts(db, g["keys"], g["key_off"], g["rect"], g["dec"])
+    assert not bad, "\n".join(bad)
+    db.close()
+
+
+def test_edge_cases(m):
+    db = m.SynthesisDatabase()
+    # empty goal list
+    assert db.top_down_many([]) == []
+    # zero limits: nothing fits except what needs no memory
+    rf_mm = m.simple_spec(m.KIND_MATMUL_ACCUM, m.DTYPE_U32, [1, 1, 1, 1], m.RF)
+    gl_mm = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
+    got = db.top_down_many([rf_mm, gl_mm], [(0, 0, 0, 0), (0, 0, 0, 0)])
+    assert got[0].found == 1 and got[0].main_cost == 2 and got[0].peaks == (0, 0, 0, 0)
+    assert got[1].found == 0
+    # lookups: a Spec outside the tables is a miss, limits above the planned top are a miss
+    other = m.simple_spec(m.KIND_MATMUL, m.DTYPE_F32, [1, 2, 2, 2], m.GL)
+    assert db.get(other).found == -1
+    assert db.get(gl_mm, (17, 16, 1024, 33554432)).found == -1
+    # limits between lattice entries read the entry below
+    a = db.get(gl_mm, (16, 16, 1024, 33554432))
+    b = db.get(gl_mm, (16, 16, 1024, 1 << 20))
+    assert a == b and a.found == 1
+    # monotone in memory: fewer registers never cost less
+    prev = None
+    for rf in range(0, 17):
+        d = db.get(gl_mm, (rf, 16, 1024, 33554432))
+        if d.found == 1:
+            if prev is not None:
+                assert d.main_cost <= prev
+            prev = d.main_cost
+    db.close()
