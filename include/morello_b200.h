@@ -120,6 +120,27 @@ int mrl_fill(mrl_ctx* ctx);
  * R-tree rectangles need no such bound (morello/src/db/pagecontents.rs:125-184). */
 int mrl_set_lattice_caps(mrl_ctx* ctx, const int32_t caps[4], int auto_raise);
 
+/* Multi-GPU (one process per GPU; no counterpart in the reference, whose workers are threads
+ * sharing one database, precompute/src/main.rs:229-240,339). Every rank plans the same job and
+ * keeps the whole table; rank r computes the "families" (Specs of one group with equal dtype and
+ * shape - Moves change neither, so families of a group are independent) it owns. Between groups
+ * the caller copies each family's rows from its owner to all ranks, on the stream given to
+ * mrl_set_stream, e.g. with ncclBroadcast over NVLink:
+ *   mrl_set_shard, mrl_plan_*, mrl_upload, then per fill: mrl_fill_begin;
+ *   for g in groups { mrl_fill_group(g); exchange rows of the families of g }; mrl_fill_end.
+ * mrl_fill_end returns 1 (and the caps to use) when an optimal peak exceeded a lattice cap: the
+ * caller applies the element-wise maximum over ranks with mrl_set_lattice_caps and refills. */
+int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world);
+int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream);
+uint64_t mrl_num_groups(const mrl_ctx* ctx);
+uint64_t mrl_num_families(const mrl_ctx* ctx);
+int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* group, uint32_t* owner, uint64_t* row_lo,
+                    uint64_t* row_hi);
+int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows); /* 12-byte rows */
+int mrl_fill_begin(mrl_ctx* ctx);
+int mrl_fill_group(mrl_ctx* ctx, uint64_t group);
+int mrl_fill_end(mrl_ctx* ctx, int32_t raised_caps[4]);
+
 /* Replaces FilesDatabase::get (morello/src/db/mod.rs:481-503, 538-573): point lookups in the
  * filled tables; found = -1 for Specs outside the tables. */
 int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,

@@ -36,6 +36,16 @@ EXPORTS = {
     "mrl_upload": (C.c_int, [C.c_void_p]),
     "mrl_fill": (C.c_int, [C.c_void_p]),
     "mrl_set_lattice_caps": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int]),
+    "mrl_set_shard": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32]),
+    "mrl_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mrl_num_groups": (C.c_uint64, [C.c_void_p]),
+    "mrl_num_families": (C.c_uint64, [C.c_void_p]),
+    "mrl_family_info": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                  C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "mrl_device_rows": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "mrl_fill_begin": (C.c_int, [C.c_void_p]),
+    "mrl_fill_group": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "mrl_fill_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "mrl_get_many": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_uint64),
                                C.POINTER(Decision)]),
     "mrl_get_stats": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),

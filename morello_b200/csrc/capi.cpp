@@ -18,6 +18,7 @@ struct mrl_ctx {
   // low caps is cheap, and fill_verified raises them until no optimal peak exceeds its cap.
   int caps[4] = {4, 2, 4, 0};
   bool auto_raise = true;
+  uint32_t rank = 0, world = 1;
 };
 
 namespace {
@@ -91,6 +92,7 @@ int fill_once(mrl_ctx* ctx) {
 
 // Fills the planned tables, raising the lattice caps until the compression is exact.
 int fill_verified(mrl_ctx* ctx) {
+  if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to fill on");
   ctx->stats.upload_seconds = 0;
   ctx->stats.h2d_bytes = 0;
   ctx->stats.fill_ms_total = 0;
@@ -115,7 +117,7 @@ int fill_verified(mrl_ctx* ctx) {
 
 int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
   double t0 = now_s();
-  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->caps);
+  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->caps, ctx->rank, ctx->world);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
   copy_plan_stats(ctx);
@@ -151,7 +153,10 @@ int mrl_ctx_create(int device, int n_threads, mrl_ctx** out) {
   ctx->n_threads = n_threads;
   memset(&ctx->stats, 0, sizeof(ctx->stats));
   *out = ctx;
-  // No silent CPU path: a context without a usable GPU is an error.
+  // device < 0: a planning-only context (closure, candidate tables, shard ownership can be
+  // inspected; nothing can be filled or looked up). Otherwise a usable GPU is required:
+  // there is no CPU path.
+  if (device < 0) return 0;
   if (ctx->dev.init(device) != 0) {
     ctx->err = std::string("no usable CUDA device: ") + ctx->dev.error();
     return -2;
@@ -245,6 +250,7 @@ int mrl_plan_goals(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off,
 
 int mrl_upload(mrl_ctx* ctx) {
   if (!ctx) return -1;
+  if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to fill on");
   if (!ctx->planned) return fail(ctx, -1, "nothing planned");
   double t0 = now_s();
   if (ctx->dev.upload(ctx->plan) != 0) return fail(ctx, -2, ctx->dev.error());
@@ -362,6 +368,77 @@ int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
   int rc = mrl_plan_precompute(ctx, size, through, dtype_mask);
   if (rc) return rc;
   return fill_verified(ctx);
+}
+
+int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world) {
+  if (!ctx) return -1;
+  if (world < 1 || rank >= world) return fail(ctx, -1, "bad shard rank / world size");
+  ctx->rank = rank;
+  ctx->world = world;
+  ctx->planned = ctx->uploaded = ctx->filled = false;
+  return 0;
+}
+
+int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream) {
+  if (!ctx) return -1;
+  return ctx->dev.set_stream((cudaStream_t)cuda_stream);
+}
+
+uint64_t mrl_num_groups(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.groups.size() : 0; }
+uint64_t mrl_num_families(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.families.size() : 0; }
+
+int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* group, uint32_t* owner, uint64_t* row_lo,
+                    uint64_t* row_hi) {
+  if (!ctx || !ctx->planned || family >= ctx->plan.families.size()) return -1;
+  const Family& f = ctx->plan.families[family];
+  if (group) *group = f.group;
+  if (owner) *owner = f.owner;
+  if (row_lo) *row_lo = f.row_lo;
+  if (row_hi) *row_hi = f.row_hi;
+  return 0;
+}
+
+int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows) {
+  if (!ctx || !ctx->uploaded) return -1;
+  if (ptr) *ptr = ctx->dev.device_rows();
+  if (n_rows) *n_rows = ctx->dev.n_rows();
+  return 0;
+}
+
+int mrl_fill_begin(mrl_ctx* ctx) {
+  if (!ctx) return -1;
+  if (!ctx->uploaded) return fail(ctx, -1, "plan not uploaded");
+  ctx->filled = false;
+  if (ctx->dev.begin_fill() != 0) return fail(ctx, -2, ctx->dev.error());
+  return 0;
+}
+
+int mrl_fill_group(mrl_ctx* ctx, uint64_t group) {
+  if (!ctx || !ctx->uploaded) return -1;
+  if (ctx->dev.run_group(ctx->plan, (uint32_t)group) != 0) return fail(ctx, -2, ctx->dev.error());
+  return 0;
+}
+
+int mrl_fill_end(mrl_ctx* ctx, int32_t raised_caps[4]) {
+  if (!ctx || !ctx->uploaded) return -1;
+  float ms = 0;
+  uint64_t launches = 0;
+  if (ctx->dev.end_fill(&ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
+  ctx->stats.fill_ms = ms;
+  ctx->stats.n_launches = launches;
+  uint32_t pk[4];
+  if (ctx->dev.max_peaks(pk) != 0) return fail(ctx, -2, ctx->dev.error());
+  bool violated = false;
+  for (int k = 0; k < 4; k++) {
+    if (raised_caps) raised_caps[k] = ctx->caps[k];
+    if (ctx->plan.compressed(k) && pk[k] > ctx->plan.cap_code[k]) {
+      violated = true;
+      if (raised_caps) raised_caps[k] = (int32_t)pk[k];
+    }
+  }
+  if (violated) return 1;  // not an error: the caller raises the caps on every rank and refills
+  ctx->filled = true;
+  return 0;
 }
 
 int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out) {

@@ -303,6 +303,52 @@ int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
   return 0;
 }
 
+int DeviceFill::set_stream(cudaStream_t s) {
+  if (own_stream_ && stream_) cudaStreamDestroy(stream_);
+  stream_ = s;
+  own_stream_ = false;
+  return 0;
+}
+
+int DeviceFill::begin_fill() {
+  CK(cudaSetDevice(device_));
+  CK(cudaEventRecord(ev0_, stream_));
+  launches_ = 0;
+  return 0;
+}
+
+// Enqueues every diagonal of one group (this rank's chunks only); does not synchronise.
+int DeviceFill::run_group(const Plan& plan, uint32_t gi) {
+  if (gi >= plan.groups.size()) { snprintf(err_, sizeof(err_), "group index out of range"); return -3; }
+  const Group& g = plan.groups[gi];
+  const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
+  if (n_chunks == 0) return 0;
+  const uint32_t blocks = (n_chunks + 3) / 4;
+  for (uint32_t d = 0; d <= g.max_diag; d++) {
+    combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, d, d_rows_,
+                                                       n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
+    launches_++;
+  }
+  CK(cudaGetLastError());
+  return 0;
+}
+
+int DeviceFill::end_fill(float* ms_out, uint64_t* launches_out) {
+  CK(cudaEventRecord(ev1_, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  float ms = 0;
+  CK(cudaEventElapsedTime(&ms, ev0_, ev1_));
+  int flag = 0;
+  CK(cudaMemcpy(&flag, d_err_, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag) {
+    snprintf(err_, sizeof(err_), "combine kernel reported a bad child index");
+    return -2;
+  }
+  if (ms_out) *ms_out = ms;
+  if (launches_out) *launches_out = launches_;
+  return 0;
+}
+
 int DeviceFill::max_peaks(uint32_t out[4]) {
   CK(cudaSetDevice(device_));
   if (!d_peaks_) CK(cudaMalloc(&d_peaks_, 4 * sizeof(uint32_t)));

@@ -16,6 +16,14 @@ class DeviceFill {
   // Runs every (group, diagonal) step. ms_out: device time of the whole schedule, measured
   // with CUDA events on the launching stream.
   int run(const Plan& plan, float* ms_out, uint64_t* launches_out);
+  // The same schedule one group at a time, for callers that exchange rows between groups
+  // (multi-GPU): begin_fill, then run_group for every group in order with the exchange in
+  // between on the same stream, then end_fill.
+  int begin_fill();
+  int run_group(const Plan& plan, uint32_t group);
+  int end_fill(float* ms_out, uint64_t* launches_out);
+  // Run on a caller-owned stream (e.g. the one a collective library orders against).
+  int set_stream(cudaStream_t s);
   // Largest peak (lattice code) per memory over the filled table: the check that a compressed
   // lattice lost nothing (every peak must stay at or below its memory's cap).
   int max_peaks(uint32_t out[4]);
@@ -40,6 +48,7 @@ class DeviceFill {
   uint32_t n_specs_ = 0;
   uint64_t n_rows_ = 0;
   uint64_t h2d_bytes_ = 0;
+  uint64_t launches_ = 0;
   cudaStream_t stream_ = nullptr;
   bool own_stream_ = false;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;

@@ -106,9 +106,13 @@ long Plan::row_of(u32 id, const u64 limits[NMEM]) const {
   return (long)(h.row_base + idx);
 }
 
-Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, const int* caps) {
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, const int* caps,
+                u32 rank, u32 world) {
   if (n_threads < 1) n_threads = 1;
+  if (world < 1 || rank >= world) throw ModelError("bad shard rank / world size");
   Plan plan;
+  plan.rank = rank;
+  plan.world = world;
   u32 top_code[NMEM];
   for (int k = 0; k < NMEM; k++) {
     u64 v = top_limits ? top_limits[k] : AVX2_MAX_MEM[k];
@@ -257,6 +261,21 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     plan.groups.push_back(g);
     i = j;
   }
+  // families: maximal runs with equal dtype and shape inside a group (ids are key-sorted, and
+  // the key starts with kind, dtype, serial flag, rank, shape)
+  for (u32 gi = 0; gi < plan.groups.size(); gi++) {
+    const Group& g = plan.groups[gi];
+    for (u32 i = g.spec_lo; i < g.spec_hi;) {
+      u32 j = i;
+      while (j < g.spec_hi && plan.specs[j].dtype == plan.specs[i].dtype && plan.specs[j].spec_shape == plan.specs[i].spec_shape) j++;
+      Family f;
+      f.spec_lo = i;
+      f.spec_hi = j;
+      f.group = gi;
+      plan.families.push_back(f);
+      i = j;
+    }
+  }
   plan.stats.seconds_layout = now_s() - t1;
 
   plan.stats.n_specs = n;
@@ -320,9 +339,43 @@ void relayout_plan(Plan& plan, const int* caps) {
   }
   plan.stats.seconds_masks = now_s() - t2;
 
-  // ---- 4. rows, chunks, schedule, byte accounting ----
+  // ---- 4. rows, owners, chunks, schedule, byte accounting ----
   double t3 = now_s();
   u64 row = 0, cols_total = 0, bytes = 0;
+  for (u32 i = 0; i < n; i++) {
+    SpecHdr& h = plan.hdrs[i];
+    u64 ncells = 1;
+    for (int k = 0; k < NMEM; k++) ncells *= (u64)__builtin_popcount(h.mask[k]);
+    h.row_base = row;
+    row += ncells;
+  }
+  // Owners: per group, heaviest family first onto the least loaded rank.
+  for (Family& f : plan.families) {
+    f.row_lo = plan.hdrs[f.spec_lo].row_base;
+    f.row_hi = (f.spec_hi < n) ? plan.hdrs[f.spec_hi].row_base : row;
+    f.owner = 0;
+  }
+  if (plan.world > 1) {
+    size_t fi = 0;
+    for (u32 gi = 0; gi < plan.groups.size(); gi++) {
+      std::vector<u32> fam;
+      while (fi < plan.families.size() && plan.families[fi].group == gi) fam.push_back((u32)fi++);
+      std::stable_sort(fam.begin(), fam.end(), [&](u32 a, u32 b) {
+        return plan.families[a].row_hi - plan.families[a].row_lo > plan.families[b].row_hi - plan.families[b].row_lo;
+      });
+      std::vector<u64> load(plan.world, 0);
+      for (u32 f : fam) {
+        u32 best = 0;
+        for (u32 r = 1; r < plan.world; r++) if (load[r] < load[best]) best = r;
+        plan.families[f].owner = best;
+        load[best] += plan.families[f].row_hi - plan.families[f].row_lo;
+      }
+    }
+  }
+  std::vector<u8> mine(n, 1);
+  if (plan.world > 1)
+    for (const Family& f : plan.families)
+      for (u32 i = f.spec_lo; i < f.spec_hi; i++) mine[i] = (f.owner == plan.rank);
   for (Group& g : plan.groups) {
     g.chunk_lo = (u32)plan.chunks.size();
     g.max_diag = 0;
@@ -334,13 +387,9 @@ void relayout_plan(Plan& plan, const int* caps) {
         nk[k] = (u32)__builtin_popcount(h.mask[k]);
         top_sum += 31 - (u32)__builtin_clz(h.mask[k]);
       }
-      g.max_diag = std::max(g.max_diag, top_sum);
       u64 ncells = (u64)nk[0] * nk[1] * nk[2] * nk[3];
       u32 ncols = nk[0] * nk[1] * nk[2];  // the GL index is fixed by the launch's diagonal
-      h.row_base = row;
-      row += ncells;
       cols_total += ncols;
-      for (u32 c0 = 0; c0 < ncols; c0 += 32) plan.chunks.push_back(Chunk{i, c0});
       // algorithmic bytes: one 12-byte row out; per candidate a 16-byte header; per child
       // of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in.
       bytes += ncells * 12;
@@ -353,6 +402,9 @@ void relayout_plan(Plan& plan, const int* caps) {
           bytes += feasible * r.nchild * 16;
         }
       }
+      if (!mine[i]) continue;
+      g.max_diag = std::max(g.max_diag, top_sum);
+      for (u32 c0 = 0; c0 < ncols; c0 += 32) plan.chunks.push_back(Chunk{i, c0});
     }
     g.chunk_hi = (u32)plan.chunks.size();
   }

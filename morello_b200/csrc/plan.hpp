@@ -44,6 +44,15 @@ struct Group {          // Specs with the same phase and log-shape sum: no depen
   u8 shape_sum = 0;
 };
 
+// Specs of one group with the same dtype and shape. Moves never change either, so families of
+// a group do not depend on each other: the unit of work handed to one GPU.
+struct Family {
+  u32 spec_lo = 0, spec_hi = 0;
+  u32 group = 0;
+  u32 owner = 0;        // rank that computes it
+  u64 row_lo = 0, row_hi = 0;
+};
+
 struct Step {           // one kernel launch
   u32 group;
   u32 diag;             // sum of the four limit slots of the cells this launch evaluates
@@ -55,7 +64,11 @@ struct Plan {
   std::vector<CandRec> cands;
   std::vector<Chunk> chunks;
   std::vector<Group> groups;
+  std::vector<Family> families;
   std::vector<Step> steps;
+  // Sharding: this process computes the families whose owner == rank; every rank keeps the
+  // whole table. world == 1: everything is local.
+  u32 rank = 0, world = 1;
   std::vector<u32> goal_ids;
   u32 top_code[NMEM] = {0, 0, 0, 0};   // lattice codes of the top limits the plan covers
   // Lattice compression. In a compressed memory k the table keeps the codes 0..cap_code[k] and
@@ -93,14 +106,14 @@ struct Plan {
   long row_of(u32 id, const u64 limits[NMEM]) const;
 
  private:
-  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, const int*);
+  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, const int*, u32, u32);
   std::vector<std::pair<std::string, u32>> sorted_keys_;  // (key, id), sorted by key
 };
 
 // Top limits are Avx2Target::max_mem() unless overridden. caps: per memory the largest lattice
 // code kept below the top (negative or >= top: no compression), see Plan::cap_code.
 Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr,
-                const int* caps = nullptr);
+                const int* caps = nullptr, u32 rank = 0, u32 world = 1);
 
 // Recomputes everything that depends on the lattice caps (breakpoint masks, row offsets, chunk
 // lists, schedule, byte accounting) and leaves Specs and candidate records alone.

@@ -160,6 +160,47 @@ class SynthesisDatabase:
     def get(self, spec: bytes, limits: Sequence[int] = MAX_MEM) -> Decision:
         return self.get_many([spec], [limits])[0]
 
+    # --- multi-GPU: shard ownership and the per-group fill (see morello_b200/sharded.py) ---
+    def set_shard(self, rank: int, world: int):
+        self._check(self._lib.mrl_set_shard(self._ctx, rank, world))
+
+    def set_stream(self, cuda_stream: int):
+        self._check(self._lib.mrl_set_stream(self._ctx, C.c_void_p(cuda_stream)))
+
+    def num_groups(self) -> int:
+        return int(self._lib.mrl_num_groups(self._ctx))
+
+    def families(self):
+        """[(group, owner rank, first row, end row)] in table order."""
+        out = []
+        g, o, lo, hi = C.c_uint32(), C.c_uint32(), C.c_uint64(), C.c_uint64()
+        for f in range(int(self._lib.mrl_num_families(self._ctx))):
+            if self._lib.mrl_family_info(self._ctx, f, C.byref(g), C.byref(o), C.byref(lo), C.byref(hi)) != 0:
+                raise IndexError(f)
+            out.append((int(g.value), int(o.value), int(lo.value), int(hi.value)))
+        return out
+
+    def device_rows(self):
+        """(device pointer, row count) of the 12-byte row table."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        if self._lib.mrl_device_rows(self._ctx, C.byref(ptr), C.byref(n)) != 0:
+            raise RuntimeError("no table on the device")
+        return int(ptr.value or 0), int(n.value)
+
+    def fill_begin(self):
+        self._check(self._lib.mrl_fill_begin(self._ctx))
+
+    def fill_group(self, group: int):
+        self._check(self._lib.mrl_fill_group(self._ctx, group))
+
+    def fill_end(self):
+        """(status, caps): status 1 = an optimal peak exceeded a lattice cap; refill with `caps`."""
+        caps = (C.c_int32 * 4)()
+        rc = self._lib.mrl_fill_end(self._ctx, caps)
+        if rc < 0:
+            self._check(rc)
+        return rc, [int(c) for c in caps]
+
     # --- export / stats ---
     def stats(self) -> dict:
         s = L.Stats()
