@@ -228,7 +228,7 @@ int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask
     std::vector<Dtype> dts = dtypes_of(dtype_mask);
     if (dts.empty()) return fail(ctx, -1, "empty dtype mask");
     double t0 = now_s();
-    std::vector<LogicalSpec> goals = precompute_goals(size, (Through)through, dts);
+    std::vector<LogicalSpec> goals = precompute_goals(size, (Through)through, dts, ctx->n_threads);
     int rc = set_plan(ctx, goals);
     ctx->stats.plan_seconds = now_s() - t0;
     return rc;

@@ -81,6 +81,11 @@ __device__ __forceinline__ MrlRow lookup(const SpecHdr* __restrict__ hdrs, const
   return r;
 }
 
+// G = lanes per cell: the G lanes of a cell take every G-th candidate each and min-reduce
+// their keys with warp shuffles; a warp covers 32 / G neighbouring columns.
+// F = the memory whose slot is fixed by the diagonal (chosen per group: the memory with the
+// most slots, so that most columns have a cell on the launch's diagonal).
+template <int G, int F>
 __global__ void __launch_bounds__(128)
 combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
                       const Chunk* __restrict__ chunks, uint32_t n_chunks, uint32_t diag,
@@ -92,22 +97,36 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   const Chunk ch = chunks[warp];
   const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch.spec]));
   const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-  const uint32_t col = ch.col_start + lane;
-  if (col >= n0 * n1 * n2) return;
-  const uint32_t i0 = col % n0, i1 = (col / n0) % n1, i2 = col / (n0 * n1);
-  const uint32_t c0 = __fns(m.x, 0, i0 + 1), c1 = __fns(m.y, 0, i1 + 1), c2 = __fns(m.z, 0, i2 + 1);
-  const int c3s = (int)diag - (int)(c0 + c1 + c2);
-  if (c3s < 0 || c3s > 31 || !((m.w >> c3s) & 1u)) return;
-  const uint32_t c3 = (uint32_t)c3s;
-  const uint32_t i3 = __popc(m.w & ((1u << c3) - 1u));
-  const uint32_t cpack = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+  const uint32_t sub = lane % G;
+  const uint32_t col = ch.col_start + lane / G;
+  // A column fixes the slot index in the three memories other than F; the launch's diagonal
+  // then fixes the code in F, and the cell exists if that code is one of the Spec's slots.
+  const uint32_t nn[4] = {n0, n1, n2, (uint32_t)__popc(m.w)};
+  const uint32_t mm[4] = {m.x, m.y, m.z, m.w};
+  uint32_t idx[4], code[4];
+  uint32_t rest = col, others = 0;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    if (k == F) continue;
+    idx[k] = rest % nn[k];
+    rest /= nn[k];
+    code[k] = __fns(mm[k], 0, idx[k] + 1);
+    others += code[k];
+  }
+  if (rest != 0) return;  // column index beyond this Spec's grid
+  const int cfs = (int)diag - (int)others;
+  if (cfs < 0 || cfs > 31 || !((mm[F] >> cfs) & 1u)) return;
+  code[F] = (uint32_t)cfs;
+  idx[F] = __popc(mm[F] & ((1u << cfs) - 1u));
+  const uint32_t i0 = idx[0], i1 = idx[1], i2 = idx[2], i3 = idx[3];
+  const uint32_t cpack = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
 
   const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ch.spec].row_base));
   const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[ch.spec].cand_off));
   const uint32_t cand_off = cl.x, ncand = cl.y;
 
   Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-  for (uint32_t ci = 0; ci < ncand; ci++) {
+  for (uint32_t ci = sub; ci < ncand; ci += G) {
     const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]));
     const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
     const uint32_t imm = a.y;
@@ -171,6 +190,19 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     }
     if (key_less(k, best)) best = k;
   }
+  if (G > 1) {
+    // The G lanes of this cell are all here (a cell is active or not as a whole).
+    const unsigned gmask = (G == 32) ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) {
+      Key other;
+      other.main = __shfl_xor_sync(gmask, best.main, o);
+      other.peaks = __shfl_xor_sync(gmask, best.peaks, o);
+      other.tail = __shfl_xor_sync(gmask, best.tail, o);
+      if (key_less(other, best)) best = other;
+    }
+    if (sub != 0) return;
+  }
   const unsigned long long out = base + ((unsigned long long)(i3 * n2 + i2) * n1 + i1) * n0 + i0;
   uint32_t* q = reinterpret_cast<uint32_t*>(rows + out);
   q[0] = best.main;
@@ -195,6 +227,18 @@ __global__ void max_peaks_kernel(const MrlRow* __restrict__ rows, unsigned long 
   }
 }
 
+// Expands the per-Spec warp counts into the chunk list the combine kernel walks.
+__global__ void expand_chunks_kernel(const uint32_t* __restrict__ warp_prefix, uint32_t n_specs,
+                                     uint32_t cols_per_warp, Chunk* __restrict__ chunks) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_specs) return;
+  const uint32_t lo = warp_prefix[i], hi = warp_prefix[i + 1];
+  for (uint32_t w = lo; w < hi; w++) {
+    chunks[w].spec = i;
+    chunks[w].col_start = (w - lo) * cols_per_warp;
+  }
+}
+
 // Point lookups for get: copies the rows at the given indices into a dense buffer.
 __global__ void gather_rows_kernel(const MrlRow* __restrict__ rows, const unsigned long long* __restrict__ idx,
                                    unsigned long long n, MrlRow* __restrict__ out) {
@@ -210,6 +254,31 @@ __global__ void gather_rows_kernel(const MrlRow* __restrict__ rows, const unsign
 }  // namespace
 
 namespace mrl {
+
+// One (group, diagonal) launch.
+static void launch_combine(int lanes, int free_dim, uint32_t blocks, cudaStream_t stream, const SpecHdr* hdrs,
+                           const CandRec* cands, const Chunk* chunks, uint32_t n_chunks, uint32_t diag, MrlRow* rows,
+                           uint32_t n_specs, uint32_t cap_pack, uint32_t top_pack, int* err) {
+#define MRL_LAUNCH(G, F)                                                                                         \
+  combine_argmin_kernel<G, F><<<blocks, 128, 0, stream>>>(hdrs, cands, chunks, n_chunks, diag, rows, n_specs,    \
+                                                          cap_pack, top_pack, err)
+  if (lanes == 2) {
+    switch (free_dim) {
+      case 0: MRL_LAUNCH(2, 0); break;
+      case 1: MRL_LAUNCH(2, 1); break;
+      case 2: MRL_LAUNCH(2, 2); break;
+      default: MRL_LAUNCH(2, 3); break;
+    }
+  } else {
+    switch (free_dim) {
+      case 0: MRL_LAUNCH(1, 0); break;
+      case 1: MRL_LAUNCH(1, 1); break;
+      case 2: MRL_LAUNCH(1, 2); break;
+      default: MRL_LAUNCH(1, 3); break;
+    }
+  }
+#undef MRL_LAUNCH
+}
 
 #define CK(x)                                                                              \
   do {                                                                                     \
@@ -260,15 +329,23 @@ int DeviceFill::upload(const Plan& plan) {
   if (!d_err_) CK(cudaMalloc(&d_err_, sizeof(int)));
   n_specs_ = (uint32_t)plan.hdrs.size();
   n_rows_ = plan.stats.n_rows;
-  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) + plan.chunks.size() * sizeof(Chunk);
+  const size_t n_warps = plan.warp_prefix.empty() ? 0 : plan.warp_prefix.back();
+  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) +
+               plan.warp_prefix.size() * sizeof(uint32_t);
+  uint32_t* d_prefix = nullptr;
   CK(cudaMalloc(&d_hdrs_, std::max<size_t>(plan.hdrs.size(), 1) * sizeof(SpecHdr)));
   CK(cudaMalloc(&d_cands_, std::max<size_t>(plan.cands.size(), 1) * sizeof(CandRec)));
-  CK(cudaMalloc(&d_chunks_, std::max<size_t>(plan.chunks.size(), 1) * sizeof(Chunk)));
+  CK(cudaMalloc(&d_chunks_, std::max<size_t>(n_warps, 1) * sizeof(Chunk)));
   CK(cudaMalloc(&d_rows_, std::max<uint64_t>(n_rows_, 1) * sizeof(MrlRow)));
+  CK(cudaMalloc(&d_prefix, std::max<size_t>(plan.warp_prefix.size(), 1) * sizeof(uint32_t)));
   CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
   CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), plan.cands.size() * sizeof(CandRec), cudaMemcpyHostToDevice, stream_));
-  CK(cudaMemcpyAsync(d_chunks_, plan.chunks.data(), plan.chunks.size() * sizeof(Chunk), cudaMemcpyHostToDevice, stream_));
+  CK(cudaMemcpyAsync(d_prefix, plan.warp_prefix.data(), plan.warp_prefix.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+  if (n_specs_) expand_chunks_kernel<<<(n_specs_ + 127) / 128, 128, 0, stream_>>>(d_prefix, n_specs_, 32u / plan.lanes_per_cell, d_chunks_);
+  CK(cudaGetLastError());
   CK(cudaMemsetAsync(d_err_, 0, sizeof(int), stream_));
+  CK(cudaStreamSynchronize(stream_));
+  cudaFree(d_prefix);
   CK(cudaStreamSynchronize(stream_));
   return 0;
 }
@@ -283,8 +360,8 @@ int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
     const Group& g = plan.groups[st.group];
     const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
     const uint32_t blocks = (n_chunks + 3) / 4;
-    combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, st.diag,
-                                                       d_rows_, n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
+    launch_combine(plan.lanes_per_cell, g.free_dim, blocks, stream_, d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, st.diag,
+                   d_rows_, n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
     launches++;
   }
   CK(cudaGetLastError());
@@ -325,8 +402,8 @@ int DeviceFill::run_group(const Plan& plan, uint32_t gi) {
   if (n_chunks == 0) return 0;
   const uint32_t blocks = (n_chunks + 3) / 4;
   for (uint32_t d = 0; d <= g.max_diag; d++) {
-    combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, d, d_rows_,
-                                                       n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
+    launch_combine(plan.lanes_per_cell, g.free_dim, blocks, stream_, d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, d, d_rows_,
+                   n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
     launches_++;
   }
   CK(cudaGetLastError());
@@ -451,7 +528,9 @@ int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_
   } while (0)
   const size_t hdr_b = plan.hdrs.size() * sizeof(SpecHdr);
   const size_t cand_b = plan.cands.size() * sizeof(CandRec);
-  const size_t chunk_b = plan.chunks.size() * sizeof(Chunk);
+  const size_t n_warps = plan.warp_prefix.empty() ? 0 : plan.warp_prefix.back();
+  const size_t chunk_b = n_warps * sizeof(Chunk);
+  const size_t prefix_b = plan.warp_prefix.size() * sizeof(uint32_t);
   const size_t row_b = (size_t)plan.stats.n_rows * sizeof(MrlRow);
   const size_t idx_b = n * sizeof(unsigned long long);
   const size_t out_b = n * sizeof(MrlRow);
@@ -459,6 +538,7 @@ int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_
   const size_t o_hdr = off; off = align256(off + hdr_b);
   const size_t o_cand = off; off = align256(off + cand_b);
   const size_t o_chunk = off; off = align256(off + chunk_b);
+  const size_t o_prefix = off; off = align256(off + prefix_b);
   const size_t o_rows = off; off = align256(off + row_b);
   const size_t o_idx = off; off = align256(off + idx_b);
   const size_t o_out = off; off = align256(off + out_b);
@@ -479,6 +559,7 @@ int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_
   SpecHdr* d_hdrs = reinterpret_cast<SpecHdr*>(base + o_hdr);
   CandRec* d_cands = reinterpret_cast<CandRec*>(base + o_cand);
   Chunk* d_chunks = reinterpret_cast<Chunk*>(base + o_chunk);
+  uint32_t* d_prefix = reinterpret_cast<uint32_t*>(base + o_prefix);
   MrlRow* d_rows = reinterpret_cast<MrlRow*>(base + o_rows);
   unsigned long long* d_idx = reinterpret_cast<unsigned long long*>(base + o_idx);
   MrlRow* d_out = reinterpret_cast<MrlRow*>(base + o_out);
@@ -488,15 +569,15 @@ int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_
   CKS(cudaMemsetAsync(d_err, 0, 256, stream));
   if (hdr_b) CKS(cudaMemcpyAsync(d_hdrs, plan.hdrs.data(), hdr_b, cudaMemcpyHostToDevice, stream));
   if (cand_b) CKS(cudaMemcpyAsync(d_cands, plan.cands.data(), cand_b, cudaMemcpyHostToDevice, stream));
-  if (chunk_b) CKS(cudaMemcpyAsync(d_chunks, plan.chunks.data(), chunk_b, cudaMemcpyHostToDevice, stream));
+  if (prefix_b) CKS(cudaMemcpyAsync(d_prefix, plan.warp_prefix.data(), prefix_b, cudaMemcpyHostToDevice, stream));
   if (idx_b) CKS(cudaMemcpyAsync(d_idx, row_idx, idx_b, cudaMemcpyHostToDevice, stream));
   const uint32_t n_specs = (uint32_t)plan.hdrs.size();
+  if (n_specs) expand_chunks_kernel<<<(n_specs + 127) / 128, 128, 0, stream>>>(d_prefix, n_specs, 32u / plan.lanes_per_cell, d_chunks);
   for (const Step& st : plan.steps) {
     const Group& g = plan.groups[st.group];
     const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
-    combine_argmin_kernel<<<(n_chunks + 3) / 4, 128, 0, stream>>>(d_hdrs, d_cands, d_chunks + g.chunk_lo, n_chunks,
-                                                                  st.diag, d_rows, n_specs, plan.cap_pack(),
-                                                                  plan.top_pack(), d_err);
+    launch_combine(plan.lanes_per_cell, g.free_dim, (n_chunks + 3) / 4, stream, d_hdrs, d_cands, d_chunks + g.chunk_lo, n_chunks,
+                   st.diag, d_rows, n_specs, plan.cap_pack(), plan.top_pack(), d_err);
   }
   if (n) gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(d_rows, d_idx, n, d_out);
   CKS(cudaGetLastError());

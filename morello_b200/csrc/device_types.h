@@ -47,8 +47,8 @@ struct CandRec {
   uint32_t pad1;
 };
 
-// A warp-sized slice of one Spec's "columns" (cells with the GL index i3 left free;
-// column = (i2*n1 + i1)*n0 + i0).
+// A warp-sized slice of one Spec's "columns": cells with the slot of one memory (the group's
+// free memory) left open; the column index runs over the other three memories, lowest first.
 struct Chunk {
   uint32_t spec;
   uint32_t col_start;

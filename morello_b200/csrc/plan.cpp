@@ -1,6 +1,8 @@
 // Host-side planner of the database fill. See plan.hpp.
 #include "plan.hpp"
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <atomic>
 #include <chrono>
 #include <mutex>
@@ -71,15 +73,20 @@ u32 code_ceil(int mem, u64 units) {
 
 }  // namespace
 
-std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes) {
-  std::vector<LogicalSpec> goals;
+std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes, int n_threads) {
+  struct Task { Bound b; std::vector<u32> pt; };
+  std::vector<Task> tasks;
   for (auto& phase : goal_phases(size, through, dtypes))
     for (const Bound& b : phase)
       for (auto& stage : diagonals(bound_point(b)))
-        for (auto& pt : stage) {
-          std::vector<LogicalSpec> v = task_point_specs(b, pt);
-          goals.insert(goals.end(), v.begin(), v.end());
-        }
+        for (auto& pt : stage) tasks.push_back(Task{b, pt});
+  std::vector<std::vector<LogicalSpec>> per_task(tasks.size());
+  parallel_for(tasks.size(), n_threads, [&](size_t i, int) { per_task[i] = task_point_specs(tasks[i].b, tasks[i].pt); });
+  std::vector<LogicalSpec> goals;
+  size_t total = 0;
+  for (auto& v : per_task) total += v.size();
+  goals.reserve(total);
+  for (auto& v : per_task) goals.insert(goals.end(), v.begin(), v.end());
   return goals;
 }
 
@@ -113,6 +120,11 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   Plan plan;
   plan.rank = rank;
   plan.world = world;
+  plan.n_threads = n_threads;
+  if (const char* e = getenv("MRL_LANES_PER_CELL")) {
+    int v = atoi(e);
+    if (v == 1 || v == 2) plan.lanes_per_cell = v;
+  }
   u32 top_code[NMEM];
   for (int k = 0; k < NMEM; k++) {
     u64 v = top_limits ? top_limits[k] : AVX2_MAX_MEM[k];
@@ -217,6 +229,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (gkey[a] != gkey[b]) return gkey[a] < gkey[b];
     return temp[a].key < temp[b].key;
   });
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort ids %.2fs\n", now_s() - t1);
   std::vector<u32> new_id(n);
   for (u32 i = 0; i < n; i++) new_id[order[i]] = i;
   for (u32& g : plan.goal_ids) g = new_id[g];
@@ -228,25 +241,33 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
   plan.cands.resize(ncand);
   {
-    u64 off = 0;
-    for (u32 i = 0; i < n; i++) {
+    std::vector<u64> offs(n + 1, 0);
+    for (u32 i = 0; i < n; i++) offs[i + 1] = offs[i] + temp[order[i]].cands.size();
+    plan.sorted_keys_.resize(n);
+    std::vector<u64> kids_t(n_threads, 0);
+    parallel_for(n, n_threads, [&](size_t i, int tid) {
       TempSpec& ts = temp[order[i]];
       plan.specs[i] = ts.ls;
       SpecHdr& h = plan.hdrs[i];
       memset(&h, 0, sizeof(h));
+      u64 off = offs[i];
       h.cand_off = (u32)off;
       h.ncand = (u32)ts.cands.size();
       for (CandRec r : ts.cands) {
         for (int j = 0; j < r.nchild; j++) r.child[j] = new_id[r.child[j]];
-        plan.stats.n_children += r.nchild;
+        kids_t[tid] += r.nchild;
         plan.cands[off++] = r;
       }
-      plan.sorted_keys_.push_back({std::move(ts.key), i});
+      plan.sorted_keys_[i] = {std::move(ts.key), (u32)i};
       std::vector<CandRec>().swap(ts.cands);
-    }
+    });
+    for (u64 k : kids_t) plan.stats.n_children += k;
   }
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   move specs+cands %.2fs\n", now_s() - t1);
   std::vector<TempSpec>().swap(temp);
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   free temp %.2fs\n", now_s() - t1);
   std::sort(plan.sorted_keys_.begin(), plan.sorted_keys_.end());
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort keys %.2fs\n", now_s() - t1);
 
   // groups
   for (u32 i = 0; i < n;) {
@@ -277,6 +298,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     }
   }
   plan.stats.seconds_layout = now_s() - t1;
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/groups/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 
   plan.stats.n_specs = n;
   plan.stats.n_cands = ncand;
@@ -287,9 +309,9 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 void relayout_plan(Plan& plan, const int* caps) {
   const u32 n = (u32)plan.hdrs.size();
   const u32* top_code = plan.top_code;
+  const int n_threads = plan.n_threads;
   for (int k = 0; k < NMEM; k++)
     plan.cap_code[k] = (caps && caps[k] >= 0 && (u32)caps[k] < top_code[k]) ? (u32)caps[k] : top_code[k];
-  plan.chunks.clear();
   plan.steps.clear();
   plan.stats.mask_sweeps = 0;
 
@@ -305,13 +327,18 @@ void relayout_plan(Plan& plan, const int* caps) {
     u32 hi = plan.compressed(k) ? plan.cap_code[k] : top_code[k];
     real_slots[k] = (hi >= 31) ? 0xFFFFFFFFu : ((2u << hi) - 1u);
   }
-  bool changed = true;
-  while (changed) {
+  // Sweeps run on all threads over disjoint Spec ranges; a thread may read a mask another thread
+  // is growing (relaxed atomics). Masks only ever gain bits, so any interleaving reaches the
+  // same least fixpoint; the loop ends after a sweep in which nothing changed.
+  std::atomic<bool> changed{true};
+  while (changed.load()) {
     changed = false;
     plan.stats.mask_sweeps++;
-    for (u32 i = 0; i < n; i++) {
+    parallel_for(n, n_threads, [&](size_t i, int) {
       SpecHdr& h = plan.hdrs[i];
-      u32 m[NMEM] = {h.mask[0], h.mask[1], h.mask[2], h.mask[3]};
+      u32 m[NMEM];
+      for (int k = 0; k < NMEM; k++) m[k] = __atomic_load_n(&h.mask[k], __ATOMIC_RELAXED);
+      const u32 m0[NMEM] = {m[0], m[1], m[2], m[3]};
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
         if (r.kind == MRL_CK_LEAF) {
@@ -321,27 +348,39 @@ void relayout_plan(Plan& plan, const int* caps) {
         for (int j = 0; j < r.nchild; j++) {
           const SpecHdr& ch = plan.hdrs[r.child[j]];
           for (int k = 0; k < NMEM; k++) {
-            if (r.kind != MRL_CK_MOVE || k != r.level) { m[k] |= ch.mask[k]; continue; }
-            u32 cm = ch.mask[k] & real_slots[k];
+            u32 cmask = __atomic_load_n(&ch.mask[k], __ATOMIC_RELAXED);
+            if (r.kind != MRL_CK_MOVE || k != r.level) { m[k] |= cmask; continue; }
+            u32 cm = cmask & real_slots[k];
+            if (mem_counts_registers((Mem)k)) {
+              // registers: every child breakpoint b becomes b + units
+              u32 hi_code = plan.compressed(k) ? plan.cap_code[k] : top_code[k];
+              u64 shifted = (r.units >= 32) ? 0 : ((u64)cm << r.units);
+              u64 keep = (hi_code >= 63) ? ~0ull : ((2ull << hi_code) - 1ull);
+              m[k] |= (u32)(shifted & keep);
+              u64 top_keep = (top_code[k] >= 63) ? ~0ull : ((2ull << top_code[k]) - 1ull);
+              if (plan.compressed(k) && (shifted & ~keep & top_keep)) m[k] |= 1u << (plan.cap_code[k] + 1);
+              continue;
+            }
             while (cm) {
               u32 b = (u32)__builtin_ctz(cm);
               cm &= cm - 1;
-              u32 code = mem_counts_registers((Mem)k) ? b + r.units
-                                                      : bit_length(next_binary_power(bit_length_inverse(b) + r.units));
+              u32 code = bit_length(next_binary_power(bit_length_inverse(b) + r.units));
               if (code <= top_code[k]) m[k] |= 1u << plan.slot_ceil(k, code);
             }
           }
         }
       }
+      bool ch_any = false;
       for (int k = 0; k < NMEM; k++)
-        if (m[k] != h.mask[k]) { h.mask[k] = m[k]; changed = true; }
-    }
+        if (m[k] != m0[k]) { __atomic_fetch_or(&h.mask[k], m[k], __ATOMIC_RELAXED); ch_any = true; }
+      if (ch_any) changed = true;
+    });
   }
   plan.stats.seconds_masks = now_s() - t2;
 
-  // ---- 4. rows, owners, chunks, schedule, byte accounting ----
+  // ---- 4. rows, owners, warps, schedule, byte accounting ----
   double t3 = now_s();
-  u64 row = 0, cols_total = 0, bytes = 0;
+  u64 row = 0;
   for (u32 i = 0; i < n; i++) {
     SpecHdr& h = plan.hdrs[i];
     u64 ncells = 1;
@@ -376,37 +415,67 @@ void relayout_plan(Plan& plan, const int* caps) {
   if (plan.world > 1)
     for (const Family& f : plan.families)
       for (u32 i = f.spec_lo; i < f.spec_hi; i++) mine[i] = (f.owner == plan.rank);
+
+  // Per Spec: warps, top diagonal and algorithmic bytes (one 12-byte row out; per candidate a
+  // 16-byte header; per child of a candidate that fits the cell's limits a 4-byte index and a
+  // 12-byte row in). Independent per Spec, so computed on all threads.
+  // Per group, the memory with the most slots in total becomes the one the diagonal fixes:
+  // a column then has a cell on as many of the group's diagonals as possible.
+  std::vector<u8> free_of(n, 3);
   for (Group& g : plan.groups) {
-    g.chunk_lo = (u32)plan.chunks.size();
-    g.max_diag = 0;
-    for (u32 i = g.spec_lo; i < g.spec_hi; i++) {
-      SpecHdr& h = plan.hdrs[i];
-      u32 nk[NMEM];
-      u32 top_sum = 0;
-      for (int k = 0; k < NMEM; k++) {
-        nk[k] = (u32)__builtin_popcount(h.mask[k]);
-        top_sum += 31 - (u32)__builtin_clz(h.mask[k]);
-      }
-      u64 ncells = (u64)nk[0] * nk[1] * nk[2] * nk[3];
-      u32 ncols = nk[0] * nk[1] * nk[2];  // the GL index is fixed by the launch's diagonal
-      cols_total += ncols;
-      // algorithmic bytes: one 12-byte row out; per candidate a 16-byte header; per child
-      // of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in.
-      bytes += ncells * 12;
-      for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
-        const CandRec& r = plan.cands[c];
-        bytes += ncells * 16;
-        if (r.nchild) {
-          u32 feasible_k = (u32)__builtin_popcount(h.mask[r.level] >> plan.slot_ceil(r.level, r.thr_code));
-          u64 feasible = ncells / nk[r.level] * feasible_k;
-          bytes += feasible * r.nchild * 16;
-        }
-      }
-      if (!mine[i]) continue;
-      g.max_diag = std::max(g.max_diag, top_sum);
-      for (u32 c0 = 0; c0 < ncols; c0 += 32) plan.chunks.push_back(Chunk{i, c0});
+    u64 tot[NMEM] = {0, 0, 0, 0};
+    for (u32 i = g.spec_lo; i < g.spec_hi; i++)
+      for (int k = 0; k < NMEM; k++) tot[k] += (u64)__builtin_popcount(plan.hdrs[i].mask[k]);
+    int best = NMEM - 1;
+    for (int k = NMEM - 2; k >= 0; k--) if (tot[k] > tot[best]) best = k;
+    if (const char* e = getenv("MRL_FREE_DIM")) { int v = atoi(e); if (v >= 0 && v < NMEM) best = v; }
+    g.free_dim = (u8)best;
+    for (u32 i = g.spec_lo; i < g.spec_hi; i++) free_of[i] = (u8)best;
+  }
+  std::vector<u32> warps(n), top_sums(n);
+  std::vector<u64> bytes_t(std::max(n_threads, 1), 0), cols_t(std::max(n_threads, 1), 0);
+  parallel_for(n, n_threads, [&](size_t i, int tid) {
+    const SpecHdr& h = plan.hdrs[i];
+    u32 nk[NMEM];
+    u32 top_sum = 0;
+    for (int k = 0; k < NMEM; k++) {
+      nk[k] = (u32)__builtin_popcount(h.mask[k]);
+      top_sum += 31 - (u32)__builtin_clz(h.mask[k]);
     }
-    g.chunk_hi = (u32)plan.chunks.size();
+    u64 ncells = (u64)nk[0] * nk[1] * nk[2] * nk[3];
+    u32 ncols = (u32)(ncells / nk[free_of[i]]);  // the slot in the group's free memory is fixed by the diagonal
+    u64 bytes = ncells * 12;
+    for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
+      const CandRec& r = plan.cands[c];
+      bytes += ncells * 16;
+      if (r.nchild) {
+        u32 feasible_k = (u32)__builtin_popcount(h.mask[r.level] >> plan.slot_ceil(r.level, r.thr_code));
+        bytes += ncells / nk[r.level] * feasible_k * r.nchild * 16;
+      }
+    }
+    bytes_t[tid] += bytes;
+    cols_t[tid] += ncols;
+    const u32 cols_per_warp = 32u / (u32)plan.lanes_per_cell;
+    warps[i] = mine[i] ? (ncols + cols_per_warp - 1) / cols_per_warp : 0;
+    top_sums[i] = top_sum;
+  });
+  u64 bytes = 0, cols_total = 0;
+  for (u64 b : bytes_t) bytes += b;
+  for (u64 c : cols_t) cols_total += c;
+  plan.warp_prefix.assign(n + 1, 0);
+  u64 wsum = 0;
+  for (u32 i = 0; i < n; i++) {
+    plan.warp_prefix[i] = (u32)wsum;
+    wsum += warps[i];
+    if (wsum > 0xFFFFFFFFull) throw ModelError("too many warps in one plan");
+  }
+  plan.warp_prefix[n] = (u32)wsum;
+  for (Group& g : plan.groups) {
+    g.chunk_lo = plan.warp_prefix[g.spec_lo];
+    g.chunk_hi = plan.warp_prefix[g.spec_hi];
+    g.max_diag = 0;
+    for (u32 i = g.spec_lo; i < g.spec_hi; i++)
+      if (mine[i]) g.max_diag = std::max(g.max_diag, top_sums[i]);
   }
   u32 max_diag = 0;
   for (const Group& g : plan.groups) max_diag = std::max(max_diag, g.max_diag);
@@ -425,6 +494,7 @@ void relayout_plan(Plan& plan, const int* caps) {
   plan.stats.max_diag = max_diag;
   plan.stats.algorithmic_bytes = bytes;
   plan.stats.seconds_layout += now_s() - t3;
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] masks %.2fs (%llu sweeps), rows/owners/warps %.2fs\n", plan.stats.seconds_masks, (unsigned long long)plan.stats.mask_sweeps, now_s() - t3);
 }
 
 }  // namespace mrl

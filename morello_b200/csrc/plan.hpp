@@ -40,6 +40,7 @@ struct Group {          // Specs with the same phase and log-shape sum: no depen
   u32 spec_lo = 0, spec_hi = 0;  // id range
   u32 chunk_lo = 0, chunk_hi = 0;
   u32 max_diag = 0;     // largest limits diagonal any member has a cell on
+  u8 free_dim = 3;      // memory whose slot the diagonal fixes; a thread owns a column of the other three
   u8 phase = 0;
   u8 shape_sum = 0;
 };
@@ -62,7 +63,13 @@ struct Plan {
   std::vector<LogicalSpec> specs;        // by id
   std::vector<SpecHdr> hdrs;             // by id
   std::vector<CandRec> cands;
-  std::vector<Chunk> chunks;
+  // warp_prefix[i] = number of warp-sized column chunks of the Specs with id < i that this rank
+  // computes (n_specs + 1 entries). The chunk list itself is expanded on the device.
+  std::vector<u32> warp_prefix;
+  int n_threads = 1;
+  // Lanes of a warp that share one cell (each takes every lanes_per_cell-th candidate); a warp
+  // covers 32 / lanes_per_cell neighbouring columns. 1 or 2.
+  int lanes_per_cell = 1;
   std::vector<Group> groups;
   std::vector<Family> families;
   std::vector<Step> steps;
@@ -120,7 +127,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 void relayout_plan(Plan& plan, const int* caps);
 
 // Goal sets.
-std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes);
+std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes,
+                                          int n_threads = 1);
 
 // Lattice code <-> value helpers shared by planner and lookups.
 inline u32 limit_code(int mem, u64 value) { return mem_counts_registers((Mem)mem) ? (u32)value : bit_length(value); }

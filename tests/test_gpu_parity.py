@@ -105,3 +105,22 @@ def test_edge_cases(m):
                 assert d.main_cost <= prev
             prev = d.main_cost
     db.close()
+
+
+def test_precompute_size4_matches_a_bounded_oracle_run(m, oracle):
+    """Size 4 (642 k logical Specs with the closure, billions of rows): the oracle cannot finish
+    it in test time, so it runs its faithful stage order under a time budget and every put it
+    made so far is checked against the full GPU tables."""
+    import os
+    o = oracle.new()
+    rep = o.precompute(4, threads=os.cpu_count() or 1, budget_s=25.0)
+    assert o.dominance_conflicts() == 0
+    keys, off, rect, dec = o.dump()
+    assert len(dec) > 10000
+    db = m.SynthesisDatabase()
+    st = db.precompute(4)
+    assert st["n_goal_specs"] == 410954
+    bad = parity_util.compare_puts(db, keys, off, rect, dec)
+    assert not bad, "\n".join(bad)
+    db.close()
+    o.close()
