@@ -5,16 +5,21 @@
   python bench.py --impl reference --gpus N --steps K ...  # the reference algorithm on host cores
 
 One step = one complete fill of the workload's database. The workload is the precompute of
-every canonical Move / Zero / Matmul Spec up to size 2 over {u32, f32} on the Avx2 target with
-default memory limits (`precompute --target avx2 --through matmul 2`): the dependency closure of
-`morello matmul 2` and its f32 twin. All inputs are synthetic by construction: the Spec space is
+every canonical Move / Zero / Matmul Spec with dimensions in {1, 2, 4} over {u32, f32} on the
+Avx2 target with default memory limits (`precompute --target avx2 --through matmul 4`): the part
+of BASELINE config 2 (dimensions up to 8) whose tables fit one GPU today - 410 954 goal logical
+Specs, 641 818 with their dependency closure. `--size 2` runs the closure of `morello matmul 2`
+(BASELINE config 1) instead. All inputs are synthetic by construction: the Spec space is
 generated from the size alone.
 
 Unit of work ("Spec resolved"): one (logical Spec, memory limits) entry of the database made
 answerable. Both arms cover the same entries - every logical Spec of the workload over the
 whole 17 x 17 x 12 x 27 limits lattice of the target - so the figure is the same numerator
 divided by each arm's time. The CUDA arm also reports how many rows it actually computed and
-the reference arm how many solves (`put`s) it needed.
+the reference arm how many solves (`put`s) it needed. At size 4 the CPU arm cannot finish in
+bench time: it runs the reference's stage order under a time budget and counts the goal Specs
+it completed (the cheap early stages - Moves, small shapes - come first, so this sample
+flatters the CPU).
 """
 import argparse
 import json
@@ -28,8 +33,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 LATTICE_POINTS = 17 * 17 * 12 * 27  # RF 0..16, VRF 0..16, L1 and GL as bit lengths (avx2.rs:59-65)
-WORKLOAD = "precompute --target avx2 --through matmul 2 (Move+Zero+Matmul, u32+f32, serial)"
-SIZE = 2
+SIZE = 4
+GOAL_SPECS = {1: 180, 2: 10454, 4: 410954}  # canonical goal Specs of the precompute of each size
+
+
+def workload_name():
+    return "precompute --target avx2 --through matmul %d (Move+Zero+Matmul, u32+f32, serial)" % SIZE
 
 
 def measured_peaks():
@@ -87,7 +96,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def run_oracle(threads, steps, warmup):
+def run_oracle(threads, steps, warmup, budget_s=0.0):
     """The reference's algorithm (top-down memoised search with a range-filling memo table and
     the precompute driver) restated in C++ under oracle/, on the host cores."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -96,12 +105,19 @@ def run_oracle(threads, steps, warmup):
     times, puts, lspecs = [], 0, 0
     for i in range(warmup + steps):
         o = fac.new()
-        r = o.precompute(SIZE, through=2, dtype_mask=3, threads=threads)
+        r = o.precompute(SIZE, through=2, dtype_mask=3, threads=threads, budget_s=budget_s)
         o.close()
         if i >= warmup:
             times.append(r["seconds"])
-        puts, lspecs = r["puts"], r["logical_specs"]
-    return times, puts, lspecs
+        puts, lspecs, finished = r["puts"], r["logical_specs"], r["finished"]
+    return times, puts, lspecs, finished
+
+
+def cpu_sample_text(finished, budget_s):
+    if finished:
+        return "the whole workload (C++ restatement of the reference algorithm, all host cores)"
+    return ("the first %.0f s of the workload in the reference's stage order (Move phase first); goal Specs "
+            "completed in that time; C++ restatement of the reference algorithm, all host cores" % budget_s)
 
 
 def reference_arm(args):
@@ -109,19 +125,20 @@ def reference_arm(args):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    times, puts, lspecs = run_oracle(cores, args.steps, args.warmup)
+    budget = 0.0 if SIZE <= 2 else args.cpu_budget
+    times, puts, lspecs, finished = run_oracle(cores, args.steps, 0 if budget else args.warmup, budget)
     per_step = sum(times) / len(times)
     value = lspecs * LATTICE_POINTS / per_step
     line = {
         "impl": "reference", "metric": "specs_resolved_per_s", "value": value, "unit": "specs/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
+        "config": {"workload": workload_name(), "logical_specs": GOAL_SPECS[SIZE],
+                   "lattice_points_per_spec": LATTICE_POINTS, "goal_specs_completed_in_sample": lspecs,
                    "reference_puts": puts},
-        "wall_s_full_db": per_step,
+        "wall_s_full_db": per_step if finished else None,
         "cpu_baseline": {"value": value, "unit": "specs/s", "cores": cores, "kind": "port",
-                         "sample": "the whole workload, once per step (C++ restatement of the reference algorithm; "
-                                   "the Rust reference cannot be built here)",
+                         "sample": cpu_sample_text(finished, budget) + " (the Rust reference cannot be built here)",
                          "puts_per_s": puts / per_step},
         "e2e": {"value": value, "unit": "specs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -212,7 +229,7 @@ def cuda_arm(args):
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
 
-    lspecs = st["n_specs"]
+    lspecs = st["n_goal_specs"]      # the Specs the workload asks for (the closure adds more rows, not more units)
     units = lspecs * LATTICE_POINTS  # one database, however many GPUs fill it
     hbm_gbs, peak_kind = measured_peaks()
     achieved = st["algorithmic_bytes"] / (ms_per_step * 1e-3) / 1e9
@@ -221,10 +238,10 @@ def cuda_arm(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "u32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
-                   "rows_computed_per_step": st["n_rows"], "candidate_records": st["n_candidates"],
+        "config": {"workload": workload_name(), "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
+                   "logical_specs_with_closure": st["n_specs"], "rows_computed_per_step": st["n_rows"], "candidate_records": st["n_candidates"],
                    "lattice_caps": st["lattice_caps"],
-                   "l2": ("row table %.0f MB; L2 flushed between fills" % (st["n_rows"] * 12 / 1e6)),
+                   "l2": ("row table %.1f GB, larger than L2; L2 also flushed between fills" % (st["n_rows"] * 12 / 1e9)),
                    "multi_gpu": ("families of each group sharded over %d ranks, NCCL broadcast between groups" % world)
                    if world > 1 else "single"},
         "wall_s_full_db": e2e_step,
@@ -242,11 +259,12 @@ def cuda_arm(args):
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
-            times, puts, _ = run_oracle(cores, 1, 0)
+            budget = 0.0 if SIZE <= 2 else args.cpu_budget
+            times, puts, done, finished = run_oracle(cores, 1, 0, budget)
             line["cpu_baseline"] = {
-                "value": lspecs * LATTICE_POINTS / times[0], "unit": "specs/s", "cores": cores, "kind": "port",
-                "sample": "the whole workload once (C++ restatement of the reference algorithm, all host cores)",
-                "wall_s": times[0], "reference_puts": puts, "puts_per_s": puts / times[0]}
+                "value": done * LATTICE_POINTS / times[0], "unit": "specs/s", "cores": cores, "kind": "port",
+                "sample": cpu_sample_text(finished, budget), "wall_s": times[0], "goal_specs_completed": done,
+                "reference_puts": puts, "puts_per_s": puts / times[0]}
         traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(traffic_path):
             with open(traffic_path) as f:
@@ -264,7 +282,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--size", type=int, default=4, choices=[1, 2, 4], help="largest Spec dimension of the workload")
+    ap.add_argument("--cpu-budget", type=float, default=20.0, help="seconds of CPU work per reference sample")
     args = ap.parse_args()
+    global SIZE
+    SIZE = args.size
     if args.impl == "reference":
         reference_arm(args)
     else:

@@ -1,6 +1,7 @@
 // C ABI of the B200 synthesis-database fill (declared in include/morello_b200.h).
 #include "../../include/morello_b200.h"
 #include "fill.hpp"
+#include <algorithm>
 #include <chrono>
 #include <thread>
 
@@ -17,6 +18,7 @@ struct mrl_ctx {
   // Lattice caps per memory (lattice codes; negative = keep every code). Start low: a fill at
   // low caps is cheap, and fill_verified raises them until no optimal peak exceeds its cap.
   int caps[4] = {4, 2, 4, 0};
+  bool caps_chosen = false;  // false: pick a starting point from the goals' largest dimension
   bool auto_raise = true;
   uint32_t rank = 0, world = 1;
 };
@@ -106,6 +108,7 @@ int fill_verified(mrl_ctx* ctx) {
       ctx->filled = true;
       return 0;
     }
+    ctx->caps_chosen = true;  // raised caps are kept for later plans on this context
     if (!ctx->auto_raise) return fail(ctx, -5, "an optimal peak exceeds the lattice caps; raise them (mrl_set_lattice_caps)");
     double t0 = now_s();
     relayout_plan(ctx->plan, ctx->caps);
@@ -115,8 +118,21 @@ int fill_verified(mrl_ctx* ctx) {
   return fail(ctx, -5, "lattice caps did not converge");
 }
 
+// Starting caps by the largest Spec dimension among the goals: the values earlier fills of that
+// size ended with. Only a starting point - every fill is checked and the caps raised if needed.
+void choose_initial_caps(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
+  if (ctx->caps_chosen) return;
+  u32 maxdim = 1;
+  for (const LogicalSpec& g : goals)
+    for (int i = 0; i < g.spec_shape.n; i++) maxdim = std::max(maxdim, g.spec_shape[i]);
+  static const int table[4][4] = {{0, 0, 3, 0}, {8, 2, 5, 0}, {-1, 12, 7, 4}, {-1, -1, 9, 6}};
+  int row = maxdim <= 1 ? 0 : (maxdim <= 2 ? 1 : (maxdim <= 4 ? 2 : 3));
+  for (int k = 0; k < 4; k++) ctx->caps[k] = table[row][k];
+}
+
 int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
   double t0 = now_s();
+  choose_initial_caps(ctx, goals);
   ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->caps, ctx->rank, ctx->world);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
@@ -284,6 +300,7 @@ int mrl_fill(mrl_ctx* ctx) {
 int mrl_set_lattice_caps(mrl_ctx* ctx, const int32_t caps[4], int auto_raise) {
   if (!ctx || !caps) return -1;
   for (int k = 0; k < 4; k++) ctx->caps[k] = caps[k];
+  ctx->caps_chosen = true;
   ctx->auto_raise = auto_raise != 0;
   if (ctx->planned) {
     relayout_plan(ctx->plan, ctx->caps);

@@ -189,13 +189,14 @@ PrecomputeReport precompute(Database& db, u32 size, Through through, const std::
             while (!worklist.empty()) {
               std::set<std::pair<std::string, Limits>> next;  // dedup like the HashSet at :346,361
               for (auto& w : worklist) {
+                if (time_budget_s > 0 && elapsed() > time_budget_s) { out_of_time = true; break; }
                 Decision d = search.solve(w.first, w.second);
                 if (d.found)
                   for (const Limits& l : next_limits(w.second, d.cost.peaks)) next.insert({w.first.key(), l});
               }
               worklist.clear();
               for (auto& n : next) worklist.push_back({LogicalSpec::from_key(n.first), n.second});
-              if (time_budget_s > 0 && elapsed() > time_budget_s) { out_of_time = true; break; }
+              if (out_of_time.load() || (time_budget_s > 0 && elapsed() > time_budget_s)) { out_of_time = true; break; }
             }
           }
           solves += search.stats.solves;
