@@ -241,7 +241,7 @@ def cuda_arm(args):
         "config": {"workload": workload_name(), "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
                    "logical_specs_with_closure": st["n_specs"], "rows_computed_per_step": st["n_rows"], "candidate_records": st["n_candidates"],
                    "lattice_caps": st["lattice_caps"],
-                   "l2": ("row table %.1f GB, larger than L2; L2 also flushed between fills" % (st["n_rows"] * 12 / 1e9)),
+                   "l2": ("row table %.1f GB, larger than L2; L2 also flushed between fills" % (st["n_rows"] * 16 / 1e9)),
                    "multi_gpu": ("families of each group sharded over %d ranks, NCCL broadcast between groups" % world)
                    if world > 1 else "single"},
         "wall_s_full_db": e2e_step,

@@ -136,7 +136,8 @@ uint64_t mrl_num_groups(const mrl_ctx* ctx);
 uint64_t mrl_num_families(const mrl_ctx* ctx);
 int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* group, uint32_t* owner, uint64_t* row_lo,
                     uint64_t* row_hi);
-int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows); /* 12-byte rows */
+int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows);
+uint32_t mrl_row_bytes(void); /* bytes per row slot in the device table */
 int mrl_fill_begin(mrl_ctx* ctx);
 int mrl_fill_group(mrl_ctx* ctx, uint64_t group);
 int mrl_fill_end(mrl_ctx* ctx, int32_t raised_caps[4]);

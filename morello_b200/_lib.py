@@ -43,6 +43,7 @@ EXPORTS = {
     "mrl_family_info": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
                                   C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "mrl_device_rows": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "mrl_row_bytes": (C.c_uint32, []),
     "mrl_fill_begin": (C.c_int, [C.c_void_p]),
     "mrl_fill_group": (C.c_int, [C.c_void_p, C.c_uint64]),
     "mrl_fill_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
@@ -63,10 +64,11 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
+    path = os.environ.get("MRL_LIB_PATH", LIB_PATH)  # override: an alternative build of the same library
+    if not os.path.exists(path):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build the CUDA extension first (python -c 'import __graft_entry__ as g; g.build()')")
-    lib = C.CDLL(LIB_PATH)
+            f"{path} is missing: build the CUDA extension first (python -c 'import __graft_entry__ as g; g.build()')")
+    lib = C.CDLL(path)
     for name, (restype, argtypes) in EXPORTS.items():
         fn = getattr(lib, name)
         fn.restype = restype

@@ -415,6 +415,8 @@ int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* group, uint32
   return 0;
 }
 
+uint32_t mrl_row_bytes(void) { return (uint32_t)sizeof(MrlRow); }
+
 int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows) {
   if (!ctx || !ctx->uploaded) return -1;
   if (ptr) *ptr = ctx->dev.device_rows();

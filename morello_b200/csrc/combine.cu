@@ -23,6 +23,10 @@
 #include <stdio.h>
 #include <mutex>
 
+#ifndef MRL_MIN_BLOCKS
+#define MRL_MIN_BLOCKS 12
+#endif
+
 namespace {
 
 __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
@@ -58,27 +62,21 @@ __device__ __forceinline__ bool key_less(const Key& a, const Key& b) {
   return a.tail < b.tail;
 }
 
-// Row of (child Spec, limits cpack): the cell whose breakpoints are the largest ones not above
-// the limits. 32 bytes of header, then 12 bytes of row.
-__device__ __forceinline__ MrlRow lookup(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
-                                         uint32_t child, uint32_t cpack) {
+// Row of a child Spec at given limits: the cell whose breakpoints are the largest ones not
+// above the limits. bm[k] = mask of the slots <= the limit's slot in memory k. One 32-byte
+// header (two loads, warp-uniform) and one 16-byte row.
+__device__ __forceinline__ uint4 lookup(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
+                                        uint32_t child, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
   const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[child]));
   const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[child].row_base));
-  const uint32_t c0 = cpack & 0xFF, c1 = (cpack >> 8) & 0xFF, c2 = (cpack >> 16) & 0xFF, c3 = cpack >> 24;
-  const uint32_t i0 = __popc(m.x & ((2u << c0) - 1u)) - 1;
-  const uint32_t i1 = __popc(m.y & ((2u << c1) - 1u)) - 1;
-  const uint32_t i2 = __popc(m.z & ((2u << c2) - 1u)) - 1;
-  const uint32_t i3 = __popc(m.w & ((2u << c3) - 1u)) - 1;
-  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-  const unsigned long long idx = base + ((unsigned long long)(i3 * n2 + i2) * n1 + i1) * n0 + i0;
-  const uint32_t* p = reinterpret_cast<const uint32_t*>(rows + idx);
-  MrlRow r;
-  // Plain loads: rows of earlier launches are final, but this buffer is written by this
-  // kernel too, so the read-only path is not used for them.
-  r.main = p[0];
-  r.peaks = p[1];
-  r.tail = p[2];
-  return r;
+  const uint32_t i0 = __popc(m.x & b0) - 1;
+  const uint32_t i1 = __popc(m.y & b1) - 1;
+  const uint32_t i2 = __popc(m.z & b2) - 1;
+  const uint32_t i3 = __popc(m.w & b3) - 1;
+  const uint32_t off = ((i3 * __popc(m.z) + i2) * __popc(m.y) + i1) * __popc(m.x) + i0;  // cells per Spec < 2^32
+  // Rows read here were written by earlier launches (lower diagonal or earlier group), never by
+  // this one, so the read-only path is safe.
+  return __ldg(reinterpret_cast<const uint4*>(rows + base + off));
 }
 
 // G = lanes per cell: the G lanes of a cell take every G-th candidate each and min-reduce
@@ -86,7 +84,7 @@ __device__ __forceinline__ MrlRow lookup(const SpecHdr* __restrict__ hdrs, const
 // F = the memory whose slot is fixed by the diagonal (chosen per group: the memory with the
 // most slots, so that most columns have a cell on the launch's diagonal).
 template <int G, int F>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
 combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
                       const Chunk* __restrict__ chunks, uint32_t n_chunks, uint32_t diag,
                       MrlRow* __restrict__ rows, uint32_t n_specs, uint32_t cap_pack, uint32_t top_pack,
@@ -96,13 +94,12 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   if (warp >= n_chunks) return;
   const Chunk ch = chunks[warp];
   const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch.spec]));
-  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
   const uint32_t sub = lane % G;
   const uint32_t col = ch.col_start + lane / G;
   // A column fixes the slot index in the three memories other than F; the launch's diagonal
   // then fixes the code in F, and the cell exists if that code is one of the Spec's slots.
-  const uint32_t nn[4] = {n0, n1, n2, (uint32_t)__popc(m.w)};
   const uint32_t mm[4] = {m.x, m.y, m.z, m.w};
+  const uint32_t nn[4] = {(uint32_t)__popc(m.x), (uint32_t)__popc(m.y), (uint32_t)__popc(m.z), (uint32_t)__popc(m.w)};
   uint32_t idx[4], code[4];
   uint32_t rest = col, others = 0;
 #pragma unroll
@@ -118,8 +115,10 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   if (cfs < 0 || cfs > 31 || !((mm[F] >> cfs) & 1u)) return;
   code[F] = (uint32_t)cfs;
   idx[F] = __popc(mm[F] & ((1u << cfs) - 1u));
-  const uint32_t i0 = idx[0], i1 = idx[1], i2 = idx[2], i3 = idx[3];
   const uint32_t cpack = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
+  // "slots at or below this cell's limit", per memory: what a child lookup at the same limits needs
+  const uint32_t bm0 = (2u << code[0]) - 1u, bm1 = (2u << code[1]) - 1u, bm2 = (2u << code[2]) - 1u,
+                 bm3 = (2u << code[3]) - 1u;
 
   const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ch.spec].row_base));
   const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[ch.spec].cand_off));
@@ -145,48 +144,63 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
       k.tail = (1u << 16) | action;
     } else {
       const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]) + 1);
-      const uint32_t kid[3] = {b.x, b.y, b.z};
-      uint32_t ccpack = cpack;
+      uint32_t c0 = bm0, c1 = bm1, c2 = bm2, c3 = bm3;
+      const uint32_t sh = peak_shift(level);
       if (kind == MRL_CK_MOVE) {
         if (lv < thr) continue;
+        // Branch and bound: a Move costs at least its own base cost. Candidates are stored
+        // cheapest-first (kernels, loops, then Moves by base cost), so most Moves end here.
+        if (imm > best.main) continue;
         uint32_t ccode;
         if (level < 2) ccode = lv - units;                      // registers: exact
         else ccode = 32 - __clz(cache_value(lv) - units);       // caches: snap down to 2^k
         // The child's limit is below the top; codes above the cap read the cap slot (nothing
         // changes between cap and top while no optimal peak exceeds the cap).
-        ccpack = with_code(cpack, level, min(ccode, cap));
+        const uint32_t cb = (2u << min(ccode, cap)) - 1u;
+        if (level == 0) c0 = cb; else if (level == 1) c1 = cb; else if (level == 2) c2 = cb; else c3 = cb;
       }
-      uint32_t main = (kind == MRL_CK_MOVE) ? imm : 0u;
-      uint32_t peaks = 0, depth = 0;
-      bool ok = true;
-      for (uint32_t j = 0; j < nchild; j++) {
-        if (kid[j] >= n_specs) { atomicExch(error_flag, 1); ok = false; break; }
-        const MrlRow r = lookup(hdrs, rows, kid[j], ccpack);
-        if (r.tail == MRL_UNSAT) { ok = false; break; }
-        uint32_t cp = r.peaks;
+      if (b.x >= n_specs || (nchild > 1 && b.y >= n_specs) || (nchild > 2 && b.z >= n_specs)) {
+        atomicExch(error_flag, 1);
+        continue;
+      }
+      // Children one at a time: a child without an implementation, or a partial sum that already
+      // exceeds the best main cost, ends the candidate before the remaining rows are fetched.
+      const uint4 r0 = lookup(hdrs, rows, b.x, c0, c1, c2, c3);
+      if (r0.z == MRL_UNSAT) continue;
+      uint4 r1 = r0, r2 = r0;
+      if (nchild > 1) {
+        if (kind == MRL_CK_MOVE && sat_add(imm, r0.x) > best.main) continue;
+        r1 = lookup(hdrs, rows, b.y, c0, c1, c2, c3);
+        if (r1.z == MRL_UNSAT) continue;
+        if (nchild > 2) {
+          r2 = lookup(hdrs, rows, b.z, c0, c1, c2, c3);
+          if (r2.z == MRL_UNSAT) continue;
+        }
+      }
+      uint32_t main, peaks, depth;
+      if (kind == MRL_CK_LOOP) {
+        main = sat_mul(r0.x, imm);
+        peaks = r0.y;
+        depth = 1u;  // a single-body tile loop has depth 1 whatever its body's depth
+      } else {
+        main = (kind == MRL_CK_MOVE) ? sat_add(imm, r0.x) : r0.x;
+        if (nchild > 1) main = sat_add(main, r1.x);
+        if (nchild > 2) main = sat_add(main, r2.x);
+        peaks = __vmaxu4(__vmaxu4(r0.y, r1.y), r2.y);
         if (kind == MRL_CK_MOVE) {
-          // own allocation sits on top of the child's peak in `level`
-          const uint32_t sh = peak_shift(level);
-          const uint32_t child_code = (cp >> sh) & 0xFFu;
+          // own allocation sits on top of the deepest child's peak in `level`; rounding to the
+          // lattice is monotone, so max-then-round equals the reference's round-per-child
+          const uint32_t child_code = (peaks >> sh) & 0xFFu;
           uint32_t ncode;
           if (level < 2) ncode = units + child_code;
           else ncode = cache_code_ceil(units + cache_value(child_code));
-          cp = (cp & ~(0xFFu << sh)) | (ncode << sh);
-          main = sat_add(main, r.main);
-        } else if (kind == MRL_CK_LOOP) {
-          main = sat_mul(r.main, imm);
-        } else {
-          main = (j == 0) ? r.main : sat_add(main, r.main);
+          peaks = (peaks & ~(0xFFu << sh)) | (ncode << sh);
         }
-        peaks = __vmaxu4(peaks, cp);
-        depth = max(depth, r.tail >> 16);
+        depth = min(max(max(r0.z >> 16, r1.z >> 16), r2.z >> 16) + 1u, 255u);
       }
-      if (!ok) continue;
-      // depth: a single-body tile loop is 1; Move and Block are 1 + deepest child (Block saturates)
-      uint32_t d = (kind == MRL_CK_LOOP) ? 1u : min(depth + 1u, 255u);
       k.main = main;
       k.peaks = peaks;
-      k.tail = (d << 16) | action;
+      k.tail = (depth << 16) | action;
     }
     if (key_less(k, best)) best = k;
   }
@@ -203,11 +217,8 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     }
     if (sub != 0) return;
   }
-  const unsigned long long out = base + ((unsigned long long)(i3 * n2 + i2) * n1 + i1) * n0 + i0;
-  uint32_t* q = reinterpret_cast<uint32_t*>(rows + out);
-  q[0] = best.main;
-  q[1] = best.peaks;
-  q[2] = best.tail;
+  const uint32_t off = ((idx[3] * nn[2] + idx[2]) * nn[1] + idx[1]) * nn[0] + idx[0];
+  *reinterpret_cast<uint4*>(rows + base + off) = make_uint4(best.main, best.peaks, best.tail, 0u);
 }
 
 // Largest peak code per memory over all satisfiable rows (checks the lattice compression).
@@ -215,8 +226,8 @@ __global__ void max_peaks_kernel(const MrlRow* __restrict__ rows, unsigned long 
   uint32_t mx = 0;
   for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (unsigned long long)gridDim.x * blockDim.x) {
-    const uint32_t* p = reinterpret_cast<const uint32_t*>(rows + i);
-    if (p[2] != MRL_UNSAT) mx = __vmaxu4(mx, p[1]);
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(rows + i));
+    if (r.z != MRL_UNSAT) mx = __vmaxu4(mx, r.y);
   }
   for (int o = 16; o > 0; o >>= 1) mx = __vmaxu4(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
   if ((threadIdx.x & 31) == 0) {
@@ -244,11 +255,7 @@ __global__ void gather_rows_kernel(const MrlRow* __restrict__ rows, const unsign
                                    unsigned long long n, MrlRow* __restrict__ out) {
   unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const uint32_t* p = reinterpret_cast<const uint32_t*>(rows + idx[i]);
-  uint32_t* q = reinterpret_cast<uint32_t*>(out + i);
-  q[0] = p[0];
-  q[1] = p[1];
-  q[2] = p[2];
+  *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(rows + idx[i]);
 }
 
 }  // namespace

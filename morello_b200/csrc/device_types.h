@@ -16,6 +16,7 @@ struct MrlRow {
   uint32_t main;   // saturating u32 main cost
   uint32_t peaks;  // RF<<24 | VRF<<16 | L1 code<<8 | GL code   (peak memory, as lattice codes)
   uint32_t tail;   // depth<<16 | action number; 0xFFFFFFFF = no implementation
+  uint32_t pad;    // 12 bytes of payload kept in a 16-byte slot: one aligned vector load per gather
 };
 #define MRL_UNSAT 0xFFFFFFFFu
 
@@ -55,7 +56,7 @@ struct Chunk {
 };
 
 #ifdef __cplusplus
-static_assert(sizeof(MrlRow) == 12, "row is 12 bytes");
+static_assert(sizeof(MrlRow) == 16, "row slot is 16 bytes");
 static_assert(sizeof(SpecHdr) == 32, "spec header is 32 bytes");
 static_assert(sizeof(CandRec) == 32, "candidate record is 32 bytes");
 #endif

@@ -253,6 +253,16 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       u64 off = offs[i];
       h.cand_off = (u32)off;
       h.ncand = (u32)ts.cands.size();
+      // Evaluation order is free (the argmin carries the action number): kernels first, then
+      // loops and blocks, then Moves by ascending base cost, so that the kernel's lower-bound
+      // test on a Move's base cost cuts as early as possible.
+      std::stable_sort(ts.cands.begin(), ts.cands.end(), [](const CandRec& a, const CandRec& b) {
+        auto rank = [](const CandRec& c) -> u64 {
+          u64 k = c.kind == MRL_CK_LEAF ? 0 : (c.kind == MRL_CK_LOOP ? 1 : (c.kind == MRL_CK_BLOCK ? 2 : 3));
+          return (k << 32) | (c.kind == MRL_CK_MOVE ? c.imm : 0u);
+        };
+        return rank(a) < rank(b);
+      });
       for (CandRec r : ts.cands) {
         for (int j = 0; j < r.nchild; j++) r.child[j] = new_id[r.child[j]];
         kids_t[tid] += r.nchild;

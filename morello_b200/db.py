@@ -181,7 +181,7 @@ class SynthesisDatabase:
         return out
 
     def device_rows(self):
-        """(device pointer, row count) of the 12-byte row table."""
+        """(device pointer, row count) of the row table (mrl_row_bytes() bytes per row)."""
         ptr, n = C.c_void_p(), C.c_uint64()
         if self._lib.mrl_device_rows(self._ctx, C.byref(ptr), C.byref(n)) != 0:
             raise RuntimeError("no table on the device")

@@ -18,10 +18,12 @@ def main():
                                      "precompute4", "precompute4_u32"])
     ap.add_argument("--fills", type=int, default=1)
     ap.add_argument("--caps", type=str, default=None, help="lattice caps RF,VRF,L1,GL (codes; -1 = all)")
+    ap.add_argument("--no-verify", action="store_true",
+                    help="keep the given caps even if an optimal peak exceeds them (profiling a smaller table)")
     args = ap.parse_args()
     db = m.SynthesisDatabase(device=0)
     if args.caps:
-        db.set_lattice_caps([int(x) for x in args.caps.split(",")])
+        db.set_lattice_caps([int(x) for x in args.caps.split(",")], auto_raise=not args.no_verify)
     if args.case.startswith("matmul"):
         size = int(args.case[6])
         dtype = m.DTYPE_F32 if args.case.endswith("f32") else m.DTYPE_U32
@@ -34,13 +36,19 @@ def main():
     try:
         db.fill()
     except RuntimeError:
+        if args.no_verify:
+            pass
         # the first fill found the starting lattice caps too small: let the library raise them
-        if args.case.startswith("matmul"):
+        elif args.case.startswith("matmul"):
             db.top_down(goal)
         else:
             db.precompute(int(args.case[10]), dtypes=dtypes)
     for _ in range(args.fills):
-        db.fill()
+        try:
+            db.fill()
+        except RuntimeError:
+            if not args.no_verify:
+                raise
     st = db.stats()
     st["achieved_GBps"] = st["algorithmic_bytes"] / (st["fill_ms"] * 1e-3) / 1e9 if st["fill_ms"] else None
     print(json.dumps(st))

@@ -12,7 +12,9 @@ The reference has no counterpart: its workers are threads sharing one in-process
 """
 from typing import List, Sequence, Tuple
 
-ROW_BYTES = 12
+def row_bytes() -> int:
+    from . import _lib
+    return int(_lib.load().mrl_row_bytes())
 
 
 def exchange_schedule(families: Sequence[Tuple[int, int, int, int]], n_groups: int) -> List[List[Tuple[int, int, int]]]:
@@ -56,6 +58,7 @@ def fill_sharded(db, dist, torch, process_group=None):
     world = dist.get_world_size(process_group)
     check_partition(fams, world, n_rows)
     sched = exchange_schedule(fams, db.num_groups())
+    ROW_BYTES = row_bytes()
     rows = torch.as_tensor(_DeviceBytes(ptr, max(n_rows, 1) * ROW_BYTES), device="cuda")
     db.set_stream(torch.cuda.current_stream().cuda_stream)
     db.fill_begin()

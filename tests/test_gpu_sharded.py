@@ -23,14 +23,14 @@ def _worker(rank, world, port):
     attempts = sharded.precompute_sharded(db, 2, dist, torch)
     assert 1 <= attempts <= 4
     ptr, n = db.device_rows()
-    got = torch.as_tensor(sharded._DeviceBytes(ptr, n * 12), device="cuda").clone()
+    got = torch.as_tensor(sharded._DeviceBytes(ptr, n * sharded.row_bytes()), device="cuda").clone()
     # the unsharded fill with the same caps on this rank's GPU
     solo = m.SynthesisDatabase(device=rank)
     solo.set_lattice_caps(db.stats()["lattice_caps"])
     solo.precompute(2)
     sptr, sn = solo.device_rows()
     assert sn == n
-    want = torch.as_tensor(sharded._DeviceBytes(sptr, sn * 12), device="cuda")
+    want = torch.as_tensor(sharded._DeviceBytes(sptr, sn * sharded.row_bytes()), device="cuda")
     assert torch.equal(got, want), "sharded table differs from the single-GPU table"
     # and lookups work on every rank
     goal = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
