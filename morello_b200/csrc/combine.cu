@@ -53,6 +53,20 @@ __device__ __forceinline__ uint32_t cache_code_ceil(uint32_t x) {
 }
 __device__ __forceinline__ uint32_t cache_value(uint32_t code) { return code ? (1u << (code - 1)) : 0u; }
 
+// Position of the n-th (0-based) set bit of m; m has more than n bits set.
+__device__ __forceinline__ uint32_t nth_set_bit(uint32_t m, uint32_t n) {
+  uint32_t pos = 0;
+#pragma unroll
+  for (int w = 16; w > 0; w >>= 1) {
+    const uint32_t low = __popc(m & ((1u << w) - 1u));
+    const bool up = n >= low;
+    n -= up ? low : 0u;
+    m = up ? (m >> w) : m;
+    pos += up ? (uint32_t)w : 0u;
+  }
+  return pos;
+}
+
 struct Key {
   uint32_t main, peaks, tail;
 };
@@ -107,7 +121,7 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     if (k == F) continue;
     idx[k] = rest % nn[k];
     rest /= nn[k];
-    code[k] = __fns(mm[k], 0, idx[k] + 1);
+    code[k] = nth_set_bit(mm[k], idx[k]);
     others += code[k];
   }
   if (rest != 0) return;  // column index beyond this Spec's grid
@@ -119,6 +133,14 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   // "slots at or below this cell's limit", per memory: what a child lookup at the same limits needs
   const uint32_t bm0 = (2u << code[0]) - 1u, bm1 = (2u << code[1]) - 1u, bm2 = (2u << code[2]) - 1u,
                  bm3 = (2u << code[3]) - 1u;
+
+  // The cell's limits as lattice codes: in a compressed memory slot cap+1 stands for the top code.
+  uint32_t lvpack = 0;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const uint32_t capk = code_of(cap_pack, k);
+    lvpack |= ((code[k] == capk + 1u) ? code_of(top_pack, k) : code[k]) << (8 * k);
+  }
 
   const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ch.spec].row_base));
   const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[ch.spec].cand_off));
@@ -133,9 +155,7 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     const uint32_t units = a.w;
     // The cell's limit in `level` as a lattice code. In a compressed memory the grid keeps the
     // codes 0..cap and, as slot cap+1, the top code.
-    const uint32_t cap = code_of(cap_pack, level);
-    const uint32_t lv_slot = code_of(cpack, level);
-    const uint32_t lv = (lv_slot == cap + 1u) ? code_of(top_pack, level) : lv_slot;
+    const uint32_t lv = code_of(lvpack, level);
     Key k;
     if (kind == MRL_CK_LEAF) {
       if (lv < thr) continue;
@@ -156,13 +176,18 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
         else ccode = 32 - __clz(cache_value(lv) - units);       // caches: snap down to 2^k
         // The child's limit is below the top; codes above the cap read the cap slot (nothing
         // changes between cap and top while no optimal peak exceeds the cap).
-        const uint32_t cb = (2u << min(ccode, cap)) - 1u;
-        if (level == 0) c0 = cb; else if (level == 1) c1 = cb; else if (level == 2) c2 = cb; else c3 = cb;
+        const uint32_t cb = (2u << min(ccode, code_of(cap_pack, level))) - 1u;
+        c0 = (level == 0) ? cb : c0;
+        c1 = (level == 1) ? cb : c1;
+        c2 = (level == 2) ? cb : c2;
+        c3 = (level == 3) ? cb : c3;
       }
+#ifdef MRL_CHECK_CHILD_IDS
       if (b.x >= n_specs || (nchild > 1 && b.y >= n_specs) || (nchild > 2 && b.z >= n_specs)) {
         atomicExch(error_flag, 1);
         continue;
       }
+#endif
       // Children one at a time: a child without an implementation, or a partial sum that already
       // exceeds the best main cost, ends the candidate before the remaining rows are fetched.
       const uint4 r0 = lookup(hdrs, rows, b.x, c0, c1, c2, c3);

@@ -16,7 +16,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["matmul1", "matmul2", "matmul2_f32", "precompute1", "precompute2", "precompute2_u32",
                                      "precompute4", "precompute4_u32"])
-    ap.add_argument("--fills", type=int, default=1)
+    ap.add_argument("--fills", type=int, default=1, help="fills of the final plan (>= 1)")
     ap.add_argument("--caps", type=str, default=None, help="lattice caps RF,VRF,L1,GL (codes; -1 = all)")
     ap.add_argument("--no-verify", action="store_true",
                     help="keep the given caps even if an optimal peak exceeds them (profiling a smaller table)")
@@ -43,7 +43,7 @@ def main():
             db.top_down(goal)
         else:
             db.precompute(int(args.case[10]), dtypes=dtypes)
-    for _ in range(args.fills):
+    for _ in range(args.fills - 1):
         try:
             db.fill()
         except RuntimeError:
