@@ -37,21 +37,22 @@ typedef struct mrl_decision {
 } mrl_decision;
 
 typedef struct mrl_stats {
-  uint64_t n_specs;           /* logical Specs in the tables (goals and their closure) */
+  uint64_t n_specs;            /* logical Specs in the tables (goals and their closure) */
   uint64_t n_goal_specs;
-  uint64_t n_candidates;      /* candidate records */
-  uint64_t n_rows;            /* (logical Spec, limits cell) rows = Specs resolved per fill */
-  uint64_t n_launches;        /* kernel launches of the last fill */
-  uint64_t algorithmic_bytes; /* bytes one fill must move (rows out, candidate headers, child rows in) */
-  uint64_t h2d_bytes;         /* bytes copied host->device by the last upload */
-  uint64_t d2h_bytes;         /* bytes copied device->host by the last query */
-  double plan_seconds;        /* host: closure, candidate tabulation, lattice masks, schedule */
+  uint64_t n_candidates;       /* candidate records */
+  uint64_t n_stages;           /* stages of the fill (plan order) */
+  uint64_t n_rows;             /* rows of the finished tables: cells of the Specs' final limits grids */
+  uint64_t n_cells_solved;     /* working-grid cells the last fill solved directly (all passes) */
+  uint64_t n_passes;           /* solve passes of the last fill, summed over stages */
+  uint64_t n_launches;         /* kernel launches of the last fill */
+  uint64_t n_combine_launches; /* of which combine launches */
+  uint64_t algorithmic_bytes;  /* bytes those solves must move (rows out, candidate headers, child rows in) */
+  uint64_t h2d_bytes;          /* bytes copied host->device by the last upload */
+  uint64_t d2h_bytes;          /* bytes copied device->host by the last query */
+  double plan_seconds;         /* host: closure, candidate tabulation, stage order */
   double upload_seconds;
-  double fill_ms;             /* device time of the last fill (CUDA events on the launch stream) */
-  double fill_ms_total;       /* device time of all fill attempts of the last precompute / top_down_many */
-  uint64_t n_launches_total;
-  uint32_t fill_attempts;     /* fills run until the lattice caps were large enough (>= 1) */
-  int32_t lattice_caps[4];    /* caps of the current tables, as lattice codes; -1 = memory not compressed */
+  double fill_ms;              /* device time of the last fill (CUDA events on the launch stream) */
+  double combine_ms;           /* of which inside the combine launches */
 } mrl_stats;
 
 enum { MRL_KIND_MOVE = 0, MRL_KIND_FILL_ZERO = 1, MRL_KIND_MATMUL_ACCUM = 2, MRL_KIND_MATMUL = 3 };
@@ -89,7 +90,7 @@ int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_o
  * callers that must not allocate device memory: a process that handed all of HBM to its tables
  * at start-up has none left to give, and worker threads that call in concurrently would be
  * serialised by the device-wide synchronisation of every cudaMalloc / cudaFree. This call makes
- * neither; the device working set of the fill (plan arrays, row table, lookup staging) lives in
+ * neither; the device working set of the fill (plan arrays, working grids, row table, lookup staging) lives in
  * one fixed array of MRL_NOALLOC_MAX_BYTES that each GPU loading the library holds until the
  * process exits. A goal set whose fill needs more is refused with status -4 and a message; use
  * mrl_top_down_many for it. The context's own tables are not touched.
@@ -105,42 +106,38 @@ int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t
  * dtype_mask: bit 0 = u32, bit 1 = f32 (DTYPES, precompute/src/main.rs:55). */
 int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask);
 
-/* The three stages of the two calls above, exposed separately for measurement: plan on the
- * host, copy the plan to the device, run the launch schedule (may be repeated). */
+/* The three steps of the two calls above, exposed separately for measurement: plan on the
+ * host, copy the plan to the device, fill (may be repeated). */
 int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask);
 int mrl_plan_goals(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n);
 int mrl_upload(mrl_ctx* ctx);
 int mrl_fill(mrl_ctx* ctx);
 
-/* The limits lattice the tables keep per memory: the codes 0..caps[k] and the top limit
- * (codes: registers raw, caches bit length; negative = keep all codes). Limits in between read
- * the cap entry, which is exact while no optimal peak exceeds the cap; every fill checks that.
- * With auto_raise (the default) mrl_precompute and mrl_top_down_many raise the caps and refill
- * until the check passes; without it they return -5. No counterpart in the reference, whose
- * R-tree rectangles need no such bound (morello/src/db/pagecontents.rs:125-184). */
-int mrl_set_lattice_caps(mrl_ctx* ctx, const int32_t caps[4], int auto_raise);
-
 /* Multi-GPU (one process per GPU; no counterpart in the reference, whose workers are threads
  * sharing one database, precompute/src/main.rs:229-240,339). Every rank plans the same job and
- * keeps the whole table; rank r computes the "families" (Specs of one group with equal dtype and
- * shape - Moves change neither, so families of a group are independent) it owns. Between groups
- * the caller copies each family's rows from its owner to all ranks, on the stream given to
- * mrl_set_stream, e.g. with ncclBroadcast over NVLink:
+ * keeps the whole table. The plan orders Specs into stages; inside a stage the "families"
+ * (Specs with equal dtype and shape - Moves change neither) are independent, and rank r computes
+ * the families it owns. Per stage the caller sums two device buffers over all ranks on the
+ * stream given to mrl_set_stream (e.g. ncclAllReduce, sum of int32, in place; a Spec's words are
+ * zero on every rank but its owner):
  *   mrl_set_shard, mrl_plan_*, mrl_upload, then per fill: mrl_fill_begin;
- *   for g in groups { mrl_fill_group(g); exchange rows of the families of g }; mrl_fill_end.
- * mrl_fill_end returns 1 (and the caps to use) when an optimal peak exceeded a lattice cap: the
- * caller applies the element-wise maximum over ranks with mrl_set_lattice_caps and refills. */
+ *   for s in stages { mrl_fill_stage_solve(s, &masks, &n); sum masks;
+ *                     mrl_fill_stage_place(s, &rows, &n); sum rows }; mrl_fill_end.
+ * masks: the limits-grid breakpoints of the stage's Specs; rows: their finished table rows. */
 int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world);
 int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream);
-uint64_t mrl_num_groups(const mrl_ctx* ctx);
+uint64_t mrl_num_stages(const mrl_ctx* ctx);
 uint64_t mrl_num_families(const mrl_ctx* ctx);
-int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* group, uint32_t* owner, uint64_t* row_lo,
-                    uint64_t* row_hi);
-int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows);
-uint32_t mrl_row_bytes(void); /* bytes per row slot in the device table */
+int mrl_stage_info(const mrl_ctx* ctx, uint64_t stage, uint32_t* spec_lo, uint32_t* spec_hi, uint32_t* family_lo,
+                   uint32_t* family_hi);
+int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* stage, uint32_t* owner, uint32_t* spec_lo,
+                    uint32_t* spec_hi);
+int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows); /* the finished table on the device */
+uint32_t mrl_row_bytes(void); /* bytes per row of the device table */
 int mrl_fill_begin(mrl_ctx* ctx);
-int mrl_fill_group(mrl_ctx* ctx, uint64_t group);
-int mrl_fill_end(mrl_ctx* ctx, int32_t raised_caps[4]);
+int mrl_fill_stage_solve(mrl_ctx* ctx, uint64_t stage, void** masks, uint64_t* mask_bytes);
+int mrl_fill_stage_place(mrl_ctx* ctx, uint64_t stage, void** rows, uint64_t* row_bytes);
+int mrl_fill_end(mrl_ctx* ctx);
 
 /* Replaces FilesDatabase::get (morello/src/db/mod.rs:481-503, 538-573): point lookups in the
  * filled tables; found = -1 for Specs outside the tables. */
@@ -154,7 +151,7 @@ int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out);
  * and its dense cell block (n0*n1*n2*n3 decisions, RF index fastest). */
 uint64_t mrl_num_specs(const mrl_ctx* ctx);
 int mrl_spec_blob(const mrl_ctx* ctx, uint64_t spec_id, uint8_t* out, size_t cap);
-int mrl_spec_grid(const mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells);
+int mrl_spec_grid(mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells);
 int mrl_export_rows(mrl_ctx* ctx, uint64_t spec_id, mrl_decision* out, size_t cap);
 
 #ifdef __cplusplus

@@ -12,10 +12,11 @@ class Decision(C.Structure):
 
 class Stats(C.Structure):
     _fields_ = [("n_specs", C.c_uint64), ("n_goal_specs", C.c_uint64), ("n_candidates", C.c_uint64),
-                ("n_rows", C.c_uint64), ("n_launches", C.c_uint64), ("algorithmic_bytes", C.c_uint64),
-                ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("plan_seconds", C.c_double),
-                ("upload_seconds", C.c_double), ("fill_ms", C.c_double), ("fill_ms_total", C.c_double),
-                ("n_launches_total", C.c_uint64), ("fill_attempts", C.c_uint32), ("lattice_caps", C.c_int32 * 4)]
+                ("n_stages", C.c_uint64), ("n_rows", C.c_uint64), ("n_cells_solved", C.c_uint64),
+                ("n_passes", C.c_uint64), ("n_launches", C.c_uint64), ("n_combine_launches", C.c_uint64),
+                ("algorithmic_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
+                ("plan_seconds", C.c_double), ("upload_seconds", C.c_double), ("fill_ms", C.c_double),
+                ("combine_ms", C.c_double)]
 
 
 EXPORTS = {
@@ -35,18 +36,20 @@ EXPORTS = {
     "mrl_plan_goals": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t]),
     "mrl_upload": (C.c_int, [C.c_void_p]),
     "mrl_fill": (C.c_int, [C.c_void_p]),
-    "mrl_set_lattice_caps": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int]),
     "mrl_set_shard": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32]),
     "mrl_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
-    "mrl_num_groups": (C.c_uint64, [C.c_void_p]),
+    "mrl_num_stages": (C.c_uint64, [C.c_void_p]),
     "mrl_num_families": (C.c_uint64, [C.c_void_p]),
+    "mrl_stage_info": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                 C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "mrl_family_info": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
-                                  C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+                                  C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "mrl_device_rows": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "mrl_row_bytes": (C.c_uint32, []),
     "mrl_fill_begin": (C.c_int, [C.c_void_p]),
-    "mrl_fill_group": (C.c_int, [C.c_void_p, C.c_uint64]),
-    "mrl_fill_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "mrl_fill_stage_solve": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "mrl_fill_stage_place": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "mrl_fill_end": (C.c_int, [C.c_void_p]),
     "mrl_get_many": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_uint64),
                                C.POINTER(Decision)]),
     "mrl_get_stats": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),

@@ -15,11 +15,6 @@ struct mrl_ctx {
   DeviceFill dev;
   mrl_stats stats;
   std::string err;
-  // Lattice caps per memory (lattice codes; negative = keep every code). Start low: a fill at
-  // low caps is cheap, and fill_verified raises them until no optimal peak exceeds its cap.
-  int caps[4] = {4, 2, 4, 0};
-  bool caps_chosen = false;  // false: pick a starting point from the goals' largest dimension
-  bool auto_raise = true;
   uint32_t rank = 0, world = 1;
 };
 
@@ -54,95 +49,46 @@ std::vector<Dtype> dtypes_of(int mask) {
   return d;
 }
 
-void copy_plan_stats(mrl_ctx* ctx) {
-  const PlanStats& ps = ctx->plan.stats;
-  ctx->stats.n_specs = ps.n_specs;
-  ctx->stats.n_goal_specs = ps.n_goal_specs;
-  ctx->stats.n_candidates = ps.n_cands;
-  ctx->stats.n_rows = ps.n_rows;
-  ctx->stats.algorithmic_bytes = ps.algorithmic_bytes;
-  for (int k = 0; k < 4; k++)
-    ctx->stats.lattice_caps[k] = ctx->plan.compressed(k) ? (int32_t)ctx->plan.cap_code[k] : -1;
+void copy_fill_stats(mrl_ctx* ctx) {
+  const FillStats& fs = ctx->dev.stats();
+  ctx->stats.n_rows = fs.n_rows;
+  ctx->stats.n_cells_solved = fs.cells_solved;
+  ctx->stats.n_passes = fs.passes;
+  ctx->stats.n_launches = fs.launches;
+  ctx->stats.n_combine_launches = fs.combine_launches;
+  ctx->stats.algorithmic_bytes = fs.alg_bytes;
+  ctx->stats.fill_ms = fs.fill_ms;
+  ctx->stats.combine_ms = fs.combine_ms;
 }
 
-// One upload + fill + check of the lattice compression. Returns 1 when some optimal peak
-// exceeded its cap (caps in ctx->caps have then been raised), 0 when the tables are exact.
-int fill_once(mrl_ctx* ctx) {
-  double t0 = now_s();
-  if (ctx->dev.upload(ctx->plan) != 0) return fail(ctx, -2, ctx->dev.error());
-  ctx->uploaded = true;
-  ctx->stats.upload_seconds += now_s() - t0;
-  ctx->stats.h2d_bytes += ctx->dev.h2d_bytes();
-  float ms = 0;
-  uint64_t launches = 0;
-  if (ctx->dev.run(ctx->plan, &ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
-  ctx->stats.fill_ms_total += ms;
-  ctx->stats.fill_ms = ms;
-  ctx->stats.n_launches = launches;
-  ctx->stats.n_launches_total += launches;
-  ctx->stats.fill_attempts++;
-  uint32_t pk[4];
-  if (ctx->dev.max_peaks(pk) != 0) return fail(ctx, -2, ctx->dev.error());
-  bool violated = false;
-  for (int k = 0; k < 4; k++)
-    if (ctx->plan.compressed(k) && pk[k] > ctx->plan.cap_code[k]) {
-      violated = true;
-      ctx->caps[k] = (int)pk[k];
-    }
-  return violated ? 1 : 0;
-}
-
-// Fills the planned tables, raising the lattice caps until the compression is exact.
-int fill_verified(mrl_ctx* ctx) {
+// Upload + fill of the planned tables.
+int upload_and_fill(mrl_ctx* ctx) {
   if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to fill on");
-  ctx->stats.upload_seconds = 0;
-  ctx->stats.h2d_bytes = 0;
-  ctx->stats.fill_ms_total = 0;
-  ctx->stats.n_launches_total = 0;
-  ctx->stats.fill_attempts = 0;
   ctx->filled = false;
-  for (int attempt = 0; attempt < 16; attempt++) {
-    int rc = fill_once(ctx);
-    if (rc < 0) return rc;
-    if (rc == 0) {
-      ctx->filled = true;
-      return 0;
-    }
-    ctx->caps_chosen = true;  // raised caps are kept for later plans on this context
-    if (!ctx->auto_raise) return fail(ctx, -5, "an optimal peak exceeds the lattice caps; raise them (mrl_set_lattice_caps)");
-    double t0 = now_s();
-    relayout_plan(ctx->plan, ctx->caps);
-    copy_plan_stats(ctx);
-    ctx->stats.plan_seconds += now_s() - t0;
-  }
-  return fail(ctx, -5, "lattice caps did not converge");
-}
-
-// Starting caps by the largest Spec dimension among the goals: the values earlier fills of that
-// size ended with. Only a starting point - every fill is checked and the caps raised if needed.
-void choose_initial_caps(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
-  if (ctx->caps_chosen) return;
-  u32 maxdim = 1;
-  for (const LogicalSpec& g : goals)
-    for (int i = 0; i < g.spec_shape.n; i++) maxdim = std::max(maxdim, g.spec_shape[i]);
-  static const int table[4][4] = {{0, 0, 3, 0}, {8, 2, 5, 0}, {-1, 12, 7, 4}, {-1, -1, 9, 6}};
-  int row = maxdim <= 1 ? 0 : (maxdim <= 2 ? 1 : (maxdim <= 4 ? 2 : 3));
-  for (int k = 0; k < 4; k++) ctx->caps[k] = table[row][k];
+  double t0 = now_s();
+  int rc = ctx->dev.upload(ctx->plan);
+  if (rc != 0) return fail(ctx, rc == -4 || rc == -6 ? rc : -2, ctx->dev.error());
+  ctx->uploaded = true;
+  ctx->stats.upload_seconds = now_s() - t0;
+  ctx->stats.h2d_bytes = ctx->dev.h2d_bytes();
+  rc = ctx->dev.run(ctx->plan);
+  copy_fill_stats(ctx);
+  if (rc != 0) return fail(ctx, rc == -4 || rc == -6 ? rc : -2, ctx->dev.error());
+  ctx->filled = true;
+  return 0;
 }
 
 int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
   double t0 = now_s();
-  choose_initial_caps(ctx, goals);
-  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->caps, ctx->rank, ctx->world);
+  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->rank, ctx->world);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
-  copy_plan_stats(ctx);
   const PlanStats& ps = ctx->plan.stats;
+  memset(&ctx->stats, 0, sizeof(ctx->stats));
   ctx->stats.n_specs = ps.n_specs;
   ctx->stats.n_goal_specs = ps.n_goal_specs;
   ctx->stats.n_candidates = ps.n_cands;
-  ctx->stats.n_rows = ps.n_rows;
-  ctx->stats.algorithmic_bytes = ps.algorithmic_bytes;
+  ctx->stats.n_stages = ps.n_stages;
   ctx->stats.plan_seconds = now_s() - t0;
   return 0;
 }
@@ -280,34 +226,31 @@ int mrl_upload(mrl_ctx* ctx) {
 int mrl_fill(mrl_ctx* ctx) {
   if (!ctx) return -1;
   if (!ctx->uploaded) return fail(ctx, -1, "plan not uploaded");
-  float ms = 0;
-  uint64_t launches = 0;
-  if (ctx->dev.run(ctx->plan, &ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
-  ctx->stats.fill_ms = ms;
-  ctx->stats.n_launches = launches;
-  uint32_t pk[4];
-  if (ctx->dev.max_peaks(pk) != 0) return fail(ctx, -2, ctx->dev.error());
-  for (int k = 0; k < 4; k++)
-    if (ctx->plan.compressed(k) && pk[k] > ctx->plan.cap_code[k]) {
-      ctx->filled = false;
-      return fail(ctx, -5, "an optimal peak exceeds the lattice caps of this plan; use mrl_precompute / "
-                           "mrl_top_down_many (they raise the caps) or mrl_set_lattice_caps");
-    }
+  ctx->filled = false;
+  int rc = ctx->dev.run(ctx->plan);
+  copy_fill_stats(ctx);
+  if (rc != 0) return fail(ctx, rc == -4 || rc == -6 ? rc : -2, ctx->dev.error());
   ctx->filled = true;
   return 0;
 }
 
-int mrl_set_lattice_caps(mrl_ctx* ctx, const int32_t caps[4], int auto_raise) {
-  if (!ctx || !caps) return -1;
-  for (int k = 0; k < 4; k++) ctx->caps[k] = caps[k];
-  ctx->caps_chosen = true;
-  ctx->auto_raise = auto_raise != 0;
-  if (ctx->planned) {
-    relayout_plan(ctx->plan, ctx->caps);
-    copy_plan_stats(ctx);
-    ctx->uploaded = ctx->filled = false;
+// Resolves each query to (Spec id, packed limit codes); `where` = its position in the caller's arrays.
+static void resolve_queries(const Plan& plan, const uint8_t* blobs, const uint64_t* blob_off, size_t n,
+                            const uint64_t* limits, mrl_decision* out, std::vector<uint32_t>& ids,
+                            std::vector<uint32_t>& packs, std::vector<size_t>& where) {
+  for (size_t i = 0; i < n; i++) {
+    memset(&out[i], 0, sizeof(out[i]));
+    out[i].found = -1;
+    LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)blobs + blob_off[i], blob_off[i + 1] - blob_off[i]));
+    if (logicalspec_canonicalize(ls) != CANON_OK) continue;
+    long id = plan.find(ls);
+    if (id < 0) continue;
+    uint32_t pack;
+    if (!plan.pack_limits(limits + 4 * i, &pack)) continue;
+    ids.push_back((uint32_t)id);
+    packs.push_back(pack);
+    where.push_back(i);
   }
-  return 0;
 }
 
 int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
@@ -315,24 +258,13 @@ int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, s
   if (!ctx) return -1;
   if (!ctx->filled) return fail(ctx, -1, "tables are not filled");
   try {
-    std::vector<uint64_t> idx;
+    std::vector<uint32_t> ids, packs;
     std::vector<size_t> where;
-    for (size_t i = 0; i < n; i++) {
-      memset(&out[i], 0, sizeof(out[i]));
-      out[i].found = -1;
-      LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)blobs + blob_off[i], blob_off[i + 1] - blob_off[i]));
-      if (logicalspec_canonicalize(ls) != CANON_OK) continue;
-      long id = ctx->plan.find(ls);
-      if (id < 0) continue;
-      long row = ctx->plan.row_of((u32)id, limits + 4 * i);
-      if (row < 0) continue;
-      idx.push_back((uint64_t)row);
-      where.push_back(i);
-    }
-    std::vector<MrlRow> rows(idx.size());
-    if (ctx->dev.read_rows(idx.data(), idx.size(), rows.data()) != 0) return fail(ctx, -2, ctx->dev.error());
-    for (size_t j = 0; j < idx.size(); j++) decode_row(rows[j], &out[where[j]]);
-    ctx->stats.d2h_bytes = idx.size() * sizeof(MrlRow);
+    resolve_queries(ctx->plan, blobs, blob_off, n, limits, out, ids, packs, where);
+    std::vector<MrlRow> rows(ids.size());
+    if (ctx->dev.lookup(ids.data(), packs.data(), ids.size(), rows.data()) != 0) return fail(ctx, -2, ctx->dev.error());
+    for (size_t j = 0; j < ids.size(); j++) decode_row(rows[j], &out[where[j]]);
+    ctx->stats.d2h_bytes = ids.size() * sizeof(MrlRow);
     return 0;
   } catch (const std::exception& e) {
     return fail(ctx, -1, e.what());
@@ -343,38 +275,28 @@ int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_o
                       mrl_decision* out) {
   int rc = mrl_plan_goals(ctx, blobs, blob_off, n);
   if (rc) return rc;
-  if ((rc = fill_verified(ctx))) return rc;
+  if ((rc = upload_and_fill(ctx))) return rc;
   return mrl_get_many(ctx, blobs, blob_off, n, limits, out);
 }
 
 int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n,
                               const uint64_t* limits, mrl_decision* out) {
   if (!ctx) return -1;
+  if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to fill on");
   try {
     std::vector<LogicalSpec> goals;
     if (parse_goals(blobs, blob_off, n, goals) != 0) return fail(ctx, -4, "goal Spec is not canonicalizable");
     // A plan of its own: the context's tables (and their device memory) are left as they are.
-    // Every lattice code is kept here (no caps): the fill is small by construction and one
-    // pass must be final.
-    const int no_caps[4] = {-1, -1, -1, -1};
-    Plan plan = build_plan(goals, ctx->n_threads, nullptr, no_caps);
-    std::vector<uint64_t> idx;
+    Plan plan = build_plan(goals, ctx->n_threads);
+    std::vector<uint32_t> ids, packs;
     std::vector<size_t> where;
-    for (size_t i = 0; i < n; i++) {
-      memset(&out[i], 0, sizeof(out[i]));
-      out[i].found = -1;
-      long id = plan.find(goals[i]);
-      if (id < 0) continue;
-      long row = plan.row_of((u32)id, limits + 4 * i);
-      if (row < 0) continue;
-      idx.push_back((uint64_t)row);
-      where.push_back(i);
-    }
-    std::vector<MrlRow> rows(idx.size());
+    resolve_queries(plan, blobs, blob_off, n, limits, out, ids, packs, where);
+    std::vector<MrlRow> rows(ids.size());
     char err[256] = {0};
-    int rc = fill_static(ctx->dev.device(), ctx->dev.stream(), plan, idx.data(), idx.size(), rows.data(), err, sizeof(err));
+    int rc = fill_static(ctx->dev.device(), ctx->dev.stream(), plan, ids.data(), packs.data(), ids.size(), rows.data(),
+                         err, sizeof(err));
     if (rc != 0) return fail(ctx, rc, err);
-    for (size_t j = 0; j < idx.size(); j++) decode_row(rows[j], &out[where[j]]);
+    for (size_t j = 0; j < ids.size(); j++) decode_row(rows[j], &out[where[j]]);
     return 0;
   } catch (const std::exception& e) {
     return fail(ctx, -1, e.what());
@@ -384,7 +306,7 @@ int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t
 int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
   int rc = mrl_plan_precompute(ctx, size, through, dtype_mask);
   if (rc) return rc;
-  return fill_verified(ctx);
+  return upload_and_fill(ctx);
 }
 
 int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world) {
@@ -401,26 +323,37 @@ int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream) {
   return ctx->dev.set_stream((cudaStream_t)cuda_stream);
 }
 
-uint64_t mrl_num_groups(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.groups.size() : 0; }
+uint64_t mrl_num_stages(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.stages.size() : 0; }
 uint64_t mrl_num_families(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.families.size() : 0; }
 
-int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* group, uint32_t* owner, uint64_t* row_lo,
-                    uint64_t* row_hi) {
+int mrl_stage_info(const mrl_ctx* ctx, uint64_t stage, uint32_t* spec_lo, uint32_t* spec_hi, uint32_t* family_lo,
+                   uint32_t* family_hi) {
+  if (!ctx || !ctx->planned || stage >= ctx->plan.stages.size()) return -1;
+  const Stage& st = ctx->plan.stages[stage];
+  if (spec_lo) *spec_lo = st.spec_lo;
+  if (spec_hi) *spec_hi = st.spec_hi;
+  if (family_lo) *family_lo = st.fam_lo;
+  if (family_hi) *family_hi = st.fam_hi;
+  return 0;
+}
+
+int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* stage, uint32_t* owner, uint32_t* spec_lo,
+                    uint32_t* spec_hi) {
   if (!ctx || !ctx->planned || family >= ctx->plan.families.size()) return -1;
   const Family& f = ctx->plan.families[family];
-  if (group) *group = f.group;
+  if (stage) *stage = f.stage;
   if (owner) *owner = f.owner;
-  if (row_lo) *row_lo = f.row_lo;
-  if (row_hi) *row_hi = f.row_hi;
+  if (spec_lo) *spec_lo = f.spec_lo;
+  if (spec_hi) *spec_hi = f.spec_hi;
   return 0;
 }
 
 uint32_t mrl_row_bytes(void) { return (uint32_t)sizeof(MrlRow); }
 
 int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows) {
-  if (!ctx || !ctx->uploaded) return -1;
+  if (!ctx || !ctx->filled) return -1;
   if (ptr) *ptr = ctx->dev.device_rows();
-  if (n_rows) *n_rows = ctx->dev.n_rows();
+  if (n_rows) *n_rows = ctx->dev.stats().n_rows;
   return 0;
 }
 
@@ -432,30 +365,30 @@ int mrl_fill_begin(mrl_ctx* ctx) {
   return 0;
 }
 
-int mrl_fill_group(mrl_ctx* ctx, uint64_t group) {
+int mrl_fill_stage_solve(mrl_ctx* ctx, uint64_t stage, void** masks, uint64_t* mask_bytes) {
   if (!ctx || !ctx->uploaded) return -1;
-  if (ctx->dev.run_group(ctx->plan, (uint32_t)group) != 0) return fail(ctx, -2, ctx->dev.error());
+  int rc = ctx->dev.solve_stage(ctx->plan, (uint32_t)stage);
+  if (rc != 0) return fail(ctx, rc == -4 || rc == -6 ? rc : -2, ctx->dev.error());
+  if (ctx->dev.stage_masks(ctx->plan, (uint32_t)stage, masks, mask_bytes) != 0) return fail(ctx, -2, ctx->dev.error());
   return 0;
 }
 
-int mrl_fill_end(mrl_ctx* ctx, int32_t raised_caps[4]) {
+int mrl_fill_stage_place(mrl_ctx* ctx, uint64_t stage, void** rows, uint64_t* row_bytes) {
   if (!ctx || !ctx->uploaded) return -1;
-  float ms = 0;
-  uint64_t launches = 0;
-  if (ctx->dev.end_fill(&ms, &launches) != 0) return fail(ctx, -2, ctx->dev.error());
-  ctx->stats.fill_ms = ms;
-  ctx->stats.n_launches = launches;
-  uint32_t pk[4];
-  if (ctx->dev.max_peaks(pk) != 0) return fail(ctx, -2, ctx->dev.error());
-  bool violated = false;
-  for (int k = 0; k < 4; k++) {
-    if (raised_caps) raised_caps[k] = ctx->caps[k];
-    if (ctx->plan.compressed(k) && pk[k] > ctx->plan.cap_code[k]) {
-      violated = true;
-      if (raised_caps) raised_caps[k] = (int32_t)pk[k];
-    }
-  }
-  if (violated) return 1;  // not an error: the caller raises the caps on every rank and refills
+  void* p = nullptr;
+  uint64_t b = 0;
+  int rc = ctx->dev.place_stage(ctx->plan, (uint32_t)stage, &p, &b);
+  if (rc != 0) return fail(ctx, rc == -4 || rc == -6 ? rc : -2, ctx->dev.error());
+  if (rows) *rows = p;
+  if (row_bytes) *row_bytes = b;
+  return 0;
+}
+
+int mrl_fill_end(mrl_ctx* ctx) {
+  if (!ctx || !ctx->uploaded) return -1;
+  int rc = ctx->dev.end_fill();
+  copy_fill_stats(ctx);
+  if (rc != 0) return fail(ctx, -2, ctx->dev.error());
   ctx->filled = true;
   return 0;
 }
@@ -476,9 +409,10 @@ int mrl_spec_blob(const mrl_ctx* ctx, uint64_t spec_id, uint8_t* out, size_t cap
   return (int)k.size();
 }
 
-int mrl_spec_grid(const mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells) {
-  if (!ctx || !ctx->planned || spec_id >= ctx->plan.specs.size()) return -1;
-  const SpecHdr& h = ctx->plan.hdrs[spec_id];
+int mrl_spec_grid(mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells) {
+  if (!ctx || !ctx->filled || spec_id >= ctx->plan.specs.size()) return -1;
+  SpecHdr h;
+  if (ctx->dev.read_hdr((uint32_t)spec_id, &h) != 0) return fail(ctx, -2, ctx->dev.error());
   uint64_t n = 1;
   for (int k = 0; k < 4; k++) { masks[k] = h.mask[k]; n *= (uint64_t)__builtin_popcount(h.mask[k]); }
   if (n_cells) *n_cells = n;
@@ -487,14 +421,13 @@ int mrl_spec_grid(const mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint6
 
 int mrl_export_rows(mrl_ctx* ctx, uint64_t spec_id, mrl_decision* out, size_t cap) {
   if (!ctx || !ctx->filled || spec_id >= ctx->plan.specs.size()) return -1;
-  const SpecHdr& h = ctx->plan.hdrs[spec_id];
+  SpecHdr h;
+  if (ctx->dev.read_hdr((uint32_t)spec_id, &h) != 0) return fail(ctx, -2, ctx->dev.error());
   uint64_t n = 1;
   for (int k = 0; k < 4; k++) n *= (uint64_t)__builtin_popcount(h.mask[k]);
   if (n > cap) return fail(ctx, -3, "export buffer too small");
-  std::vector<uint64_t> idx(n);
-  for (uint64_t i = 0; i < n; i++) idx[i] = h.row_base + i;
   std::vector<MrlRow> rows(n);
-  if (ctx->dev.read_rows(idx.data(), n, rows.data()) != 0) return fail(ctx, -2, ctx->dev.error());
+  if (ctx->dev.read_rows(h.row_base, n, rows.data()) != 0) return fail(ctx, -2, ctx->dev.error());
   for (uint64_t i = 0; i < n; i++) decode_row(rows[i], &out[i]);
   return 0;
 }

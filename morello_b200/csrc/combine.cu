@@ -1,15 +1,24 @@
-// combine_argmin: the CUDA side of the synthesis-database fill (sm_100a).
+// The CUDA side of the synthesis-database fill (sm_100a).
 //
-// One launch evaluates, for one group of logical Specs (same phase and log-shape sum, so no
-// dependencies among them), every table cell that lies on one diagonal of the memory-limits
-// lattice. A thread owns one "column" of a Spec's cell grid (RF, VRF and L1 indices fixed;
-// the GL index is whatever puts the cell on the launch's diagonal), loops over the Spec's
-// candidate records, gathers the child rows each candidate needs at the child's limits,
-// combines them into a Cost and keeps the lexicographic minimum. Lanes of a warp hold
-// neighbouring RF indices of the same Spec, so the rows they gather from one child are
-// neighbours in memory.
+// Specs are processed stage by stage (plan.hpp). For one stage the device
+//   1. derives each Spec's working limits grid: per memory the lattice codes at which its
+//      result can change - thresholds of its own candidates plus the (shifted) breakpoints of
+//      the finished tables of its children (derive_masks_kernel, place_kernel);
+//   2. solves every cell of those grids directly, one launch per occupied limits diagonal
+//      (combine_argmin_kernel): a thread owns one "column" of a Spec's grid, walks the Spec's
+//      candidate records, gathers the child rows each candidate needs at the child's limits,
+//      combines them into a Cost and keeps the lexicographic minimum;
+//   3. finds which breakpoints are real - some pair of neighbouring cells differs
+//      (real_masks_kernel) - and repeats 1-3 while a Spec's grid still lacks a breakpoint that
+//      a same-stage child turned out to have (relayout Moves are the only same-stage
+//      dependency; the first pass ignores them);
+//   4. compacts the working grids to the real breakpoints and appends them to the table
+//      (final_count_kernel, scan_block_sums_kernel, compact_kernel).
+// Step 3's fixpoint is exact: when every Spec's grid contains all thresholds and all shifted
+// breakpoints of the computed tables of its children, induction over the limits lattice shows
+// every computed cell equals the direct solve at every limit inside the cell.
 //
-// What it replaces in the reference (paths inside the Morello repository):
+// What the combine replaces in the reference (paths inside the Morello repository):
 //   morello/src/scheduling/mod.rs:286-368     ActionSolver::compute_cost
 //   morello/src/imp/loops.rs:207-242          loop main cost (serial, no boundary regions)
 //   morello/src/memorylimits.rs:159-224,409-470  peak propagation, limit subtraction
@@ -20,7 +29,10 @@
 #include "device_types.h"
 #include "fill.hpp"
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdio.h>
+#include <string.h>
+#include <algorithm>
 #include <mutex>
 
 #ifndef MRL_MIN_BLOCKS
@@ -39,9 +51,6 @@ __device__ __forceinline__ uint32_t sat_mul(uint32_t a, uint32_t b) {
 }
 // cpack: limit codes packed one per byte, RF in byte 0 .. GL in byte 3.
 __device__ __forceinline__ uint32_t code_of(uint32_t cpack, uint32_t level) { return (cpack >> (8 * level)) & 0xFFu; }
-__device__ __forceinline__ uint32_t with_code(uint32_t cpack, uint32_t level, uint32_t code) {
-  return (cpack & ~(0xFFu << (8 * level))) | (code << (8 * level));
-}
 // peaks word: RF in byte 3 .. GL in byte 0 (so that a plain u32 compare is lexicographic).
 __device__ __forceinline__ uint32_t peak_shift(uint32_t level) { return 8 * (3 - level); }
 
@@ -67,6 +76,10 @@ __device__ __forceinline__ uint32_t nth_set_bit(uint32_t m, uint32_t n) {
   return pos;
 }
 
+__device__ __forceinline__ uint32_t sel4(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t k) {
+  return k == 0 ? a0 : (k == 1 ? a1 : (k == 2 ? a2 : a3));
+}
+
 struct Key {
   uint32_t main, peaks, tail;
 };
@@ -77,10 +90,17 @@ __device__ __forceinline__ bool key_less(const Key& a, const Key& b) {
 }
 
 // Row of a child Spec at given limits: the cell whose breakpoints are the largest ones not
-// above the limits. bm[k] = mask of the slots <= the limit's slot in memory k. One 32-byte
-// header (two loads, warp-uniform) and one 16-byte row.
+// above the limits. b_k = mask of the codes <= the limit's code in memory k. One 32-byte
+// header (two loads) and one 16-byte row.
+// Row `base` of the table: bit 63 set = a working row of the stage being solved (temp buffer).
+#define MRL_TEMP_FLAG (1ull << 63)
+__device__ __forceinline__ const MrlRow* row_at(const MrlRow* rows, const MrlRow* temp, unsigned long long base) {
+  return ((base & MRL_TEMP_FLAG) ? temp : rows) + (base & ~MRL_TEMP_FLAG);
+}
+
 __device__ __forceinline__ uint4 lookup(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
-                                        uint32_t child, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+                                        const MrlRow* __restrict__ temp, uint32_t child, uint32_t b0, uint32_t b1,
+                                        uint32_t b2, uint32_t b3) {
   const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[child]));
   const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[child].row_base));
   const uint32_t i0 = __popc(m.x & b0) - 1;
@@ -88,74 +108,78 @@ __device__ __forceinline__ uint4 lookup(const SpecHdr* __restrict__ hdrs, const 
   const uint32_t i2 = __popc(m.z & b2) - 1;
   const uint32_t i3 = __popc(m.w & b3) - 1;
   const uint32_t off = ((i3 * __popc(m.z) + i2) * __popc(m.y) + i1) * __popc(m.x) + i0;  // cells per Spec < 2^32
-  // Rows read here were written by earlier launches (lower diagonal or earlier group), never by
+  // Rows read here were written by earlier launches (lower diagonal or earlier stage), never by
   // this one, so the read-only path is safe.
-  return __ldg(reinterpret_cast<const uint4*>(rows + base + off));
+  return __ldg(reinterpret_cast<const uint4*>(row_at(rows, temp, base) + off));
 }
 
-// G = lanes per cell: the G lanes of a cell take every G-th candidate each and min-reduce
-// their keys with warp shuffles; a warp covers 32 / G neighbouring columns.
-// F = the memory whose slot is fixed by the diagonal (chosen per group: the memory with the
-// most slots, so that most columns have a cell on the launch's diagonal).
-template <int G, int F>
+// Geometry of one thread's column. A column fixes the slot index in the three memories other
+// than the Spec's free memory F.
+struct Column {
+  uint32_t spec, F;
+  uint32_t mm[4], nn[4], idx[4], code[4];
+  uint32_t others;  // sum of the codes of the fixed memories
+  bool valid;
+};
+__device__ __forceinline__ Column decode_column(const SpecHdr* __restrict__ hdrs, const Chunk ch, uint32_t lane) {
+  Column c;
+  c.spec = ch.spec;
+  c.F = ch.col_start >> 30;
+  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch.spec]));
+  c.mm[0] = m.x; c.mm[1] = m.y; c.mm[2] = m.z; c.mm[3] = m.w;
+  uint32_t rest = (ch.col_start & 0x3FFFFFFFu) + lane;
+  c.others = 0;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    c.nn[k] = (uint32_t)__popc(c.mm[k]);
+    const uint32_t nk = ((uint32_t)k == c.F) ? 1u : c.nn[k];
+    c.idx[k] = rest % nk;
+    rest /= nk;
+    c.code[k] = nth_set_bit(c.mm[k], c.idx[k]);  // for F: slot 0, code 0
+    c.others += c.code[k];
+  }
+  c.valid = rest == 0;  // false: column index beyond this Spec's grid
+  return c;
+}
+
+// One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes).
 __global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
 combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
                       const Chunk* __restrict__ chunks, uint32_t n_chunks, uint32_t diag,
-                      MrlRow* __restrict__ rows, uint32_t n_specs, uint32_t cap_pack, uint32_t top_pack,
-                      int* __restrict__ error_flag) {
+                      const MrlRow* __restrict__ rows, MrlRow* __restrict__ temp, uint32_t n_specs,
+                      uint32_t* __restrict__ error_flag) {
   const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
   if (warp >= n_chunks) return;
   const Chunk ch = chunks[warp];
-  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch.spec]));
-  const uint32_t sub = lane % G;
-  const uint32_t col = ch.col_start + lane / G;
-  // A column fixes the slot index in the three memories other than F; the launch's diagonal
-  // then fixes the code in F, and the cell exists if that code is one of the Spec's slots.
-  const uint32_t mm[4] = {m.x, m.y, m.z, m.w};
-  const uint32_t nn[4] = {(uint32_t)__popc(m.x), (uint32_t)__popc(m.y), (uint32_t)__popc(m.z), (uint32_t)__popc(m.w)};
-  uint32_t idx[4], code[4];
-  uint32_t rest = col, others = 0;
+  Column c = decode_column(hdrs, ch, lane);
+  if (!c.valid) return;
+  // The launch's diagonal fixes the code in F; the cell exists if that code is one of the
+  // Spec's breakpoints there.
+  const uint32_t mF = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
+  const int cfs = (int)diag - (int)c.others;
+  if (cfs < 0 || cfs > 31 || !((mF >> cfs) & 1u)) return;
+  const uint32_t iF = __popc(mF & ((1u << cfs) - 1u));
 #pragma unroll
-  for (int k = 0; k < 4; k++) {
-    if (k == F) continue;
-    idx[k] = rest % nn[k];
-    rest /= nn[k];
-    code[k] = nth_set_bit(mm[k], idx[k]);
-    others += code[k];
-  }
-  if (rest != 0) return;  // column index beyond this Spec's grid
-  const int cfs = (int)diag - (int)others;
-  if (cfs < 0 || cfs > 31 || !((mm[F] >> cfs) & 1u)) return;
-  code[F] = (uint32_t)cfs;
-  idx[F] = __popc(mm[F] & ((1u << cfs) - 1u));
-  const uint32_t cpack = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
-  // "slots at or below this cell's limit", per memory: what a child lookup at the same limits needs
-  const uint32_t bm0 = (2u << code[0]) - 1u, bm1 = (2u << code[1]) - 1u, bm2 = (2u << code[2]) - 1u,
-                 bm3 = (2u << code[3]) - 1u;
-
-  // The cell's limits as lattice codes: in a compressed memory slot cap+1 stands for the top code.
-  uint32_t lvpack = 0;
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    const uint32_t capk = code_of(cap_pack, k);
-    lvpack |= ((code[k] == capk + 1u) ? code_of(top_pack, k) : code[k]) << (8 * k);
-  }
+  for (int k = 0; k < 4; k++)
+    if ((uint32_t)k == c.F) { c.code[k] = (uint32_t)cfs; c.idx[k] = iF; }
+  const uint32_t cpack = c.code[0] | (c.code[1] << 8) | (c.code[2] << 16) | (c.code[3] << 24);
+  // "codes at or below this cell's limit", per memory: what a child lookup at the same limits needs
+  const uint32_t bm0 = (2u << c.code[0]) - 1u, bm1 = (2u << c.code[1]) - 1u, bm2 = (2u << c.code[2]) - 1u,
+                 bm3 = (2u << c.code[3]) - 1u;
 
   const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ch.spec].row_base));
   const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[ch.spec].cand_off));
   const uint32_t cand_off = cl.x, ncand = cl.y;
 
   Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-  for (uint32_t ci = sub; ci < ncand; ci += G) {
+  for (uint32_t ci = 0; ci < ncand; ci++) {
     const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]));
     const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
     const uint32_t imm = a.y;
     const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, pcode = (a.z >> 16) & 0xFFu;
     const uint32_t units = a.w;
-    // The cell's limit in `level` as a lattice code. In a compressed memory the grid keeps the
-    // codes 0..cap and, as slot cap+1, the top code.
-    const uint32_t lv = code_of(lvpack, level);
+    const uint32_t lv = code_of(cpack, level);  // the cell's limit in `level`
     Key k;
     if (kind == MRL_CK_LEAF) {
       if (lv < thr) continue;
@@ -174,9 +198,7 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
         uint32_t ccode;
         if (level < 2) ccode = lv - units;                      // registers: exact
         else ccode = 32 - __clz(cache_value(lv) - units);       // caches: snap down to 2^k
-        // The child's limit is below the top; codes above the cap read the cap slot (nothing
-        // changes between cap and top while no optimal peak exceeds the cap).
-        const uint32_t cb = (2u << min(ccode, code_of(cap_pack, level))) - 1u;
+        const uint32_t cb = (2u << ccode) - 1u;
         c0 = (level == 0) ? cb : c0;
         c1 = (level == 1) ? cb : c1;
         c2 = (level == 2) ? cb : c2;
@@ -184,21 +206,21 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
       }
 #ifdef MRL_CHECK_CHILD_IDS
       if (b.x >= n_specs || (nchild > 1 && b.y >= n_specs) || (nchild > 2 && b.z >= n_specs)) {
-        atomicExch(error_flag, 1);
+        atomicExch(error_flag, 1u);
         continue;
       }
 #endif
       // Children one at a time: a child without an implementation, or a partial sum that already
       // exceeds the best main cost, ends the candidate before the remaining rows are fetched.
-      const uint4 r0 = lookup(hdrs, rows, b.x, c0, c1, c2, c3);
+      const uint4 r0 = lookup(hdrs, rows, temp, b.x, c0, c1, c2, c3);
       if (r0.z == MRL_UNSAT) continue;
       uint4 r1 = r0, r2 = r0;
       if (nchild > 1) {
         if (kind == MRL_CK_MOVE && sat_add(imm, r0.x) > best.main) continue;
-        r1 = lookup(hdrs, rows, b.y, c0, c1, c2, c3);
+        r1 = lookup(hdrs, rows, temp, b.y, c0, c1, c2, c3);
         if (r1.z == MRL_UNSAT) continue;
         if (nchild > 2) {
-          r2 = lookup(hdrs, rows, b.z, c0, c1, c2, c3);
+          r2 = lookup(hdrs, rows, temp, b.z, c0, c1, c2, c3);
           if (r2.z == MRL_UNSAT) continue;
         }
       }
@@ -229,88 +251,363 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     }
     if (key_less(k, best)) best = k;
   }
-  if (G > 1) {
-    // The G lanes of this cell are all here (a cell is active or not as a whole).
-    const unsigned gmask = (G == 32) ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+  const uint32_t off = ((c.idx[3] * c.nn[2] + c.idx[2]) * c.nn[1] + c.idx[1]) * c.nn[0] + c.idx[0];
+  // Specs of the stage being solved always live in the working buffer.
+  *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + off) = make_uint4(best.main, best.peaks, best.tail, 0u);
+}
+
+// ---- working grids ---------------------------------------------------------------------
+
+struct Grid {   // what a Spec's masks imply
+  uint32_t nn[4];
+  unsigned long long cells;
+  uint32_t F, cols, warps;
+};
+__device__ __forceinline__ Grid grid_of(const uint4 m) {
+  Grid g;
+  g.nn[0] = __popc(m.x); g.nn[1] = __popc(m.y); g.nn[2] = __popc(m.z); g.nn[3] = __popc(m.w);
+  g.cells = (unsigned long long)g.nn[0] * g.nn[1] * g.nn[2] * g.nn[3];
+  // The free memory is the one with the most slots (lowest index on ties): a column then has
+  // a cell on as many diagonals as possible.
+  g.F = 0;
+  uint32_t best = g.nn[0];
 #pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) {
-      Key other;
-      other.main = __shfl_xor_sync(gmask, best.main, o);
-      other.peaks = __shfl_xor_sync(gmask, best.peaks, o);
-      other.tail = __shfl_xor_sync(gmask, best.tail, o);
-      if (key_less(other, best)) best = other;
+  for (int k = 1; k < 4; k++)
+    if (g.nn[k] > best) { best = g.nn[k]; g.F = k; }
+  g.cols = (uint32_t)(g.cells / best);
+  g.warps = (g.cols + 31u) / 32u;
+  return g;
+}
+
+__device__ __forceinline__ void or_level(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t level,
+                                         uint32_t bits) {
+  r0 |= (level == 0) ? bits : 0u;
+  r1 |= (level == 1) ? bits : 0u;
+  r2 |= (level == 2) ? bits : 0u;
+  r3 |= (level == 3) ? bits : 0u;
+}
+
+// Where a child's breakpoints in the destination memory of a Move show up in the parent: the
+// child sees limit - units (registers) or that snapped down to a power of two (caches), so a
+// child breakpoint at code b becomes the smallest parent code whose child code reaches b.
+__device__ __forceinline__ uint32_t shift_mask(uint32_t cm, uint32_t level, uint32_t units, uint32_t top) {
+  const uint32_t keep = (2u << top) - 1u;   // top <= 30
+  if (level < 2) return units >= 32 ? 0u : (uint32_t)(((unsigned long long)cm << units) & keep);
+  uint32_t out = 0;
+  while (cm) {
+    const uint32_t b = __ffs(cm) - 1;
+    cm &= cm - 1;
+    const unsigned long long v = (unsigned long long)cache_value(b) + units;
+    if (v > 0x40000000ull) continue;
+    const uint32_t code = cache_code_ceil((uint32_t)v);
+    if (code <= top) out |= 1u << code;
+  }
+  return out;
+}
+
+// Pass step 1: per Spec of the stage, the masks its working grid needs. `first`: same-stage
+// children are ignored (nothing is known about them yet); later passes add the breakpoints the
+// previous pass found in them (rmask). Also totals what a solve under the new masks takes.
+__global__ void __launch_bounds__(128)
+derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, const uint4* __restrict__ rmask,
+                    const uint8_t* __restrict__ mine, uint32_t lo, uint32_t hi, int first, uint32_t top_pack,
+                    PassCounters* __restrict__ ctr) {
+  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
+  const bool active = i < hi && (!mine || mine[i]);
+  unsigned long long cells = 0, warps = 0, bytes = 0;
+  uint32_t d0 = 0, d1 = 0, d2 = 0, d3 = 0, changed = 0;
+  if (active) {
+    const uint4 old = *reinterpret_cast<const uint4*>(&hdrs[i]);
+    const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
+    uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
+    for (uint32_t ci = 0; ci < cl.y; ci++) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+      const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+      const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, units = a.w;
+      if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
+      if (kind == MRL_CK_LEAF) continue;
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
+      for (uint32_t j = 0; j < nchild; j++) {
+        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+        uint4 cm;
+        if (child < lo) cm = *reinterpret_cast<const uint4*>(&hdrs[child]);   // finished stage: final masks
+        else if (first) continue;
+        else cm = rmask[child];
+        if (kind == MRL_CK_MOVE) {
+          const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(top_pack, level));
+          r0 |= (level == 0) ? s : cm.x;
+          r1 |= (level == 1) ? s : cm.y;
+          r2 |= (level == 2) ? s : cm.z;
+          r3 |= (level == 3) ? s : cm.w;
+        } else {
+          r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
+        }
+      }
     }
-    if (sub != 0) return;
+    uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
+    changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
+    if (changed) *reinterpret_cast<uint4*>(&hdrs[i]) = nm;
+    const Grid g = grid_of(nm);
+    cells = g.cells;
+    warps = g.warps;
+    // occupied diagonals: the sum set of the four masks, as a 128-bit set
+    unsigned long long slo = 1, shi = 0;
+    const uint32_t mk[4] = {nm.x, nm.y, nm.z, nm.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      unsigned long long nlo = 0, nhi = 0;
+      uint32_t mbits = mk[k];
+      while (mbits) {
+        const uint32_t bpos = __ffs(mbits) - 1;
+        mbits &= mbits - 1;
+        nlo |= slo << bpos;
+        nhi |= (shi << bpos) | (bpos ? (slo >> (64 - bpos)) : 0ull);
+      }
+      slo = nlo; shi = nhi;
+    }
+    d0 = (uint32_t)slo; d1 = (uint32_t)(slo >> 32); d2 = (uint32_t)shi; d3 = (uint32_t)(shi >> 32);
+    // algorithmic bytes of one solve: a 12-byte row out; per candidate a 16-byte header; per
+    // child of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in
+    bytes = cells * 12ull;
+    for (uint32_t ci = 0; ci < cl.y; ci++) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+      const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+      const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu;
+      bytes += cells * 16ull;
+      if (nchild) {
+        unsigned long long feasible = cells;
+        if (kind == MRL_CK_MOVE) {
+          const uint32_t ml = sel4(nm.x, nm.y, nm.z, nm.w, level);
+          feasible = cells / (uint32_t)__popc(ml) * (uint32_t)__popc(ml >> thr);
+        }
+        bytes += feasible * nchild * 16ull;
+      }
+    }
   }
-  const uint32_t off = ((idx[3] * nn[2] + idx[2]) * nn[1] + idx[1]) * nn[0] + idx[0];
-  *reinterpret_cast<uint4*>(rows + base + off) = make_uint4(best.main, best.peaks, best.tail, 0u);
+  // warp totals, then one atomic per warp and counter
+  for (int o = 16; o > 0; o >>= 1) {
+    cells += __shfl_xor_sync(0xFFFFFFFFu, cells, o);
+    warps += __shfl_xor_sync(0xFFFFFFFFu, warps, o);
+    bytes += __shfl_xor_sync(0xFFFFFFFFu, bytes, o);
+  }
+  d0 = __reduce_or_sync(0xFFFFFFFFu, d0);
+  d1 = __reduce_or_sync(0xFFFFFFFFu, d1);
+  d2 = __reduce_or_sync(0xFFFFFFFFu, d2);
+  d3 = __reduce_or_sync(0xFFFFFFFFu, d3);
+  changed = __reduce_or_sync(0xFFFFFFFFu, changed);
+  if ((threadIdx.x & 31) == 0 && cells) {
+    atomicAdd(&ctr->cells, cells);
+    atomicAdd(&ctr->warps, warps);
+    atomicAdd(&ctr->alg_bytes, bytes);
+    if (d0) atomicOr(&ctr->diag_bits[0], d0);
+    if (d1) atomicOr(&ctr->diag_bits[1], d1);
+    if (d2) atomicOr(&ctr->diag_bits[2], d2);
+    if (d3) atomicOr(&ctr->diag_bits[3], d3);
+    if (changed) atomicOr(&ctr->changed, 1u);
+  }
 }
 
-// Largest peak code per memory over all satisfiable rows (checks the lattice compression).
-__global__ void max_peaks_kernel(const MrlRow* __restrict__ rows, unsigned long long n, uint32_t* __restrict__ out4) {
-  uint32_t mx = 0;
-  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (unsigned long long)gridDim.x * blockDim.x) {
-    const uint4 r = __ldg(reinterpret_cast<const uint4*>(rows + i));
-    if (r.z != MRL_UNSAT) mx = __vmaxu4(mx, r.y);
+// Exclusive prefix of v over the block (blockDim.x == 256); *total = the block's sum.
+__device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long v, unsigned long long* total) {
+  __shared__ unsigned long long warp_sum[8];
+  __shared__ unsigned long long block_total;
+  const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  unsigned long long inc = v;
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= (uint32_t)o) inc += t;
   }
-  for (int o = 16; o > 0; o >>= 1) mx = __vmaxu4(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-  if ((threadIdx.x & 31) == 0) {
-    atomicMax(&out4[0], (mx >> 24) & 0xFFu);
-    atomicMax(&out4[1], (mx >> 16) & 0xFFu);
-    atomicMax(&out4[2], (mx >> 8) & 0xFFu);
-    atomicMax(&out4[3], mx & 0xFFu);
+  __syncthreads();   // protects the shared arrays across consecutive calls
+  if (lane == 31) warp_sum[w] = inc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long run = 0;
+    for (int k = 0; k < 8; k++) { const unsigned long long t = warp_sum[k]; warp_sum[k] = run; run += t; }
+    block_total = run;
+  }
+  __syncthreads();
+  *total = block_total;
+  return warp_sum[w] + inc - v;
+}
+
+// Pass step 2: gives every Spec of the stage its working rows (in the temp buffer) and its
+// chunks, and resets its real-breakpoint masks.
+__global__ void __launch_bounds__(256)
+place_kernel(SpecHdr* __restrict__ hdrs, uint4* __restrict__ rmask, const uint8_t* __restrict__ mine, uint32_t lo,
+             uint32_t hi, unsigned long long temp_cap, Chunk* __restrict__ chunks, unsigned long long chunk_cap,
+             PassCounters* __restrict__ ctr) {
+  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
+  const bool active = i < hi && (!mine || mine[i]);
+  Grid g;
+  g.cells = 0; g.warps = 0; g.F = 0;
+  if (active) g = grid_of(*reinterpret_cast<const uint4*>(&hdrs[i]));
+  unsigned long long tot_cells, tot_warps;
+  const unsigned long long my_row = block_excl_scan(g.cells, &tot_cells);
+  const unsigned long long my_chunk = block_excl_scan(active ? g.warps : 0ull, &tot_warps);
+  __shared__ unsigned long long row0, chunk0;
+  if (threadIdx.x == 0) {
+    row0 = atomicAdd(&ctr->temp_rows, tot_cells);
+    chunk0 = atomicAdd(&ctr->n_chunks, (uint32_t)tot_warps);
+  }
+  __syncthreads();
+  if (!active) return;
+  const unsigned long long rb = row0 + my_row;
+  const unsigned long long cb = chunk0 + my_chunk;
+  if (rb + g.cells > temp_cap || cb + g.warps > chunk_cap) { atomicOr(&ctr->error, 2u); return; }
+  hdrs[i].row_base = rb | MRL_TEMP_FLAG;
+  rmask[i] = make_uint4(1u, 1u, 1u, 1u);
+  for (uint32_t w = 0; w < g.warps; w++) {
+    Chunk c;
+    c.spec = i;
+    c.col_start = (w * 32u) | (g.F << 30);
+    chunks[cb + w] = c;
   }
 }
 
-// Expands the per-Spec warp counts into the chunk list the combine kernel walks.
-__global__ void expand_chunks_kernel(const uint32_t* __restrict__ warp_prefix, uint32_t n_specs,
-                                     uint32_t cols_per_warp, Chunk* __restrict__ chunks) {
-  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_specs) return;
-  const uint32_t lo = warp_prefix[i], hi = warp_prefix[i + 1];
-  for (uint32_t w = lo; w < hi; w++) {
-    chunks[w].spec = i;
-    chunks[w].col_start = (w - lo) * cols_per_warp;
+// Pass step 4: which breakpoints of the working grids are real. A breakpoint (memory k, code c)
+// is real when some cell starting at c differs from its neighbour one slot lower in k.
+__global__ void __launch_bounds__(128)
+real_masks_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
+                  const MrlRow* __restrict__ temp, uint4* __restrict__ rmask) {
+  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (warp >= n_chunks) return;   // whole warps leave together
+  const Chunk ch = chunks[warp];
+  const Column c = decode_column(hdrs, ch, lane);
+  uint32_t bits[4] = {0, 0, 0, 0};
+  if (c.valid) {
+    const unsigned long long base = hdrs[ch.spec].row_base & ~MRL_TEMP_FLAG;
+    const uint32_t st[4] = {1u, c.nn[0], c.nn[0] * c.nn[1], c.nn[0] * c.nn[1] * c.nn[2]};
+    const uint32_t mF = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
+    const uint32_t nF = sel4(c.nn[0], c.nn[1], c.nn[2], c.nn[3], c.F);
+    const uint32_t stF = sel4(st[0], st[1], st[2], st[3], c.F);
+    uint32_t off0 = 0;
+#pragma unroll
+    for (int k = 0; k < 4; k++) off0 += c.idx[k] * st[k];   // idx[F] is 0
+    uint4 prev = make_uint4(0, 0, 0, 0);
+    uint32_t fbits = 0, mrest = mF;
+    for (uint32_t s = 0; s < nF; s++) {
+      const uint32_t codeF = __ffs(mrest) - 1;
+      mrest &= mrest - 1;
+      const unsigned long long r_at = base + off0 + (unsigned long long)s * stF;
+      const uint4 r = *reinterpret_cast<const uint4*>(temp + r_at);
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        if ((uint32_t)k == c.F || c.idx[k] == 0) continue;
+        const uint4 nb = *reinterpret_cast<const uint4*>(temp + r_at - st[k]);
+        if (nb.x != r.x || nb.y != r.y || nb.z != r.z) bits[k] |= 1u << c.code[k];
+      }
+      if (s > 0 && (prev.x != r.x || prev.y != r.y || prev.z != r.z)) fbits |= 1u << codeF;
+      prev = r;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+      if ((uint32_t)k == c.F) bits[k] = fbits;
+  }
+#pragma unroll
+  for (int k = 0; k < 4; k++) bits[k] = __reduce_or_sync(0xFFFFFFFFu, bits[k]);
+  if (lane == 0) {
+    uint32_t* out = reinterpret_cast<uint32_t*>(&rmask[ch.spec]);
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+      if (bits[k]) atomicOr(out + k, bits[k]);
   }
 }
 
-// Point lookups for get: copies the rows at the given indices into a dense buffer.
-__global__ void gather_rows_kernel(const MrlRow* __restrict__ rows, const unsigned long long* __restrict__ idx,
-                                   unsigned long long n, MrlRow* __restrict__ out) {
-  unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+// ---- compaction: working grids -> final table ---------------------------------------------
+
+// Final cell count per Spec of the stage and the sum per block of 256 Specs.
+__global__ void __launch_bounds__(256)
+final_count_kernel(const uint4* __restrict__ rmask, uint32_t lo, uint32_t hi, uint32_t* __restrict__ fcount,
+                   unsigned long long* __restrict__ block_sums) {
+  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned long long n = 0;
+  if (i < hi) {
+    const uint4 m = rmask[i];
+    n = (unsigned long long)__popc(m.x) * __popc(m.y) * __popc(m.z) * __popc(m.w);
+    fcount[i - lo] = (uint32_t)n;
+  }
+  unsigned long long total;
+  block_excl_scan(n, &total);
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+}
+
+// Exclusive scan of the block sums (one block), and the stage's place in the table:
+// stage_info[0] = first final row of the stage, stage_info[1] = its row count.
+__global__ void __launch_bounds__(256)
+scan_block_sums_kernel(unsigned long long* __restrict__ block_sums, uint32_t n_blocks,
+                       unsigned long long* __restrict__ final_top, unsigned long long* __restrict__ stage_info) {
+  unsigned long long carry = 0;
+  for (uint32_t b0 = 0; b0 < n_blocks; b0 += 256) {
+    const uint32_t b = b0 + threadIdx.x;
+    const unsigned long long v = b < n_blocks ? block_sums[b] : 0ull;
+    unsigned long long total;
+    const unsigned long long ex = block_excl_scan(v, &total);
+    if (b < n_blocks) block_sums[b] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0) {
+    stage_info[0] = *final_top;
+    stage_info[1] = carry;
+    *final_top += carry;
+  }
+}
+
+// Copies each Spec's real cells from its working grid to its final rows and repoints the header.
+// Specs computed by another rank get zero rows (the exchange adds the owner's rows onto them).
+__global__ void __launch_bounds__(256)
+compact_kernel(SpecHdr* __restrict__ hdrs, const uint4* __restrict__ rmask, const uint8_t* __restrict__ mine,
+               uint32_t lo, uint32_t hi, const uint32_t* __restrict__ fcount,
+               const unsigned long long* __restrict__ block_sums, const unsigned long long* __restrict__ stage_info,
+               MrlRow* __restrict__ rows, unsigned long long row_cap, const MrlRow* __restrict__ temp,
+               PassCounters* __restrict__ ctr) {
+  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned long long n = i < hi ? fcount[i - lo] : 0u;
+  unsigned long long total;
+  const unsigned long long ex = block_excl_scan(n, &total);
+  if (i >= hi) return;
+  const unsigned long long fbase = stage_info[0] + block_sums[blockIdx.x] + ex;
+  if (fbase + n > row_cap) { atomicOr(&ctr->error, 4u); return; }
+  const uint4 fm = rmask[i];
+  if (!mine || mine[i]) {
+    const uint4 tm = *reinterpret_cast<const uint4*>(&hdrs[i]);
+    const unsigned long long tbase = hdrs[i].row_base & ~MRL_TEMP_FLAG;
+    const uint32_t f0 = __popc(fm.x), f1 = __popc(fm.y), f2 = __popc(fm.z);
+    const uint32_t t0 = __popc(tm.x), t1 = __popc(tm.y), t2 = __popc(tm.z);
+    for (uint32_t j = 0; j < (uint32_t)n; j++) {
+      uint32_t rest = j;
+      const uint32_t j0 = rest % f0; rest /= f0;
+      const uint32_t j1 = rest % f1; rest /= f1;
+      const uint32_t j2 = rest % f2; rest /= f2;
+      const uint32_t j3 = rest;
+      const uint32_t i0 = __popc(tm.x & ((2u << nth_set_bit(fm.x, j0)) - 1u)) - 1;
+      const uint32_t i1 = __popc(tm.y & ((2u << nth_set_bit(fm.y, j1)) - 1u)) - 1;
+      const uint32_t i2 = __popc(tm.z & ((2u << nth_set_bit(fm.z, j2)) - 1u)) - 1;
+      const uint32_t i3 = __popc(tm.w & ((2u << nth_set_bit(fm.w, j3)) - 1u)) - 1;
+      const uint32_t toff = ((i3 * t2 + i2) * t1 + i1) * t0 + i0;
+      *reinterpret_cast<uint4*>(rows + fbase + j) = *reinterpret_cast<const uint4*>(temp + tbase + toff);
+    }
+  } else {
+    for (uint32_t j = 0; j < (uint32_t)n; j++) *reinterpret_cast<uint4*>(rows + fbase + j) = make_uint4(0, 0, 0, 0);
+  }
+  *reinterpret_cast<uint4*>(&hdrs[i]) = fm;
+  hdrs[i].row_base = fbase;
+}
+
+// Point lookups for get: the row of (Spec id, packed limit codes), into a dense buffer.
+__global__ void lookup_rows_kernel(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
+                                   const uint2* __restrict__ queries, unsigned long long n, MrlRow* __restrict__ out) {
+  const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(rows + idx[i]);
+  const uint2 q = queries[i];
+  const uint4 r = lookup(hdrs, rows, rows, q.x, (2u << code_of(q.y, 0)) - 1u, (2u << code_of(q.y, 1)) - 1u,
+                         (2u << code_of(q.y, 2)) - 1u, (2u << code_of(q.y, 3)) - 1u);
+  *reinterpret_cast<uint4*>(out + i) = r;
 }
 
 }  // namespace
 
 namespace mrl {
-
-// One (group, diagonal) launch.
-static void launch_combine(int lanes, int free_dim, uint32_t blocks, cudaStream_t stream, const SpecHdr* hdrs,
-                           const CandRec* cands, const Chunk* chunks, uint32_t n_chunks, uint32_t diag, MrlRow* rows,
-                           uint32_t n_specs, uint32_t cap_pack, uint32_t top_pack, int* err) {
-#define MRL_LAUNCH(G, F)                                                                                         \
-  combine_argmin_kernel<G, F><<<blocks, 128, 0, stream>>>(hdrs, cands, chunks, n_chunks, diag, rows, n_specs,    \
-                                                          cap_pack, top_pack, err)
-  if (lanes == 2) {
-    switch (free_dim) {
-      case 0: MRL_LAUNCH(2, 0); break;
-      case 1: MRL_LAUNCH(2, 1); break;
-      case 2: MRL_LAUNCH(2, 2); break;
-      default: MRL_LAUNCH(2, 3); break;
-    }
-  } else {
-    switch (free_dim) {
-      case 0: MRL_LAUNCH(1, 0); break;
-      case 1: MRL_LAUNCH(1, 1); break;
-      case 2: MRL_LAUNCH(1, 2); break;
-      default: MRL_LAUNCH(1, 3); break;
-    }
-  }
-#undef MRL_LAUNCH
-}
 
 #define CK(x)                                                                              \
   do {                                                                                     \
@@ -321,17 +618,44 @@ static void launch_combine(int lanes, int free_dim, uint32_t blocks, cudaStream_
     }                                                                                      \
   } while (0)
 
+static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
 DeviceFill::~DeviceFill() { release(); }
 
+int DeviceFill::alloc_(void** p, size_t bytes) {
+  bytes = std::max<size_t>(bytes, 256);
+  if (fixed_) {
+    const size_t off = align256(buf_off_);
+    if (off + bytes > buf_bytes_) {
+      snprintf(err_, sizeof(err_),
+               "this fill needs more than the %zu bytes of device memory the no-allocation entry point has; "
+               "use mrl_top_down_many for it", buf_bytes_);
+      return -4;
+    }
+    *p = buf_ + off;
+    buf_off_ = off + bytes;
+    return 0;
+  }
+  CK(cudaMalloc(p, bytes));
+  return 0;
+}
+
+void DeviceFill::free_(void* p) {
+  if (p && !fixed_) cudaFree(p);
+}
+
 void DeviceFill::release() {
-  if (d_hdrs_) cudaFree(d_hdrs_);
-  if (d_cands_) cudaFree(d_cands_);
-  if (d_chunks_) cudaFree(d_chunks_);
-  if (d_rows_) cudaFree(d_rows_);
-  if (d_err_) cudaFree(d_err_);
-  if (d_peaks_) cudaFree(d_peaks_);
-  d_peaks_ = nullptr;
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_chunks_ = nullptr; d_rows_ = nullptr; d_err_ = nullptr;
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
+  d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
+  d_stage_ = nullptr;
+  stage_bytes_ = 0;
+  row_cap_ = temp_cap_ = chunk_cap_ = 0;
+  buf_off_ = 0;
+  if (h_ctr_) { cudaFreeHost(h_ctr_); h_ctr_ = nullptr; }
+  for (cudaEvent_t e : ev_pool_) cudaEventDestroy(e);
+  ev_pool_.clear();
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
   ev0_ = ev1_ = nullptr;
@@ -347,69 +671,23 @@ int DeviceFill::init(int device) {
     CK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     own_stream_ = true;
   }
+  return init_events();
+}
+
+int DeviceFill::init_events() {
   if (!ev0_) CK(cudaEventCreate(&ev0_));
   if (!ev1_) CK(cudaEventCreate(&ev1_));
   return 0;
 }
 
-int DeviceFill::upload(const Plan& plan) {
-  CK(cudaSetDevice(device_));
-  if (d_hdrs_) { cudaFree(d_hdrs_); d_hdrs_ = nullptr; }
-  if (d_cands_) { cudaFree(d_cands_); d_cands_ = nullptr; }
-  if (d_chunks_) { cudaFree(d_chunks_); d_chunks_ = nullptr; }
-  if (d_rows_) { cudaFree(d_rows_); d_rows_ = nullptr; }
-  if (!d_err_) CK(cudaMalloc(&d_err_, sizeof(int)));
-  n_specs_ = (uint32_t)plan.hdrs.size();
-  n_rows_ = plan.stats.n_rows;
-  const size_t n_warps = plan.warp_prefix.empty() ? 0 : plan.warp_prefix.back();
-  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) +
-               plan.warp_prefix.size() * sizeof(uint32_t);
-  uint32_t* d_prefix = nullptr;
-  CK(cudaMalloc(&d_hdrs_, std::max<size_t>(plan.hdrs.size(), 1) * sizeof(SpecHdr)));
-  CK(cudaMalloc(&d_cands_, std::max<size_t>(plan.cands.size(), 1) * sizeof(CandRec)));
-  CK(cudaMalloc(&d_chunks_, std::max<size_t>(n_warps, 1) * sizeof(Chunk)));
-  CK(cudaMalloc(&d_rows_, std::max<uint64_t>(n_rows_, 1) * sizeof(MrlRow)));
-  CK(cudaMalloc(&d_prefix, std::max<size_t>(plan.warp_prefix.size(), 1) * sizeof(uint32_t)));
-  CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
-  CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), plan.cands.size() * sizeof(CandRec), cudaMemcpyHostToDevice, stream_));
-  CK(cudaMemcpyAsync(d_prefix, plan.warp_prefix.data(), plan.warp_prefix.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
-  if (n_specs_) expand_chunks_kernel<<<(n_specs_ + 127) / 128, 128, 0, stream_>>>(d_prefix, n_specs_, 32u / plan.lanes_per_cell, d_chunks_);
-  CK(cudaGetLastError());
-  CK(cudaMemsetAsync(d_err_, 0, sizeof(int), stream_));
-  CK(cudaStreamSynchronize(stream_));
-  cudaFree(d_prefix);
-  CK(cudaStreamSynchronize(stream_));
-  return 0;
-}
-
-int DeviceFill::run(const Plan& plan, float* ms_out, uint64_t* launches_out) {
-  CK(cudaSetDevice(device_));
-  // No clearing pass: every cell lies on exactly one (group, diagonal) step and is written
-  // there, and no cell is read before its step.
-  CK(cudaEventRecord(ev0_, stream_));
-  uint64_t launches = 0;
-  for (const Step& st : plan.steps) {
-    const Group& g = plan.groups[st.group];
-    const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
-    const uint32_t blocks = (n_chunks + 3) / 4;
-    launch_combine(plan.lanes_per_cell, g.free_dim, blocks, stream_, d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, st.diag,
-                   d_rows_, n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
-    launches++;
-  }
-  CK(cudaGetLastError());
-  CK(cudaEventRecord(ev1_, stream_));
-  CK(cudaStreamSynchronize(stream_));
-  float ms = 0;
-  CK(cudaEventElapsedTime(&ms, ev0_, ev1_));
-  int flag = 0;
-  CK(cudaMemcpy(&flag, d_err_, sizeof(int), cudaMemcpyDeviceToHost));
-  if (flag) {
-    snprintf(err_, sizeof(err_), "combine kernel reported a bad child index");
-    return -2;
-  }
-  if (ms_out) *ms_out = ms;
-  if (launches_out) *launches_out = launches;
-  return 0;
+void DeviceFill::attach_buffer(void* base, size_t bytes, cudaStream_t stream, int device) {
+  fixed_ = true;
+  buf_ = static_cast<unsigned char*>(base);
+  buf_bytes_ = bytes;
+  buf_off_ = 0;
+  stream_ = stream;
+  own_stream_ = false;
+  device_ = device;
 }
 
 int DeviceFill::set_stream(cudaStream_t s) {
@@ -419,90 +697,355 @@ int DeviceFill::set_stream(cudaStream_t s) {
   return 0;
 }
 
+int DeviceFill::upload(const Plan& plan) {
+  CK(cudaSetDevice(device_));
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
+  d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
+  d_stage_ = nullptr;
+  stage_bytes_ = 0;
+  buf_off_ = 0;
+  n_specs_ = (uint32_t)plan.hdrs.size();
+  uint32_t max_stage = 1;
+  for (const Stage& st : plan.stages) max_stage = std::max(max_stage, st.spec_hi - st.spec_lo);
+  int rc;
+  if ((rc = alloc_((void**)&d_ctr_, 256))) return rc;
+  d_final_top_ = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(d_ctr_) + 64);
+  d_stage_info_ = d_final_top_ + 1;
+  if ((rc = alloc_((void**)&d_hdrs_, plan.hdrs.size() * sizeof(SpecHdr)))) return rc;
+  if ((rc = alloc_((void**)&d_cands_, plan.cands.size() * sizeof(CandRec)))) return rc;
+  if ((rc = alloc_((void**)&d_rmask_, plan.hdrs.size() * sizeof(uint4)))) return rc;
+  if (!plan.mine.empty() && (rc = alloc_((void**)&d_mine_, plan.mine.size()))) return rc;
+  if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage * sizeof(uint32_t)))) return rc;
+  if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage / 256 + 1) * sizeof(unsigned long long)))) return rc;
+  if (fixed_) {
+    // Everything left is split once: lookup staging, chunks, working rows and final rows.
+    stage_bytes_ = 64 << 10;
+    if ((rc = alloc_(&d_stage_, stage_bytes_))) return rc;
+    const size_t left = buf_bytes_ > align256(buf_off_) + 1024 ? buf_bytes_ - align256(buf_off_) - 1024 : 0;
+    chunk_cap_ = left / 16 / sizeof(Chunk);
+    temp_cap_ = left / 2 / sizeof(MrlRow);
+    row_cap_ = (left - left / 16 - left / 2) / sizeof(MrlRow);
+    if (chunk_cap_ == 0 || row_cap_ == 0) {
+      snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
+               "entry point has; use mrl_top_down_many for it", buf_bytes_);
+      return -4;
+    }
+    if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
+    if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
+    if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
+  } else {
+    chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)n_specs_ * 2);
+    temp_cap_ = std::max<uint64_t>(1u << 20, (uint64_t)max_stage * 64);
+    row_cap_ = std::max<uint64_t>(1u << 20, (uint64_t)n_specs_ * 16);
+    if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
+    if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
+    if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
+    if (!h_ctr_) CK(cudaHostAlloc((void**)&h_ctr_, 256, cudaHostAllocDefault));
+  }
+  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) + plan.mine.size();
+  CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
+  if (!plan.hdrs.empty())
+    CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
+  if (!plan.cands.empty())
+    CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), plan.cands.size() * sizeof(CandRec), cudaMemcpyHostToDevice, stream_));
+  if (d_mine_) CK(cudaMemcpyAsync(d_mine_, plan.mine.data(), plan.mine.size(), cudaMemcpyHostToDevice, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  stats_ = FillStats();
+  final_bound_ = 0;
+  return 0;
+}
+
+int DeviceFill::read_counters_(PassCounters* out) {
+  if (h_ctr_) {
+    CK(cudaMemcpyAsync(h_ctr_, d_ctr_, sizeof(PassCounters) + 24, cudaMemcpyDeviceToHost, stream_));
+    CK(cudaStreamSynchronize(stream_));
+    *out = *h_ctr_;
+    final_top_seen_ = reinterpret_cast<const unsigned long long*>(h_ctr_ + 1)[0];
+    stage_info_seen_[0] = reinterpret_cast<const unsigned long long*>(h_ctr_ + 1)[1];
+    stage_info_seen_[1] = reinterpret_cast<const unsigned long long*>(h_ctr_ + 1)[2];
+  } else {
+    unsigned char tmp[sizeof(PassCounters) + 24];
+    CK(cudaMemcpyAsync(tmp, d_ctr_, sizeof(tmp), cudaMemcpyDeviceToHost, stream_));
+    CK(cudaStreamSynchronize(stream_));
+    memcpy(out, tmp, sizeof(PassCounters));
+    unsigned long long v[3];
+    memcpy(v, tmp + sizeof(PassCounters), 24);
+    final_top_seen_ = v[0];
+    stage_info_seen_[0] = v[1];
+    stage_info_seen_[1] = v[2];
+  }
+  return 0;
+}
+
+// Makes room for `need` final rows; the rows placed so far move along.
+int DeviceFill::ensure_rows_(uint64_t need, bool refresh) {
+  if (need <= row_cap_) return 0;
+  if (refresh) {
+    // The bound on the rows placed so far may be loose: use the exact count before growing.
+    PassCounters c;
+    if (read_counters_(&c) != 0) return -1;
+    need = need - final_bound_ + final_top_seen_;
+    final_bound_ = final_top_seen_;
+    if (need <= row_cap_) return 0;
+  }
+  if (fixed_) {
+    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
+             "entry point has; use mrl_top_down_many for it", buf_bytes_);
+    return -4;
+  }
+  size_t free_b = 0, total_b = 0;
+  CK(cudaMemGetInfo(&free_b, &total_b));
+  uint64_t cap = std::max<uint64_t>(need, row_cap_ * 2);
+  if (cap * sizeof(MrlRow) + (1ull << 30) > free_b) cap = need;
+  if (cap * sizeof(MrlRow) + (256ull << 20) > free_b) {
+    snprintf(err_, sizeof(err_), "out of device memory: the table needs %llu rows", (unsigned long long)need);
+    return -6;
+  }
+  MrlRow* nr = nullptr;
+  CK(cudaMalloc((void**)&nr, cap * sizeof(MrlRow)));
+  if (final_bound_) CK(cudaMemcpyAsync(nr, d_rows_, final_bound_ * sizeof(MrlRow), cudaMemcpyDeviceToDevice, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  cudaFree(d_rows_);
+  d_rows_ = nr;
+  row_cap_ = cap;
+  return 0;
+}
+
+int DeviceFill::ensure_temp_(uint64_t need) {
+  if (need <= temp_cap_) return 0;
+  if (fixed_) {
+    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
+             "entry point has; use mrl_top_down_many for it", buf_bytes_);
+    return -4;
+  }
+  CK(cudaStreamSynchronize(stream_));
+  cudaFree(d_temp_);
+  d_temp_ = nullptr;
+  temp_cap_ = 0;
+  const uint64_t cap = need + need / 4;
+  CK(cudaMalloc((void**)&d_temp_, cap * sizeof(MrlRow)));
+  temp_cap_ = cap;
+  return 0;
+}
+
+int DeviceFill::ensure_chunks_(uint64_t need) {
+  if (need <= chunk_cap_) return 0;
+  if (need > 0xFFFFFFF0ull) { snprintf(err_, sizeof(err_), "stage too large: %llu chunks", (unsigned long long)need); return -6; }
+  if (fixed_) {
+    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
+             "entry point has; use mrl_top_down_many for it", buf_bytes_);
+    return -4;
+  }
+  CK(cudaStreamSynchronize(stream_));
+  cudaFree(d_chunks_);
+  d_chunks_ = nullptr;
+  chunk_cap_ = 0;
+  const uint64_t cap = need + need / 4;
+  CK(cudaMalloc((void**)&d_chunks_, cap * sizeof(Chunk)));
+  chunk_cap_ = cap;
+  return 0;
+}
+
 int DeviceFill::begin_fill() {
   CK(cudaSetDevice(device_));
+  stats_ = FillStats();
+  final_bound_ = 0;
+  ev_used_ = 0;
+  CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
   CK(cudaEventRecord(ev0_, stream_));
-  launches_ = 0;
+  filling_ = true;
   return 0;
 }
 
-// Enqueues every diagonal of one group (this rank's chunks only); does not synchronise.
-int DeviceFill::run_group(const Plan& plan, uint32_t gi) {
-  if (gi >= plan.groups.size()) { snprintf(err_, sizeof(err_), "group index out of range"); return -3; }
-  const Group& g = plan.groups[gi];
-  const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
-  if (n_chunks == 0) return 0;
-  const uint32_t blocks = (n_chunks + 3) / 4;
-  for (uint32_t d = 0; d <= g.max_diag; d++) {
-    launch_combine(plan.lanes_per_cell, g.free_dim, blocks, stream_, d_hdrs_, d_cands_, d_chunks_ + g.chunk_lo, n_chunks, d, d_rows_,
-                   n_specs_, plan.cap_pack(), plan.top_pack(), d_err_);
-    launches_++;
+// Solves one stage: passes of (derive masks, place, one combine launch per occupied diagonal,
+// find real breakpoints) until no working grid lacks a breakpoint of a same-stage child.
+int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
+  if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
+  const Stage& st = plan.stages[si];
+  const uint32_t lo = st.spec_lo, hi = st.spec_hi, n = hi - lo;
+  last_cells_ = 0;
+  if (n == 0) return 0;
+  if (d_mine_) CK(cudaMemsetAsync(d_rmask_ + lo, 0, (size_t)n * sizeof(uint4), stream_));
+  const uint32_t top_pack = plan.top_pack();
+  for (int pass = 0;; pass++) {
+    if (pass >= 128) { snprintf(err_, sizeof(err_), "stage %u did not reach a consistent limits grid", si); return -2; }
+    CK(cudaMemsetAsync(d_ctr_, 0, offsetof(PassCounters, error), stream_));   // the error word is sticky
+    derive_masks_kernel<<<(n + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, lo, hi, pass == 0,
+                                                              top_pack, d_ctr_);
+    stats_.launches++;
+    PassCounters c;
+    if (read_counters_(&c) != 0) return -1;
+    if (c.error) {
+      snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u (1: bad child index, 2: working "
+               "buffers too small, 4: row arena too small)", c.error, si);
+      return -2;
+    }
+    if (pass > 0 && !c.changed) break;
+    if (c.cells == 0) break;   // nothing of this stage is computed by this rank
+    int rc;
+    if ((rc = ensure_chunks_(c.warps))) return rc;
+    if ((rc = ensure_temp_(c.cells))) return rc;
+    place_kernel<<<(n + 255) / 256, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, lo, hi, temp_cap_, d_chunks_,
+                                                       chunk_cap_, d_ctr_);
+    const uint32_t n_chunks = (uint32_t)c.warps;
+    const uint32_t blocks = (n_chunks + 3) / 4;
+    if (ev_used_ + 2 > ev_pool_.size()) {
+      for (int k = 0; k < 64; k++) {
+        cudaEvent_t e;
+        CK(cudaEventCreate(&e));
+        ev_pool_.push_back(e);
+      }
+    }
+    CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
+    for (uint32_t d = 0; d < 128; d++) {
+      if (!((c.diag_bits[d >> 5] >> (d & 31)) & 1u)) continue;
+      combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_, n_chunks, d, d_rows_, d_temp_,
+                                                         n_specs_, &d_ctr_->error);
+      stats_.combine_launches++;
+    }
+    CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
+    real_masks_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_temp_, d_rmask_);
+    CK(cudaGetLastError());
+    stats_.launches += 2;
+    stats_.passes++;
+    stats_.cells_solved += c.cells;
+    stats_.alg_bytes += c.alg_bytes;
+    last_cells_ = c.cells;
   }
-  CK(cudaGetLastError());
   return 0;
 }
 
-int DeviceFill::end_fill(float* ms_out, uint64_t* launches_out) {
+int DeviceFill::stage_masks(const Plan& plan, uint32_t si, void** ptr, uint64_t* bytes) {
+  if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
+  const Stage& st = plan.stages[si];
+  if (ptr) *ptr = d_rmask_ + st.spec_lo;
+  if (bytes) *bytes = (uint64_t)(st.spec_hi - st.spec_lo) * sizeof(uint4);
+  return 0;
+}
+
+// Appends the stage's compacted grids to the table. With rows_ptr: also reports where they
+// went (the slice other ranks need), which costs one synchronisation.
+int DeviceFill::place_stage(const Plan& plan, uint32_t si, void** rows_ptr, uint64_t* bytes) {
+  if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
+  const Stage& st = plan.stages[si];
+  const uint32_t lo = st.spec_lo, hi = st.spec_hi, n = hi - lo;
+  if (rows_ptr) *rows_ptr = d_rows_;
+  if (bytes) *bytes = 0;
+  if (n == 0) return 0;
+  const uint32_t nb = (n + 255) / 256;
+  int rc;
+  const bool exact = d_mine_ || rows_ptr;
+  if (!exact) {
+    // final cells <= working cells of the last pass: room for that many is enough
+    if ((rc = ensure_rows_(final_bound_ + last_cells_, true))) return rc;
+    final_bound_ += last_cells_;
+  }
+  final_count_kernel<<<nb, 256, 0, stream_>>>(d_rmask_, lo, hi, d_fcount_, d_block_sums_);
+  scan_block_sums_kernel<<<1, 256, 0, stream_>>>(d_block_sums_, nb, d_final_top_, d_stage_info_);
+  stats_.launches += 2;
+  if (exact) {
+    // other ranks' Specs count too: ask the device how many rows the stage takes
+    PassCounters c;
+    if (read_counters_(&c) != 0) return -1;
+    final_bound_ = stage_info_seen_[0];   // rows to keep if the arena has to grow
+    if ((rc = ensure_rows_(final_bound_ + stage_info_seen_[1], false))) return rc;
+    final_bound_ += stage_info_seen_[1];
+  }
+  compact_kernel<<<nb, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, lo, hi, d_fcount_, d_block_sums_, d_stage_info_,
+                                          d_rows_, row_cap_, d_temp_, d_ctr_);
+  CK(cudaGetLastError());
+  stats_.launches++;
+  if (rows_ptr) {
+    *rows_ptr = d_rows_ + stage_info_seen_[0];
+    if (bytes) *bytes = stage_info_seen_[1] * sizeof(MrlRow);
+  }
+  return 0;
+}
+
+int DeviceFill::end_fill() {
   CK(cudaEventRecord(ev1_, stream_));
-  CK(cudaStreamSynchronize(stream_));
-  float ms = 0;
-  CK(cudaEventElapsedTime(&ms, ev0_, ev1_));
-  int flag = 0;
-  CK(cudaMemcpy(&flag, d_err_, sizeof(int), cudaMemcpyDeviceToHost));
-  if (flag) {
-    snprintf(err_, sizeof(err_), "combine kernel reported a bad child index");
+  PassCounters c;
+  if (read_counters_(&c) != 0) return -1;
+  filling_ = false;
+  CK(cudaEventElapsedTime(&stats_.fill_ms, ev0_, ev1_));
+  float cms = 0;
+  for (size_t k = 0; k + 1 < ev_used_; k += 2) {
+    float t = 0;
+    CK(cudaEventElapsedTime(&t, ev_pool_[k], ev_pool_[k + 1]));
+    cms += t;
+  }
+  stats_.combine_ms = cms;
+  stats_.launches += stats_.combine_launches;
+  stats_.n_rows = final_top_seen_;
+  final_bound_ = final_top_seen_;
+  if (c.error) {
+    snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x (1: bad child index, 2: working buffers too small, "
+             "4: row arena too small)", c.error);
     return -2;
   }
-  if (ms_out) *ms_out = ms;
-  if (launches_out) *launches_out = launches_;
   return 0;
 }
 
-int DeviceFill::max_peaks(uint32_t out[4]) {
-  CK(cudaSetDevice(device_));
-  if (!d_peaks_) CK(cudaMalloc(&d_peaks_, 4 * sizeof(uint32_t)));
-  CK(cudaMemsetAsync(d_peaks_, 0, 4 * sizeof(uint32_t), stream_));
-  if (n_rows_) max_peaks_kernel<<<148 * 8, 256, 0, stream_>>>(d_rows_, n_rows_, d_peaks_);
-  CK(cudaGetLastError());
-  CK(cudaMemcpyAsync(out, d_peaks_, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_));
-  CK(cudaStreamSynchronize(stream_));
-  return 0;
+int DeviceFill::run(const Plan& plan) {
+  int rc;
+  if ((rc = begin_fill())) return rc;
+  for (uint32_t s = 0; s < plan.stages.size(); s++) {
+    if ((rc = solve_stage(plan, s))) return rc;
+    if ((rc = place_stage(plan, s, nullptr, nullptr))) return rc;
+  }
+  return end_fill();
 }
 
-int DeviceFill::read_rows(const uint64_t* row_idx, size_t n, MrlRow* out) {
+int DeviceFill::lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t n, MrlRow* out) {
   CK(cudaSetDevice(device_));
   if (n == 0) return 0;
   for (size_t i = 0; i < n; i++)
-    if (row_idx[i] >= n_rows_) { snprintf(err_, sizeof(err_), "row index out of range"); return -3; }
-  unsigned long long* d_idx = nullptr;
-  MrlRow* d_out = nullptr;
-  CK(cudaMalloc(&d_idx, n * sizeof(unsigned long long)));
-  if (cudaMalloc(&d_out, n * sizeof(MrlRow)) != cudaSuccess) {
-    cudaFree(d_idx);
-    snprintf(err_, sizeof(err_), "cudaMalloc failed in read_rows");
-    return -1;
+    if (spec_ids[i] >= n_specs_) { snprintf(err_, sizeof(err_), "Spec id out of range"); return -3; }
+  const size_t per = sizeof(uint2) + sizeof(MrlRow);
+  size_t batch = n;
+  if (fixed_) batch = std::min(n, stage_bytes_ / 2 / per);
+  else if (stage_bytes_ < 2 * align256(n * sizeof(MrlRow))) {
+    CK(cudaStreamSynchronize(stream_));
+    if (d_stage_) cudaFree(d_stage_);
+    d_stage_ = nullptr;
+    stage_bytes_ = 0;
+    CK(cudaMalloc(&d_stage_, 2 * align256(n * sizeof(MrlRow))));
+    stage_bytes_ = 2 * align256(n * sizeof(MrlRow));
   }
-  cudaError_t e = cudaMemcpyAsync(d_idx, row_idx, n * sizeof(unsigned long long), cudaMemcpyHostToDevice, stream_);
-  if (e == cudaSuccess) {
-    gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream_>>>(d_rows_, d_idx, n, d_out);
-    e = cudaGetLastError();
+  if (batch == 0) { snprintf(err_, sizeof(err_), "lookup staging too small"); return -4; }
+  std::vector<uint2> q(batch);
+  for (size_t done = 0; done < n; done += batch) {
+    const size_t m = std::min(batch, n - done);
+    for (size_t i = 0; i < m; i++) q[i] = make_uint2(spec_ids[done + i], cpacks[done + i]);
+    uint2* d_q = static_cast<uint2*>(d_stage_);
+    MrlRow* d_out = reinterpret_cast<MrlRow*>(static_cast<unsigned char*>(d_stage_) + stage_bytes_ / 2);
+    CK(cudaMemcpyAsync(d_q, q.data(), m * sizeof(uint2), cudaMemcpyHostToDevice, stream_));
+    lookup_rows_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream_>>>(d_hdrs_, d_rows_, d_q, m, d_out);
+    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(out + done, d_out, m * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
+    CK(cudaStreamSynchronize(stream_));
   }
-  if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, n * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
-  cudaFree(d_idx);
-  cudaFree(d_out);
-  if (e != cudaSuccess) { snprintf(err_, sizeof(err_), "read_rows failed: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
 
-int DeviceFill::download(std::vector<MrlRow>& out) {
+int DeviceFill::read_hdr(uint32_t spec, SpecHdr* out) {
   CK(cudaSetDevice(device_));
-  out.resize(n_rows_);
-  CK(cudaMemcpyAsync(out.data(), d_rows_, n_rows_ * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
+  if (spec >= n_specs_) { snprintf(err_, sizeof(err_), "Spec id out of range"); return -3; }
+  CK(cudaMemcpyAsync(out, d_hdrs_ + spec, sizeof(SpecHdr), cudaMemcpyDeviceToHost, stream_));
   CK(cudaStreamSynchronize(stream_));
   return 0;
 }
 
+int DeviceFill::read_rows(uint64_t first, uint64_t n, MrlRow* out) {
+  CK(cudaSetDevice(device_));
+  if (first + n > stats_.n_rows) { snprintf(err_, sizeof(err_), "row range out of the table"); return -3; }
+  if (n == 0) return 0;
+  CK(cudaMemcpyAsync(out, d_rows_ + first, n * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  return 0;
+}
 
 // ---------------------------------------------------------------------------------------
 // Fill without device allocation.
@@ -511,23 +1054,19 @@ int DeviceFill::download(std::vector<MrlRow>& out) {
 // reserved all of HBM for its replicated tables at start-up has nothing left to hand out, and
 // a worker pool that calls top_down_many from many threads would be serialised by the
 // device-wide synchronisation every cudaMalloc / cudaFree implies. For them the whole device
-// working set of one small fill - plan arrays, row table, lookup staging - is carved out of
-// the fixed array below instead of being allocated per call. Every GPU that loads this
-// library holds the array until the process exits.
+// working set of one small fill - plan arrays, working buffers, row table, lookup staging - is
+// carved out of the fixed array below instead of being allocated per call. Every GPU that
+// loads this library holds the array until the process exits.
 //
 // In host code `g_static_scratch` is only a stand-in for the device array, not a device
 // address; the address a kernel may use comes from cudaGetSymbolAddress, asked once per
 // device with that device current (static_scratch_address).
 namespace {
 __device__ __align__(256) unsigned char g_static_scratch[MRL_STATIC_SCRATCH_BYTES];
-}
 
-namespace {
 constexpr int kMaxDevices = 64;
 void* g_scratch_addr[kMaxDevices] = {nullptr};
 std::mutex g_scratch_mu;
-
-size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 // Device address of the static array on `device`, resolved on first use.
 cudaError_t static_scratch_address(int device, void** out) {
@@ -546,80 +1085,26 @@ cudaError_t static_scratch_address(int device, void** out) {
 }
 }  // namespace
 
-// Runs `plan` entirely inside the static array and copies the rows at `row_idx` to `out`
-// (host). No cudaMalloc / cudaFree. Returns -4 with a message when the plan does not fit.
-int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint64_t* row_idx, size_t n,
-                MrlRow* out, char* err, size_t err_len) {
-#define CKS(x)                                                                        \
-  do {                                                                                \
-    cudaError_t e_ = (x);                                                             \
-    if (e_ != cudaSuccess) {                                                          \
-      snprintf(err, err_len, "%s failed: %s", #x, cudaGetErrorString(e_));            \
-      return -1;                                                                      \
-    }                                                                                 \
-  } while (0)
-  const size_t hdr_b = plan.hdrs.size() * sizeof(SpecHdr);
-  const size_t cand_b = plan.cands.size() * sizeof(CandRec);
-  const size_t n_warps = plan.warp_prefix.empty() ? 0 : plan.warp_prefix.back();
-  const size_t chunk_b = n_warps * sizeof(Chunk);
-  const size_t prefix_b = plan.warp_prefix.size() * sizeof(uint32_t);
-  const size_t row_b = (size_t)plan.stats.n_rows * sizeof(MrlRow);
-  const size_t idx_b = n * sizeof(unsigned long long);
-  const size_t out_b = n * sizeof(MrlRow);
-  size_t off = 256;  // first 256 bytes: the error flag
-  const size_t o_hdr = off; off = align256(off + hdr_b);
-  const size_t o_cand = off; off = align256(off + cand_b);
-  const size_t o_chunk = off; off = align256(off + chunk_b);
-  const size_t o_prefix = off; off = align256(off + prefix_b);
-  const size_t o_rows = off; off = align256(off + row_b);
-  const size_t o_idx = off; off = align256(off + idx_b);
-  const size_t o_out = off; off = align256(off + out_b);
-  if (off > (size_t)MRL_STATIC_SCRATCH_BYTES) {
-    snprintf(err, err_len,
-             "this fill needs %zu bytes of device memory but the no-allocation entry point has a fixed %zu; "
-             "use mrl_top_down_many for it", off, (size_t)MRL_STATIC_SCRATCH_BYTES);
-    return -4;
+// Runs `plan` entirely inside the static array and copies the rows of the given (Spec id,
+// packed limit codes) queries to `out` (host). No cudaMalloc / cudaFree. Returns -4 with a
+// message when the fill does not fit.
+int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint32_t* spec_ids, const uint32_t* cpacks,
+                size_t n, MrlRow* out, char* err, size_t err_len) {
+  void* base = nullptr;
+  cudaError_t e = static_scratch_address(device, &base);
+  if (e == cudaSuccess) e = cudaSetDevice(device);
+  if (e != cudaSuccess) {
+    snprintf(err, err_len, "static scratch unavailable: %s", cudaGetErrorString(e));
+    return -1;
   }
-  for (size_t i = 0; i < n; i++)
-    if (row_idx[i] >= plan.stats.n_rows) { snprintf(err, err_len, "row index out of range"); return -3; }
-
-  void* base_v = nullptr;
-  CKS(static_scratch_address(device, &base_v));
-  CKS(cudaSetDevice(device));
-  unsigned char* base = static_cast<unsigned char*>(base_v);
-  int* d_err = reinterpret_cast<int*>(base);
-  SpecHdr* d_hdrs = reinterpret_cast<SpecHdr*>(base + o_hdr);
-  CandRec* d_cands = reinterpret_cast<CandRec*>(base + o_cand);
-  Chunk* d_chunks = reinterpret_cast<Chunk*>(base + o_chunk);
-  uint32_t* d_prefix = reinterpret_cast<uint32_t*>(base + o_prefix);
-  MrlRow* d_rows = reinterpret_cast<MrlRow*>(base + o_rows);
-  unsigned long long* d_idx = reinterpret_cast<unsigned long long*>(base + o_idx);
-  MrlRow* d_out = reinterpret_cast<MrlRow*>(base + o_out);
-
-  // The array keeps whatever the previous call left. Only the error flag has to start at
-  // zero; every table cell is written by its own step before anything reads it.
-  CKS(cudaMemsetAsync(d_err, 0, 256, stream));
-  if (hdr_b) CKS(cudaMemcpyAsync(d_hdrs, plan.hdrs.data(), hdr_b, cudaMemcpyHostToDevice, stream));
-  if (cand_b) CKS(cudaMemcpyAsync(d_cands, plan.cands.data(), cand_b, cudaMemcpyHostToDevice, stream));
-  if (prefix_b) CKS(cudaMemcpyAsync(d_prefix, plan.warp_prefix.data(), prefix_b, cudaMemcpyHostToDevice, stream));
-  if (idx_b) CKS(cudaMemcpyAsync(d_idx, row_idx, idx_b, cudaMemcpyHostToDevice, stream));
-  const uint32_t n_specs = (uint32_t)plan.hdrs.size();
-  if (n_specs) expand_chunks_kernel<<<(n_specs + 127) / 128, 128, 0, stream>>>(d_prefix, n_specs, 32u / plan.lanes_per_cell, d_chunks);
-  for (const Step& st : plan.steps) {
-    const Group& g = plan.groups[st.group];
-    const uint32_t n_chunks = g.chunk_hi - g.chunk_lo;
-    launch_combine(plan.lanes_per_cell, g.free_dim, (n_chunks + 3) / 4, stream, d_hdrs, d_cands, d_chunks + g.chunk_lo, n_chunks,
-                   st.diag, d_rows, n_specs, plan.cap_pack(), plan.top_pack(), d_err);
-  }
-  if (n) gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(d_rows, d_idx, n, d_out);
-  CKS(cudaGetLastError());
-  int flag = 0;
-  if (out_b) CKS(cudaMemcpyAsync(out, d_out, out_b, cudaMemcpyDeviceToHost, stream));
-  CKS(cudaMemcpyAsync(&flag, d_err, sizeof(int), cudaMemcpyDeviceToHost, stream));
-  CKS(cudaStreamSynchronize(stream));
-  if (flag) { snprintf(err, err_len, "combine kernel reported a bad child index"); return -2; }
-  return 0;
-#undef CKS
+  DeviceFill f;
+  f.attach_buffer(base, (size_t)MRL_STATIC_SCRATCH_BYTES, stream, device);
+  int rc = f.init_events();
+  if (rc == 0) rc = f.upload(plan);
+  if (rc == 0) rc = f.run(plan);
+  if (rc == 0) rc = f.lookup(spec_ids, cpacks, n, out);
+  if (rc != 0) snprintf(err, err_len, "%s", f.error());
+  return rc;
 }
 
 }  // namespace mrl

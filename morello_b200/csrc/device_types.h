@@ -23,6 +23,8 @@ struct MrlRow {
 // Per logical Spec: breakpoint masks of its limits grid (bit c set = code c starts a new
 // cell; bit 0 always set), the first row of its dense cell block and its candidates.
 // Cell (i0,i1,i2,i3) has row ((i3*n2 + i2)*n1 + i1)*n0 + i0 with n_k = popcount(mask[k]).
+// While a stage is being solved its Specs point at a working grid in the scratch end of the
+// row arena; once the stage is consistent they point at the compacted final grid.
 struct SpecHdr {
   uint32_t mask[4];
   uint64_t row_base;
@@ -48,15 +50,30 @@ struct CandRec {
   uint32_t pad1;
 };
 
-// A warp-sized slice of one Spec's "columns": cells with the slot of one memory (the group's
-// free memory) left open; the column index runs over the other three memories, lowest first.
+// A warp-sized slice of one Spec's "columns": cells with the slot of one memory (the Spec's
+// free memory F, the one with the most slots) left open; the column index runs over the other
+// three memories, lowest first. col_start = first column | F << 30.
 struct Chunk {
   uint32_t spec;
   uint32_t col_start;
+};
+
+// Counters one solve pass of a stage leaves for the host (zeroed before every pass).
+struct PassCounters {
+  uint32_t changed;             // some Spec's working grid gained a breakpoint
+  uint32_t n_chunks;            // chunk cursor (place kernel)
+  unsigned long long cells;     // working cells of the stage under the current masks
+  unsigned long long warps;     // chunks those cells need
+  unsigned long long temp_rows; // row cursor (place kernel)
+  unsigned long long alg_bytes; // algorithmic bytes of one solve of those cells
+  uint32_t diag_bits[4];        // occupied limits diagonals (bit d of the 128-bit set)
+  uint32_t error;               // bad child index / capacity overrun seen by a kernel
+  uint32_t pad;
 };
 
 #ifdef __cplusplus
 static_assert(sizeof(MrlRow) == 16, "row slot is 16 bytes");
 static_assert(sizeof(SpecHdr) == 32, "spec header is 32 bytes");
 static_assert(sizeof(CandRec) == 32, "candidate record is 32 bytes");
+static_assert(sizeof(PassCounters) == 64, "pass counters are 64 bytes");
 #endif

@@ -63,6 +63,22 @@ u32 shape_log_sum(const LogicalSpec& ls) {
   return s;
 }
 
+// Third component of the stage order. Moves to a faster memory lower the sum of the operands'
+// memory indices, and the prologue / epilogue Moves of a Matmul or Fill lie in an earlier phase.
+// Inside the Move phase they do not: Move(GL -> L1) relayouts its source through
+// Move(GL -> GL), whose own destination moves lead back to Move(GL -> L1). There only the
+// slowest memory a Spec touches never grows along an action, so it orders the stages.
+u32 level_rank(const LogicalSpec& ls) {
+  u32 s = 0, mx = 0;
+  for (int i = 0; i < ls.nops(); i++) {
+    s += (u32)ls.aux[i].mem;
+    mx = std::max(mx, (u32)ls.aux[i].mem);
+  }
+  return ls.kind == K_MOVE ? mx : s;
+}
+
+u32 stage_key(const LogicalSpec& ls) { return ((u32)ls.kind << 16) | (shape_log_sum(ls) << 8) | level_rank(ls); }
+
 // Smallest limit code whose value is >= units, and the code of the peak `units` itself
 // leaves behind (registers: raw; caches: rounded to a power of two,
 // morello/src/memorylimits.rs:159-170,458-470).
@@ -98,33 +114,25 @@ long Plan::find(const LogicalSpec& ls) const {
   return it->second;
 }
 
-long Plan::row_of(u32 id, const u64 limits[NMEM]) const {
-  const SpecHdr& h = hdrs[id];
-  u64 idx = 0, stride = 1;
+bool Plan::pack_limits(const u64 limits[NMEM], u32* out) const {
+  u32 pack = 0;
   for (int k = 0; k < NMEM; k++) {
+    if (!mem_counts_registers((Mem)k) && limits[k] != 0 && !is_pow2(limits[k])) return false;
     u32 code = limit_code(k, limits[k]);
-    if (code > top_code[k]) return -1;  // beyond the limits this table was filled for
-    code = slot_of_code(k, code);
-    u32 below = h.mask[k] & (code >= 31 ? 0xFFFFFFFFu : ((2u << code) - 1u));
-    u32 i = (u32)__builtin_popcount(below) - 1;
-    idx += stride * i;
-    stride *= (u32)__builtin_popcount(h.mask[k]);
+    if (code > top_code[k]) return false;  // beyond the limits this table was filled for
+    pack |= code << (8 * k);
   }
-  return (long)(h.row_base + idx);
+  *out = pack;
+  return true;
 }
 
-Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, const int* caps,
-                u32 rank, u32 world) {
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, u32 rank, u32 world) {
   if (n_threads < 1) n_threads = 1;
   if (world < 1 || rank >= world) throw ModelError("bad shard rank / world size");
   Plan plan;
   plan.rank = rank;
   plan.world = world;
   plan.n_threads = n_threads;
-  if (const char* e = getenv("MRL_LANES_PER_CELL")) {
-    int v = atoi(e);
-    if (v == 1 || v == 2) plan.lanes_per_cell = v;
-  }
   u32 top_code[NMEM];
   for (int k = 0; k < NMEM; k++) {
     u64 v = top_limits ? top_limits[k] : AVX2_MAX_MEM[k];
@@ -132,7 +140,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     top_code[k] = limit_code(k, v);
     if (top_code[k] > 30) throw ModelError("memory limit too large for the lattice masks");
     plan.top_code[k] = top_code[k];
-    plan.cap_code[k] = (caps && caps[k] >= 0 && (u32)caps[k] < top_code[k]) ? (u32)caps[k] : top_code[k];
   }
 
   // ---- 1. discovery: closure of the goals under "is a sub-Spec of some candidate" ----
@@ -219,12 +226,12 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   const u32 n = (u32)temp.size();
   plan.stats.seconds_discover = now_s() - t0;
 
-  // ---- 2. final ids: group-major (phase, log-shape sum), then key order ----
+  // ---- 2. final ids: stage-major (phase, log-shape sum, memory-level sum), then key order ----
   double t1 = now_s();
   std::vector<u32> order(n);
   for (u32 i = 0; i < n; i++) order[i] = i;
   std::vector<u32> gkey(n);
-  for (u32 i = 0; i < n; i++) gkey[i] = ((u32)temp[i].ls.kind << 8) | shape_log_sum(temp[i].ls);
+  for (u32 i = 0; i < n; i++) gkey[i] = stage_key(temp[i].ls);
   std::sort(order.begin(), order.end(), [&](u32 a, u32 b) {
     if (gkey[a] != gkey[b]) return gkey[a] < gkey[b];
     return temp[a].key < temp[b].key;
@@ -279,232 +286,97 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   std::sort(plan.sorted_keys_.begin(), plan.sorted_keys_.end());
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort keys %.2fs\n", now_s() - t1);
 
-  // groups
+  // stages, and inside them families: maximal runs with equal dtype and shape (ids are
+  // key-sorted, and the key starts with kind, dtype, serial flag, rank, shape)
   for (u32 i = 0; i < n;) {
-    u32 gk = ((u32)plan.specs[i].kind << 8) | shape_log_sum(plan.specs[i]);
+    const u32 sk = stage_key(plan.specs[i]);
     u32 j = i;
-    while (j < n && ((((u32)plan.specs[j].kind << 8) | shape_log_sum(plan.specs[j])) == gk)) j++;
-    Group g;
-    g.spec_lo = i;
-    g.spec_hi = j;
-    g.phase = (u8)(gk >> 8);
-    g.shape_sum = (u8)(gk & 0xff);
-    plan.groups.push_back(g);
+    while (j < n && stage_key(plan.specs[j]) == sk) j++;
+    Stage st;
+    st.spec_lo = i;
+    st.spec_hi = j;
+    st.phase = (u8)(sk >> 16);
+    st.shape_sum = (u8)((sk >> 8) & 0xff);
+    st.level_rank = (u8)(sk & 0xff);
+    st.fam_lo = (u32)plan.families.size();
+    for (u32 a = i; a < j;) {
+      u32 b = a;
+      u64 w = 0;
+      while (b < j && plan.specs[b].dtype == plan.specs[a].dtype && plan.specs[b].spec_shape == plan.specs[a].spec_shape) {
+        w += plan.hdrs[b].ncand + 1;
+        b++;
+      }
+      Family f;
+      f.spec_lo = a;
+      f.spec_hi = b;
+      f.stage = (u32)plan.stages.size();
+      f.weight = w;
+      plan.families.push_back(f);
+      a = b;
+    }
+    st.fam_hi = (u32)plan.families.size();
+    plan.stages.push_back(st);
     i = j;
   }
-  // families: maximal runs with equal dtype and shape inside a group (ids are key-sorted, and
-  // the key starts with kind, dtype, serial flag, rank, shape)
-  for (u32 gi = 0; gi < plan.groups.size(); gi++) {
-    const Group& g = plan.groups[gi];
-    for (u32 i = g.spec_lo; i < g.spec_hi;) {
-      u32 j = i;
-      while (j < g.spec_hi && plan.specs[j].dtype == plan.specs[i].dtype && plan.specs[j].spec_shape == plan.specs[i].spec_shape) j++;
-      Family f;
-      f.spec_lo = i;
-      f.spec_hi = j;
-      f.group = gi;
-      plan.families.push_back(f);
-      i = j;
-    }
-  }
-  plan.stats.seconds_layout = now_s() - t1;
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/groups/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 
-  plan.stats.n_specs = n;
-  plan.stats.n_cands = ncand;
-  relayout_plan(plan, caps);
-  return plan;
-}
-
-void relayout_plan(Plan& plan, const int* caps) {
-  const u32 n = (u32)plan.hdrs.size();
-  const u32* top_code = plan.top_code;
-  const int n_threads = plan.n_threads;
-  for (int k = 0; k < NMEM; k++)
-    plan.cap_code[k] = (caps && caps[k] >= 0 && (u32)caps[k] < top_code[k]) ? (u32)caps[k] : top_code[k];
-  plan.steps.clear();
-  plan.stats.mask_sweeps = 0;
-
-  // ---- 3. breakpoint masks: least fixpoint of "a parent's result can change wherever one
-  //         of its candidates becomes feasible or one of its children's results changes" ----
-  double t2 = now_s();
-  for (u32 i = 0; i < n; i++) for (int k = 0; k < NMEM; k++) plan.hdrs[i].mask[k] = 1u;
-  // Masks live in slot space (Plan::cap_code). A threshold at limit code t sets slot_ceil(t).
-  // A Move lowers its children's limit in the destination memory, so their code there is always
-  // below the top: only the child's slots 0..cap (real codes) feed the parent's thresholds.
-  u32 real_slots[NMEM];   // mask of slots that are plain codes (0..cap, or 0..top when not compressed)
-  for (int k = 0; k < NMEM; k++) {
-    u32 hi = plan.compressed(k) ? plan.cap_code[k] : top_code[k];
-    real_slots[k] = (hi >= 31) ? 0xFFFFFFFFu : ((2u << hi) - 1u);
-  }
-  // Sweeps run on all threads over disjoint Spec ranges; a thread may read a mask another thread
-  // is growing (relaxed atomics). Masks only ever gain bits, so any interleaving reaches the
-  // same least fixpoint; the loop ends after a sweep in which nothing changed.
-  std::atomic<bool> changed{true};
-  while (changed.load()) {
-    changed = false;
-    plan.stats.mask_sweeps++;
+  // The order the device relies on: a child never lies in a later stage; a child inside its
+  // parent's stage belongs to a Move that consumes memory (so it sits at strictly lower limits)
+  // and to the parent's family.
+  {
+    std::vector<u32> stage_of(n), fam_of(n);
+    for (u32 si = 0; si < plan.stages.size(); si++)
+      for (u32 i = plan.stages[si].spec_lo; i < plan.stages[si].spec_hi; i++) stage_of[i] = si;
+    for (u32 fi = 0; fi < plan.families.size(); fi++)
+      for (u32 i = plan.families[fi].spec_lo; i < plan.families[fi].spec_hi; i++) fam_of[i] = fi;
+    std::atomic<int> bad{0};
+    std::atomic<u64> bad_pair{0};
     parallel_for(n, n_threads, [&](size_t i, int) {
-      SpecHdr& h = plan.hdrs[i];
-      u32 m[NMEM];
-      for (int k = 0; k < NMEM; k++) m[k] = __atomic_load_n(&h.mask[k], __ATOMIC_RELAXED);
-      const u32 m0[NMEM] = {m[0], m[1], m[2], m[3]};
+      const SpecHdr& h = plan.hdrs[i];
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
-        if (r.kind == MRL_CK_LEAF) {
-          m[r.level] |= 1u << plan.slot_ceil(r.level, r.thr_code);
-          continue;
-        }
         for (int j = 0; j < r.nchild; j++) {
-          const SpecHdr& ch = plan.hdrs[r.child[j]];
-          for (int k = 0; k < NMEM; k++) {
-            u32 cmask = __atomic_load_n(&ch.mask[k], __ATOMIC_RELAXED);
-            if (r.kind != MRL_CK_MOVE || k != r.level) { m[k] |= cmask; continue; }
-            u32 cm = cmask & real_slots[k];
-            if (mem_counts_registers((Mem)k)) {
-              // registers: every child breakpoint b becomes b + units
-              u32 hi_code = plan.compressed(k) ? plan.cap_code[k] : top_code[k];
-              u64 shifted = (r.units >= 32) ? 0 : ((u64)cm << r.units);
-              u64 keep = (hi_code >= 63) ? ~0ull : ((2ull << hi_code) - 1ull);
-              m[k] |= (u32)(shifted & keep);
-              u64 top_keep = (top_code[k] >= 63) ? ~0ull : ((2ull << top_code[k]) - 1ull);
-              if (plan.compressed(k) && (shifted & ~keep & top_keep)) m[k] |= 1u << (plan.cap_code[k] + 1);
-              continue;
-            }
-            while (cm) {
-              u32 b = (u32)__builtin_ctz(cm);
-              cm &= cm - 1;
-              u32 code = bit_length(next_binary_power(bit_length_inverse(b) + r.units));
-              if (code <= top_code[k]) m[k] |= 1u << plan.slot_ceil(k, code);
-            }
+          const u32 ch = r.child[j];
+          if (stage_of[ch] > stage_of[i]) { bad = 1; bad_pair = ((u64)i << 32) | ch; }
+          if (stage_of[ch] == stage_of[i] && (r.kind != MRL_CK_MOVE || r.units == 0 || fam_of[ch] != fam_of[i])) {
+            bad = 2;
+            bad_pair = ((u64)i << 32) | ch;
           }
         }
       }
-      bool ch_any = false;
-      for (int k = 0; k < NMEM; k++)
-        if (m[k] != m0[k]) { __atomic_fetch_or(&h.mask[k], m[k], __ATOMIC_RELAXED); ch_any = true; }
-      if (ch_any) changed = true;
     });
+    const std::string who = bad.load() ? (": parent " + plan.specs[bad_pair.load() >> 32].str() + ", child " +
+                                          plan.specs[bad_pair.load() & 0xFFFFFFFFu].str()) : std::string();
+    if (bad.load() == 1) throw ModelError("planner: a child Spec lies in a later stage than its parent" + who);
+    if (bad.load() == 2) throw ModelError("planner: a same-stage child is not below its parent in the limits lattice" + who);
   }
-  plan.stats.seconds_masks = now_s() - t2;
 
-  // ---- 4. rows, owners, warps, schedule, byte accounting ----
-  double t3 = now_s();
-  u64 row = 0;
-  for (u32 i = 0; i < n; i++) {
-    SpecHdr& h = plan.hdrs[i];
-    u64 ncells = 1;
-    for (int k = 0; k < NMEM; k++) ncells *= (u64)__builtin_popcount(h.mask[k]);
-    h.row_base = row;
-    row += ncells;
-  }
-  // Owners: per group, heaviest family first onto the least loaded rank.
-  for (Family& f : plan.families) {
-    f.row_lo = plan.hdrs[f.spec_lo].row_base;
-    f.row_hi = (f.spec_hi < n) ? plan.hdrs[f.spec_hi].row_base : row;
-    f.owner = 0;
-  }
+  // Owners: per stage, heaviest family first onto the least loaded rank.
   if (plan.world > 1) {
-    size_t fi = 0;
-    for (u32 gi = 0; gi < plan.groups.size(); gi++) {
+    plan.mine.assign(n, 0);
+    for (const Stage& st : plan.stages) {
       std::vector<u32> fam;
-      while (fi < plan.families.size() && plan.families[fi].group == gi) fam.push_back((u32)fi++);
-      std::stable_sort(fam.begin(), fam.end(), [&](u32 a, u32 b) {
-        return plan.families[a].row_hi - plan.families[a].row_lo > plan.families[b].row_hi - plan.families[b].row_lo;
-      });
+      for (u32 f = st.fam_lo; f < st.fam_hi; f++) fam.push_back(f);
+      std::stable_sort(fam.begin(), fam.end(), [&](u32 a, u32 b) { return plan.families[a].weight > plan.families[b].weight; });
       std::vector<u64> load(plan.world, 0);
       for (u32 f : fam) {
         u32 best = 0;
         for (u32 r = 1; r < plan.world; r++) if (load[r] < load[best]) best = r;
         plan.families[f].owner = best;
-        load[best] += plan.families[f].row_hi - plan.families[f].row_lo;
+        load[best] += plan.families[f].weight;
       }
     }
-  }
-  std::vector<u8> mine(n, 1);
-  if (plan.world > 1)
     for (const Family& f : plan.families)
-      for (u32 i = f.spec_lo; i < f.spec_hi; i++) mine[i] = (f.owner == plan.rank);
+      if (f.owner == plan.rank)
+        for (u32 i = f.spec_lo; i < f.spec_hi; i++) plan.mine[i] = 1;
+  }
+  plan.stats.seconds_layout = now_s() - t1;
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 
-  // Per Spec: warps, top diagonal and algorithmic bytes (one 12-byte row out; per candidate a
-  // 16-byte header; per child of a candidate that fits the cell's limits a 4-byte index and a
-  // 12-byte row in). Independent per Spec, so computed on all threads.
-  // Per group, the memory with the most slots in total becomes the one the diagonal fixes:
-  // a column then has a cell on as many of the group's diagonals as possible.
-  std::vector<u8> free_of(n, 3);
-  for (Group& g : plan.groups) {
-    u64 tot[NMEM] = {0, 0, 0, 0};
-    for (u32 i = g.spec_lo; i < g.spec_hi; i++)
-      for (int k = 0; k < NMEM; k++) tot[k] += (u64)__builtin_popcount(plan.hdrs[i].mask[k]);
-    int best = NMEM - 1;
-    for (int k = NMEM - 2; k >= 0; k--) if (tot[k] > tot[best]) best = k;
-    if (const char* e = getenv("MRL_FREE_DIM")) { int v = atoi(e); if (v >= 0 && v < NMEM) best = v; }
-    g.free_dim = (u8)best;
-    for (u32 i = g.spec_lo; i < g.spec_hi; i++) free_of[i] = (u8)best;
-  }
-  std::vector<u32> warps(n), top_sums(n);
-  std::vector<u64> bytes_t(std::max(n_threads, 1), 0), cols_t(std::max(n_threads, 1), 0);
-  parallel_for(n, n_threads, [&](size_t i, int tid) {
-    const SpecHdr& h = plan.hdrs[i];
-    u32 nk[NMEM];
-    u32 top_sum = 0;
-    for (int k = 0; k < NMEM; k++) {
-      nk[k] = (u32)__builtin_popcount(h.mask[k]);
-      top_sum += 31 - (u32)__builtin_clz(h.mask[k]);
-    }
-    u64 ncells = (u64)nk[0] * nk[1] * nk[2] * nk[3];
-    u32 ncols = (u32)(ncells / nk[free_of[i]]);  // the slot in the group's free memory is fixed by the diagonal
-    u64 bytes = ncells * 12;
-    for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
-      const CandRec& r = plan.cands[c];
-      bytes += ncells * 16;
-      if (r.nchild) {
-        u32 feasible_k = (u32)__builtin_popcount(h.mask[r.level] >> plan.slot_ceil(r.level, r.thr_code));
-        bytes += ncells / nk[r.level] * feasible_k * r.nchild * 16;
-      }
-    }
-    bytes_t[tid] += bytes;
-    cols_t[tid] += ncols;
-    const u32 cols_per_warp = 32u / (u32)plan.lanes_per_cell;
-    warps[i] = mine[i] ? (ncols + cols_per_warp - 1) / cols_per_warp : 0;
-    top_sums[i] = top_sum;
-  });
-  u64 bytes = 0, cols_total = 0;
-  for (u64 b : bytes_t) bytes += b;
-  for (u64 c : cols_t) cols_total += c;
-  plan.warp_prefix.assign(n + 1, 0);
-  u64 wsum = 0;
-  for (u32 i = 0; i < n; i++) {
-    plan.warp_prefix[i] = (u32)wsum;
-    wsum += warps[i];
-    if (wsum > 0xFFFFFFFFull) throw ModelError("too many warps in one plan");
-  }
-  plan.warp_prefix[n] = (u32)wsum;
-  for (Group& g : plan.groups) {
-    g.chunk_lo = plan.warp_prefix[g.spec_lo];
-    g.chunk_hi = plan.warp_prefix[g.spec_hi];
-    g.max_diag = 0;
-    for (u32 i = g.spec_lo; i < g.spec_hi; i++)
-      if (mine[i]) g.max_diag = std::max(g.max_diag, top_sums[i]);
-  }
-  u32 max_diag = 0;
-  for (const Group& g : plan.groups) max_diag = std::max(max_diag, g.max_diag);
-  // Group-major: a group only needs earlier groups (any limits) and, inside itself, cells on
-  // lower diagonals. Moves keep kind, dtype and shape, so they never leave their group;
-  // tile-outs and splits go to a smaller log-shape sum; ToAccum and Move prologues/epilogues
-  // go to an earlier phase.
-  for (u32 gi = 0; gi < plan.groups.size(); gi++)
-    if (plan.groups[gi].chunk_hi > plan.groups[gi].chunk_lo)
-      for (u32 d = 0; d <= plan.groups[gi].max_diag; d++) plan.steps.push_back(Step{gi, d});
-
-  plan.stats.n_rows = row;
-  plan.stats.n_columns = cols_total;
-  plan.stats.n_groups = plan.groups.size();
-  plan.stats.n_steps = plan.steps.size();
-  plan.stats.max_diag = max_diag;
-  plan.stats.algorithmic_bytes = bytes;
-  plan.stats.seconds_layout += now_s() - t3;
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] masks %.2fs (%llu sweeps), rows/owners/warps %.2fs\n", plan.stats.seconds_masks, (unsigned long long)plan.stats.mask_sweeps, now_s() - t3);
+  plan.stats.n_specs = n;
+  plan.stats.n_cands = ncand;
+  plan.stats.n_stages = plan.stages.size();
+  plan.stats.n_families = plan.families.size();
+  return plan;
 }
 
 }  // namespace mrl

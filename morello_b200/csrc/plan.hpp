@@ -1,16 +1,17 @@
 // Host-side planner of the database fill.
 //
-// Turns a set of goal logical Specs into the flat arrays the combine kernel walks:
+// Turns a set of goal logical Specs into the flat arrays the device side walks:
 //   * the dependency closure of the goals (every sub-Spec any candidate action can ask for),
 //   * per Spec its candidate records (action number, combine kind, immediates, child ids),
-//   * per Spec the breakpoints of its memory-limits lattice (one bit mask per memory), which
-//     give the Spec a dense 4-D grid of cells; one table row per cell,
-//   * the schedule: groups of Specs ordered by (phase, log-shape sum) crossed with limits
-//     diagonals, a total order in which every child row precedes its parent row.
+//   * the order: Specs sorted into stages by (phase, log-shape sum, memory-level sum). Every
+//     child of a Spec lies in an earlier stage, except the children of same-memory relayout
+//     Moves, which stay in the stage but sit at strictly lower memory limits.
+// The limits grids (which lattice codes each Spec's table distinguishes) are not planned here:
+// the device derives them stage by stage from the finished tables of the children.
 //
 // This replaces, for the path built here, the reference's on-demand recursion
 // (morello/src/search/algo.rs:61-95) and its paged R-tree tables
-// (morello/src/db/mod.rs:538-573,650-766): every (logical Spec, limits) point gets its own
+// (morello/src/db/mod.rs:538-573,650-766): every cell of a Spec's limits grid gets its own
 // direct solve, so a point lookup is an index computation instead of a rectangle search.
 #pragma once
 #include "model/actions.hpp"
@@ -26,80 +27,47 @@ struct PlanStats {
   u64 n_goal_specs = 0;
   u64 n_cands = 0;
   u64 n_children = 0;
-  u64 n_rows = 0;
-  u64 n_columns = 0;
-  u64 n_groups = 0;
-  u64 n_steps = 0;
-  u64 max_diag = 0;
-  u64 algorithmic_bytes = 0;  // per full fill
-  u64 mask_sweeps = 0;
-  double seconds_discover = 0, seconds_masks = 0, seconds_layout = 0;
+  u64 n_stages = 0;
+  u64 n_families = 0;
+  double seconds_discover = 0, seconds_layout = 0;
 };
 
-struct Group {          // Specs with the same phase and log-shape sum: no dependencies inside
+// Specs with the same phase (kind), log-shape sum and memory-level rank (sum over operands of
+// the memory index RF 0, VRF 1, L1 2, GL 3; for Move Specs the largest index instead). Tile-outs
+// and splits shrink the shape, ToAccum and the Move prologues/epilogues of Matmul and Fill Specs
+// go to an earlier phase, Moves to a faster memory lower the level sum: only relayout Moves
+// (same memory, other layout) - and, in the Move phase, Moves that keep the slowest memory -
+// keep a child inside the stage.
+struct Stage {
   u32 spec_lo = 0, spec_hi = 0;  // id range
-  u32 chunk_lo = 0, chunk_hi = 0;
-  u32 max_diag = 0;     // largest limits diagonal any member has a cell on
-  u8 free_dim = 3;      // memory whose slot the diagonal fixes; a thread owns a column of the other three
+  u32 fam_lo = 0, fam_hi = 0;    // family range
   u8 phase = 0;
   u8 shape_sum = 0;
+  u8 level_rank = 0;
 };
 
-// Specs of one group with the same dtype and shape. Moves never change either, so families of
-// a group do not depend on each other: the unit of work handed to one GPU.
+// Specs of one stage with the same dtype and shape. Moves never change either, so families of
+// a stage do not depend on each other: the unit of work handed to one GPU.
 struct Family {
   u32 spec_lo = 0, spec_hi = 0;
-  u32 group = 0;
+  u32 stage = 0;
   u32 owner = 0;        // rank that computes it
-  u64 row_lo = 0, row_hi = 0;
-};
-
-struct Step {           // one kernel launch
-  u32 group;
-  u32 diag;             // sum of the four limit slots of the cells this launch evaluates
+  u64 weight = 0;       // candidate records (the load-balancing estimate)
 };
 
 struct Plan {
   std::vector<LogicalSpec> specs;        // by id
-  std::vector<SpecHdr> hdrs;             // by id
+  std::vector<SpecHdr> hdrs;             // by id; masks and row_base are filled in on the device
   std::vector<CandRec> cands;
-  // warp_prefix[i] = number of warp-sized column chunks of the Specs with id < i that this rank
-  // computes (n_specs + 1 entries). The chunk list itself is expanded on the device.
-  std::vector<u32> warp_prefix;
   int n_threads = 1;
-  // Lanes of a warp that share one cell (each takes every lanes_per_cell-th candidate); a warp
-  // covers 32 / lanes_per_cell neighbouring columns. 1 or 2.
-  int lanes_per_cell = 1;
-  std::vector<Group> groups;
+  std::vector<Stage> stages;
   std::vector<Family> families;
-  std::vector<Step> steps;
   // Sharding: this process computes the families whose owner == rank; every rank keeps the
   // whole table. world == 1: everything is local.
   u32 rank = 0, world = 1;
+  std::vector<u8> mine;                  // by id: 1 = computed by this rank (empty when world == 1)
   std::vector<u32> goal_ids;
   u32 top_code[NMEM] = {0, 0, 0, 0};   // lattice codes of the top limits the plan covers
-  // Lattice compression. In a compressed memory k the table keeps the codes 0..cap_code[k] and
-  // the top code only ("slots" 0..cap and cap+1); limits strictly between map to the cap slot.
-  // That is exact as long as no optimal peak exceeds the cap (checked after every fill): a
-  // result whose peak fits under the cap is already available at the cap, so nothing changes
-  // between cap and top. cap_code[k] == top_code[k] means memory k is not compressed.
-  u32 cap_code[NMEM] = {0, 0, 0, 0};
-  bool compressed(int k) const { return cap_code[k] + 1 < top_code[k]; }
-  u32 slot_of_code(int k, u32 code) const {
-    if (!compressed(k)) return code;
-    if (code == top_code[k]) return cap_code[k] + 1;
-    return code < cap_code[k] ? code : cap_code[k];
-  }
-  // Smallest slot whose limit is >= the limit `code` (for feasibility thresholds).
-  u32 slot_ceil(int k, u32 code) const {
-    if (!compressed(k) || code <= cap_code[k]) return code;
-    return cap_code[k] + 1;
-  }
-  u32 cap_pack() const {   // one byte per memory, 255 = not compressed
-    u32 r = 0;
-    for (int k = 0; k < NMEM; k++) r |= (compressed(k) ? cap_code[k] : 255u) << (8 * k);
-    return r;
-  }
   u32 top_pack() const {
     u32 r = 0;
     for (int k = 0; k < NMEM; k++) r |= top_code[k] << (8 * k);
@@ -109,22 +77,18 @@ struct Plan {
 
   // id of a logical Spec (canonical form), or -1.
   long find(const LogicalSpec& ls) const;
-  // Row index of (spec id, limits) or -1 when limits exceed the planned top.
-  long row_of(u32 id, const u64 limits[NMEM]) const;
+  // Limits as packed lattice codes (RF in byte 0 .. GL in byte 3); false when the limits are
+  // not lattice points or exceed the planned top.
+  bool pack_limits(const u64 limits[NMEM], u32* out) const;
 
  private:
-  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, const int*, u32, u32);
+  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32);
   std::vector<std::pair<std::string, u32>> sorted_keys_;  // (key, id), sorted by key
 };
 
-// Top limits are Avx2Target::max_mem() unless overridden. caps: per memory the largest lattice
-// code kept below the top (negative or >= top: no compression), see Plan::cap_code.
+// Top limits are Avx2Target::max_mem() unless overridden.
 Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr,
-                const int* caps = nullptr, u32 rank = 0, u32 world = 1);
-
-// Recomputes everything that depends on the lattice caps (breakpoint masks, row offsets, chunk
-// lists, schedule, byte accounting) and leaves Specs and candidate records alone.
-void relayout_plan(Plan& plan, const int* caps);
+                u32 rank = 0, u32 world = 1);
 
 // Goal sets.
 std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes,

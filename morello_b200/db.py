@@ -145,11 +145,6 @@ class SynthesisDatabase:
     def fill(self):
         self._check(self._lib.mrl_fill(self._ctx))
 
-    def set_lattice_caps(self, caps: Sequence[int], auto_raise: bool = True):
-        """Per memory (RF, VRF, L1, GL) the largest limit code kept below the top; -1 keeps all."""
-        arr = (C.c_int32 * 4)(*caps)
-        self._check(self._lib.mrl_set_lattice_caps(self._ctx, arr, int(auto_raise)))
-
     # --- FilesDatabase::get ---
     def get_many(self, specs: Sequence[bytes], limits: Sequence[Sequence[int]]) -> List[Decision]:
         data, off, lim = _pack(specs, limits)
@@ -160,20 +155,30 @@ class SynthesisDatabase:
     def get(self, spec: bytes, limits: Sequence[int] = MAX_MEM) -> Decision:
         return self.get_many([spec], [limits])[0]
 
-    # --- multi-GPU: shard ownership and the per-group fill (see morello_b200/sharded.py) ---
+    # --- multi-GPU: shard ownership and the per-stage fill (see morello_b200/sharded.py) ---
     def set_shard(self, rank: int, world: int):
         self._check(self._lib.mrl_set_shard(self._ctx, rank, world))
 
     def set_stream(self, cuda_stream: int):
         self._check(self._lib.mrl_set_stream(self._ctx, C.c_void_p(cuda_stream)))
 
-    def num_groups(self) -> int:
-        return int(self._lib.mrl_num_groups(self._ctx))
+    def num_stages(self) -> int:
+        return int(self._lib.mrl_num_stages(self._ctx))
+
+    def stages(self):
+        """[(first Spec id, end Spec id, first family, end family)] in plan order."""
+        out = []
+        a, b, c, d = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        for s in range(self.num_stages()):
+            if self._lib.mrl_stage_info(self._ctx, s, C.byref(a), C.byref(b), C.byref(c), C.byref(d)) != 0:
+                raise IndexError(s)
+            out.append((int(a.value), int(b.value), int(c.value), int(d.value)))
+        return out
 
     def families(self):
-        """[(group, owner rank, first row, end row)] in table order."""
+        """[(stage, owner rank, first Spec id, end Spec id)] in plan order."""
         out = []
-        g, o, lo, hi = C.c_uint32(), C.c_uint32(), C.c_uint64(), C.c_uint64()
+        g, o, lo, hi = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
         for f in range(int(self._lib.mrl_num_families(self._ctx))):
             if self._lib.mrl_family_info(self._ctx, f, C.byref(g), C.byref(o), C.byref(lo), C.byref(hi)) != 0:
                 raise IndexError(f)
@@ -181,7 +186,7 @@ class SynthesisDatabase:
         return out
 
     def device_rows(self):
-        """(device pointer, row count) of the row table (mrl_row_bytes() bytes per row)."""
+        """(device pointer, row count) of the finished table (mrl_row_bytes() bytes per row)."""
         ptr, n = C.c_void_p(), C.c_uint64()
         if self._lib.mrl_device_rows(self._ctx, C.byref(ptr), C.byref(n)) != 0:
             raise RuntimeError("no table on the device")
@@ -190,24 +195,26 @@ class SynthesisDatabase:
     def fill_begin(self):
         self._check(self._lib.mrl_fill_begin(self._ctx))
 
-    def fill_group(self, group: int):
-        self._check(self._lib.mrl_fill_group(self._ctx, group))
+    def fill_stage_solve(self, stage: int):
+        """Solves this rank's share of a stage; (device pointer, bytes) of the stage's breakpoint masks."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        self._check(self._lib.mrl_fill_stage_solve(self._ctx, stage, C.byref(ptr), C.byref(n)))
+        return int(ptr.value or 0), int(n.value)
+
+    def fill_stage_place(self, stage: int):
+        """Appends the stage to the table; (device pointer, bytes) of the stage's rows."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        self._check(self._lib.mrl_fill_stage_place(self._ctx, stage, C.byref(ptr), C.byref(n)))
+        return int(ptr.value or 0), int(n.value)
 
     def fill_end(self):
-        """(status, caps): status 1 = an optimal peak exceeded a lattice cap; refill with `caps`."""
-        caps = (C.c_int32 * 4)()
-        rc = self._lib.mrl_fill_end(self._ctx, caps)
-        if rc < 0:
-            self._check(rc)
-        return rc, [int(c) for c in caps]
+        self._check(self._lib.mrl_fill_end(self._ctx))
 
     # --- export / stats ---
     def stats(self) -> dict:
         s = L.Stats()
         self._check(self._lib.mrl_get_stats(self._ctx, C.byref(s)))
-        out = {name: getattr(s, name) for name, _ in L.Stats._fields_}
-        out["lattice_caps"] = [int(x) for x in s.lattice_caps]
-        return out
+        return {name: getattr(s, name) for name, _ in L.Stats._fields_}
 
     def num_specs(self) -> int:
         return int(self._lib.mrl_num_specs(self._ctx))

@@ -20,13 +20,11 @@ def _worker(rank, world, port):
     import morello_b200 as m
     from morello_b200 import sharded
     db = m.SynthesisDatabase(device=rank)
-    attempts = sharded.precompute_sharded(db, 2, dist, torch)
-    assert 1 <= attempts <= 4
+    sharded.precompute_sharded(db, 2, dist, torch)
     ptr, n = db.device_rows()
     got = torch.as_tensor(sharded._DeviceBytes(ptr, n * sharded.row_bytes()), device="cuda").clone()
-    # the unsharded fill with the same caps on this rank's GPU
+    # the unsharded fill on this rank's GPU
     solo = m.SynthesisDatabase(device=rank)
-    solo.set_lattice_caps(db.stats()["lattice_caps"])
     solo.precompute(2)
     sptr, sn = solo.device_rows()
     assert sn == n

@@ -1,5 +1,5 @@
 """Host-side logic of the multi-GPU fill on CPU: two gloo ranks agree on who owns which family,
-and the per-group broadcast schedule rebuilds the whole table on every rank."""
+and the per-stage sum over ranks rebuilds every Spec's words on every rank."""
 import os
 import sys
 
@@ -21,31 +21,30 @@ def _worker(rank, world, port, out_dir):
     from morello_b200 import sharded
     db = m.SynthesisDatabase(device=-1)  # planning only: no GPU here
     db.set_shard(rank, world)
-    db.set_lattice_caps([8, 2, 5, 0])
     db.plan_precompute(2)
     fams = db.families()
-    n_rows = db.stats()["n_rows"]
-    sharded.check_partition(fams, world, n_rows)
-    sched = sharded.exchange_schedule(fams, db.num_groups())
+    stages = db.stages()
+    n_specs = db.stats()["n_specs"]
+    assert len(stages) == db.num_stages() == db.stats()["n_stages"]
+    sharded.check_partition(fams, stages, world, n_specs)
     # every rank must have computed the same ownership
     mine = torch.tensor([o for _, o, _, _ in fams], dtype=torch.int64)
     ref = mine.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(mine, ref)
-    # stand-in for the fill: a rank "computes" f(row) for the rows it owns, group by group,
-    # then the schedule's broadcasts run; children are always in earlier groups.
-    table = torch.full((n_rows,), -1, dtype=torch.int64)
-    for g, ranges in enumerate(sched):
-        for owner, lo, hi in ranges:
-            if owner == rank:
-                table[lo:hi] = torch.arange(lo, hi) * 7 + 3
-        for owner, lo, hi in ranges:
-            dist.broadcast(table[lo:hi], src=owner)
-    assert torch.equal(table, torch.arange(n_rows) * 7 + 3)
-    loads = [0] * world
-    for _, o, lo, hi in fams:
-        loads[o] += hi - lo
-    np.save(os.path.join(out_dir, f"loads_{rank}.npy"), np.array(loads))
+    # stand-in for the fill: per stage a rank "computes" four mask words for each Spec of the
+    # families it owns and leaves the others zero; the sum over ranks is the exchange.
+    owner_of = torch.empty(n_specs, dtype=torch.int64)
+    for _stage, o, lo, hi in fams:
+        owner_of[lo:hi] = o
+    want = (torch.arange(n_specs * 4, dtype=torch.int32) * 7 + 3).reshape(n_specs, 4)
+    table = torch.zeros((n_specs, 4), dtype=torch.int32)
+    for lo, hi, _flo, _fhi in stages:
+        own = owner_of[lo:hi] == rank
+        table[lo:hi][own] = want[lo:hi][own]
+        dist.all_reduce(table[lo:hi], op=dist.ReduceOp.SUM)
+    assert torch.equal(table, want)
+    np.save(os.path.join(out_dir, f"loads_{rank}.npy"), np.array(sharded.rank_loads(fams, world)))
     db.close()
     dist.destroy_process_group()
 
@@ -59,10 +58,15 @@ def test_two_rank_ownership_and_exchange_schedule(built_extension, tmp_path):
     assert loads.sum() > 0 and loads.min() > 0.25 * loads.max()  # both ranks get real work
 
 
-def test_exchange_schedule_merges_neighbours():
+def test_check_partition_rejects_gaps_and_bad_owners():
     from morello_b200 import sharded
-    fams = [(0, 0, 0, 10), (0, 0, 10, 20), (0, 1, 20, 25), (1, 1, 25, 40), (1, 1, 40, 40), (1, 0, 40, 50)]
-    assert sharded.exchange_schedule(fams, 2) == [[(0, 0, 20), (1, 20, 25)], [(1, 25, 40), (0, 40, 50)]]
-    sharded.check_partition(fams, 2, 50)
+    stages = [(0, 20, 0, 2), (20, 50, 2, 4)]
+    fams = [(0, 0, 0, 10), (0, 1, 10, 20), (1, 1, 20, 40), (1, 0, 40, 50)]
+    sharded.check_partition(fams, stages, 2, 50)
+    assert sharded.rank_loads(fams, 2) == [20, 30]
     with pytest.raises(ValueError):
-        sharded.check_partition(fams, 2, 51)
+        sharded.check_partition(fams, stages, 2, 51)
+    with pytest.raises(ValueError):
+        sharded.check_partition(fams, stages, 1, 50)  # owner 1 does not exist
+    with pytest.raises(ValueError):
+        sharded.check_partition([(0, 0, 0, 10), (0, 1, 11, 20)] + fams[2:], stages, 2, 50)
