@@ -142,34 +142,33 @@ __device__ __forceinline__ Column decode_column(const SpecHdr* __restrict__ hdrs
   return c;
 }
 
-// One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes).
+// One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes),
+// listed by scatter_cells_kernel: every thread has a cell, and neighbouring threads mostly have
+// neighbouring cells of one Spec.
 __global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
 combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                      const Chunk* __restrict__ chunks, uint32_t n_chunks, uint32_t diag,
+                      const CellRef* __restrict__ cells, uint32_t n_cells,
                       const MrlRow* __restrict__ rows, MrlRow* __restrict__ temp, uint32_t n_specs,
                       uint32_t* __restrict__ error_flag) {
-  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const uint32_t lane = threadIdx.x & 31;
-  if (warp >= n_chunks) return;
-  const Chunk ch = chunks[warp];
-  Column c = decode_column(hdrs, ch, lane);
-  if (!c.valid) return;
-  // The launch's diagonal fixes the code in F; the cell exists if that code is one of the
-  // Spec's breakpoints there.
-  const uint32_t mF = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
-  const int cfs = (int)diag - (int)c.others;
-  if (cfs < 0 || cfs > 31 || !((mF >> cfs) & 1u)) return;
-  const uint32_t iF = __popc(mF & ((1u << cfs) - 1u));
-#pragma unroll
-  for (int k = 0; k < 4; k++)
-    if ((uint32_t)k == c.F) { c.code[k] = (uint32_t)cfs; c.idx[k] = iF; }
-  const uint32_t cpack = c.code[0] | (c.code[1] << 8) | (c.code[2] << 16) | (c.code[3] << 24);
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_cells) return;
+  const CellRef ref = cells[t];
+  const uint32_t spec = ref.spec;
+  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[spec]));
+  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+  uint32_t rest = ref.cell;
+  const uint32_t i0 = rest % n0; rest /= n0;
+  const uint32_t i1 = rest % n1; rest /= n1;
+  const uint32_t i2 = rest % n2;
+  const uint32_t i3 = rest / n2;
+  const uint32_t cpack = nth_set_bit(m.x, i0) | (nth_set_bit(m.y, i1) << 8) | (nth_set_bit(m.z, i2) << 16) |
+                         (nth_set_bit(m.w, i3) << 24);
   // "codes at or below this cell's limit", per memory: what a child lookup at the same limits needs
-  const uint32_t bm0 = (2u << c.code[0]) - 1u, bm1 = (2u << c.code[1]) - 1u, bm2 = (2u << c.code[2]) - 1u,
-                 bm3 = (2u << c.code[3]) - 1u;
+  const uint32_t bm0 = (2u << code_of(cpack, 0)) - 1u, bm1 = (2u << code_of(cpack, 1)) - 1u,
+                 bm2 = (2u << code_of(cpack, 2)) - 1u, bm3 = (2u << code_of(cpack, 3)) - 1u;
 
-  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ch.spec].row_base));
-  const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[ch.spec].cand_off));
+  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[spec].row_base));
+  const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[spec].cand_off));
   const uint32_t cand_off = cl.x, ncand = cl.y;
 
   Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
@@ -251,9 +250,8 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     }
     if (key_less(k, best)) best = k;
   }
-  const uint32_t off = ((c.idx[3] * c.nn[2] + c.idx[2]) * c.nn[1] + c.idx[1]) * c.nn[0] + c.idx[0];
   // Specs of the stage being solved always live in the working buffer.
-  *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + off) = make_uint4(best.main, best.peaks, best.tail, 0u);
+  *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + ref.cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
 }
 
 // ---- working grids ---------------------------------------------------------------------
@@ -315,7 +313,7 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
   const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
   const bool active = i < hi && (!mine || mine[i]);
   unsigned long long cells = 0, warps = 0, bytes = 0;
-  uint32_t d0 = 0, d1 = 0, d2 = 0, d3 = 0, changed = 0;
+  uint32_t changed = 0;
   if (active) {
     const uint4 old = *reinterpret_cast<const uint4*>(&hdrs[i]);
     const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
@@ -350,22 +348,6 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
     const Grid g = grid_of(nm);
     cells = g.cells;
     warps = g.warps;
-    // occupied diagonals: the sum set of the four masks, as a 128-bit set
-    unsigned long long slo = 1, shi = 0;
-    const uint32_t mk[4] = {nm.x, nm.y, nm.z, nm.w};
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-      unsigned long long nlo = 0, nhi = 0;
-      uint32_t mbits = mk[k];
-      while (mbits) {
-        const uint32_t bpos = __ffs(mbits) - 1;
-        mbits &= mbits - 1;
-        nlo |= slo << bpos;
-        nhi |= (shi << bpos) | (bpos ? (slo >> (64 - bpos)) : 0ull);
-      }
-      slo = nlo; shi = nhi;
-    }
-    d0 = (uint32_t)slo; d1 = (uint32_t)(slo >> 32); d2 = (uint32_t)shi; d3 = (uint32_t)(shi >> 32);
     // algorithmic bytes of one solve: a 12-byte row out; per candidate a 16-byte header; per
     // child of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in
     bytes = cells * 12ull;
@@ -390,19 +372,11 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
     warps += __shfl_xor_sync(0xFFFFFFFFu, warps, o);
     bytes += __shfl_xor_sync(0xFFFFFFFFu, bytes, o);
   }
-  d0 = __reduce_or_sync(0xFFFFFFFFu, d0);
-  d1 = __reduce_or_sync(0xFFFFFFFFu, d1);
-  d2 = __reduce_or_sync(0xFFFFFFFFu, d2);
-  d3 = __reduce_or_sync(0xFFFFFFFFu, d3);
   changed = __reduce_or_sync(0xFFFFFFFFu, changed);
   if ((threadIdx.x & 31) == 0 && cells) {
     atomicAdd(&ctr->cells, cells);
     atomicAdd(&ctr->warps, warps);
     atomicAdd(&ctr->alg_bytes, bytes);
-    if (d0) atomicOr(&ctr->diag_bits[0], d0);
-    if (d1) atomicOr(&ctr->diag_bits[1], d1);
-    if (d2) atomicOr(&ctr->diag_bits[2], d2);
-    if (d3) atomicOr(&ctr->diag_bits[3], d3);
     if (changed) atomicOr(&ctr->changed, 1u);
   }
 }
@@ -461,6 +435,73 @@ place_kernel(SpecHdr* __restrict__ hdrs, uint4* __restrict__ rmask, const uint8_
     c.spec = i;
     c.col_start = (w * 32u) | (g.F << 30);
     chunks[cb + w] = c;
+  }
+}
+
+// Pass step 3a: how many working cells lie on each limits diagonal. Thread per column.
+__global__ void __launch_bounds__(128)
+diag_histogram_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
+                      DiagTable* __restrict__ diag) {
+  __shared__ uint32_t hist[MRL_MAX_DIAG];
+  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) hist[k] = 0;
+  __syncthreads();
+  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (warp < n_chunks) {
+    const Column c = decode_column(hdrs, chunks[warp], lane);
+    if (c.valid) {
+      uint32_t mrest = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
+      while (mrest) {
+        const uint32_t codeF = __ffs(mrest) - 1;
+        mrest &= mrest - 1;
+        atomicAdd(&hist[(c.others + codeF) & (MRL_MAX_DIAG - 1)], 1u);
+      }
+    }
+  }
+  __syncthreads();
+  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x)
+    if (hist[k]) atomicAdd(&diag->count[k], hist[k]);
+}
+
+// Pass step 3b: lists the working cells diagonal by diagonal (diag->base set by the host from the
+// histogram). A block counts its own cells per diagonal, reserves that many list slots per
+// diagonal with one atomic each, then writes its cells.
+__global__ void __launch_bounds__(128)
+scatter_cells_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
+                     DiagTable* __restrict__ diag, CellRef* __restrict__ cells) {
+  __shared__ uint32_t hist[MRL_MAX_DIAG];
+  __shared__ unsigned long long start[MRL_MAX_DIAG];
+  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) hist[k] = 0;
+  __syncthreads();
+  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  Column c;
+  c.valid = false;
+  if (warp < n_chunks) c = decode_column(hdrs, chunks[warp], lane);
+  const uint32_t mF = c.valid ? sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F) : 0u;
+  for (uint32_t mrest = mF; mrest; mrest &= mrest - 1)
+    atomicAdd(&hist[(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
+  __syncthreads();
+  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) {
+    const uint32_t n = hist[k];
+    if (n) start[k] = diag->base[k] + atomicAdd(&diag->cursor[k], n);
+    hist[k] = 0;   // becomes the block-local cursor
+  }
+  __syncthreads();
+  if (!c.valid) return;
+  const uint32_t st[4] = {1u, c.nn[0], c.nn[0] * c.nn[1], c.nn[0] * c.nn[1] * c.nn[2]};
+  const uint32_t stF = sel4(st[0], st[1], st[2], st[3], c.F);
+  uint32_t off0 = 0;
+#pragma unroll
+  for (int k = 0; k < 4; k++) off0 += c.idx[k] * st[k];   // idx[F] is 0
+  uint32_t s = 0;
+  for (uint32_t mrest = mF; mrest; mrest &= mrest - 1, s++) {
+    const uint32_t d = (c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1);
+    const uint32_t pos = atomicAdd(&hist[d], 1u);
+    CellRef r;
+    r.spec = c.spec;
+    r.cell = off0 + s * stF;
+    cells[start[d] + pos] = r;
   }
 }
 
@@ -646,14 +687,15 @@ void DeviceFill::free_(void* p) {
 
 void DeviceFill::release() {
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
-  d_stage_ = nullptr;
+  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr;
   stage_bytes_ = 0;
-  row_cap_ = temp_cap_ = chunk_cap_ = 0;
+  row_cap_ = temp_cap_ = chunk_cap_ = cell_cap_ = 0;
   buf_off_ = 0;
   if (h_ctr_) { cudaFreeHost(h_ctr_); h_ctr_ = nullptr; }
+  if (h_diag_) { cudaFreeHost(h_diag_); h_diag_ = nullptr; }
   for (cudaEvent_t e : ev_pool_) cudaEventDestroy(e);
   ev_pool_.clear();
   if (ev0_) cudaEventDestroy(ev0_);
@@ -700,10 +742,10 @@ int DeviceFill::set_stream(cudaStream_t s) {
 int DeviceFill::upload(const Plan& plan) {
   CK(cudaSetDevice(device_));
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
-  d_stage_ = nullptr;
+  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr;
   stage_bytes_ = 0;
   buf_off_ = 0;
   n_specs_ = (uint32_t)plan.hdrs.size();
@@ -711,6 +753,7 @@ int DeviceFill::upload(const Plan& plan) {
   for (const Stage& st : plan.stages) max_stage = std::max(max_stage, st.spec_hi - st.spec_lo);
   int rc;
   if ((rc = alloc_((void**)&d_ctr_, 256))) return rc;
+  if ((rc = alloc_((void**)&d_diag_, sizeof(DiagTable)))) return rc;
   d_final_top_ = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(d_ctr_) + 64);
   d_stage_info_ = d_final_top_ + 1;
   if ((rc = alloc_((void**)&d_hdrs_, plan.hdrs.size() * sizeof(SpecHdr)))) return rc;
@@ -724,9 +767,11 @@ int DeviceFill::upload(const Plan& plan) {
     stage_bytes_ = 64 << 10;
     if ((rc = alloc_(&d_stage_, stage_bytes_))) return rc;
     const size_t left = buf_bytes_ > align256(buf_off_) + 1024 ? buf_bytes_ - align256(buf_off_) - 1024 : 0;
-    chunk_cap_ = left / 16 / sizeof(Chunk);
-    temp_cap_ = left / 2 / sizeof(MrlRow);
-    row_cap_ = (left - left / 16 - left / 2) / sizeof(MrlRow);
+    // per working cell: 16 bytes of row, 8 of cell list, under 1 of chunks; the rest is the table
+    chunk_cap_ = left / 32 / sizeof(Chunk);
+    temp_cap_ = left * 14 / 32 / sizeof(MrlRow);
+    cell_cap_ = left * 7 / 32 / sizeof(CellRef);
+    row_cap_ = (left - left / 32 - left * 14 / 32 - left * 7 / 32) / sizeof(MrlRow);
     if (chunk_cap_ == 0 || row_cap_ == 0) {
       snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
                "entry point has; use mrl_top_down_many for it", buf_bytes_);
@@ -734,15 +779,19 @@ int DeviceFill::upload(const Plan& plan) {
     }
     if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
     if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
+    if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
     if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
   } else {
     chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)n_specs_ * 2);
     temp_cap_ = std::max<uint64_t>(1u << 20, (uint64_t)max_stage * 64);
+    cell_cap_ = temp_cap_;
     row_cap_ = std::max<uint64_t>(1u << 20, (uint64_t)n_specs_ * 16);
     if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
     if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
+    if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
     if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
     if (!h_ctr_) CK(cudaHostAlloc((void**)&h_ctr_, 256, cudaHostAllocDefault));
+    if (!h_diag_) CK(cudaHostAlloc((void**)&h_diag_, sizeof(DiagTable), cudaHostAllocDefault));
   }
   h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) + plan.mine.size();
   CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
@@ -830,6 +879,23 @@ int DeviceFill::ensure_temp_(uint64_t need) {
   return 0;
 }
 
+int DeviceFill::ensure_cells_(uint64_t need) {
+  if (need <= cell_cap_) return 0;
+  if (fixed_) {
+    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
+             "entry point has; use mrl_top_down_many for it", buf_bytes_);
+    return -4;
+  }
+  CK(cudaStreamSynchronize(stream_));
+  cudaFree(d_cells_);
+  d_cells_ = nullptr;
+  cell_cap_ = 0;
+  const uint64_t cap = need + need / 4;
+  CK(cudaMalloc((void**)&d_cells_, cap * sizeof(CellRef)));
+  cell_cap_ = cap;
+  return 0;
+}
+
 int DeviceFill::ensure_chunks_(uint64_t need) {
   if (need <= chunk_cap_) return 0;
   if (need > 0xFFFFFFF0ull) { snprintf(err_, sizeof(err_), "stage too large: %llu chunks", (unsigned long long)need); return -6; }
@@ -887,10 +953,23 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
     int rc;
     if ((rc = ensure_chunks_(c.warps))) return rc;
     if ((rc = ensure_temp_(c.cells))) return rc;
+    if (c.cells >= 0xFFFFFFF0ull) { snprintf(err_, sizeof(err_), "stage %u too large: %llu working cells", si, (unsigned long long)c.cells); return -6; }
+    if ((rc = ensure_cells_(c.cells))) return rc;
     place_kernel<<<(n + 255) / 256, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, lo, hi, temp_cap_, d_chunks_,
                                                        chunk_cap_, d_ctr_);
     const uint32_t n_chunks = (uint32_t)c.warps;
     const uint32_t blocks = (n_chunks + 3) / 4;
+    // cells per limits diagonal, then the cell lists
+    CK(cudaMemsetAsync(d_diag_, 0, sizeof(DiagTable), stream_));
+    diag_histogram_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_diag_);
+    DiagTable* hd = h_diag_ ? h_diag_ : &diag_pageable_;
+    CK(cudaMemcpyAsync(hd->count, d_diag_->count, sizeof(hd->count), cudaMemcpyDeviceToHost, stream_));
+    CK(cudaStreamSynchronize(stream_));
+    unsigned long long run = 0;
+    for (int d = 0; d < MRL_MAX_DIAG; d++) { hd->base[d] = run; run += hd->count[d]; }
+    if (run != c.cells) { snprintf(err_, sizeof(err_), "stage %u: diagonal histogram counts %llu cells, expected %llu", si, run, (unsigned long long)c.cells); return -2; }
+    CK(cudaMemcpyAsync(d_diag_->base, hd->base, sizeof(hd->base), cudaMemcpyHostToDevice, stream_));
+    scatter_cells_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_diag_, d_cells_);
     if (ev_used_ + 2 > ev_pool_.size()) {
       for (int k = 0; k < 64; k++) {
         cudaEvent_t e;
@@ -899,16 +978,17 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
       }
     }
     CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
-    for (uint32_t d = 0; d < 128; d++) {
-      if (!((c.diag_bits[d >> 5] >> (d & 31)) & 1u)) continue;
-      combine_argmin_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_chunks_, n_chunks, d, d_rows_, d_temp_,
-                                                         n_specs_, &d_ctr_->error);
+    for (uint32_t d = 0; d < MRL_MAX_DIAG; d++) {
+      const uint32_t nd = hd->count[d];
+      if (!nd) continue;
+      combine_argmin_kernel<<<(nd + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_cells_ + hd->base[d], nd, d_rows_,
+                                                                   d_temp_, n_specs_, &d_ctr_->error);
       stats_.combine_launches++;
     }
     CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
     real_masks_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_temp_, d_rmask_);
     CK(cudaGetLastError());
-    stats_.launches += 2;
+    stats_.launches += 4;
     stats_.passes++;
     stats_.cells_solved += c.cells;
     stats_.alg_bytes += c.alg_bytes;

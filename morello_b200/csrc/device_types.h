@@ -66,9 +66,24 @@ struct PassCounters {
   unsigned long long warps;     // chunks those cells need
   unsigned long long temp_rows; // row cursor (place kernel)
   unsigned long long alg_bytes; // algorithmic bytes of one solve of those cells
-  uint32_t diag_bits[4];        // occupied limits diagonals (bit d of the 128-bit set)
-  uint32_t error;               // bad child index / capacity overrun seen by a kernel
+  uint32_t pad0[4];
+  uint32_t error;               // bad child index / capacity overrun seen by a kernel (sticky over a fill)
   uint32_t pad;
+};
+
+// Per limits diagonal (sum of the four codes, < 128) of the stage being solved: how many working
+// cells lie on it, and where their descriptors start in the cell list.
+#define MRL_MAX_DIAG 128
+struct DiagTable {
+  uint32_t count[MRL_MAX_DIAG];
+  uint32_t cursor[MRL_MAX_DIAG];
+  unsigned long long base[MRL_MAX_DIAG];
+};
+
+// One working cell: Spec id and the cell's linear index in the Spec's working grid.
+struct CellRef {
+  uint32_t spec;
+  uint32_t cell;
 };
 
 #ifdef __cplusplus

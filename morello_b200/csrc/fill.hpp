@@ -57,6 +57,7 @@ class DeviceFill {
   int ensure_rows_(uint64_t need, bool refresh);
   int ensure_temp_(uint64_t need);
   int ensure_chunks_(uint64_t need);
+  int ensure_cells_(uint64_t need);
   int read_counters_(PassCounters* out);
 
   int device_ = 0;
@@ -68,6 +69,10 @@ class DeviceFill {
   uint4* d_rmask_ = nullptr;
   uint8_t* d_mine_ = nullptr;
   Chunk* d_chunks_ = nullptr;
+  CellRef* d_cells_ = nullptr;   // working cells of the pass, listed diagonal by diagonal
+  DiagTable* d_diag_ = nullptr;
+  DiagTable* h_diag_ = nullptr;  // pinned
+  DiagTable diag_pageable_;      // used instead when nothing may be allocated
   MrlRow* d_rows_ = nullptr;   // the table
   MrlRow* d_temp_ = nullptr;   // working grids of the stage being solved
   uint32_t* d_fcount_ = nullptr;
@@ -79,7 +84,7 @@ class DeviceFill {
   size_t stage_bytes_ = 0;
   PassCounters* h_ctr_ = nullptr;       // pinned
   uint32_t n_specs_ = 0;
-  uint64_t row_cap_ = 0, temp_cap_ = 0, chunk_cap_ = 0;
+  uint64_t row_cap_ = 0, temp_cap_ = 0, chunk_cap_ = 0, cell_cap_ = 0;
   uint64_t final_bound_ = 0;            // upper bound of the final rows placed so far
   unsigned long long final_top_seen_ = 0, stage_info_seen_[2] = {0, 0};  // last values read back
   uint64_t last_cells_ = 0;             // working cells of the last pass of the stage being solved

@@ -163,6 +163,17 @@ inline u8 layout_prune_size_one(Layout& l, const Shape& shape, u8 contig) {
 
 // ---- drop_unneeded_packings (layout.rs:674-766) ----
 inline void layout_drop_unneeded_packings(Layout& l, const Shape& tile) {
+  {
+    // Nothing to drop in an all-Dynamic layout (the common case): merged layouts never hold two
+    // neighbouring Dynamic dims of one logical dim.
+    bool any_strip = false;
+    for (int i = 0; i < l.n; i++) any_strip |= l.d[i].kind != PD_DYNAMIC;
+    if (!any_strip) {
+      bool twin = false;
+      for (int i = 1; i < l.n; i++) twin |= l.d[i].ldim == l.d[i - 1].ldim;
+      if (!twin) return;
+    }
+  }
   const int n = l.n;
   const int contig = l.contig;
   const int first_contig = n - contig;

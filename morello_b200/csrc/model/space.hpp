@@ -104,7 +104,15 @@ inline std::vector<LogicalSpec> task_point_specs(const Bound& b, const std::vect
   for (int i = 0; i < b.spec_shape.n; i++) proto.spec_shape.d[i] = 1u << pt[p++];
   int nops = proto.nops();
   std::vector<std::vector<Aux>> variants(nops);
-  for (int i = 0; i < nops; i++) variants[i] = aux_variants(proto.operand_shape(i), b.dtype, (Mem)pt[p++]);
+  for (int i = 0; i < nops; i++) {
+    // is_canonical is per operand (plus one cross-operand rule for Moves, checked below), so
+    // the operand's variants are filtered before the product is taken.
+    const Shape shp = proto.operand_shape(i);
+    for (const Aux& a : aux_variants(shp, b.dtype, (Mem)pt[p++]))
+      if (check_tensor_vector_size(shp, b.dtype, a.mem, a.vector_size) == CANON_OK && aux_is_canonical(a, shp))
+        variants[i].push_back(a);
+    if (variants[i].empty()) return {};
+  }
   proto.serial_only = pt[p++] == 0;
   std::vector<LogicalSpec> out;
   std::vector<size_t> idx(nops, 0);

@@ -143,20 +143,24 @@ struct LogicalSpec {
   u64 volume() const { return spec_shape.volume(); }  // spec.rs:2133-2152
 
   // Compact, injective byte key (hash-map key and the C-ABI's Spec blob).
-  std::string key() const {
-    std::string s;
-    s.reserve(64);
-    s.push_back((char)kind); s.push_back((char)dtype); s.push_back((char)serial_only); s.push_back((char)spec_shape.n);
-    for (int i = 0; i < spec_shape.n; i++) { s.push_back((char)(spec_shape[i] & 0xff)); s.push_back((char)(spec_shape[i] >> 8)); }
+  static constexpr int MAX_KEY = 4 + 2 * MAX_RANK + MAX_OPS * (4 + 4 * MAX_PHYS);
+  int key_into(char* s) const {
+    int p = 0;
+    s[p++] = (char)kind; s[p++] = (char)dtype; s[p++] = (char)serial_only; s[p++] = (char)spec_shape.n;
+    for (int i = 0; i < spec_shape.n; i++) { s[p++] = (char)(spec_shape[i] & 0xff); s[p++] = (char)(spec_shape[i] >> 8); }
     for (int i = 0; i < nops(); i++) {
       const Aux& a = aux[i];
-      s.push_back((char)a.mem); s.push_back((char)a.vector_size); s.push_back((char)a.layout.n); s.push_back((char)a.layout.contig);
+      s[p++] = (char)a.mem; s[p++] = (char)a.vector_size; s[p++] = (char)a.layout.n; s[p++] = (char)a.layout.contig;
       for (int j = 0; j < a.layout.n; j++) {
-        s.push_back((char)a.layout.d[j].ldim); s.push_back((char)a.layout.d[j].kind);
-        s.push_back((char)(a.layout.d[j].size & 0xff)); s.push_back((char)(a.layout.d[j].size >> 8));
+        s[p++] = (char)a.layout.d[j].ldim; s[p++] = (char)a.layout.d[j].kind;
+        s[p++] = (char)(a.layout.d[j].size & 0xff); s[p++] = (char)(a.layout.d[j].size >> 8);
       }
     }
-    return s;
+    return p;
+  }
+  std::string key() const {
+    char buf[MAX_KEY];
+    return std::string(buf, (size_t)key_into(buf));
   }
   static LogicalSpec from_key(const std::string& s) {
     LogicalSpec l;

@@ -13,17 +13,108 @@ namespace mrl {
 
 namespace {
 
-constexpr int NSHARD = 512;
+constexpr int NSHARD = 1024;
 
-struct Shard {
+// 64-bit hash of a Spec key (8 bytes at a time, multiply-xorshift mixing).
+u64 hash_key(const char* p, int len) {
+  u64 h = 0x9E3779B97F4A7C15ull ^ (u64)len;
+  int i = 0;
+  for (; i + 8 <= len; i += 8) {
+    u64 w;
+    memcpy(&w, p + i, 8);
+    h = (h ^ w) * 0xD6E8FEB86659FD93ull;
+    h ^= h >> 32;
+  }
+  u64 w = 0;
+  if (i < len) memcpy(&w, p + i, (size_t)(len - i));
+  h = (h ^ w) * 0xD6E8FEB86659FD93ull;
+  h ^= h >> 32;
+  h *= 0xD6E8FEB86659FD93ull;
+  h ^= h >> 29;
+  return h;
+}
+
+// One shard of the key -> id map used during discovery: open addressing over (hash, id) with
+// the key bytes kept in a shard-local arena for the equality check.
+struct KeyShard {
+  struct Entry { u64 h; u32 id; u32 off; u32 len; u32 used; };
   std::mutex mu;
-  std::unordered_map<std::string, u32> map;
+  std::vector<Entry> tab;
+  std::string arena;
+  size_t count = 0;
+  KeyShard() : tab(256) { for (auto& e : tab) e.used = 0; }
+  // Returns the id stored for the key, or inserts `fresh_id()` and returns it with *inserted.
+  template <class F>
+  u32 find_or_insert(u64 h, const char* key, int len, F fresh_id, bool* inserted) {
+    std::lock_guard<std::mutex> g(mu);
+    size_t mask = tab.size() - 1;
+    size_t i = (size_t)(h >> 10) & mask;
+    while (tab[i].used) {
+      const Entry& e = tab[i];
+      if (e.h == h && e.len == (u32)len && memcmp(arena.data() + e.off, key, (size_t)len) == 0) {
+        *inserted = false;
+        return e.id;
+      }
+      i = (i + 1) & mask;
+    }
+    if ((count + 1) * 2 > tab.size()) {
+      std::vector<Entry> bigger(tab.size() * 2);
+      for (auto& e : bigger) e.used = 0;
+      const size_t m2 = bigger.size() - 1;
+      for (const Entry& e : tab) {
+        if (!e.used) continue;
+        size_t j = (size_t)(e.h >> 10) & m2;
+        while (bigger[j].used) j = (j + 1) & m2;
+        bigger[j] = e;
+      }
+      tab.swap(bigger);
+      mask = tab.size() - 1;
+      i = (size_t)(h >> 10) & mask;
+      while (tab[i].used) i = (i + 1) & mask;
+    }
+    Entry e;
+    e.h = h;
+    e.id = fresh_id();
+    e.off = (u32)arena.size();
+    e.len = (u32)len;
+    e.used = 1;
+    arena.append(key, (size_t)len);
+    tab[i] = e;
+    count++;
+    *inserted = true;
+    return e.id;
+  }
 };
 
 struct TempSpec {
   LogicalSpec ls;
   std::string key;
   std::vector<CandRec> cands;  // child[] holds temporary ids
+};
+
+// Growing array of TempSpec in fixed blocks: elements never move, blocks are allocated on demand
+// from any thread, and an element is constructed by the thread that discovers the Spec.
+class TempSpecs {
+ public:
+  static constexpr u32 BLOCK_BITS = 15, BLOCK = 1u << BLOCK_BITS, MAX_BLOCKS = 1u << 17;
+  TempSpecs() : blocks_(MAX_BLOCKS) { for (auto& b : blocks_) b.store(nullptr, std::memory_order_relaxed); }
+  ~TempSpecs() { for (auto& b : blocks_) free(b.load(std::memory_order_relaxed)); }
+  TempSpec& operator[](u32 id) { return blocks_[id >> BLOCK_BITS].load(std::memory_order_acquire)[id & (BLOCK - 1)]; }
+  TempSpec& construct(u32 id) {
+    std::atomic<TempSpec*>& slot = blocks_[id >> BLOCK_BITS];
+    TempSpec* b = slot.load(std::memory_order_acquire);
+    if (!b) {
+      TempSpec* fresh = static_cast<TempSpec*>(malloc(sizeof(TempSpec) * BLOCK));
+      if (!fresh) throw std::bad_alloc();
+      if (slot.compare_exchange_strong(b, fresh, std::memory_order_acq_rel)) b = fresh;
+      else free(fresh);
+    }
+    return *new (&b[id & (BLOCK - 1)]) TempSpec();
+  }
+  void destroy(u32 id) { (*this)[id].~TempSpec(); }
+
+ private:
+  std::vector<std::atomic<TempSpec*>> blocks_;
 };
 
 double now_s() {
@@ -107,11 +198,16 @@ std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::
 }
 
 long Plan::find(const LogicalSpec& ls) const {
-  std::string k = ls.key();
-  auto it = std::lower_bound(sorted_keys_.begin(), sorted_keys_.end(), k,
-                             [](const std::pair<std::string, u32>& a, const std::string& b) { return a.first < b; });
-  if (it == sorted_keys_.end() || it->first != k) return -1;
-  return it->second;
+  if (find_tab_.empty()) return -1;
+  char buf[LogicalSpec::MAX_KEY];
+  const int len = ls.key_into(buf);
+  const u64 h = hash_key(buf, len);
+  const size_t mask = find_tab_.size() - 1;
+  for (size_t i = (size_t)h & mask;; i = (i + 1) & mask) {
+    const u32 id = find_tab_[i];
+    if (id == 0xFFFFFFFFu) return -1;
+    if (specs[id] == ls) return id;
+  }
 }
 
 bool Plan::pack_limits(const u64 limits[NMEM], u32* out) const {
@@ -144,41 +240,36 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 
   // ---- 1. discovery: closure of the goals under "is a sub-Spec of some candidate" ----
   double t0 = now_s();
-  std::vector<Shard> shards(NSHARD);
-  std::vector<TempSpec> temp;
+  std::vector<KeyShard> shards(NSHARD);
+  TempSpecs temp;
   std::atomic<u32> next_id{0};
-  auto shard_of = [&](const std::string& k) -> Shard& { return shards[std::hash<std::string>()(k) % NSHARD]; };
 
-  std::vector<u32> frontier;
-  {
-    for (const LogicalSpec& g0 : goals) {
-      LogicalSpec g = g0;
-      if (logicalspec_canonicalize(g) != CANON_OK) throw ModelError("goal Spec cannot be canonicalized: " + g0.str());
-      std::string k = g.key();
-      Shard& sh = shard_of(k);
-      auto it = sh.map.find(k);
-      if (it == sh.map.end()) {
-        u32 id = next_id++;
-        sh.map.emplace(k, id);
-        TempSpec ts;
-        ts.ls = g;
-        ts.key = k;
-        temp.push_back(std::move(ts));
-        frontier.push_back(id);
-        plan.goal_ids.push_back(id);
-      } else {
-        plan.goal_ids.push_back(it->second);
-      }
+  plan.goal_ids.assign(goals.size(), 0);
+  parallel_for(goals.size(), n_threads, [&](size_t gi, int) {
+    LogicalSpec g = goals[gi];
+    if (logicalspec_canonicalize(g) != CANON_OK) throw ModelError("goal Spec cannot be canonicalized: " + goals[gi].str());
+    char kb[LogicalSpec::MAX_KEY];
+    const int kl = g.key_into(kb);
+    const u64 h = hash_key(kb, kl);
+    bool inserted = false;
+    const u32 id = shards[h % NSHARD].find_or_insert(h, kb, kl, [&]() { return next_id++; }, &inserted);
+    if (inserted) {
+      TempSpec& ts = temp.construct(id);
+      ts.ls = g;
+      ts.key.assign(kb, (size_t)kl);
     }
-  }
-  plan.stats.n_goal_specs = frontier.size();
+    plan.goal_ids[gi] = id;
+  });
+  plan.stats.n_goal_specs = next_id.load();
 
-  while (!frontier.empty()) {
-    struct NewSpec { u32 id; LogicalSpec ls; std::string key; };
-    std::vector<std::vector<NewSpec>> fresh(n_threads);
-    parallel_for(frontier.size(), n_threads, [&](size_t fi, int tid) {
-      TempSpec& ts = temp[frontier[fi]];
-      std::vector<Candidate> cs;
+  // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
+  for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
+    struct alignas(128) PerThread { std::vector<Candidate> scratch; };
+    std::vector<PerThread> per_thread(n_threads);
+    parallel_for(round_hi - round_lo, n_threads, [&](size_t fi, int tid) {
+      TempSpec& ts = temp[round_lo + (u32)fi];
+      std::vector<Candidate>& cs = per_thread[tid].scratch;
+      cs.clear();
       tabulate_candidates(ts.ls, cs);
       ts.cands.reserve(cs.size());
       for (const Candidate& c : cs) {
@@ -195,63 +286,79 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         r.thr_code = (u8)thr;
         r.peak_code = (c.kind == CK_LEAF) ? (u8)code_ceil(c.level, c.units) : 0;
         for (int j = 0; j < c.nchild; j++) {
-          std::string k = c.child[j].key();
-          Shard& sh = shard_of(k);
-          u32 id;
-          {
-            std::lock_guard<std::mutex> g(sh.mu);
-            auto it = sh.map.find(k);
-            if (it != sh.map.end()) id = it->second;
-            else {
-              id = next_id++;
-              sh.map.emplace(k, id);
-              fresh[tid].push_back(NewSpec{id, c.child[j], k});
-            }
+          char kb[LogicalSpec::MAX_KEY];
+          const int kl = c.child[j].key_into(kb);
+          const u64 h = hash_key(kb, kl);
+          bool inserted = false;
+          const u32 id = shards[h % NSHARD].find_or_insert(h, kb, kl, [&]() { return next_id++; }, &inserted);
+          if (inserted) {
+            TempSpec& fresh = temp.construct(id);
+            fresh.ls = c.child[j];
+            fresh.key.assign(kb, (size_t)kl);
           }
           r.child[j] = id;
         }
         ts.cands.push_back(r);
       }
     });
-    frontier.clear();
-    temp.resize(next_id.load());
-    for (auto& v : fresh)
-      for (auto& ns : v) {
-        temp[ns.id].ls = ns.ls;
-        temp[ns.id].key = std::move(ns.key);
-        frontier.push_back(ns.id);
-      }
-    std::sort(frontier.begin(), frontier.end());
   }
-  const u32 n = (u32)temp.size();
+  { std::vector<KeyShard>().swap(shards); }
+  const u32 n = next_id.load();
   plan.stats.seconds_discover = now_s() - t0;
 
   // ---- 2. final ids: stage-major (phase, log-shape sum, memory-level sum), then key order ----
   double t1 = now_s();
   std::vector<u32> order(n);
-  for (u32 i = 0; i < n; i++) order[i] = i;
   std::vector<u32> gkey(n);
   for (u32 i = 0; i < n; i++) gkey[i] = stage_key(temp[i].ls);
-  std::sort(order.begin(), order.end(), [&](u32 a, u32 b) {
-    if (gkey[a] != gkey[b]) return gkey[a] < gkey[b];
-    return temp[a].key < temp[b].key;
-  });
+  {
+    // bucket by stage key, then sort every bucket by Spec key on all threads
+    std::vector<u32> uniq(gkey);
+    std::sort(uniq.begin(), uniq.end());
+    uniq.erase(std::unique(uniq.begin(), uniq.end()), uniq.end());
+    std::vector<u32> start(uniq.size() + 1, 0);
+    std::vector<u32> bucket(n);
+    for (u32 i = 0; i < n; i++) {
+      bucket[i] = (u32)(std::lower_bound(uniq.begin(), uniq.end(), gkey[i]) - uniq.begin());
+      start[bucket[i] + 1]++;
+    }
+    for (size_t b = 0; b < uniq.size(); b++) start[b + 1] += start[b];
+    std::vector<u32> cur(start.begin(), start.end() - 1);
+    for (u32 i = 0; i < n; i++) order[cur[bucket[i]]++] = i;
+    std::vector<u32> by_size(uniq.size());
+    for (u32 b = 0; b < uniq.size(); b++) by_size[b] = b;
+    std::sort(by_size.begin(), by_size.end(), [&](u32 a, u32 b) { return start[a + 1] - start[a] > start[b + 1] - start[b]; });
+    std::atomic<size_t> nextb{0};
+    std::vector<std::thread> pool;
+    for (int t = 0; t < n_threads; t++)
+      pool.emplace_back([&]() {
+        for (;;) {
+          const size_t k = nextb.fetch_add(1);
+          if (k >= by_size.size()) break;
+          const u32 b = by_size[k];
+          std::sort(order.begin() + start[b], order.begin() + start[b + 1],
+                    [&](u32 x, u32 y) { return temp[x].key < temp[y].key; });
+        }
+      });
+    for (auto& th : pool) th.join();
+  }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort ids %.2fs\n", now_s() - t1);
   std::vector<u32> new_id(n);
   for (u32 i = 0; i < n; i++) new_id[order[i]] = i;
   for (u32& g : plan.goal_ids) g = new_id[g];
 
-  plan.specs.resize(n);
-  plan.hdrs.resize(n);
+  plan.specs.reset(n);
+  plan.hdrs.reset(n);
   u64 ncand = 0;
   for (u32 i = 0; i < n; i++) ncand += temp[order[i]].cands.size();
   if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
-  plan.cands.resize(ncand);
+  plan.cands.reset(ncand);
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]     counted cands %.2fs\n", now_s() - t1);
   {
     std::vector<u64> offs(n + 1, 0);
     for (u32 i = 0; i < n; i++) offs[i + 1] = offs[i] + temp[order[i]].cands.size();
-    plan.sorted_keys_.resize(n);
     std::vector<u64> kids_t(n_threads, 0);
+    if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]     offsets %.2fs\n", now_s() - t1);
     parallel_for(n, n_threads, [&](size_t i, int tid) {
       TempSpec& ts = temp[order[i]];
       plan.specs[i] = ts.ls;
@@ -270,21 +377,39 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         };
         return rank(a) < rank(b);
       });
+      u64 kids = 0;
       for (CandRec r : ts.cands) {
         for (int j = 0; j < r.nchild; j++) r.child[j] = new_id[r.child[j]];
-        kids_t[tid] += r.nchild;
+        kids += r.nchild;
         plan.cands[off++] = r;
       }
-      plan.sorted_keys_[i] = {std::move(ts.key), (u32)i};
-      std::vector<CandRec>().swap(ts.cands);
+      __atomic_fetch_add(&kids_t[0], kids, __ATOMIC_RELAXED);
     });
     for (u64 k : kids_t) plan.stats.n_children += k;
   }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   move specs+cands %.2fs\n", now_s() - t1);
-  std::vector<TempSpec>().swap(temp);
+  parallel_for(n, n_threads, [&](size_t i, int) { temp.destroy((u32)i); });
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   free temp %.2fs\n", now_s() - t1);
-  std::sort(plan.sorted_keys_.begin(), plan.sorted_keys_.end());
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort keys %.2fs\n", now_s() - t1);
+  // id lookup table for find(): open addressing over the Spec key hash, ids only (equality is
+  // checked on the Spec itself)
+  {
+    size_t cap = 64;
+    while (cap < (size_t)n * 2) cap *= 2;
+    plan.find_tab_.assign(cap, 0xFFFFFFFFu);
+    std::vector<u64> hs(n);
+    parallel_for(n, n_threads, [&](size_t i, int) {
+      char kb[LogicalSpec::MAX_KEY];
+      const int kl = plan.specs[i].key_into(kb);
+      hs[i] = hash_key(kb, kl);
+    });
+    const size_t mask = cap - 1;
+    for (u32 i = 0; i < n; i++) {
+      size_t j = (size_t)hs[i] & mask;
+      while (plan.find_tab_[j] != 0xFFFFFFFFu) j = (j + 1) & mask;
+      plan.find_tab_[j] = i;
+    }
+  }
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   find table %.2fs\n", now_s() - t1);
 
   // stages, and inside them families: maximal runs with equal dtype and shape (ids are
   // key-sorted, and the key starts with kind, dtype, serial flag, rank, shape)

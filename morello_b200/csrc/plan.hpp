@@ -17,10 +17,48 @@
 #include "model/actions.hpp"
 #include "model/space.hpp"
 #include "device_types.h"
+#include <cstdlib>
+#include <new>
 #include <string>
 #include <vector>
 
 namespace mrl {
+
+// Uninitialised storage for plain records. Nothing is written at allocation, so the pages of a
+// large array are first touched by the threads that fill it, in parallel.
+template <class T>
+class RawVec {
+ public:
+  RawVec() {}
+  ~RawVec() { free(p_); }
+  RawVec(const RawVec&) = delete;
+  RawVec& operator=(const RawVec&) = delete;
+  RawVec(RawVec&& o) noexcept : p_(o.p_), n_(o.n_) { o.p_ = nullptr; o.n_ = 0; }
+  RawVec& operator=(RawVec&& o) noexcept {
+    if (this != &o) { free(p_); p_ = o.p_; n_ = o.n_; o.p_ = nullptr; o.n_ = 0; }
+    return *this;
+  }
+  void reset(size_t n) {
+    free(p_);
+    p_ = nullptr;
+    n_ = 0;
+    if (n) {
+      p_ = static_cast<T*>(malloc(n * sizeof(T)));
+      if (!p_) throw std::bad_alloc();
+      n_ = n;
+    }
+  }
+  size_t size() const { return n_; }
+  bool empty() const { return n_ == 0; }
+  T* data() { return p_; }
+  const T* data() const { return p_; }
+  T& operator[](size_t i) { return p_[i]; }
+  const T& operator[](size_t i) const { return p_[i]; }
+
+ private:
+  T* p_ = nullptr;
+  size_t n_ = 0;
+};
 
 struct PlanStats {
   u64 n_specs = 0;
@@ -56,9 +94,9 @@ struct Family {
 };
 
 struct Plan {
-  std::vector<LogicalSpec> specs;        // by id
-  std::vector<SpecHdr> hdrs;             // by id; masks and row_base are filled in on the device
-  std::vector<CandRec> cands;
+  RawVec<LogicalSpec> specs;             // by id
+  RawVec<SpecHdr> hdrs;                  // by id; masks and row_base are filled in on the device
+  RawVec<CandRec> cands;
   int n_threads = 1;
   std::vector<Stage> stages;
   std::vector<Family> families;
@@ -83,7 +121,7 @@ struct Plan {
 
  private:
   friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32);
-  std::vector<std::pair<std::string, u32>> sorted_keys_;  // (key, id), sorted by key
+  std::vector<u32> find_tab_;  // open-addressing table of ids by Spec key hash (0xFFFFFFFF = empty)
 };
 
 // Top limits are Avx2Target::max_mem() unless overridden.
