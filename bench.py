@@ -4,19 +4,19 @@
   python bench.py --gpus N --steps K --warmup W            # the CUDA path
   python bench.py --impl reference --gpus N --steps K ...  # the reference algorithm on host cores
 
-One step = one complete fill of the workload's database. The workload is the precompute of
-every canonical Move / Zero / Matmul Spec with dimensions in {1, 2, 4} over {u32, f32} on the
-Avx2 target with default memory limits (`precompute --target avx2 --through matmul 4`): the part
-of BASELINE config 2 (dimensions up to 8) whose tables fit one GPU today - 410 954 goal logical
-Specs, 641 818 with their dependency closure. `--size 2` runs the closure of `morello matmul 2`
-(BASELINE config 1) instead. All inputs are synthetic by construction: the Spec space is
+One step = one complete fill of the workload's database. The workload is BASELINE config 2:
+the precompute of every canonical Move / Zero / Matmul Spec with dimensions in {1, 2, 4, 8} over
+{u32, f32} on the Avx2 target with default memory limits (`precompute --target avx2 --through
+matmul 8`): 10.6 M goal logical Specs, 14.7 M with their dependency closure, 400 M candidate
+records. `--size 4` and `--size 2` run the smaller precomputes (size 2 is the closure of `morello
+matmul 2`, BASELINE config 1). All inputs are synthetic by construction: the Spec space is
 generated from the size alone.
 
 Unit of work ("Spec resolved"): one (logical Spec, memory limits) entry of the database made
-answerable. Both arms cover the same entries - every logical Spec of the workload over the
+answerable. Both arms cover the same entries - every goal logical Spec of the workload over the
 whole 17 x 17 x 12 x 27 limits lattice of the target - so the figure is the same numerator
-divided by each arm's time. The CUDA arm also reports how many rows it actually computed and
-the reference arm how many solves (`put`s) it needed. At size 4 the CPU arm cannot finish in
+divided by each arm's time. The CUDA arm also reports how many cells it solved directly and
+the reference arm how many solves (`put`s) it needed. Beyond size 2 the CPU arm cannot finish in
 bench time: it runs the reference's stage order under a time budget and counts the goal Specs
 it completed (the cheap early stages - Moves, small shapes - come first, so this sample
 flatters the CPU).
@@ -33,8 +33,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 LATTICE_POINTS = 17 * 17 * 12 * 27  # RF 0..16, VRF 0..16, L1 and GL as bit lengths (avx2.rs:59-65)
-SIZE = 4
-GOAL_SPECS = {1: 180, 2: 10454, 4: 410954}  # canonical goal Specs of the precompute of each size
+SIZE = 8
+GOAL_SPECS = {1: 180, 2: 10454, 4: 410954, 8: 10613126}  # canonical goal Specs of the precompute of each size
 
 
 def workload_name():
@@ -159,30 +159,32 @@ def cuda_arm(args):
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device: the fill has no CPU path")
 
-    # N > 1: ONE database fill sharded over the ranks (families of a group are split between the
-    # GPUs, rows are broadcast between groups), so total work is fixed: strong scaling.
+    # N > 1: ONE database fill sharded over the ranks (the families of a stage are split between
+    # the GPUs, masks and rows are summed over the ranks per stage), so total work is fixed:
+    # strong scaling.
     from morello_b200 import sharded
     db = m.SynthesisDatabase(device=local_rank)
 
     def one_fill():
         if world > 1:
-            rc, _ = sharded.fill_sharded(db, dist, torch)
-            assert rc == 0
+            sharded.fill_sharded(db, dist, torch)
         else:
             db.fill()
 
     if world > 1:
         sharded.precompute_sharded(db, SIZE, dist, torch)
     else:
-        db.precompute(SIZE)  # plans, finds lattice caps that lose nothing, leaves plan and tables on the device
-    for _ in range(max(args.warmup, 3)):
+        db.precompute(SIZE)  # plans, uploads, fills: leaves plan and tables on the device
+    for _ in range(max(args.warmup, 3) - 1):
         one_fill()
 
     # End to end through the public call: host planning, host->device copy of the plan, the fill,
-    # and a device->host read of every goal Spec's decision at the top limits.
-    goal_blobs = [db.spec_blob(i) for i in range(0, db.num_specs(), max(1, db.num_specs() // 512))]
+    # and a device->host read of a sample of the goal Specs' decisions at the top limits.
+    n_specs = db.num_specs()
+    goal_blobs = [db.spec_blob(i) for i in range(0, n_specs, max(1, n_specs // 512))]
     e2e_s = []
-    for i in range(1 + max(1, min(args.steps, 3))):
+    e2e_runs = 1 if SIZE >= 8 else 3
+    for i in range((0 if SIZE >= 8 else 1) + e2e_runs):   # small sizes: one untimed run first
         fresh = m.SynthesisDatabase(device=local_rank)  # a new database: nothing carried over
         if world > 1:
             dist.barrier()
@@ -193,10 +195,10 @@ def cuda_arm(args):
             fresh.precompute(SIZE)
         got = fresh.get_many(goal_blobs, [m.MAX_MEM] * len(goal_blobs))
         dt = time.perf_counter() - t0
-        if i > 0:
-            e2e_s.append(dt)
+        e2e_s.append(dt)
         st2 = fresh.stats()
         fresh.close()
+    e2e_s = e2e_s[-e2e_runs:]
     assert all(g.found in (0, 1) for g in got)
     e2e_step = sorted(e2e_s)[len(e2e_s) // 2]  # median
     if world > 1:
@@ -211,49 +213,63 @@ def cuda_arm(args):
     if rank == 0:
         sampler.start()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
-    fill_ms = []
+    fill_ms, combine_ms, launches = [], [], 0
     for _ in range(args.steps):
         flush.fill_(1)
         torch.cuda.synchronize()
         one_fill()  # device time measured inside with CUDA events on the launching stream
-        fill_ms.append(db.stats()["fill_ms"])
+        s1 = db.stats()
+        fill_ms.append(s1["fill_ms"])
+        combine_ms.append(s1["combine_ms"])
+        launches += int(s1["n_launches"])
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     clocks = sampler.stop() if rank == 0 else None
     st = db.stats()
     total_ms = sum(fill_ms)
+    alg_bytes = float(st["algorithmic_bytes"])   # of this rank's solves
     if world > 1:
         t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
+        t = torch.tensor([float(launches)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        launches = int(t.item())
     ms_per_step = total_ms / args.steps
+    combine_ms_per_step = sum(combine_ms) / args.steps
 
     lspecs = st["n_goal_specs"]      # the Specs the workload asks for (the closure adds more rows, not more units)
     units = lspecs * LATTICE_POINTS  # one database, however many GPUs fill it
     hbm_gbs, peak_kind = measured_peaks()
-    achieved = st["algorithmic_bytes"] / (ms_per_step * 1e-3) / 1e9
+    # the dominant kernel: algorithmic bytes of its launches / CUDA-event time inside its launches
+    achieved = alg_bytes / (combine_ms_per_step * 1e-3) / 1e9
+    table_gb = st["n_rows"] * 16 / 1e9
+    plan_gb = (st["n_candidates"] * 32 + st["n_specs"] * 48) / 1e9
     line = {
         "metric": "specs_resolved_per_s", "value": units / (ms_per_step * 1e-3), "unit": "specs/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "u32",
         "data": "synthetic",
         "config": {"workload": workload_name(), "logical_specs": lspecs, "lattice_points_per_spec": LATTICE_POINTS,
-                   "logical_specs_with_closure": st["n_specs"], "rows_computed_per_step": st["n_rows"], "candidate_records": st["n_candidates"],
-                   "lattice_caps": st["lattice_caps"],
-                   "l2": ("row table %.1f GB, larger than L2; L2 also flushed between fills" % (st["n_rows"] * 16 / 1e9)),
-                   "multi_gpu": ("families of each group sharded over %d ranks, NCCL broadcast between groups" % world)
-                   if world > 1 else "single"},
+                   "logical_specs_with_closure": st["n_specs"], "candidate_records": st["n_candidates"],
+                   "stages": st["n_stages"], "table_rows": st["n_rows"], "cells_solved_per_step": st["n_cells_solved"],
+                   "solve_passes_per_step": st["n_passes"],
+                   "l2": ("candidate records and headers %.1f GB + table %.2f GB, larger than L2; L2 also flushed "
+                          "between fills" % (plan_gb, table_gb)),
+                   "multi_gpu": ("families of each stage sharded over %d ranks; masks and rows summed over the ranks "
+                                 "per stage (NCCL all-reduce)" % world) if world > 1 else "single"},
         "wall_s_full_db": e2e_step,
-        "rows_per_s": st["n_rows"] / (ms_per_step * 1e-3),
+        "cells_solved_per_s": st["n_cells_solved"] / (ms_per_step * 1e-3),
         "e2e": {"value": units / e2e_step, "unit": "specs/s", "h2d_bytes_per_step": st2["h2d_bytes"],
                 "d2h_bytes_per_step": st2["d2h_bytes"], "plan_s": st2["plan_seconds"],
-                "upload_s": st2["upload_seconds"], "fill_ms_all_attempts": st2["fill_ms_total"],
-                "fill_attempts": st2["fill_attempts"], "wall_s": e2e_step, "wall_s_runs": e2e_s},
-        "gpu_launches": int(st["n_launches"]) * args.steps,
+                "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "wall_s": e2e_step, "wall_s_runs": e2e_s},
+        "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "combine_argmin_kernel",
-                     "algorithmic_bytes_per_step": st["algorithmic_bytes"]},
+                     "algorithmic_bytes_per_step": st["algorithmic_bytes"], "kernel_ms_per_step": combine_ms_per_step,
+                     "kernel_launches_per_step": st["n_combine_launches"],
+                     "whole_fill_GBps": alg_bytes / (ms_per_step * 1e-3) / 1e9},
         "clocks": clocks,
     }
     if rank == 0:
@@ -268,7 +284,7 @@ def cuda_arm(args):
         traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(traffic_path):
             with open(traffic_path) as f:
-                line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_step")
+                line["roofline"]["traffic"] = json.load(f).get(str(SIZE), {}).get("dram_bytes_per_step")
         print(json.dumps(line))
     db.close()
     if world > 1:
@@ -278,11 +294,11 @@ def cuda_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--size", type=int, default=4, choices=[1, 2, 4], help="largest Spec dimension of the workload")
+    ap.add_argument("--size", type=int, default=8, choices=[1, 2, 4, 8], help="largest Spec dimension of the workload")
     ap.add_argument("--cpu-budget", type=float, default=20.0, help="seconds of CPU work per reference sample")
     args = ap.parse_args()
     global SIZE

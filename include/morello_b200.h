@@ -144,6 +144,14 @@ int mrl_fill_end(mrl_ctx* ctx);
 int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
                  mrl_decision* out);
 
+/* Self-check of the filled tables, no counterpart in the reference (its closest relative is the
+ * proptest that synthesis at peak memory yields the same decision, morello/src/search/mod.rs:152-199):
+ * at n_samples pseudo-random points of (Spec x limits lattice) - every point when n_samples is 0 -
+ * the decision recomputed on the GPU from the children's tables (morello/src/scheduling/mod.rs:286-368)
+ * must equal what the Spec's own table returns there. n_mismatch == 0 means the tables satisfy the
+ * recurrence that defines the database at every checked point. */
+int mrl_verify(mrl_ctx* ctx, uint64_t n_samples, uint64_t seed, uint64_t* n_checked, uint64_t* n_mismatch);
+
 int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out);
 
 /* Table export (the data a FilesDatabase::put stream would have produced,

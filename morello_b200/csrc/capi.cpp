@@ -393,6 +393,14 @@ int mrl_fill_end(mrl_ctx* ctx) {
   return 0;
 }
 
+int mrl_verify(mrl_ctx* ctx, uint64_t n_samples, uint64_t seed, uint64_t* n_checked, uint64_t* n_mismatch) {
+  if (!ctx) return -1;
+  if (!ctx->filled) return fail(ctx, -1, "tables are not filled");
+  uint64_t first_bad = 0;
+  if (ctx->dev.verify(ctx->plan, n_samples, seed, n_checked, n_mismatch, &first_bad) != 0) return fail(ctx, -2, ctx->dev.error());
+  return 0;
+}
+
 int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out) {
   if (!ctx || !out) return -1;
   *out = ctx->stats;

@@ -142,32 +142,17 @@ __device__ __forceinline__ Column decode_column(const SpecHdr* __restrict__ hdrs
   return c;
 }
 
-// One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes),
-// listed by scatter_cells_kernel: every thread has a cell, and neighbouring threads mostly have
-// neighbouring cells of one Spec.
-__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
-combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                      const CellRef* __restrict__ cells, uint32_t n_cells,
-                      const MrlRow* __restrict__ rows, MrlRow* __restrict__ temp, uint32_t n_specs,
-                      uint32_t* __restrict__ error_flag) {
-  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_cells) return;
-  const CellRef ref = cells[t];
-  const uint32_t spec = ref.spec;
-  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[spec]));
-  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-  uint32_t rest = ref.cell;
-  const uint32_t i0 = rest % n0; rest /= n0;
-  const uint32_t i1 = rest % n1; rest /= n1;
-  const uint32_t i2 = rest % n2;
-  const uint32_t i3 = rest / n2;
-  const uint32_t cpack = nth_set_bit(m.x, i0) | (nth_set_bit(m.y, i1) << 8) | (nth_set_bit(m.z, i2) << 16) |
-                         (nth_set_bit(m.w, i3) << 24);
-  // "codes at or below this cell's limit", per memory: what a child lookup at the same limits needs
+// The direct solve of one (Spec, limits) point from the tables of the Spec's children: walks the
+// candidate records, applies the limits-dependent feasibility tests, gathers the child rows at
+// the children's limits, combines them and keeps the lexicographic minimum. cpack = the limits
+// as lattice codes (RF in byte 0 .. GL in byte 3).
+__device__ __forceinline__ Key solve_point(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
+                                           const MrlRow* __restrict__ rows, const MrlRow* __restrict__ temp,
+                                           uint32_t spec, uint32_t cpack, uint32_t n_specs,
+                                           uint32_t* __restrict__ error_flag) {
+  // "codes at or below this point's limit", per memory: what a child lookup at the same limits needs
   const uint32_t bm0 = (2u << code_of(cpack, 0)) - 1u, bm1 = (2u << code_of(cpack, 1)) - 1u,
                  bm2 = (2u << code_of(cpack, 2)) - 1u, bm3 = (2u << code_of(cpack, 3)) - 1u;
-
-  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[spec].row_base));
   const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[spec].cand_off));
   const uint32_t cand_off = cl.x, ncand = cl.y;
 
@@ -205,7 +190,7 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
       }
 #ifdef MRL_CHECK_CHILD_IDS
       if (b.x >= n_specs || (nchild > 1 && b.y >= n_specs) || (nchild > 2 && b.z >= n_specs)) {
-        atomicExch(error_flag, 1u);
+        if (error_flag) atomicExch(error_flag, 1u);
         continue;
       }
 #endif
@@ -250,8 +235,72 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
     }
     if (key_less(k, best)) best = k;
   }
+  return best;
+}
+
+// One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes),
+// listed by scatter_cells_kernel: every thread has a cell, and neighbouring threads mostly have
+// neighbouring cells of one Spec.
+__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
+combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
+                      const CellRef* __restrict__ cells, uint32_t n_cells,
+                      const MrlRow* __restrict__ rows, MrlRow* __restrict__ temp, uint32_t n_specs,
+                      uint32_t* __restrict__ error_flag) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_cells) return;
+  const CellRef ref = cells[t];
+  const uint32_t spec = ref.spec;
+  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[spec]));
+  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+  uint32_t rest = ref.cell;
+  const uint32_t i0 = rest % n0; rest /= n0;
+  const uint32_t i1 = rest % n1; rest /= n1;
+  const uint32_t i2 = rest % n2;
+  const uint32_t i3 = rest / n2;
+  const uint32_t cpack = nth_set_bit(m.x, i0) | (nth_set_bit(m.y, i1) << 8) | (nth_set_bit(m.z, i2) << 16) |
+                         (nth_set_bit(m.w, i3) << 24);
+  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[spec].row_base));
+  const Key best = solve_point(hdrs, cands, rows, temp, spec, cpack, n_specs, error_flag);
   // Specs of the stage being solved always live in the working buffer.
   *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + ref.cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
+}
+
+// Consistency check of a finished table: at sampled (or all) points of the limits lattice, for
+// sampled (or all) Specs, the direct solve from the children's tables must equal what the Spec's
+// own table returns there. Every point where that holds is a point where the table satisfies
+// the defining recurrence of the fill, whatever grid the table is stored on.
+__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
+verify_points_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
+                     const MrlRow* __restrict__ rows, uint32_t n_specs, uint32_t top_pack, unsigned long long first,
+                     unsigned long long count, unsigned long long total_points, unsigned long long seed, int exhaustive,
+                     unsigned long long* __restrict__ out /* [0] mismatches, [1] first bad sample + 1 */) {
+  const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const uint32_t e0 = code_of(top_pack, 0) + 1, e1 = code_of(top_pack, 1) + 1, e2 = code_of(top_pack, 2) + 1,
+                 e3 = code_of(top_pack, 3) + 1;
+  const unsigned long long per_spec = (unsigned long long)e0 * e1 * e2 * e3;
+  unsigned long long s = first + i;
+  if (!exhaustive) {
+    // splitmix64 of (seed, sample index): a point of the (Spec x lattice) product
+    unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (s + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    s = z % total_points;
+  }
+  const uint32_t spec = (uint32_t)(s / per_spec);
+  uint32_t p = (uint32_t)(s % per_spec);
+  const uint32_t c0 = p % e0; p /= e0;
+  const uint32_t c1 = p % e1; p /= e1;
+  const uint32_t c2 = p % e2;
+  const uint32_t c3 = p / e2;
+  const uint32_t cpack = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+  const Key k = solve_point(hdrs, cands, rows, rows, spec, cpack, n_specs, nullptr);
+  const uint4 r = lookup(hdrs, rows, rows, spec, (2u << c0) - 1u, (2u << c1) - 1u, (2u << c2) - 1u, (2u << c3) - 1u);
+  if (k.main != r.x || k.peaks != r.y || k.tail != r.z) {
+    atomicAdd(&out[0], 1ull);
+    atomicMin(&out[1], first + i);
+  }
 }
 
 // ---- working grids ---------------------------------------------------------------------
@@ -1107,6 +1156,37 @@ int DeviceFill::lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t 
     CK(cudaMemcpyAsync(out + done, d_out, m * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
     CK(cudaStreamSynchronize(stream_));
   }
+  return 0;
+}
+
+// Checks the finished table against its defining recurrence at n_samples pseudo-random points of
+// (Spec x limits lattice), or at every point when n_samples == 0.
+int DeviceFill::verify(const Plan& plan, uint64_t n_samples, uint64_t seed, uint64_t* checked, uint64_t* mismatches,
+                       uint64_t* first_bad) {
+  CK(cudaSetDevice(device_));
+  const uint32_t top = plan.top_pack();
+  unsigned long long per_spec = 1;
+  for (int k = 0; k < 4; k++) per_spec *= ((top >> (8 * k)) & 0xFFu) + 1u;
+  const unsigned long long total = per_spec * n_specs_;
+  const bool exhaustive = n_samples == 0;
+  const unsigned long long count = exhaustive ? total : n_samples;
+  unsigned long long* d_out = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(d_ctr_) + 96);
+  const unsigned long long init[2] = {0ull, ~0ull};
+  CK(cudaMemcpyAsync(d_out, init, sizeof(init), cudaMemcpyHostToDevice, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  const unsigned long long batch = 1ull << 28;
+  for (unsigned long long first = 0; first < count && total; first += batch) {
+    const unsigned long long n = std::min(batch, count - first);
+    verify_points_kernel<<<(unsigned)((n + 127) / 128), 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rows_, n_specs_, top, first, n,
+                                                                          total, seed, exhaustive ? 1 : 0, d_out);
+    CK(cudaGetLastError());
+  }
+  unsigned long long res[2] = {0, 0};
+  CK(cudaMemcpyAsync(res, d_out, sizeof(res), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  if (checked) *checked = total ? count : 0;
+  if (mismatches) *mismatches = res[0];
+  if (first_bad) *first_bad = res[1];
   return 0;
 }
 

@@ -41,6 +41,8 @@ class DeviceFill {
   int set_stream(cudaStream_t s);
   // Point lookups: rows of (Spec id, packed limit codes).
   int lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t n, MrlRow* out);
+  int verify(const Plan& plan, uint64_t n_samples, uint64_t seed, uint64_t* checked, uint64_t* mismatches,
+             uint64_t* first_bad);
   int read_hdr(uint32_t spec, SpecHdr* out);
   int read_rows(uint64_t first, uint64_t n, MrlRow* out);
   void release();

@@ -210,6 +210,14 @@ class SynthesisDatabase:
     def fill_end(self):
         self._check(self._lib.mrl_fill_end(self._ctx))
 
+    def verify(self, n_samples: int = 0, seed: int = 1):
+        """(points checked, mismatches): recomputes the decision from the children's tables at
+        n_samples pseudo-random (Spec, limits) points - all of them when n_samples is 0 - and
+        compares with the table."""
+        checked, bad = C.c_uint64(), C.c_uint64()
+        self._check(self._lib.mrl_verify(self._ctx, n_samples, seed, C.byref(checked), C.byref(bad)))
+        return int(checked.value), int(bad.value)
+
     # --- export / stats ---
     def stats(self) -> dict:
         s = L.Stats()

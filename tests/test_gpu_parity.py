@@ -108,9 +108,9 @@ def test_edge_cases(m):
 
 
 def test_precompute_size4_matches_a_bounded_oracle_run(m, oracle):
-    """Size 4 (642 k logical Specs with the closure, billions of rows): the oracle cannot finish
-    it in test time, so it runs its faithful stage order under a time budget and every put it
-    made so far is checked against the full GPU tables."""
+    """Size 4 (642 k logical Specs with the closure): the oracle cannot finish it in test time, so
+    it runs its faithful stage order under a time budget and every put it made so far is checked
+    against the full GPU tables."""
     import os
     o = oracle.new()
     rep = o.precompute(4, threads=os.cpu_count() or 1, budget_s=25.0)
@@ -124,3 +124,53 @@ def test_precompute_size4_matches_a_bounded_oracle_run(m, oracle):
     assert not bad, "\n".join(bad)
     db.close()
     o.close()
+
+
+def test_size2_tables_satisfy_the_recurrence_at_every_lattice_point(m):
+    """Property over the whole table, independent of the oracle: at every one of the 93 636
+    limits of every Spec, re-deriving the decision from the children's tables gives the stored
+    decision. By induction over the lattice this pins the table to the direct solve everywhere,
+    including inside the cells of the compacted grids."""
+    db = m.SynthesisDatabase()
+    st = db.precompute(2)
+    checked, bad = db.verify(0)
+    assert checked == st["n_specs"] * 17 * 17 * 12 * 27 and bad == 0
+    db.close()
+
+
+def test_verify_notices_a_corrupted_row(m):
+    import torch
+    from morello_b200 import sharded
+    db = m.SynthesisDatabase()
+    db.precompute(1)
+    assert db.verify(0)[1] == 0
+    ptr, n = db.device_rows()
+    rows = torch.as_tensor(sharded._DeviceBytes(ptr, n * sharded.row_bytes()), device="cuda").view(torch.int32)
+    rows[4 * (n // 2)] += 1      # main cost of one row in the middle of the table
+    torch.cuda.synchronize()
+    assert db.verify(0)[1] > 0
+    db.close()
+
+
+def test_size8_full_workload_properties(m):
+    """BASELINE config 2 at full size (10.6 M goal Specs): the recurrence at 500 M random
+    (Spec, limits) points, and a second fill reproduces the table bit for bit."""
+    import torch
+    from morello_b200 import sharded
+    db = m.SynthesisDatabase()
+    st = db.precompute(8)
+    assert st["n_goal_specs"] == 10613126
+    checked, bad = db.verify(500_000_000, seed=7)
+    assert checked == 500_000_000 and bad == 0
+    ptr, n = db.device_rows()
+    before = torch.as_tensor(sharded._DeviceBytes(ptr, n * sharded.row_bytes()), device="cuda").clone()
+    db.fill()
+    ptr2, n2 = db.device_rows()
+    assert n2 == n
+    after = torch.as_tensor(sharded._DeviceBytes(ptr2, n2 * sharded.row_bytes()), device="cuda")
+    assert torch.equal(before, after)
+    # known answers of the small goals still hold inside the big database
+    goal = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
+    d = db.get(goal)
+    assert (d.found, d.action, d.main_cost, d.depth, d.peaks) == (1, 1, 127, 7, (8, 0, 4, 0))
+    db.close()
