@@ -125,6 +125,14 @@ int mrl_fill(mrl_ctx* ctx);
  *                     mrl_fill_stage_place(s, &rows, &n); sum rows }; mrl_fill_end.
  * masks: the limits-grid breakpoints of the stage's Specs; rows: their finished table rows. */
 int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world);
+/* The ranks of one node share its host cores, so only one of them should plan: it exposes its
+ * plan as eight flat host byte ranges (mrl_plan_share), the caller carries the bytes to the other
+ * ranks (e.g. ncclBroadcast through device staging), which receive them into ranges of the same
+ * sizes (mrl_plan_adopt gives the pointers) and finish with mrl_plan_adopt_done. The planning rank
+ * must have called mrl_set_shard with the same world size before planning. */
+int mrl_plan_share(mrl_ctx* ctx, void* ptrs[8], uint64_t sizes[8]);
+int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8]);
+int mrl_plan_adopt_done(mrl_ctx* ctx, double plan_seconds);
 int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream);
 uint64_t mrl_num_stages(const mrl_ctx* ctx);
 uint64_t mrl_num_families(const mrl_ctx* ctx);

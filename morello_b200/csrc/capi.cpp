@@ -323,6 +323,48 @@ int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream) {
   return ctx->dev.set_stream((cudaStream_t)cuda_stream);
 }
 
+int mrl_plan_share(mrl_ctx* ctx, void* ptrs[8], uint64_t sizes[8]) {
+  if (!ctx || !ptrs || !sizes) return -1;
+  if (!ctx->planned) return fail(ctx, -1, "nothing planned");
+  u64 sz[Plan::N_BLOBS];
+  ctx->plan.share_blobs(ptrs, sz);
+  for (int k = 0; k < Plan::N_BLOBS; k++) sizes[k] = sz[k];
+  return 0;
+}
+
+int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8]) {
+  if (!ctx || !sizes || !ptrs) return -1;
+  try {
+    u64 sz[Plan::N_BLOBS];
+    for (int k = 0; k < Plan::N_BLOBS; k++) sz[k] = sizes[k];
+    ctx->plan = Plan();
+    ctx->planned = ctx->uploaded = ctx->filled = false;
+    ctx->plan.adopt_alloc(sz);
+    ctx->plan.share_blobs(ptrs, sz);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
+}
+
+int mrl_plan_adopt_done(mrl_ctx* ctx, double plan_seconds) {
+  if (!ctx) return -1;
+  try {
+    ctx->plan.adopt_done(ctx->rank, ctx->world, ctx->n_threads);
+    const PlanStats& ps = ctx->plan.stats;
+    memset(&ctx->stats, 0, sizeof(ctx->stats));
+    ctx->stats.n_specs = ps.n_specs;
+    ctx->stats.n_goal_specs = ps.n_goal_specs;
+    ctx->stats.n_candidates = ps.n_cands;
+    ctx->stats.n_stages = ps.n_stages;
+    ctx->stats.plan_seconds = plan_seconds;
+    ctx->planned = true;
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
+}
+
 uint64_t mrl_num_stages(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.stages.size() : 0; }
 uint64_t mrl_num_families(const mrl_ctx* ctx) { return ctx && ctx->planned ? ctx->plan.families.size() : 0; }
 

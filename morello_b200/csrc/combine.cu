@@ -31,6 +31,7 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <algorithm>
 #include <mutex>
@@ -766,6 +767,7 @@ int DeviceFill::init(int device) {
 }
 
 int DeviceFill::init_events() {
+  stage_log_ = getenv("MRL_STAGE_LOG") != nullptr;
   if (!ev0_) CK(cudaEventCreate(&ev0_));
   if (!ev1_) CK(cudaEventCreate(&ev1_));
   return 0;
@@ -1037,6 +1039,8 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
     CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
     real_masks_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_temp_, d_rmask_);
     CK(cudaGetLastError());
+    if (stage_log_) fprintf(stderr, "[fill] stage %u (phase %u, shape %u, level %u, %u Specs) pass %d: %llu cells, %u chunks\n", si,
+                            st.phase, st.shape_sum, st.level_rank, n, pass, (unsigned long long)c.cells, n_chunks);
     stats_.launches += 4;
     stats_.passes++;
     stats_.cells_solved += c.cells;

@@ -92,6 +92,7 @@ class DeviceFill {
   uint64_t last_cells_ = 0;             // working cells of the last pass of the stage being solved
   uint64_t h2d_bytes_ = 0;
   bool filling_ = false;
+  bool stage_log_ = false;              // MRL_STAGE_LOG: one line per solve pass on stderr
   FillStats stats_;
   cudaStream_t stream_ = nullptr;
   bool own_stream_ = false;

@@ -210,6 +210,61 @@ long Plan::find(const LogicalSpec& ls) const {
   }
 }
 
+void Plan::share_blobs(void* ptrs[N_BLOBS], u64 sizes[N_BLOBS]) {
+  for (int k = 0; k < NMEM; k++) meta_.top_code[k] = top_code[k];
+  meta_.world = world;
+  meta_.pad = 0;
+  meta_.stats = stats;
+  ptrs[0] = &meta_;              sizes[0] = sizeof(Meta);
+  ptrs[1] = specs.data();        sizes[1] = specs.size() * sizeof(LogicalSpec);
+  ptrs[2] = hdrs.data();         sizes[2] = hdrs.size() * sizeof(SpecHdr);
+  ptrs[3] = cands.data();        sizes[3] = cands.size() * sizeof(CandRec);
+  ptrs[4] = stages.data();       sizes[4] = stages.size() * sizeof(Stage);
+  ptrs[5] = families.data();     sizes[5] = families.size() * sizeof(Family);
+  ptrs[6] = goal_ids.data();     sizes[6] = goal_ids.size() * sizeof(u32);
+  ptrs[7] = find_tab_.data();    sizes[7] = find_tab_.size() * sizeof(u32);
+}
+
+void Plan::adopt_alloc(const u64 sizes[N_BLOBS]) {
+  if (sizes[0] != sizeof(Meta) || sizes[1] % sizeof(LogicalSpec) || sizes[2] % sizeof(SpecHdr) ||
+      sizes[3] % sizeof(CandRec) || sizes[4] % sizeof(Stage) || sizes[5] % sizeof(Family) || sizes[6] % sizeof(u32) ||
+      sizes[7] % sizeof(u32) || sizes[1] / sizeof(LogicalSpec) != sizes[2] / sizeof(SpecHdr))
+    throw ModelError("shared plan: sizes do not describe a plan of this library version");
+  specs.reset(sizes[1] / sizeof(LogicalSpec));
+  hdrs.reset(sizes[2] / sizeof(SpecHdr));
+  cands.reset(sizes[3] / sizeof(CandRec));
+  stages.assign(sizes[4] / sizeof(Stage), Stage());
+  families.assign(sizes[5] / sizeof(Family), Family());
+  goal_ids.assign(sizes[6] / sizeof(u32), 0);
+  find_tab_.assign(sizes[7] / sizeof(u32), 0xFFFFFFFFu);
+  mine.clear();
+}
+
+void Plan::compute_mine_() {
+  mine.clear();
+  if (world <= 1) return;
+  mine.assign(hdrs.size(), 0);
+  for (const Family& f : families)
+    if (f.owner == rank)
+      for (u32 i = f.spec_lo; i < f.spec_hi; i++) mine[i] = 1;
+}
+
+void Plan::adopt_done(u32 rank_, u32 world_, int n_threads_) {
+  if (meta_.world != world_) throw ModelError("shared plan was made for another world size");
+  if (world_ < 1 || rank_ >= world_) throw ModelError("bad shard rank / world size");
+  for (int k = 0; k < NMEM; k++) top_code[k] = meta_.top_code[k];
+  stats = meta_.stats;
+  rank = rank_;
+  world = world_;
+  n_threads = n_threads_;
+  if (stats.n_specs != hdrs.size() || stats.n_cands != cands.size() || stats.n_stages != stages.size() ||
+      stats.n_families != families.size())
+    throw ModelError("shared plan: contents do not match their description");
+  for (const Family& f : families)
+    if (f.owner >= world || f.spec_hi > hdrs.size() || f.spec_lo > f.spec_hi) throw ModelError("shared plan: bad family");
+  compute_mine_();
+}
+
 bool Plan::pack_limits(const u64 limits[NMEM], u32* out) const {
   u32 pack = 0;
   for (int k = 0; k < NMEM; k++) {
@@ -477,7 +532,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 
   // Owners: per stage, heaviest family first onto the least loaded rank.
   if (plan.world > 1) {
-    plan.mine.assign(n, 0);
     for (const Stage& st : plan.stages) {
       std::vector<u32> fam;
       for (u32 f = st.fam_lo; f < st.fam_hi; f++) fam.push_back(f);
@@ -490,9 +544,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         load[best] += plan.families[f].weight;
       }
     }
-    for (const Family& f : plan.families)
-      if (f.owner == plan.rank)
-        for (u32 i = f.spec_lo; i < f.spec_hi; i++) plan.mine[i] = 1;
+    plan.compute_mine_();
   }
   plan.stats.seconds_layout = now_s() - t1;
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);

@@ -113,6 +113,16 @@ struct Plan {
   }
   PlanStats stats;
 
+  // A plan as eight flat byte ranges (0 meta, 1 specs, 2 hdrs, 3 cands, 4 stages, 5 families,
+  // 6 goal ids, 7 id lookup table), so that one process can plan and hand the result to others
+  // (ranks of a multi-GPU fill on one node share the host cores; only one of them should plan).
+  static constexpr int N_BLOBS = 8;
+  void share_blobs(void* ptrs[N_BLOBS], u64 sizes[N_BLOBS]);
+  // Receiving side: allocate by size, let the caller fill the ranges (share_blobs gives the
+  // pointers), then adopt_done() for this rank of `world`.
+  void adopt_alloc(const u64 sizes[N_BLOBS]);
+  void adopt_done(u32 rank, u32 world, int n_threads);
+
   // id of a logical Spec (canonical form), or -1.
   long find(const LogicalSpec& ls) const;
   // Limits as packed lattice codes (RF in byte 0 .. GL in byte 3); false when the limits are
@@ -122,6 +132,12 @@ struct Plan {
  private:
   friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32);
   std::vector<u32> find_tab_;  // open-addressing table of ids by Spec key hash (0xFFFFFFFF = empty)
+  struct Meta {                // blob 0
+    u32 top_code[NMEM];
+    u32 world, pad;
+    PlanStats stats;
+  } meta_;
+  void compute_mine_();
 };
 
 // Top limits are Avx2Target::max_mem() unless overridden.

@@ -159,6 +159,21 @@ class SynthesisDatabase:
     def set_shard(self, rank: int, world: int):
         self._check(self._lib.mrl_set_shard(self._ctx, rank, world))
 
+    def plan_share(self):
+        """[(host pointer, bytes)] x 8: this context's plan as flat byte ranges."""
+        ptrs, sizes = (C.c_void_p * 8)(), (C.c_uint64 * 8)()
+        self._check(self._lib.mrl_plan_share(self._ctx, ptrs, sizes))
+        return [(int(ptrs[k] or 0), int(sizes[k])) for k in range(8)]
+
+    def plan_adopt(self, sizes: Sequence[int]):
+        """Allocates an empty plan of the given range sizes; returns the pointers to fill."""
+        ptrs, sz = (C.c_void_p * 8)(), (C.c_uint64 * 8)(*sizes)
+        self._check(self._lib.mrl_plan_adopt(self._ctx, sz, ptrs))
+        return [int(ptrs[k] or 0) for k in range(8)]
+
+    def plan_adopt_done(self, plan_seconds: float = 0.0):
+        self._check(self._lib.mrl_plan_adopt_done(self._ctx, plan_seconds))
+
     def set_stream(self, cuda_stream: int):
         self._check(self._lib.mrl_set_stream(self._ctx, C.c_void_p(cuda_stream)))
 

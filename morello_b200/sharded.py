@@ -11,7 +11,9 @@ every rank but its owner, so the sum is a gather. Kernels only ever read local H
 The reference has no counterpart: its workers are threads sharing one in-process database
 (precompute/src/main.rs:229-240,339).
 """
-from typing import List, Sequence, Tuple
+import ctypes
+import time
+from typing import Callable, List, Sequence, Tuple
 
 
 def row_bytes() -> int:
@@ -75,10 +77,49 @@ def fill_sharded(db, dist, torch, process_group=None):
     db.fill_end()
 
 
+def plan_on_one_rank(db, plan_fn: Callable[[], None], dist, torch, process_group=None, device="cuda",
+                     chunk_bytes=256 << 20):
+    """Plans on the first rank only and hands the plan to the others. The ranks of one node share
+    its host cores, so planning once with all of them beats every rank planning on a share.
+    The plan's eight byte ranges travel by broadcast, staged through `device` memory in chunks
+    ("cuda" for NCCL, "cpu" for gloo)."""
+    rank, world = dist.get_rank(process_group), dist.get_world_size(process_group)
+    src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
+    db.set_shard(rank, world)
+    t0 = time.perf_counter()
+    if world == 1:
+        plan_fn()
+        return
+    sizes = torch.zeros(8, dtype=torch.int64, device=device)
+    if rank == 0:
+        plan_fn()
+        blobs = db.plan_share()
+        sizes.copy_(torch.tensor([n for _, n in blobs], dtype=torch.int64))
+    dist.broadcast(sizes, src=src, group=process_group)
+    if rank != 0:
+        want = [int(x) for x in sizes.tolist()]
+        blobs = list(zip(db.plan_adopt(want), want))
+    chunk = max(1, min(chunk_bytes, max(n for _, n in blobs)))
+    host = torch.empty(chunk, dtype=torch.uint8, pin_memory=(device == "cuda"))
+    stage = torch.empty(chunk, dtype=torch.uint8, device=device) if device == "cuda" else host
+    for ptr, nbytes in blobs:
+        for off in range(0, nbytes, chunk):
+            n = min(chunk, nbytes - off)
+            if rank == 0:
+                ctypes.memmove(host.data_ptr(), ptr + off, n)
+                if stage is not host:
+                    stage[:n].copy_(host[:n])
+            dist.broadcast(stage[:n], src=src, group=process_group)
+            if rank != 0:
+                if stage is not host:
+                    host[:n].copy_(stage[:n])
+                ctypes.memmove(ptr + off, host.data_ptr(), n)
+    if rank != 0:
+        db.plan_adopt_done(time.perf_counter() - t0)
+
+
 def precompute_sharded(db, size, dist, torch, through=2, dtypes=(4, 6), process_group=None):
     """`precompute` on all ranks of the process group."""
-    rank, world = dist.get_rank(process_group), dist.get_world_size(process_group)
-    db.set_shard(rank, world)
-    db.plan_precompute(size, through, dtypes)
+    plan_on_one_rank(db, lambda: db.plan_precompute(size, through, dtypes), dist, torch, process_group)
     db.upload()
     fill_sharded(db, dist, torch, process_group)

@@ -20,8 +20,8 @@ def _worker(rank, world, port, out_dir):
     import morello_b200 as m
     from morello_b200 import sharded
     db = m.SynthesisDatabase(device=-1)  # planning only: no GPU here
-    db.set_shard(rank, world)
-    db.plan_precompute(2)
+    # rank 0 plans; the plan travels to rank 1 as flat byte ranges (over gloo here)
+    sharded.plan_on_one_rank(db, lambda: db.plan_precompute(2), dist, torch, device="cpu", chunk_bytes=1 << 20)
     fams = db.families()
     stages = db.stages()
     n_specs = db.stats()["n_specs"]
@@ -44,6 +44,21 @@ def _worker(rank, world, port, out_dir):
         table[lo:hi][own] = want[lo:hi][own]
         dist.all_reduce(table[lo:hi], op=dist.ReduceOp.SUM)
     assert torch.equal(table, want)
+    # the adopted plan is the planned one: same Specs in the same order, same lookups
+    own = m.SynthesisDatabase(device=-1)
+    own.set_shard(rank, world)
+    own.plan_precompute(2)
+    assert own.families() == fams and own.stages() == stages
+    for i in range(0, n_specs, 97):
+        assert own.spec_blob(i) == db.spec_blob(i)
+    # headers, candidate records, stages, families, goal ids, lookup table: byte for byte (Specs
+    # are compared through their canonical blobs above: unused tail bytes of a Spec may differ)
+    for (pa, na), (pb, nb) in zip(own.plan_share()[2:], db.plan_share()[2:]):
+        assert na == nb
+        if na:
+            import ctypes
+            assert ctypes.string_at(pa, na) == ctypes.string_at(pb, nb)
+    own.close()
     np.save(os.path.join(out_dir, f"loads_{rank}.npy"), np.array(sharded.rank_loads(fams, world)))
     db.close()
     dist.destroy_process_group()
