@@ -353,66 +353,121 @@ __device__ __forceinline__ uint32_t shift_mask(uint32_t cm, uint32_t level, uint
   return out;
 }
 
-// Pass step 1: per Spec of the stage, the masks its working grid needs. `first`: same-stage
-// children are ignored (nothing is known about them yet); later passes add the breakpoints the
-// previous pass found in them (rmask). Also totals what a solve under the new masks takes.
+// Pass step 1: per Spec of the stage, the masks its working grid needs. child_source says what
+// is known about same-stage children: 0 = nothing (first pass: they are ignored), 1 = the
+// breakpoints in rmask (found real by the previous pass; or, when seeding, the children's own
+// first working masks). A Spec whose masks grew is marked dirty. seed_copy: also copy the new
+// masks to rmask (so that a following launch can read them as the children's breakpoints).
 __global__ void __launch_bounds__(128)
-derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, const uint4* __restrict__ rmask,
-                    const uint8_t* __restrict__ mine, uint32_t lo, uint32_t hi, int first, uint32_t top_pack,
-                    PassCounters* __restrict__ ctr) {
+derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, uint4* __restrict__ rmask,
+                    const uint8_t* __restrict__ mine, uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi,
+                    int first, int child_source, int seed_copy, uint32_t top_pack) {
   const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  const bool active = i < hi && (!mine || mine[i]);
-  unsigned long long cells = 0, warps = 0, bytes = 0;
-  uint32_t changed = 0;
-  if (active) {
-    const uint4 old = *reinterpret_cast<const uint4*>(&hdrs[i]);
-    const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
-    uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
-    for (uint32_t ci = 0; ci < cl.y; ci++) {
-      const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-      const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-      const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, units = a.w;
-      if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
-      if (kind == MRL_CK_LEAF) continue;
-      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
-      for (uint32_t j = 0; j < nchild; j++) {
-        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
-        uint4 cm;
-        if (child < lo) cm = *reinterpret_cast<const uint4*>(&hdrs[child]);   // finished stage: final masks
-        else if (first) continue;
-        else cm = rmask[child];
-        if (kind == MRL_CK_MOVE) {
-          const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(top_pack, level));
-          r0 |= (level == 0) ? s : cm.x;
-          r1 |= (level == 1) ? s : cm.y;
-          r2 |= (level == 2) ? s : cm.z;
-          r3 |= (level == 3) ? s : cm.w;
-        } else {
-          r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
-        }
+  if (i >= hi || (mine && !mine[i])) return;
+  const uint4 old = *reinterpret_cast<const uint4*>(&hdrs[i]);
+  const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
+  uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
+  for (uint32_t ci = 0; ci < cl.y; ci++) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+    const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+    const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, units = a.w;
+    if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
+    if (kind == MRL_CK_LEAF) continue;
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
+    for (uint32_t j = 0; j < nchild; j++) {
+      const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+      uint4 cm;
+      if (child < lo) cm = *reinterpret_cast<const uint4*>(&hdrs[child]);   // finished stage: final masks
+      else if (child_source == 0) continue;
+      else cm = rmask[child];
+      if (kind == MRL_CK_MOVE) {
+        const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(top_pack, level));
+        r0 |= (level == 0) ? s : cm.x;
+        r1 |= (level == 1) ? s : cm.y;
+        r2 |= (level == 2) ? s : cm.z;
+        r3 |= (level == 3) ? s : cm.w;
+      } else {
+        r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
       }
     }
-    uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
-    changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
-    if (changed) *reinterpret_cast<uint4*>(&hdrs[i]) = nm;
+  }
+  const uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
+  const bool changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
+  if (changed) {
+    *reinterpret_cast<uint4*>(&hdrs[i]) = nm;
+    dirty[i] = 1;
+  }
+  if (seed_copy) rmask[i] = nm;
+}
+
+// A Spec with a dirty same-stage child has to be solved again too (its lookups may change).
+// Monotone, so racing with other threads' marks is harmless; run until totals_kernel reports
+// no unmarked Spec with a dirty child.
+__global__ void __launch_bounds__(128)
+spread_dirty_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
+                    const uint8_t* __restrict__ mine, uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi) {
+  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= hi || (mine && !mine[i]) || dirty[i]) return;
+  const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
+  for (uint32_t ci = 0; ci < cl.y; ci++) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+    const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+    if (kind != MRL_CK_MOVE) continue;   // only Moves have same-stage children
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
+    for (uint32_t j = 0; j < nchild; j++) {
+      const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+      if (child >= lo && dirty[child]) { dirty[i] = 1; return; }
+    }
+  }
+}
+
+// Totals of what the coming solve takes (dirty Specs only), the working cells of the whole stage,
+// and whether the dirty marks are closed under "has a dirty same-stage child".
+__global__ void __launch_bounds__(128)
+totals_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, const uint8_t* __restrict__ mine,
+              uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi, PassCounters* __restrict__ ctr) {
+  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
+  const bool active = i < hi && (!mine || mine[i]);
+  unsigned long long cells = 0, warps = 0, bytes = 0, all_cells = 0;
+  uint32_t open_marks = 0;
+  if (active) {
+    const uint4 nm = *reinterpret_cast<const uint4*>(&hdrs[i]);
+    const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
     const Grid g = grid_of(nm);
-    cells = g.cells;
-    warps = g.warps;
-    // algorithmic bytes of one solve: a 12-byte row out; per candidate a 16-byte header; per
-    // child of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in
-    bytes = cells * 12ull;
-    for (uint32_t ci = 0; ci < cl.y; ci++) {
-      const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-      const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-      const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu;
-      bytes += cells * 16ull;
-      if (nchild) {
-        unsigned long long feasible = cells;
-        if (kind == MRL_CK_MOVE) {
-          const uint32_t ml = sel4(nm.x, nm.y, nm.z, nm.w, level);
-          feasible = cells / (uint32_t)__popc(ml) * (uint32_t)__popc(ml >> thr);
+    all_cells = g.cells;
+    bool is_dirty = dirty[i] != 0;
+    if (!is_dirty) {
+      for (uint32_t ci = 0; ci < cl.y && !is_dirty; ci++) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+        const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+        if (kind != MRL_CK_MOVE) continue;
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
+        for (uint32_t j = 0; j < nchild; j++) {
+          const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+          if (child >= lo && dirty[child]) is_dirty = true;
         }
-        bytes += feasible * nchild * 16ull;
+      }
+      if (is_dirty) { dirty[i] = 1; open_marks = 1; }
+    }
+    if (is_dirty) {
+      cells = g.cells;
+      warps = g.warps;
+      // algorithmic bytes of one solve: a 12-byte row out; per candidate a 16-byte header; per
+      // child of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in
+      bytes = cells * 12ull;
+      for (uint32_t ci = 0; ci < cl.y; ci++) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+        const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+        const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu;
+        bytes += cells * 16ull;
+        if (nchild) {
+          unsigned long long feasible = cells;
+          if (kind == MRL_CK_MOVE) {
+            const uint32_t ml = sel4(nm.x, nm.y, nm.z, nm.w, level);
+            feasible = cells / (uint32_t)__popc(ml) * (uint32_t)__popc(ml >> thr);
+          }
+          bytes += feasible * nchild * 16ull;
+        }
       }
     }
   }
@@ -421,13 +476,17 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
     cells += __shfl_xor_sync(0xFFFFFFFFu, cells, o);
     warps += __shfl_xor_sync(0xFFFFFFFFu, warps, o);
     bytes += __shfl_xor_sync(0xFFFFFFFFu, bytes, o);
+    all_cells += __shfl_xor_sync(0xFFFFFFFFu, all_cells, o);
   }
-  changed = __reduce_or_sync(0xFFFFFFFFu, changed);
-  if ((threadIdx.x & 31) == 0 && cells) {
-    atomicAdd(&ctr->cells, cells);
-    atomicAdd(&ctr->warps, warps);
-    atomicAdd(&ctr->alg_bytes, bytes);
-    if (changed) atomicOr(&ctr->changed, 1u);
+  open_marks = __reduce_or_sync(0xFFFFFFFFu, open_marks);
+  if ((threadIdx.x & 31) == 0) {
+    if (cells) {
+      atomicAdd(&ctr->cells, cells);
+      atomicAdd(&ctr->warps, warps);
+      atomicAdd(&ctr->alg_bytes, bytes);
+    }
+    if (all_cells) atomicAdd(&ctr->all_cells, all_cells);
+    if (open_marks) atomicOr(&ctr->changed, 1u);
   }
 }
 
@@ -454,14 +513,16 @@ __device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long
   return warp_sum[w] + inc - v;
 }
 
-// Pass step 2: gives every Spec of the stage its working rows (in the temp buffer) and its
-// chunks, and resets its real-breakpoint masks.
+// Pass step 2: gives every dirty Spec of the stage fresh working rows (in the temp buffer, from
+// temp_top up; Specs that are not solved again keep theirs) and its chunks, and resets its
+// real-breakpoint masks.
 __global__ void __launch_bounds__(256)
-place_kernel(SpecHdr* __restrict__ hdrs, uint4* __restrict__ rmask, const uint8_t* __restrict__ mine, uint32_t lo,
-             uint32_t hi, unsigned long long temp_cap, Chunk* __restrict__ chunks, unsigned long long chunk_cap,
+place_kernel(SpecHdr* __restrict__ hdrs, uint4* __restrict__ rmask, const uint8_t* __restrict__ mine,
+             uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi, unsigned long long temp_top,
+             unsigned long long temp_cap, Chunk* __restrict__ chunks, unsigned long long chunk_cap,
              PassCounters* __restrict__ ctr) {
   const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  const bool active = i < hi && (!mine || mine[i]);
+  const bool active = i < hi && (!mine || mine[i]) && dirty[i];
   Grid g;
   g.cells = 0; g.warps = 0; g.F = 0;
   if (active) g = grid_of(*reinterpret_cast<const uint4*>(&hdrs[i]));
@@ -475,11 +536,12 @@ place_kernel(SpecHdr* __restrict__ hdrs, uint4* __restrict__ rmask, const uint8_
   }
   __syncthreads();
   if (!active) return;
-  const unsigned long long rb = row0 + my_row;
+  const unsigned long long rb = temp_top + row0 + my_row;
   const unsigned long long cb = chunk0 + my_chunk;
   if (rb + g.cells > temp_cap || cb + g.warps > chunk_cap) { atomicOr(&ctr->error, 2u); return; }
   hdrs[i].row_base = rb | MRL_TEMP_FLAG;
   rmask[i] = make_uint4(1u, 1u, 1u, 1u);
+  dirty[i] = 0;   // solved by this pass
   for (uint32_t w = 0; w < g.warps; w++) {
     Chunk c;
     c.spec = i;
@@ -737,10 +799,10 @@ void DeviceFill::free_(void* p) {
 
 void DeviceFill::release() {
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
-  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr;
+  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
   row_cap_ = temp_cap_ = chunk_cap_ = cell_cap_ = 0;
   buf_off_ = 0;
@@ -768,6 +830,7 @@ int DeviceFill::init(int device) {
 
 int DeviceFill::init_events() {
   stage_log_ = getenv("MRL_STAGE_LOG") != nullptr;
+  if (const char* e = getenv("MRL_SEED_HOPS")) seed_hops_ = std::max(0, std::min(8, atoi(e)));
   if (!ev0_) CK(cudaEventCreate(&ev0_));
   if (!ev1_) CK(cudaEventCreate(&ev1_));
   return 0;
@@ -793,10 +856,10 @@ int DeviceFill::set_stream(cudaStream_t s) {
 int DeviceFill::upload(const Plan& plan) {
   CK(cudaSetDevice(device_));
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
-  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr;
+  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
   buf_off_ = 0;
   n_specs_ = (uint32_t)plan.hdrs.size();
@@ -810,6 +873,7 @@ int DeviceFill::upload(const Plan& plan) {
   if ((rc = alloc_((void**)&d_hdrs_, plan.hdrs.size() * sizeof(SpecHdr)))) return rc;
   if ((rc = alloc_((void**)&d_cands_, plan.cands.size() * sizeof(CandRec)))) return rc;
   if ((rc = alloc_((void**)&d_rmask_, plan.hdrs.size() * sizeof(uint4)))) return rc;
+  if ((rc = alloc_((void**)&d_dirty_, plan.hdrs.size()))) return rc;
   if (!plan.mine.empty() && (rc = alloc_((void**)&d_mine_, plan.mine.size()))) return rc;
   if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage * sizeof(uint32_t)))) return rc;
   if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage / 256 + 1) * sizeof(unsigned long long)))) return rc;
@@ -913,19 +977,22 @@ int DeviceFill::ensure_rows_(uint64_t need, bool refresh) {
   return 0;
 }
 
-int DeviceFill::ensure_temp_(uint64_t need) {
+// Room for `need` working rows; the first `keep` rows (grids of Specs that are not solved again
+// in this pass) move along.
+int DeviceFill::ensure_temp_(uint64_t need, uint64_t keep) {
   if (need <= temp_cap_) return 0;
   if (fixed_) {
     snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
              "entry point has; use mrl_top_down_many for it", buf_bytes_);
     return -4;
   }
+  const uint64_t cap = need + need / 4;
+  MrlRow* nt = nullptr;
+  CK(cudaMalloc((void**)&nt, cap * sizeof(MrlRow)));
+  if (keep) CK(cudaMemcpyAsync(nt, d_temp_, keep * sizeof(MrlRow), cudaMemcpyDeviceToDevice, stream_));
   CK(cudaStreamSynchronize(stream_));
   cudaFree(d_temp_);
-  d_temp_ = nullptr;
-  temp_cap_ = 0;
-  const uint64_t cap = need + need / 4;
-  CK(cudaMalloc((void**)&d_temp_, cap * sizeof(MrlRow)));
+  d_temp_ = nt;
   temp_cap_ = cap;
   return 0;
 }
@@ -985,29 +1052,54 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
   last_cells_ = 0;
   if (n == 0) return 0;
   if (d_mine_) CK(cudaMemsetAsync(d_rmask_ + lo, 0, (size_t)n * sizeof(uint4), stream_));
+  CK(cudaMemsetAsync(d_dirty_ + lo, 0, n, stream_));
   const uint32_t top_pack = plan.top_pack();
+  const uint32_t nb128 = (n + 127) / 128;
+  uint64_t temp_top = 0;   // working rows handed out so far in this stage
   for (int pass = 0;; pass++) {
     if (pass >= 128) { snprintf(err_, sizeof(err_), "stage %u did not reach a consistent limits grid", si); return -2; }
-    CK(cudaMemsetAsync(d_ctr_, 0, offsetof(PassCounters, error), stream_));   // the error word is sticky
-    derive_masks_kernel<<<(n + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, lo, hi, pass == 0,
-                                                              top_pack, d_ctr_);
+    // masks: the first pass knows nothing about same-stage children; later passes add the real
+    // breakpoints the previous passes found in them. Specs whose masks grew become dirty.
+    derive_masks_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, d_dirty_, lo, hi, pass == 0,
+                                                    pass == 0 ? 0 : 1, pass == 0 && seed_hops_ > 0, top_pack);
     stats_.launches++;
+    if (pass == 0)
+      for (int h = 0; h < seed_hops_; h++) {
+        // optional seeding: assume the same-stage children's breakpoints are their own first masks
+        derive_masks_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, d_dirty_, lo, hi, 0, 1,
+                                                        h + 1 < seed_hops_, top_pack);
+        stats_.launches++;
+      }
+    // close the dirty marks under "has a dirty same-stage child", then total the pass
     PassCounters c;
-    if (read_counters_(&c) != 0) return -1;
-    if (c.error) {
-      snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u (1: bad child index, 2: working "
-               "buffers too small, 4: row arena too small)", c.error, si);
-      return -2;
+    for (int round = 0;; round++) {
+      if (round >= 4096) { snprintf(err_, sizeof(err_), "stage %u: dirty marks did not settle", si); return -2; }
+      if (pass > 0)
+        for (int k = 0; k < 3; k++) {
+          spread_dirty_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_mine_, d_dirty_, lo, hi);
+          stats_.launches++;
+        }
+      CK(cudaMemsetAsync(d_ctr_, 0, offsetof(PassCounters, error), stream_));   // the error word is sticky
+      totals_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_mine_, d_dirty_, lo, hi, d_ctr_);
+      stats_.launches++;
+      if (read_counters_(&c) != 0) return -1;
+      if (c.error) {
+        snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u (1: bad child index, 2: working "
+                 "buffers too small, 4: row arena too small)", c.error, si);
+        return -2;
+      }
+      if (pass == 0 || !c.changed) break;
     }
-    if (pass > 0 && !c.changed) break;
-    if (c.cells == 0) break;   // nothing of this stage is computed by this rank
+    last_cells_ = c.all_cells;
+    if (c.cells == 0) break;   // nothing left to solve: every working grid is consistent
     int rc;
     if ((rc = ensure_chunks_(c.warps))) return rc;
-    if ((rc = ensure_temp_(c.cells))) return rc;
+    if ((rc = ensure_temp_(temp_top + c.cells, temp_top))) return rc;
     if (c.cells >= 0xFFFFFFF0ull) { snprintf(err_, sizeof(err_), "stage %u too large: %llu working cells", si, (unsigned long long)c.cells); return -6; }
     if ((rc = ensure_cells_(c.cells))) return rc;
-    place_kernel<<<(n + 255) / 256, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, lo, hi, temp_cap_, d_chunks_,
-                                                       chunk_cap_, d_ctr_);
+    place_kernel<<<(n + 255) / 256, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, d_dirty_, lo, hi, temp_top, temp_cap_,
+                                                       d_chunks_, chunk_cap_, d_ctr_);
+    temp_top += c.cells;
     const uint32_t n_chunks = (uint32_t)c.warps;
     const uint32_t blocks = (n_chunks + 3) / 4;
     // cells per limits diagonal, then the cell lists
@@ -1045,7 +1137,6 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
     stats_.passes++;
     stats_.cells_solved += c.cells;
     stats_.alg_bytes += c.alg_bytes;
-    last_cells_ = c.cells;
   }
   return 0;
 }

@@ -60,13 +60,14 @@ struct Chunk {
 
 // Counters one solve pass of a stage leaves for the host (zeroed before every pass).
 struct PassCounters {
-  uint32_t changed;             // some Spec's working grid gained a breakpoint
+  uint32_t changed;             // a Spec was marked for solving by totals_kernel itself (marks were not closed)
   uint32_t n_chunks;            // chunk cursor (place kernel)
-  unsigned long long cells;     // working cells of the stage under the current masks
+  unsigned long long cells;     // working cells of the Specs to solve in this pass
   unsigned long long warps;     // chunks those cells need
   unsigned long long temp_rows; // row cursor (place kernel)
   unsigned long long alg_bytes; // algorithmic bytes of one solve of those cells
-  uint32_t pad0[4];
+  unsigned long long all_cells; // working cells of all the stage's Specs under the current masks
+  uint32_t pad0[2];
   uint32_t error;               // bad child index / capacity overrun seen by a kernel (sticky over a fill)
   uint32_t pad;
 };

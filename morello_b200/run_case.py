@@ -1,6 +1,7 @@
 """Runs one named fill on cuda:0 and prints its statistics as JSON.
 
     python -m morello_b200.run_case matmul2 [--fills N]      # closure of `morello matmul 2` (u32)
+    python -m morello_b200.run_case matmul8                  # closure of one 8x8x8 Matmul (473 k Specs, < 1 GB on the device)
     python -m morello_b200.run_case precompute1|precompute2  # the precompute of that size
     python -m morello_b200.run_case precompute4_u32          # size 4, u32 tables only
 
@@ -14,7 +15,7 @@ import morello_b200 as m
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["matmul1", "matmul2", "matmul2_f32", "precompute1", "precompute2", "precompute2_u32",
+    ap.add_argument("case", choices=["matmul1", "matmul2", "matmul2_f32", "matmul8", "precompute1", "precompute2", "precompute2_u32",
                                      "precompute4", "precompute4_u32", "precompute8", "precompute8_u32"])
     ap.add_argument("--fills", type=int, default=1, help="fills of the final plan (>= 1)")
     args = ap.parse_args()
