@@ -150,7 +150,8 @@ __device__ __forceinline__ Column decode_column(const SpecHdr* __restrict__ hdrs
 __device__ __forceinline__ Key solve_point(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
                                            const MrlRow* __restrict__ rows, const MrlRow* __restrict__ temp,
                                            uint32_t spec, uint32_t cpack, uint32_t n_specs,
-                                           uint32_t* __restrict__ error_flag) {
+                                           uint32_t* __restrict__ error_flag, uint32_t first_cand = 0,
+                                           uint32_t cand_stride = 1) {
   // "codes at or below this point's limit", per memory: what a child lookup at the same limits needs
   const uint32_t bm0 = (2u << code_of(cpack, 0)) - 1u, bm1 = (2u << code_of(cpack, 1)) - 1u,
                  bm2 = (2u << code_of(cpack, 2)) - 1u, bm3 = (2u << code_of(cpack, 3)) - 1u;
@@ -158,7 +159,7 @@ __device__ __forceinline__ Key solve_point(const SpecHdr* __restrict__ hdrs, con
   const uint32_t cand_off = cl.x, ncand = cl.y;
 
   Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-  for (uint32_t ci = 0; ci < ncand; ci++) {
+  for (uint32_t ci = first_cand; ci < ncand; ci += cand_stride) {
     const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]));
     const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
     const uint32_t imm = a.y;
@@ -241,29 +242,52 @@ __device__ __forceinline__ Key solve_point(const SpecHdr* __restrict__ hdrs, con
 
 // One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes),
 // listed by scatter_cells_kernel: every thread has a cell, and neighbouring threads mostly have
-// neighbouring cells of one Spec.
+// neighbouring cells of one Spec. G = lanes per cell. A launch with few cells cannot fill the
+// GPU and lasts as long as one cell's chain of dependent loads (tens of microseconds with ~30
+// candidates); there the G lanes of a cell take every G-th candidate each and min-reduce their
+// keys with shuffles, which shortens the chain G-fold. Large launches use G = 1, which keeps the
+// lower-bound cut across all candidates of a cell.
+template <int G>
 __global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
 combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
                       const CellRef* __restrict__ cells, uint32_t n_cells,
                       const MrlRow* __restrict__ rows, MrlRow* __restrict__ temp, uint32_t n_specs,
                       uint32_t* __restrict__ error_flag) {
-  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_cells) return;
-  const CellRef ref = cells[t];
-  const uint32_t spec = ref.spec;
-  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[spec]));
-  const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-  uint32_t rest = ref.cell;
-  const uint32_t i0 = rest % n0; rest /= n0;
-  const uint32_t i1 = rest % n1; rest /= n1;
-  const uint32_t i2 = rest % n2;
-  const uint32_t i3 = rest / n2;
-  const uint32_t cpack = nth_set_bit(m.x, i0) | (nth_set_bit(m.y, i1) << 8) | (nth_set_bit(m.z, i2) << 16) |
-                         (nth_set_bit(m.w, i3) << 24);
-  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[spec].row_base));
-  const Key best = solve_point(hdrs, cands, rows, temp, spec, cpack, n_specs, error_flag);
+  const uint32_t t = (blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const uint32_t sub = threadIdx.x % G;
+  const bool valid = t < n_cells;   // the G lanes of a cell agree; no lane leaves before the shuffles
+  Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+  CellRef ref;
+  ref.spec = 0;
+  ref.cell = 0;
+  unsigned long long base = 0;
+  if (valid) {
+    ref = cells[t];
+    const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ref.spec]));
+    const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+    uint32_t rest = ref.cell;
+    const uint32_t i0 = rest % n0; rest /= n0;
+    const uint32_t i1 = rest % n1; rest /= n1;
+    const uint32_t i2 = rest % n2;
+    const uint32_t i3 = rest / n2;
+    const uint32_t cpack = nth_set_bit(m.x, i0) | (nth_set_bit(m.y, i1) << 8) | (nth_set_bit(m.z, i2) << 16) |
+                           (nth_set_bit(m.w, i3) << 24);
+    base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ref.spec].row_base));
+    best = solve_point(hdrs, cands, rows, temp, ref.spec, cpack, n_specs, error_flag, sub, G);
+  }
+  if (G > 1) {
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) {
+      Key other;
+      other.main = __shfl_xor_sync(0xFFFFFFFFu, best.main, o);
+      other.peaks = __shfl_xor_sync(0xFFFFFFFFu, best.peaks, o);
+      other.tail = __shfl_xor_sync(0xFFFFFFFFu, best.tail, o);
+      if (key_less(other, best)) best = other;
+    }
+  }
   // Specs of the stage being solved always live in the working buffer.
-  *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + ref.cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
+  if (valid && sub == 0)
+    *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + ref.cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
 }
 
 // Consistency check of a finished table: at sampled (or all) points of the limits lattice, for
@@ -1124,8 +1148,16 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
     for (uint32_t d = 0; d < MRL_MAX_DIAG; d++) {
       const uint32_t nd = hd->count[d];
       if (!nd) continue;
-      combine_argmin_kernel<<<(nd + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_cells_ + hd->base[d], nd, d_rows_,
-                                                                   d_temp_, n_specs_, &d_ctr_->error);
+      // lanes per cell by launch size: what fills the GPU (227 k threads) runs one lane per cell
+      const CellRef* list = d_cells_ + hd->base[d];
+      if (nd > 65536)
+        combine_argmin_kernel<1><<<(nd + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
+      else if (nd > 16384)
+        combine_argmin_kernel<4><<<(nd + 31) / 32, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
+      else if (nd > 4096)
+        combine_argmin_kernel<8><<<(nd + 15) / 16, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
+      else
+        combine_argmin_kernel<32><<<(nd + 3) / 4, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
       stats_.combine_launches++;
     }
     CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
