@@ -116,8 +116,9 @@ int mrl_fill(mrl_ctx* ctx);
 /* Multi-GPU (one process per GPU; no counterpart in the reference, whose workers are threads
  * sharing one database, precompute/src/main.rs:229-240,339). Every rank plans the same job and
  * keeps the whole table. The plan orders Specs into stages; inside a stage the "families"
- * (Specs with equal dtype and shape - Moves change neither) are independent, and rank r computes
- * the families it owns. Per stage the caller sums two device buffers over all ranks on the
+ * (Specs with equal dtype and shape - Moves change neither) are independent, and outside the Move
+ * phase so are the Specs of a family whose operands sit in different memories; rank r computes
+ * the Specs it owns (mrl_spec_owners). Per stage the caller sums two device buffers over all ranks on the
  * stream given to mrl_set_stream (e.g. ncclAllReduce, sum of int32, in place; a Spec's words are
  * zero on every rank but its owner):
  *   mrl_set_shard, mrl_plan_*, mrl_upload, then per fill: mrl_fill_begin;
@@ -140,6 +141,7 @@ int mrl_stage_info(const mrl_ctx* ctx, uint64_t stage, uint32_t* spec_lo, uint32
                    uint32_t* family_hi);
 int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* stage, uint32_t* owner, uint32_t* spec_lo,
                     uint32_t* spec_hi);
+int mrl_spec_owners(const mrl_ctx* ctx, uint8_t* out, uint64_t n); /* rank that computes each Spec; n = mrl_num_specs */
 int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows); /* the finished table on the device */
 uint32_t mrl_row_bytes(void); /* bytes per row of the device table */
 int mrl_fill_begin(mrl_ctx* ctx);

@@ -47,6 +47,7 @@ EXPORTS = {
                                  C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "mrl_family_info": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
                                   C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "mrl_spec_owners": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint64]),
     "mrl_device_rows": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "mrl_row_bytes": (C.c_uint32, []),
     "mrl_fill_begin": (C.c_int, [C.c_void_p]),

@@ -390,6 +390,13 @@ int mrl_family_info(const mrl_ctx* ctx, uint64_t family, uint32_t* stage, uint32
   return 0;
 }
 
+int mrl_spec_owners(const mrl_ctx* ctx, uint8_t* out, uint64_t n) {
+  if (!ctx || !ctx->planned || !out || n != ctx->plan.hdrs.size()) return -1;
+  if (ctx->plan.owner.empty()) memset(out, 0, n);
+  else memcpy(out, ctx->plan.owner.data(), n);
+  return 0;
+}
+
 uint32_t mrl_row_bytes(void) { return (uint32_t)sizeof(MrlRow); }
 
 int mrl_device_rows(const mrl_ctx* ctx, void** ptr, uint64_t* n_rows) {

@@ -240,13 +240,50 @@ void Plan::adopt_alloc(const u64 sizes[N_BLOBS]) {
   mine.clear();
 }
 
-void Plan::compute_mine_() {
+// Unit of work handed to one rank: the Specs of a family whose operands sit in the same
+// memories. Relayout Moves (the only same-stage dependency outside the Move phase) keep every
+// operand's memory, so such units do not depend on each other; in the Move phase same-stage
+// Moves do change memories and the unit is the whole family. Deterministic in (plan, world):
+// every rank computes the same owners.
+static inline u32 unit_tag(const LogicalSpec& ls) {
+  if (ls.kind == K_MOVE) return 0;
+  u32 t = 1;
+  for (int i = 0; i < ls.nops(); i++) t = t * 4 + (u32)ls.aux[i].mem;
+  return t;   // < 256
+}
+
+void Plan::assign_owners_() {
   mine.clear();
+  owner.clear();
+  for (Family& f : families) f.owner = 0;
   if (world <= 1) return;
-  mine.assign(hdrs.size(), 0);
-  for (const Family& f : families)
-    if (f.owner == rank)
-      for (u32 i = f.spec_lo; i < f.spec_hi; i++) mine[i] = 1;
+  const u32 n = (u32)hdrs.size();
+  owner.assign(n, 0);
+  for (const Stage& st : stages) {
+    // weights per (family, tag)
+    std::vector<u64> w((size_t)(st.fam_hi - st.fam_lo) * 256, 0);
+    for (u32 f = st.fam_lo; f < st.fam_hi; f++)
+      for (u32 i = families[f].spec_lo; i < families[f].spec_hi; i++)
+        w[(size_t)(f - st.fam_lo) * 256 + unit_tag(specs[i])] += hdrs[i].ncand + 1;
+    std::vector<u32> units;
+    for (u32 u = 0; u < w.size(); u++) if (w[u]) units.push_back(u);
+    std::stable_sort(units.begin(), units.end(), [&](u32 a, u32 b) { return w[a] > w[b]; });
+    std::vector<u64> load(world, 0);
+    std::vector<u8> unit_owner(w.size(), 0);
+    for (u32 u : units) {   // heaviest first onto the least loaded rank
+      u32 best = 0;
+      for (u32 r = 1; r < world; r++) if (load[r] < load[best]) best = r;
+      unit_owner[u] = (u8)best;
+      load[best] += w[u];
+    }
+    for (u32 f = st.fam_lo; f < st.fam_hi; f++) {
+      for (u32 i = families[f].spec_lo; i < families[f].spec_hi; i++)
+        owner[i] = unit_owner[(size_t)(f - st.fam_lo) * 256 + unit_tag(specs[i])];
+      families[f].owner = owner[families[f].spec_lo];
+    }
+  }
+  mine.assign(n, 0);
+  for (u32 i = 0; i < n; i++) mine[i] = owner[i] == rank;
 }
 
 void Plan::adopt_done(u32 rank_, u32 world_, int n_threads_) {
@@ -261,8 +298,8 @@ void Plan::adopt_done(u32 rank_, u32 world_, int n_threads_) {
       stats.n_families != families.size())
     throw ModelError("shared plan: contents do not match their description");
   for (const Family& f : families)
-    if (f.owner >= world || f.spec_hi > hdrs.size() || f.spec_lo > f.spec_hi) throw ModelError("shared plan: bad family");
-  compute_mine_();
+    if (f.spec_hi > hdrs.size() || f.spec_lo > f.spec_hi) throw ModelError("shared plan: bad family");
+  assign_owners_();
 }
 
 bool Plan::pack_limits(const u64 limits[NMEM], u32* out) const {
@@ -530,21 +567,26 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (bad.load() == 2) throw ModelError("planner: a same-stage child is not below its parent in the limits lattice" + who);
   }
 
-  // Owners: per stage, heaviest family first onto the least loaded rank.
+  if (plan.world > 255) throw ModelError("at most 255 ranks");
+  plan.assign_owners_();
   if (plan.world > 1) {
-    for (const Stage& st : plan.stages) {
-      std::vector<u32> fam;
-      for (u32 f = st.fam_lo; f < st.fam_hi; f++) fam.push_back(f);
-      std::stable_sort(fam.begin(), fam.end(), [&](u32 a, u32 b) { return plan.families[a].weight > plan.families[b].weight; });
-      std::vector<u64> load(plan.world, 0);
-      for (u32 f : fam) {
-        u32 best = 0;
-        for (u32 r = 1; r < plan.world; r++) if (load[r] < load[best]) best = r;
-        plan.families[f].owner = best;
-        load[best] += plan.families[f].weight;
+    // a same-stage child must be solved by the rank that solves its parent
+    std::atomic<int> split{0};
+    parallel_for(n, n_threads, [&](size_t i, int) {
+      const SpecHdr& h = plan.hdrs[i];
+      for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
+        const CandRec& r = plan.cands[c];
+        if (r.kind != MRL_CK_MOVE) continue;
+        for (int j = 0; j < r.nchild; j++)
+          if (plan.owner[r.child[j]] != plan.owner[i] && r.child[j] >= plan.stages[0].spec_lo) {
+            // children in earlier stages may belong to anyone; same-stage ones may not
+            const LogicalSpec& a = plan.specs[i];
+            const LogicalSpec& b = plan.specs[r.child[j]];
+            if (stage_key(a) == stage_key(b)) split = 1;
+          }
       }
-    }
-    plan.compute_mine_();
+    });
+    if (split.load()) throw ModelError("planner: a same-stage child belongs to another rank than its parent");
   }
   plan.stats.seconds_layout = now_s() - t1;
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);

@@ -85,11 +85,12 @@ struct Stage {
 };
 
 // Specs of one stage with the same dtype and shape. Moves never change either, so families of
-// a stage do not depend on each other: the unit of work handed to one GPU.
+// a stage do not depend on each other. Outside the Move phase a family splits further into
+// independent units by the operands' memories (Plan::owner is per Spec).
 struct Family {
   u32 spec_lo = 0, spec_hi = 0;
   u32 stage = 0;
-  u32 owner = 0;        // rank that computes it
+  u32 owner = 0;        // rank that computes its first Spec (informational)
   u64 weight = 0;       // candidate records (the load-balancing estimate)
 };
 
@@ -103,6 +104,7 @@ struct Plan {
   // Sharding: this process computes the families whose owner == rank; every rank keeps the
   // whole table. world == 1: everything is local.
   u32 rank = 0, world = 1;
+  std::vector<u8> owner;                 // by id: rank that computes the Spec (empty when world == 1)
   std::vector<u8> mine;                  // by id: 1 = computed by this rank (empty when world == 1)
   std::vector<u32> goal_ids;
   u32 top_code[NMEM] = {0, 0, 0, 0};   // lattice codes of the top limits the plan covers
@@ -137,7 +139,7 @@ struct Plan {
     u32 world, pad;
     PlanStats stats;
   } meta_;
-  void compute_mine_();
+  void assign_owners_();
 };
 
 // Top limits are Avx2Target::max_mem() unless overridden.

@@ -200,6 +200,14 @@ class SynthesisDatabase:
             out.append((int(g.value), int(o.value), int(lo.value), int(hi.value)))
         return out
 
+    def spec_owners(self) -> bytes:
+        """One byte per Spec id: the rank that computes it (all zero when not sharded)."""
+        n = self.num_specs()
+        buf = C.create_string_buffer(max(n, 1))
+        if self._lib.mrl_spec_owners(self._ctx, buf, n) != 0:
+            raise RuntimeError("nothing planned")
+        return buf.raw[:n]
+
     def device_rows(self):
         """(device pointer, row count) of the finished table (mrl_row_bytes() bytes per row)."""
         ptr, n = C.c_void_p(), C.c_uint64()

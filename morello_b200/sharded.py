@@ -22,32 +22,34 @@ def row_bytes() -> int:
 
 
 def check_partition(families: Sequence[Tuple[int, int, int, int]], stages: Sequence[Tuple[int, int, int, int]],
-                    world: int, n_specs: int):
-    """families: (stage, owner, first Spec id, end Spec id); stages: (first Spec id, end Spec id,
-    first family, end family). Families tile the Spec ids in order, stage by stage, and every
-    owner is a valid rank."""
+                    owners: bytes, world: int, n_specs: int):
+    """families: (stage, owner of the first Spec, first Spec id, end Spec id); stages: (first Spec
+    id, end Spec id, first family, end family); owners: one byte per Spec id. Families tile the Spec
+    ids in order, stage by stage, and every Spec's owner is a valid rank."""
     pos = 0
     fam = 0
     for s, (lo, hi, flo, fhi) in enumerate(stages):
         if lo != pos or flo != fam or fhi < flo:
             raise ValueError(f"stage {s} starts at Spec {lo} / family {flo}, expected {pos} / {fam}")
         for f in range(flo, fhi):
-            stage, owner, a, b = families[f]
-            if stage != s or a != pos or b <= a or not (0 <= owner < world):
-                raise ValueError(f"bad family {f}: stage {stage}, Specs {a}..{b} (expected start {pos}), owner {owner}")
+            stage, _owner, a, b = families[f]
+            if stage != s or a != pos or b <= a:
+                raise ValueError(f"bad family {f}: stage {stage}, Specs {a}..{b} (expected start {pos})")
             pos = b
         if pos != hi:
             raise ValueError(f"families of stage {s} end at Spec {pos}, the stage at {hi}")
         fam = fhi
     if pos != n_specs or fam != len(families):
         raise ValueError(f"stages cover {pos} Specs of {n_specs}")
+    if len(owners) != n_specs or (n_specs and max(owners) >= world):
+        raise ValueError("an owner is not a rank of this world")
 
 
-def rank_loads(families: Sequence[Tuple[int, int, int, int]], world: int) -> List[int]:
+def rank_loads(owners: bytes, world: int) -> List[int]:
     """Specs per rank (the planner balances candidate records, which track this closely)."""
     loads = [0] * world
-    for _stage, owner, lo, hi in families:
-        loads[owner] += hi - lo
+    for o in owners:
+        loads[o] += 1
     return loads
 
 

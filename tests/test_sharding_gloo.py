@@ -26,17 +26,16 @@ def _worker(rank, world, port, out_dir):
     stages = db.stages()
     n_specs = db.stats()["n_specs"]
     assert len(stages) == db.num_stages() == db.stats()["n_stages"]
-    sharded.check_partition(fams, stages, world, n_specs)
+    owners = db.spec_owners()
+    sharded.check_partition(fams, stages, owners, world, n_specs)
     # every rank must have computed the same ownership
-    mine = torch.tensor([o for _, o, _, _ in fams], dtype=torch.int64)
+    mine = torch.tensor(list(owners), dtype=torch.int64)
     ref = mine.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(mine, ref)
     # stand-in for the fill: per stage a rank "computes" four mask words for each Spec of the
     # families it owns and leaves the others zero; the sum over ranks is the exchange.
-    owner_of = torch.empty(n_specs, dtype=torch.int64)
-    for _stage, o, lo, hi in fams:
-        owner_of[lo:hi] = o
+    owner_of = mine
     want = (torch.arange(n_specs * 4, dtype=torch.int32) * 7 + 3).reshape(n_specs, 4)
     table = torch.zeros((n_specs, 4), dtype=torch.int32)
     for lo, hi, _flo, _fhi in stages:
@@ -48,7 +47,7 @@ def _worker(rank, world, port, out_dir):
     own = m.SynthesisDatabase(device=-1)
     own.set_shard(rank, world)
     own.plan_precompute(2)
-    assert own.families() == fams and own.stages() == stages
+    assert own.families() == fams and own.stages() == stages and own.spec_owners() == owners
     for i in range(0, n_specs, 97):
         assert own.spec_blob(i) == db.spec_blob(i)
     # headers, candidate records, stages, families, goal ids, lookup table: byte for byte (Specs
@@ -59,7 +58,7 @@ def _worker(rank, world, port, out_dir):
             import ctypes
             assert ctypes.string_at(pa, na) == ctypes.string_at(pb, nb)
     own.close()
-    np.save(os.path.join(out_dir, f"loads_{rank}.npy"), np.array(sharded.rank_loads(fams, world)))
+    np.save(os.path.join(out_dir, f"loads_{rank}.npy"), np.array(sharded.rank_loads(owners, world)))
     db.close()
     dist.destroy_process_group()
 
@@ -77,11 +76,12 @@ def test_check_partition_rejects_gaps_and_bad_owners():
     from morello_b200 import sharded
     stages = [(0, 20, 0, 2), (20, 50, 2, 4)]
     fams = [(0, 0, 0, 10), (0, 1, 10, 20), (1, 1, 20, 40), (1, 0, 40, 50)]
-    sharded.check_partition(fams, stages, 2, 50)
-    assert sharded.rank_loads(fams, 2) == [20, 30]
+    owners = bytes([0] * 10 + [1] * 10 + [1] * 20 + [0] * 10)
+    sharded.check_partition(fams, stages, owners, 2, 50)
+    assert sharded.rank_loads(owners, 2) == [20, 30]
     with pytest.raises(ValueError):
-        sharded.check_partition(fams, stages, 2, 51)
+        sharded.check_partition(fams, stages, owners, 2, 51)
     with pytest.raises(ValueError):
-        sharded.check_partition(fams, stages, 1, 50)  # owner 1 does not exist
+        sharded.check_partition(fams, stages, owners, 1, 50)  # owner 1 does not exist
     with pytest.raises(ValueError):
-        sharded.check_partition([(0, 0, 0, 10), (0, 1, 11, 20)] + fams[2:], stages, 2, 50)
+        sharded.check_partition([(0, 0, 0, 10), (0, 1, 11, 20)] + fams[2:], stages, owners, 2, 50)
