@@ -211,9 +211,43 @@ inline LogicalSpec make_move_spec(const TensorSpec& left, const TensorSpec& righ
   return l;
 }
 
+// Leaf kernels in per-kind order; inapplicable kernels take no action number (cpu.rs:477-611).
+// Appends the applicable ones numbered from first_action and returns the next free number. This
+// is the only part of a Spec's candidate list that depends on the dtype itself rather than on
+// its byte size.
+inline u32 tabulate_leaves(const LogicalSpec& spec, u32 first_action, std::vector<Candidate>& out) {
+  u32 action = first_action;
+  static const LeafKernel accum_ks[] = {LK_MULTADD, LK_BCAST_VEC_MULTADD, LK_DOT_PRODUCT_LOOP};
+  static const LeafKernel move_ks[] = {LK_ASSIGN};
+  static const LeafKernel zero_ks[] = {LK_MEMSET_ZERO, LK_VALUE_ZERO, LK_VECTOR_ZERO};
+  const LeafKernel* ks = nullptr;
+  int nk = 0;
+  switch (spec.kind) {
+    case K_MATMUL_ACCUM: ks = accum_ks; nk = 3; break;
+    case K_MOVE: ks = move_ks; nk = 1; break;
+    case K_FILL_ZERO: ks = zero_ks; nk = 3; break;
+    default: break;
+  }
+  for (int i = 0; i < nk; i++) {
+    LeafInfo li = leaf_kernel_info(ks[i], spec);
+    if (!li.applies) continue;
+    Candidate c;
+    c.action = (u16)action++;
+    c.kind = CK_LEAF;
+    c.nchild = 0;
+    c.imm = li.main;
+    c.level = li.level;
+    c.units = li.units;
+    out.push_back(c);
+  }
+  return action;
+}
+
 // ---- the enumeration ----
-// Returns the total number of enumerated actions (applicable or not).
-inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& out) {
+// Returns the total number of enumerated actions (applicable or not); [*leaf_first, *leaf_end) =
+// the action numbers of the leaf-kernel section.
+inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& out, u32* leaf_first = nullptr,
+                               u32* leaf_end = nullptr) {
   if (!spec.serial_only) throw ModelError("only serial-only Specs are tabulated");
   u32 action = 0;
   const int nops = spec.nops();
@@ -308,29 +342,10 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
     }
   }
 
-  // 3. Leaf kernels in per-kind order; inapplicable kernels take no action number
-  //    (cpu.rs:477-611).
-  {
-    std::vector<LeafKernel> ks;
-    switch (spec.kind) {
-      case K_MATMUL_ACCUM: ks = {LK_MULTADD, LK_BCAST_VEC_MULTADD, LK_DOT_PRODUCT_LOOP}; break;
-      case K_MOVE: ks = {LK_ASSIGN}; break;
-      case K_FILL_ZERO: ks = {LK_MEMSET_ZERO, LK_VALUE_ZERO, LK_VECTOR_ZERO}; break;
-      default: break;
-    }
-    for (LeafKernel k : ks) {
-      LeafInfo li = leaf_kernel_info(k, spec);
-      if (!li.applies) continue;
-      Candidate c;
-      c.action = (u16)action++;
-      c.kind = CK_LEAF;
-      c.nchild = 0;
-      c.imm = li.main;
-      c.level = li.level;
-      c.units = li.units;
-      out.push_back(c);
-    }
-  }
+  // 3. Leaf kernels
+  if (leaf_first) *leaf_first = action;
+  action = tabulate_leaves(spec, action, out);
+  if (leaf_end) *leaf_end = action;
 
   // 4. Kind-specific tail (cpu.rs:685-699)
   if (spec.kind == K_MATMUL) {  // ToAccum (to_accum.rs:12-62; mod.rs:526-546)

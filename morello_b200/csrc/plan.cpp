@@ -90,6 +90,7 @@ struct TempSpec {
   LogicalSpec ls;
   std::string key;
   std::vector<CandRec> cands;  // child[] holds temporary ids
+  u16 leaf_first = 0, leaf_end = 0;  // action numbers of the leaf-kernel section [first, end)
 };
 
 // Growing array of TempSpec in fixed blocks: elements never move, blocks are allocated on demand
@@ -314,6 +315,48 @@ bool Plan::pack_limits(const u64 limits[NMEM], u32* out) const {
   return true;
 }
 
+namespace {
+
+// The limits-independent record of one candidate, without child ids. False: the candidate never
+// fits, at any limits in the lattice.
+bool make_rec(const Candidate& c, const u32* top_code, CandRec& r) {
+  memset(&r, 0, sizeof(r));
+  r.action = c.action;
+  r.kind = c.kind;
+  r.nchild = c.nchild;
+  r.imm = c.imm;
+  r.level = c.level;
+  r.units = c.units;
+  const u32 thr = (c.kind == CK_MOVE || c.kind == CK_LEAF) ? code_ceil(c.level, c.units) : 0;
+  if (thr > top_code[c.level]) return false;
+  r.thr_code = (u8)thr;
+  r.peak_code = (c.kind == CK_LEAF) ? (u8)code_ceil(c.level, c.units) : 0;
+  return true;
+}
+
+// Evaluation order of a Spec's records is free (the argmin carries the action number): kernels
+// first, then loops and blocks, then Moves by ascending base cost, so that the kernel's
+// lower-bound test on a Move's base cost cuts as early as possible.
+u64 cand_rank(const CandRec& c) {
+  const u64 k = c.kind == MRL_CK_LEAF ? 0 : (c.kind == MRL_CK_LOOP ? 1 : (c.kind == MRL_CK_BLOCK ? 2 : 3));
+  return (k << 32) | (c.kind == MRL_CK_MOVE ? c.imm : 0u);
+}
+bool cand_before(const CandRec& a, const CandRec& b) { return cand_rank(a) < cand_rank(b); }
+
+// Two 64-bit hashes of a goal's canonical key with the dtype byte forced to `as`.
+std::pair<u64, u64> twin_hash(const LogicalSpec& g0, Dtype as) {
+  LogicalSpec g = g0;
+  g.dtype = as;
+  if (logicalspec_canonicalize(g) != CANON_OK) return {0, 0};
+  char kb[LogicalSpec::MAX_KEY + 8];
+  const int kl = g.key_into(kb);
+  const u64 h1 = hash_key(kb, kl);
+  kb[kl] = (char)0x5a;
+  return {h1, hash_key(kb, kl + 1)};
+}
+
+}  // namespace
+
 Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, u32 rank, u32 world) {
   if (n_threads < 1) n_threads = 1;
   if (world < 1 || rank >= world) throw ModelError("bad shard rank / world size");
@@ -330,6 +373,33 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     plan.top_code[k] = top_code[k];
   }
 
+  // ---- 0. dtype twins ----
+  // When the goals come in two dtypes of one byte size (u32 and f32) and the two goal sets are
+  // each other's images under swapping the dtype, only the first dtype is discovered and
+  // tabulated: a Spec's Moves, tile-outs and splits depend on the dtype's size only, so the twin's
+  // records are the same with its own leaf kernels put in (step 2). A sample of the twins is
+  // tabulated directly afterwards and compared. MRL_NO_TWIN disables this.
+  bool twin = false;
+  Dtype dt_a = DT_U8, dt_b = DT_U8;
+  {
+    int seen[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (const LogicalSpec& g : goals) seen[g.dtype & 7] = 1;
+    int n_dt = 0;
+    for (int d = 0; d < 8; d++)
+      if (seen[d]) { if (n_dt == 0) dt_a = (Dtype)d; else dt_b = (Dtype)d; n_dt++; }
+    if (n_dt == 2 && dtype_size(dt_a) == dtype_size(dt_b) && !getenv("MRL_NO_TWIN")) {
+      std::vector<std::pair<u64, u64>> ha, hb;
+      std::vector<std::pair<u64, u64>> all(goals.size());
+      parallel_for(goals.size(), n_threads, [&](size_t i, int) { all[i] = twin_hash(goals[i], dt_a); });
+      for (size_t i = 0; i < goals.size(); i++) (goals[i].dtype == dt_a ? ha : hb).push_back(all[i]);
+      std::sort(ha.begin(), ha.end());
+      std::sort(hb.begin(), hb.end());
+      ha.erase(std::unique(ha.begin(), ha.end()), ha.end());
+      hb.erase(std::unique(hb.begin(), hb.end()), hb.end());
+      twin = ha == hb && !ha.empty() && ha.front() != std::pair<u64, u64>{0, 0};
+    }
+  }
+
   // ---- 1. discovery: closure of the goals under "is a sub-Spec of some candidate" ----
   double t0 = now_s();
   std::vector<KeyShard> shards(NSHARD);
@@ -339,6 +409,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   plan.goal_ids.assign(goals.size(), 0);
   parallel_for(goals.size(), n_threads, [&](size_t gi, int) {
     LogicalSpec g = goals[gi];
+    if (twin) g.dtype = dt_a;   // the twin's id is derived from this one in step 2
     if (logicalspec_canonicalize(g) != CANON_OK) throw ModelError("goal Spec cannot be canonicalized: " + goals[gi].str());
     char kb[LogicalSpec::MAX_KEY];
     const int kl = g.key_into(kb);
@@ -352,7 +423,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     }
     plan.goal_ids[gi] = id;
   });
-  plan.stats.n_goal_specs = next_id.load();
+  plan.stats.n_goal_specs = (u64)next_id.load() * (twin ? 2 : 1);
 
   // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
   for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
@@ -362,21 +433,14 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       TempSpec& ts = temp[round_lo + (u32)fi];
       std::vector<Candidate>& cs = per_thread[tid].scratch;
       cs.clear();
-      tabulate_candidates(ts.ls, cs);
+      u32 leaf_first = 0, leaf_end = 0;
+      tabulate_candidates(ts.ls, cs, &leaf_first, &leaf_end);
+      ts.leaf_first = (u16)leaf_first;
+      ts.leaf_end = (u16)leaf_end;
       ts.cands.reserve(cs.size());
       for (const Candidate& c : cs) {
         CandRec r;
-        memset(&r, 0, sizeof(r));
-        r.action = c.action;
-        r.kind = c.kind;
-        r.nchild = c.nchild;
-        r.imm = c.imm;
-        r.level = c.level;
-        r.units = c.units;
-        u32 thr = (c.kind == CK_MOVE || c.kind == CK_LEAF) ? code_ceil(c.level, c.units) : 0;
-        if (thr > top_code[c.level]) continue;  // never fits, at any limits in the lattice
-        r.thr_code = (u8)thr;
-        r.peak_code = (c.kind == CK_LEAF) ? (u8)code_ceil(c.level, c.units) : 0;
+        if (!make_rec(c, top_code, r)) continue;
         for (int j = 0; j < c.nchild; j++) {
           char kb[LogicalSpec::MAX_KEY];
           const int kl = c.child[j].key_into(kb);
@@ -435,67 +499,124 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     for (auto& th : pool) th.join();
   }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort ids %.2fs\n", now_s() - t1);
-  std::vector<u32> new_id(n);
-  for (u32 i = 0; i < n; i++) new_id[order[i]] = i;
-  for (u32& g : plan.goal_ids) g = new_id[g];
+  // Final ids. Without twins: the sorted position. With twins every stage holds its discovered
+  // Specs followed by their twins (the key orders by dtype right after the kind, and dt_a < dt_b):
+  // position i of a stage that starts at sorted position lo and has cnt Specs becomes id i + lo,
+  // its twin id i + lo + cnt.
+  const u32 mult = twin ? 2u : 1u;
+  if ((u64)n * mult > 0xFFFFFFF0ull) throw ModelError("too many Specs");
+  const u32 N = n * mult;
+  std::vector<u32> id_a(n), id_b(twin ? n : 0);   // by temporary id
+  std::vector<u32> pos_a(n), pos_b(twin ? n : 0); // by sorted position
+  for (u32 i = 0; i < n;) {
+    u32 j = i;
+    while (j < n && gkey[order[j]] == gkey[order[i]]) j++;
+    for (u32 k = i; k < j; k++) {
+      pos_a[k] = twin ? k + i : k;
+      id_a[order[k]] = pos_a[k];
+      if (twin) { pos_b[k] = pos_a[k] + (j - i); id_b[order[k]] = pos_b[k]; }
+    }
+    i = j;
+  }
+  for (size_t gi = 0; gi < goals.size(); gi++)
+    plan.goal_ids[gi] = (twin && goals[gi].dtype == dt_b) ? id_b[plan.goal_ids[gi]] : id_a[plan.goal_ids[gi]];
 
-  plan.specs.reset(n);
-  plan.hdrs.reset(n);
-  u64 ncand = 0;
-  for (u32 i = 0; i < n; i++) ncand += temp[order[i]].cands.size();
+  plan.specs.reset(N);
+  plan.hdrs.reset(N);
+  // candidate records per final id; a twin swaps the leaf records for its own
+  std::vector<u64> offs((size_t)N + 1, 0);
+  parallel_for(n, n_threads, [&](size_t i, int) {
+    const TempSpec& ts = temp[order[i]];
+    offs[pos_a[i] + 1] = ts.cands.size();
+    if (twin) {
+      size_t nleaf_a = 0;
+      for (const CandRec& r : ts.cands) nleaf_a += r.kind == MRL_CK_LEAF;
+      LogicalSpec sb = ts.ls;
+      sb.dtype = dt_b;
+      std::vector<Candidate> lv;
+      tabulate_leaves(sb, ts.leaf_first, lv);
+      size_t nleaf_b = 0;
+      CandRec r;
+      for (const Candidate& c : lv) nleaf_b += make_rec(c, top_code, r);
+      offs[pos_b[i] + 1] = ts.cands.size() - nleaf_a + nleaf_b;
+    }
+  });
+  for (u32 i = 0; i < N; i++) offs[i + 1] += offs[i];
+  const u64 ncand = offs[N];
   if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
   plan.cands.reset(ncand);
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]     counted cands %.2fs\n", now_s() - t1);
   {
-    std::vector<u64> offs(n + 1, 0);
-    for (u32 i = 0; i < n; i++) offs[i + 1] = offs[i] + temp[order[i]].cands.size();
-    std::vector<u64> kids_t(n_threads, 0);
-    if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]     offsets %.2fs\n", now_s() - t1);
-    parallel_for(n, n_threads, [&](size_t i, int tid) {
+    std::vector<u64> kids_t(1, 0);
+    parallel_for(n, n_threads, [&](size_t i, int) {
       TempSpec& ts = temp[order[i]];
-      plan.specs[i] = ts.ls;
-      SpecHdr& h = plan.hdrs[i];
-      memset(&h, 0, sizeof(h));
-      u64 off = offs[i];
-      h.cand_off = (u32)off;
-      h.ncand = (u32)ts.cands.size();
-      // Evaluation order is free (the argmin carries the action number): kernels first, then
-      // loops and blocks, then Moves by ascending base cost, so that the kernel's lower-bound
-      // test on a Move's base cost cuts as early as possible.
-      std::stable_sort(ts.cands.begin(), ts.cands.end(), [](const CandRec& a, const CandRec& b) {
-        auto rank = [](const CandRec& c) -> u64 {
-          u64 k = c.kind == MRL_CK_LEAF ? 0 : (c.kind == MRL_CK_LOOP ? 1 : (c.kind == MRL_CK_BLOCK ? 2 : 3));
-          return (k << 32) | (c.kind == MRL_CK_MOVE ? c.imm : 0u);
-        };
-        return rank(a) < rank(b);
-      });
+      std::stable_sort(ts.cands.begin(), ts.cands.end(), cand_before);
       u64 kids = 0;
-      for (CandRec r : ts.cands) {
-        for (int j = 0; j < r.nchild; j++) r.child[j] = new_id[r.child[j]];
-        kids += r.nchild;
-        plan.cands[off++] = r;
+      {
+        const u32 id = pos_a[i];
+        plan.specs[id] = ts.ls;
+        SpecHdr& h = plan.hdrs[id];
+        memset(&h, 0, sizeof(h));
+        u64 off = offs[id];
+        h.cand_off = (u32)off;
+        h.ncand = (u32)ts.cands.size();
+        for (CandRec r : ts.cands) {
+          for (int j = 0; j < r.nchild; j++) r.child[j] = id_a[r.child[j]];
+          kids += r.nchild;
+          plan.cands[off++] = r;
+        }
+      }
+      if (twin) {
+        const u32 id = pos_b[i];
+        LogicalSpec sb = ts.ls;
+        sb.dtype = dt_b;
+        plan.specs[id] = sb;
+        SpecHdr& h = plan.hdrs[id];
+        memset(&h, 0, sizeof(h));
+        u64 off = offs[id];
+        h.cand_off = (u32)off;
+        h.ncand = (u32)(offs[id + 1] - offs[id]);
+        // its own leaf kernels, numbered from where the leaf section starts ...
+        std::vector<Candidate> lv;
+        const u32 leaf_end_b = tabulate_leaves(sb, ts.leaf_first, lv);
+        for (const Candidate& c : lv) {
+          CandRec r;
+          if (make_rec(c, top_code, r)) plan.cands[off++] = r;
+        }
+        // ... then the first dtype's other records; what is numbered after the leaf section
+        // (ToAccum, splits) moves by the difference in applicable kernels
+        const int shift = (int)leaf_end_b - (int)ts.leaf_end;
+        for (CandRec r : ts.cands) {
+          if (r.kind == MRL_CK_LEAF) continue;
+          if (r.kind == MRL_CK_BLOCK || (r.kind == MRL_CK_LOOP && r.action >= ts.leaf_end)) r.action = (u16)((int)r.action + shift);
+          for (int j = 0; j < r.nchild; j++) r.child[j] = id_b[r.child[j]];
+          kids += r.nchild;
+          plan.cands[off++] = r;
+        }
+        if (off != offs[id + 1]) throw ModelError("planner: twin record count mismatch");
       }
       __atomic_fetch_add(&kids_t[0], kids, __ATOMIC_RELAXED);
     });
-    for (u64 k : kids_t) plan.stats.n_children += k;
+    plan.stats.n_children += kids_t[0];
   }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   move specs+cands %.2fs\n", now_s() - t1);
   parallel_for(n, n_threads, [&](size_t i, int) { temp.destroy((u32)i); });
+  // from here on everything is about the final arrays (N Specs)
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   free temp %.2fs\n", now_s() - t1);
   // id lookup table for find(): open addressing over the Spec key hash, ids only (equality is
   // checked on the Spec itself)
   {
     size_t cap = 64;
-    while (cap < (size_t)n * 2) cap *= 2;
+    while (cap < (size_t)N * 2) cap *= 2;
     plan.find_tab_.assign(cap, 0xFFFFFFFFu);
-    std::vector<u64> hs(n);
-    parallel_for(n, n_threads, [&](size_t i, int) {
+    std::vector<u64> hs(N);
+    parallel_for(N, n_threads, [&](size_t i, int) {
       char kb[LogicalSpec::MAX_KEY];
       const int kl = plan.specs[i].key_into(kb);
       hs[i] = hash_key(kb, kl);
     });
     const size_t mask = cap - 1;
-    for (u32 i = 0; i < n; i++) {
+    for (u32 i = 0; i < N; i++) {
       size_t j = (size_t)hs[i] & mask;
       while (plan.find_tab_[j] != 0xFFFFFFFFu) j = (j + 1) & mask;
       plan.find_tab_[j] = i;
@@ -505,10 +626,10 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 
   // stages, and inside them families: maximal runs with equal dtype and shape (ids are
   // key-sorted, and the key starts with kind, dtype, serial flag, rank, shape)
-  for (u32 i = 0; i < n;) {
+  for (u32 i = 0; i < N;) {
     const u32 sk = stage_key(plan.specs[i]);
     u32 j = i;
-    while (j < n && stage_key(plan.specs[j]) == sk) j++;
+    while (j < N && stage_key(plan.specs[j]) == sk) j++;
     Stage st;
     st.spec_lo = i;
     st.spec_hi = j;
@@ -540,14 +661,14 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // parent's stage belongs to a Move that consumes memory (so it sits at strictly lower limits)
   // and to the parent's family.
   {
-    std::vector<u32> stage_of(n), fam_of(n);
+    std::vector<u32> stage_of(N), fam_of(N);
     for (u32 si = 0; si < plan.stages.size(); si++)
       for (u32 i = plan.stages[si].spec_lo; i < plan.stages[si].spec_hi; i++) stage_of[i] = si;
     for (u32 fi = 0; fi < plan.families.size(); fi++)
       for (u32 i = plan.families[fi].spec_lo; i < plan.families[fi].spec_hi; i++) fam_of[i] = fi;
     std::atomic<int> bad{0};
     std::atomic<u64> bad_pair{0};
-    parallel_for(n, n_threads, [&](size_t i, int) {
+    parallel_for(N, n_threads, [&](size_t i, int) {
       const SpecHdr& h = plan.hdrs[i];
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
@@ -572,7 +693,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   if (plan.world > 1) {
     // a same-stage child must be solved by the rank that solves its parent
     std::atomic<int> split{0};
-    parallel_for(n, n_threads, [&](size_t i, int) {
+    parallel_for(N, n_threads, [&](size_t i, int) {
       const SpecHdr& h = plan.hdrs[i];
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
@@ -588,10 +709,37 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     });
     if (split.load()) throw ModelError("planner: a same-stage child belongs to another rank than its parent");
   }
+  if (twin) {
+    // Sample check of the twin derivation: tabulate every 2039th Spec (originals and twins alike)
+    // directly and compare with the records built above, byte for byte.
+    const u32 step = 2039;
+    std::atomic<long> bad{-1};
+    parallel_for((N + step - 1) / step, n_threads, [&](size_t k, int) {
+      const u32 id = (u32)k * step;
+      std::vector<Candidate> cs;
+      tabulate_candidates(plan.specs[id], cs);
+      std::vector<CandRec> recs;
+      for (const Candidate& c : cs) {
+        CandRec r;
+        if (!make_rec(c, top_code, r)) continue;
+        for (int j = 0; j < c.nchild; j++) {
+          const long ch = plan.find(c.child[j]);
+          if (ch < 0) { bad = id; return; }
+          r.child[j] = (u32)ch;
+        }
+        recs.push_back(r);
+      }
+      std::stable_sort(recs.begin(), recs.end(), cand_before);
+      const SpecHdr& h = plan.hdrs[id];
+      if (recs.size() != h.ncand || (h.ncand && memcmp(recs.data(), &plan.cands[h.cand_off], h.ncand * sizeof(CandRec)) != 0)) bad = id;
+    });
+    if (bad.load() >= 0)
+      throw ModelError("planner: records derived for a dtype twin differ from direct tabulation: " + plan.specs[(u32)bad.load()].str());
+  }
   plan.stats.seconds_layout = now_s() - t1;
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 
-  plan.stats.n_specs = n;
+  plan.stats.n_specs = N;
   plan.stats.n_cands = ncand;
   plan.stats.n_stages = plan.stages.size();
   plan.stats.n_families = plan.families.size();

@@ -1,0 +1,47 @@
+"""Host planner checks that need no GPU (planning-only contexts)."""
+import ctypes
+import os
+
+import pytest
+
+
+@pytest.fixture()
+def m(built_extension):
+    import morello_b200
+    return morello_b200
+
+
+@pytest.mark.parametrize("size", [1, 2, 4])
+def test_dtype_twin_plan_equals_direct_plan(m, size, monkeypatch):
+    """u32 and f32 goals: the planner tabulates u32 only and derives the f32 records. The result
+    must be the plan it builds when both dtypes are tabulated - headers, candidate records,
+    stages, families, goal ids and the id lookup table byte for byte, Specs by their blobs."""
+    monkeypatch.delenv("MRL_NO_TWIN", raising=False)
+    a = m.SynthesisDatabase(device=-1)
+    a.plan_precompute(size)
+    monkeypatch.setenv("MRL_NO_TWIN", "1")
+    b = m.SynthesisDatabase(device=-1)
+    b.plan_precompute(size)
+    keys = ("n_specs", "n_goal_specs", "n_candidates", "n_stages")
+    sa, sb = a.stats(), b.stats()
+    assert {k: sa[k] for k in keys} == {k: sb[k] for k in keys}
+    for (pa, na), (pb, nb) in list(zip(a.plan_share(), b.plan_share()))[2:]:
+        assert na == nb and ctypes.string_at(pa, na) == ctypes.string_at(pb, nb)
+    for i in range(0, a.num_specs(), 7 if size < 4 else 101):
+        assert a.spec_blob(i) == b.spec_blob(i)
+    a.close()
+    b.close()
+
+
+def test_single_dtype_and_uneven_goal_sets_are_planned_directly(m):
+    """Twins are only used when the two goal sets mirror each other."""
+    db = m.SynthesisDatabase(device=-1)
+    db.plan_precompute(2, dtypes=(m.DTYPE_F32,))
+    n_f32 = db.stats()["n_specs"]
+    db.plan_precompute(2)
+    assert db.stats()["n_specs"] == 2 * n_f32
+    goals = [m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL),
+             m.simple_spec(m.KIND_MATMUL, m.DTYPE_F32, [1, 2, 2, 1], m.GL)]
+    db.plan_goals(goals)       # different shapes per dtype: no twin derivation, still a valid plan
+    assert db.stats()["n_goal_specs"] == 2
+    db.close()
