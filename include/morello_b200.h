@@ -154,6 +154,13 @@ int mrl_fill_end(mrl_ctx* ctx);
 int mrl_get_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
                  mrl_decision* out);
 
+/* Replaces FilesDatabase::get_impl (morello/src/db/mod.rs:505-516; morello/src/reconstruct.rs:14-80)
+ * as called from frontend/src/main.rs:299-304: re-applies, from the given Spec down, the action the
+ * tables store for each (Spec, limits) and writes the resulting tree as text, one line per node:
+ *   <2 spaces per level><Spec> @ [rf, vrf, l1, gl]: #<action> <what> cost <main> peaks [..] depth <d>
+ * Returns the text length (NUL not counted) or a negative status (-3: `cap` too small). */
+long mrl_get_impl(mrl_ctx* ctx, const uint8_t* blob, size_t len, const uint64_t limits[4], char* out, size_t cap);
+
 /* Self-check of the filled tables, no counterpart in the reference (its closest relative is the
  * proptest that synthesis at peak memory yields the same decision, morello/src/search/mod.rs:152-199):
  * at n_samples pseudo-random points of (Spec x limits lattice) - every point when n_samples is 0 -

@@ -56,6 +56,7 @@ EXPORTS = {
     "mrl_fill_end": (C.c_int, [C.c_void_p]),
     "mrl_get_many": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_uint64),
                                C.POINTER(Decision)]),
+    "mrl_get_impl": (C.c_long, [C.c_void_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_uint64), C.c_char_p, C.c_size_t]),
     "mrl_verify": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "mrl_get_stats": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),
     "mrl_num_specs": (C.c_uint64, [C.c_void_p]),

@@ -1,6 +1,7 @@
 // C ABI of the B200 synthesis-database fill (declared in include/morello_b200.h).
 #include "../../include/morello_b200.h"
 #include "fill.hpp"
+#include "model/impl_text.hpp"
 #include <algorithm>
 #include <chrono>
 #include <thread>
@@ -440,6 +441,52 @@ int mrl_fill_end(mrl_ctx* ctx) {
   if (rc != 0) return fail(ctx, -2, ctx->dev.error());
   ctx->filled = true;
   return 0;
+}
+
+namespace {
+// One node of the reconstruction and, below it, its sub-Specs at the limits the stored action
+// leaves them (morello/src/reconstruct.rs:14-80).
+void reconstruct(mrl_ctx* ctx, const LogicalSpec& ls, const u64 limits[4], int level, std::string& out) {
+  const long id = ctx->plan.find(ls);
+  uint32_t pack = 0;
+  if (id < 0 || !ctx->plan.pack_limits(limits, &pack)) throw ModelError("not in the tables: " + ls.str());
+  const uint32_t id32 = (uint32_t)id;
+  MrlRow row;
+  if (ctx->dev.lookup(&id32, &pack, 1, &row) != 0) throw ModelError(ctx->dev.error());
+  mrl_decision d;
+  decode_row(row, &d);
+  if (d.found != 1) throw ModelError("no implementation for " + ls.str());
+  std::vector<Candidate> cs;
+  tabulate_candidates(ls, cs);
+  const Candidate* chosen = nullptr;
+  for (const Candidate& c : cs) if (c.action == d.action) chosen = &c;
+  if (!chosen) throw ModelError("stored action is not among the Spec's actions: " + ls.str());
+  out += impl_line(level, ls, limits, d.action, action_text(*chosen), d.main_cost, d.peaks, d.depth);
+  u64 child_limits[4] = {limits[0], limits[1], limits[2], limits[3]};
+  if (chosen->kind == CK_MOVE) {
+    const int m = chosen->level;
+    if (limits[m] < chosen->units) throw ModelError("stored Move does not fit its limits");
+    const u64 rem = limits[m] - chosen->units;
+    child_limits[m] = mem_counts_registers((Mem)m) ? rem : prev_power_of_two(rem);
+  }
+  for (int j = 0; j < chosen->nchild; j++) reconstruct(ctx, chosen->child[j], child_limits, level + 1, out);
+}
+}  // namespace
+
+long mrl_get_impl(mrl_ctx* ctx, const uint8_t* blob, size_t len, const uint64_t limits[4], char* out, size_t cap) {
+  if (!ctx) return -1;
+  if (!ctx->filled) return fail(ctx, -1, "tables are not filled");
+  try {
+    LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)blob, len));
+    if (logicalspec_canonicalize(ls) != CANON_OK) return fail(ctx, -4, "Spec is not canonicalizable");
+    std::string text;
+    reconstruct(ctx, ls, limits, 0, text);
+    if (text.size() + 1 > cap) return fail(ctx, -3, "implementation text needs " + std::to_string(text.size() + 1) + " bytes");
+    memcpy(out, text.c_str(), text.size() + 1);
+    return (long)text.size();
+  } catch (const std::exception& e) {
+    return fail(ctx, -1, e.what());
+  }
 }
 
 int mrl_verify(mrl_ctx* ctx, uint64_t n_samples, uint64_t seed, uint64_t* n_checked, uint64_t* n_mismatch) {

@@ -921,10 +921,16 @@ int DeviceFill::upload(const Plan& plan) {
     if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
     if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
   } else {
-    chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)n_specs_ * 2);
-    temp_cap_ = std::max<uint64_t>(1u << 20, (uint64_t)max_stage * 64);
-    cell_cap_ = temp_cap_;
-    row_cap_ = std::max<uint64_t>(1u << 20, (uint64_t)n_specs_ * 16);
+    // Starting sizes from what fills of this kind ended with (about 40 table rows per Spec and
+    // 700 working cells per Spec of the largest stage at size 8), within a quarter of the free
+    // memory each; every buffer still grows on demand.
+    size_t free_b = 0, total_b = 0;
+    CK(cudaMemGetInfo(&free_b, &total_b));
+    const uint64_t quarter = free_b / 4;
+    chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)max_stage * 32);
+    temp_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage * 700, quarter / sizeof(MrlRow)));
+    cell_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage * 400, quarter / sizeof(CellRef)));
+    row_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)n_specs_ * 40, quarter / sizeof(MrlRow)));
     if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
     if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
     if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;

@@ -38,7 +38,15 @@ struct Candidate {
   u8 level = 0;   // memory index that `units` refers to
   u32 units = 0;  // MOVE: units consumed in `level`; LEAF: kernel allocation in `level`
   LogicalSpec child[3];
+  // What the action is, for printing a reconstructed implementation (no effect on the fill).
+  u8 what = 0;    // ActionWhat
+  u8 arg0 = 0;    // Move: operand index; TileOut: dimension; Kernel: LeafKernel
+  u8 arg1 = 0;    // Move: destination memory
+  u32 arg2 = 0;   // Move: vector size; TileOut: tile size; Split: k
+  Layout lay;     // Move: destination layout as enumerated
 };
+
+enum ActionWhat : u8 { ACT_MOVE = 0, ACT_TILE_OUT = 1, ACT_SPLIT = 2, ACT_KERNEL = 3, ACT_TO_ACCUM = 4 };
 
 // ---- leaf kernels ----
 inline bool is_rf_or_l1(Mem m) { return m == RF || m == L1; }
@@ -238,6 +246,8 @@ inline u32 tabulate_leaves(const LogicalSpec& spec, u32 first_action, std::vecto
     c.imm = li.main;
     c.level = li.level;
     c.units = li.units;
+    c.what = ACT_KERNEL;
+    c.arg0 = (u8)ks[i];
     out.push_back(c);
   }
   return action;
@@ -276,6 +286,11 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
     c.child[n++] = body;
     if (epilogue) c.child[n++] = make_move_spec(p.new_spec, ops[i], spec.serial_only);
     c.nchild = (u8)n;
+    c.what = ACT_MOVE;
+    c.arg0 = (u8)i;
+    c.arg1 = (u8)mem;
+    c.arg2 = vs;
+    c.lay = layout;
     out.push_back(c);
   };
   for (int i = 0; i < nops; i++) {
@@ -337,6 +352,9 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
         if (iters > 0xFFFFFFFFull) throw ModelError("loop iteration count overflows u32");
         c.imm = (u32)iters;
         c.child[0] = body;
+        c.what = ACT_TILE_OUT;
+        c.arg0 = (u8)dim;
+        c.arg2 = size;
         out.push_back(c);
       }
     }
@@ -365,6 +383,7 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
     if (logicalspec_canonicalize(acc) != CANON_OK) throw ModelError("ToAccum: accumulating Spec is not canonicalizable");
     c.child[0] = fill;
     c.child[1] = acc;
+    c.what = ACT_TO_ACCUM;
     out.push_back(c);
   } else if (spec.kind == K_MATMUL_ACCUM) {  // Split (common_actions.rs:123-197; tiling.rs:478-541)
     const u32 b = spec.spec_shape[0], m = spec.spec_shape[1], K = spec.spec_shape[2], n = spec.spec_shape[3];
@@ -389,6 +408,8 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
       c.nchild = 1;
       c.imm = K / k;
       c.child[0] = body;
+      c.what = ACT_SPLIT;
+      c.arg2 = k;
       out.push_back(c);
     }
   }

@@ -233,6 +233,16 @@ class SynthesisDatabase:
     def fill_end(self):
         self._check(self._lib.mrl_fill_end(self._ctx))
 
+    # --- FilesDatabase::get_impl ---
+    def get_impl(self, spec: bytes, limits: Sequence[int] = MAX_MEM) -> str:
+        """The optimal implementation of (Spec, limits) reconstructed from the tables, as text."""
+        lim = (C.c_uint64 * 4)(*limits)
+        buf = C.create_string_buffer(1 << 20)
+        n = self._lib.mrl_get_impl(self._ctx, spec, len(spec), lim, buf, len(buf))
+        if n < 0:
+            self._check(int(n))
+        return buf.raw[:n].decode()
+
     def verify(self, n_samples: int = 0, seed: int = 1):
         """(points checked, mismatches): recomputes the decision from the children's tables at
         n_samples pseudo-random (Spec, limits) points - all of them when n_samples is 0 - and

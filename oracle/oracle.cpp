@@ -1,5 +1,6 @@
 // TEST INFRASTRUCTURE — NOT PART OF THE PRODUCT PATH. See oracle.hpp.
 #include "oracle.hpp"
+#include "../morello_b200/csrc/model/impl_text.hpp"
 #include <algorithm>
 #include <chrono>
 #include <set>
@@ -281,6 +282,45 @@ int orc_top_down(void* h, const uint8_t* key, uint32_t key_len, const uint64_t* 
     Search s(((OrcHandle*)h)->db);
     fill_decision(out, s.solve(ls, l));
     return 0;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "oracle error: %s\n", e.what());
+    return -1;
+  }
+}
+
+// Reconstruction of the optimal implementation from stored actions
+// (morello/src/reconstruct.rs:14-80): solve (or look up) the Spec, re-apply the stored action,
+// recurse into the sub-Specs at the limits the action leaves them. Appends one line per node.
+static void reconstruct(Search& s, const LogicalSpec& ls, const Limits& limits, int level, std::string& out) {
+  const Decision d = s.solve(ls, limits);
+  if (!d.found) throw ModelError("no implementation for " + ls.str());
+  std::vector<Candidate> cs;
+  tabulate_candidates(ls, cs);
+  const Candidate* chosen = nullptr;
+  for (const Candidate& c : cs) if (c.action == d.action) chosen = &c;
+  if (!chosen) throw ModelError("stored action is not among the Spec's actions: " + ls.str());
+  out += impl_line(level, ls, limits.data(), d.action, action_text(*chosen), d.cost.main, d.cost.peaks.data(), d.cost.depth);
+  Limits child_limits = limits;
+  if (chosen->kind == CK_MOVE) {
+    Limits consumed = {0, 0, 0, 0};
+    consumed[chosen->level] = chosen->units;
+    if (!checked_sub_snap_down(limits, consumed, child_limits)) throw ModelError("stored Move does not fit its limits");
+  }
+  for (int j = 0; j < chosen->nchild; j++) reconstruct(s, chosen->child[j], child_limits, level + 1, out);
+}
+
+// FilesDatabase::get_impl (morello/src/db/mod.rs:505-516) as text. Returns the length, or < 0.
+long orc_get_impl(void* h, const uint8_t* key, uint32_t key_len, const uint64_t* limits, char* out, uint64_t cap) {
+  try {
+    LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)key, key_len));
+    if (logicalspec_canonicalize(ls) != CANON_OK) return -2;
+    Limits l = {limits[0], limits[1], limits[2], limits[3]};
+    Search s(((OrcHandle*)h)->db);
+    std::string text;
+    reconstruct(s, ls, l, 0, text);
+    if (text.size() + 1 > cap) return -3;
+    memcpy(out, text.c_str(), text.size() + 1);
+    return (long)text.size();
   } catch (const std::exception& e) {
     fprintf(stderr, "oracle error: %s\n", e.what());
     return -1;

@@ -55,6 +55,16 @@ class Oracle:
             raise RuntimeError(f"oracle top_down failed ({rc})")
         return out
 
+    def get_impl(self, key: bytes, limits) -> str:
+        """The optimal implementation of (Spec, limits) as text, one line per node."""
+        lim = (C.c_uint64 * 4)(*limits)
+        buf = C.create_string_buffer(1 << 20)
+        self.lib.orc_get_impl.restype = C.c_long
+        n = self.lib.orc_get_impl(self.h, key, len(key), lim, buf, len(buf))
+        if n < 0:
+            raise RuntimeError(f"oracle get_impl failed ({n})")
+        return buf.raw[:n].decode()
+
     def num_puts(self):
         return int(self.lib.orc_num_puts(self.h))
 

@@ -55,6 +55,9 @@ def main():
         d = o.top_down(goal, MAX_MEM)
         save(f"matmul2_{dtype_name}.npz", o, {"goal": np.frombuffer(goal, dtype=np.uint8),
                                               "goal_decision": np.array([d.found, d.action, d.main, d.depth] + list(d.peaks))})
+        # the optimal implementation reconstructed from the stored actions, one line per node
+        with open(os.path.join(HERE, f"impl_matmul2_{dtype_name}.txt"), "w") as f:
+            f.write(o.get_impl(goal, MAX_MEM))
         o.close()
 
 

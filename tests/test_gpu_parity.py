@@ -78,6 +78,27 @@ def test_gpu_tables_match_committed_golden_fixtures(m, name):
     db.close()
 
 
+@pytest.mark.parametrize("dtype_name", ["u32", "f32"])
+def test_reconstructed_implementation_matches_oracle_and_golden(m, oracle, dtype_name):
+    """get_impl (morello/src/db/mod.rs:505-516): the tree reconstructed from the GPU tables is the
+    oracle's, line for line - also at lower limits and for a Move goal."""
+    import os
+    dtype = m.DTYPE_U32 if dtype_name == "u32" else m.DTYPE_F32
+    goal = m.simple_spec(m.KIND_MATMUL, dtype, [1, 2, 2, 2], m.GL)
+    move = m.simple_spec(m.KIND_MOVE, dtype, [2, 2], m.GL)
+    db = m.SynthesisDatabase()
+    db.top_down_many([goal, move])
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"impl_matmul2_{dtype_name}.txt")) as f:
+        assert db.get_impl(goal) == f.read()
+    o = oracle.new()
+    for spec, limits in ((goal, m.MAX_MEM), (goal, (6, 0, 64, 1024)), (move, m.MAX_MEM), (move, (3, 16, 8, 4096))):
+        assert db.get_impl(spec, limits) == o.get_impl(spec, limits)
+    with pytest.raises(RuntimeError, match="no implementation"):
+        db.get_impl(goal, (2, 0, 0, 0))
+    o.close()
+    db.close()
+
+
 def test_edge_cases(m):
     db = m.SynthesisDatabase()
     # empty goal list

@@ -3,6 +3,7 @@ import os
 import subprocess
 
 import numpy as np
+import pytest
 
 import oracle_lib
 
@@ -43,6 +44,22 @@ def test_matmul2_top_down_matches_golden(oracle):
         assert [d.found, d.action, d.main, d.depth] + list(d.peaks) == list(g["goal_decision"])
         assert _sorted_puts(*o.dump()) == _sorted_puts(g["keys"], g["key_off"], g["rect"], g["dec"])
         o.close()
+
+
+@pytest.mark.parametrize("dtype_name", ["u32", "f32"])
+def test_reconstructed_implementation_matches_golden(oracle, dtype_name):
+    """get_impl: re-applying the stored actions from the goal down gives the committed tree."""
+    g = np.load(os.path.join(GOLDEN, f"matmul2_{dtype_name}.npz"))
+    with open(os.path.join(GOLDEN, f"impl_matmul2_{dtype_name}.txt")) as f:
+        want = f.read()
+    o = oracle.new()
+    got = o.get_impl(g["goal"].tobytes(), (16, 16, 1024, 33554432))
+    o.close()
+    assert got == want
+    lines = want.splitlines()
+    cost = {"u32": 127, "f32": 119}[dtype_name]   # MultAdd costs 2 on integers, 1 on f32 (cpu.rs:2315-2340): 8 kernels
+    assert len(lines) == 17 and lines[0].startswith("Matmul(1x2x2x2") and f" cost {cost} " in lines[0]
+    assert lines[-1].lstrip().startswith("MatmulAccum(1x1x1x1") and "Kernel(MultAdd)" in lines[-1]
 
 
 def test_hand_derived_matmul1_cost(oracle):
