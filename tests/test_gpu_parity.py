@@ -147,6 +147,29 @@ def test_precompute_size4_matches_a_bounded_oracle_run(m, oracle):
     o.close()
 
 
+@pytest.mark.parametrize("dtype_name,shape", [("u32", [1, 2, 2, 4]), ("f32", [1, 2, 2, 4]), ("u32", [1, 4, 2, 2]),
+                                              ("f32", [1, 2, 4, 4])])
+def test_mid_size_matmul_goals_match_oracle(m, oracle, dtype_name, shape):
+    """Goals beyond size 2 that the oracle's top-down search still finishes in seconds: dimensions
+    of 4, vector registers and packed layouts in the closure. Every put of the oracle (up to
+    0.8 M per goal) is checked against the GPU tables at both corners of its rectangle."""
+    dtype = m.DTYPE_U32 if dtype_name == "u32" else m.DTYPE_F32
+    goal = m.simple_spec(m.KIND_MATMUL, dtype, shape, m.GL)
+    o = oracle.new()
+    want = o.top_down(goal, m.MAX_MEM)
+    db = m.SynthesisDatabase()
+    got = db.top_down(goal)
+    assert (got.found, got.action, got.main_cost, got.depth, tuple(got.peaks)) == \
+        (want.found, want.action, want.main, want.depth, tuple(want.peaks))
+    assert o.dominance_conflicts() == 0
+    keys, off, rect, dec = o.dump()
+    bad = parity_util.compare_puts(db, keys, off, rect, dec)
+    assert not bad, "\n".join(bad)
+    assert db.get_impl(goal) == o.get_impl(goal, m.MAX_MEM)
+    db.close()
+    o.close()
+
+
 def test_size2_tables_satisfy_the_recurrence_at_every_lattice_point(m):
     """Property over the whole table, independent of the oracle: at every one of the 93 636
     limits of every Spec, re-deriving the decision from the children's tables gives the stored
