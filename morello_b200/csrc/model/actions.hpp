@@ -16,6 +16,8 @@
 // (Move solver); morello/src/scheduling/to_accum.rs:12-62; morello/src/scheduling/select.rs:13-56.
 #pragma once
 #include "spec.hpp"
+#include <memory>
+#include <unordered_map>
 
 namespace mrl {
 
@@ -38,6 +40,9 @@ struct Candidate {
   u8 level = 0;   // memory index that `units` refers to
   u32 units = 0;  // MOVE: units consumed in `level`; LEAF: kernel allocation in `level`
   LogicalSpec child[3];
+  // Optional memo slots for the ids a caller gives to child[j] (see MoveMemo): Move prologues
+  // and epilogues depend on the moved operand only and recur across thousands of parent Specs.
+  u32* child_id_slot[3] = {nullptr, nullptr, nullptr};
   // What the action is, for printing a reconstructed implementation (no effect on the fill).
   u8 what = 0;    // ActionWhat
   u8 arg0 = 0;    // Move: operand index; TileOut: dimension; Kernel: LeafKernel
@@ -253,64 +258,135 @@ inline u32 tabulate_leaves(const LogicalSpec& spec, u32 first_action, std::vecto
   return action;
 }
 
+// ---- Moves of one operand (common_actions.rs:301-376), independent of the rest of the Spec ----
+struct MoveOption {
+  u16 action_rel = 0;      // position among the operand's enumerated Moves
+  u8 mem = 0;              // destination memory
+  u32 vs = 0;              // destination vector size
+  Layout layout;           // destination layout as enumerated
+  Aux new_aux;             // the moved operand afterwards
+  bool cache_miss = false;
+  u32 units = 0;
+  u32 imm = 0;             // move cost of source + destination
+  u32 pro_id = 0xFFFFFFFFu, epi_id = 0xFFFFFFFFu;  // memo slots for the caller's ids of the Move Specs below
+  LogicalSpec pro, epi;    // prologue Move(source -> new), epilogue Move(new -> source)
+};
+struct OperandMoves {
+  u32 n_actions = 0;       // enumerated Moves of the operand, applicable or not
+  std::vector<MoveOption> opts;  // the applicable ones, in enumeration order
+};
+
+inline void operand_moves(const TensorSpec& op, bool serial_only, OperandMoves& out) {
+  out.n_actions = 0;
+  out.opts.clear();
+  const u32 src_cost = move_cost(op);
+  auto emit = [&](Mem mem, const Layout& layout, u32 vs) {
+    const u32 rel = out.n_actions++;
+    MovePlan p = plan_move(op, mem, layout, vs);
+    if (!p.applies) return;
+    MoveOption o;
+    o.action_rel = (u16)rel;
+    o.mem = (u8)mem;
+    o.vs = vs;
+    o.layout = layout;
+    o.new_aux = p.new_spec.aux;
+    o.cache_miss = p.cache_miss;
+    o.units = (u32)p.units;
+    o.imm = src_cost + move_cost(p.new_spec);
+    o.pro = make_move_spec(op, p.new_spec, serial_only);
+    o.epi = make_move_spec(p.new_spec, op, serial_only);
+    out.opts.push_back(o);
+  };
+  std::vector<Layout> dest_layouts = move_destination_layouts(op.shape, op.dtype);
+  std::vector<Mem> dest_mems = possible_destination_memories(op.aux.mem);
+  bool contains_source_layout = false;
+  for (const Layout& layout : dest_layouts) {
+    if (!contains_source_layout && layout == op.aux.layout) contains_source_layout = true;
+    for (Mem mem : dest_mems) {
+      const std::vector<u32>& vb = mem_vector_bytes(mem);
+      if (vb.empty()) emit(mem, layout, 0);
+      else for (u32 b : vb) emit(mem, layout, b / dtype_size(op.dtype));
+    }
+  }
+  if (!contains_source_layout) {
+    for (Mem mem : dest_mems) {
+      if (mem_is_addressed(mem)) continue;
+      emit(mem, op.aux.layout, 0);  // caches have no vector sizes
+    }
+  }
+}
+
+// Memo of operand_moves by operand (shape, dtype, aux). One per thread; entries never move.
+class MoveMemo {
+ public:
+  OperandMoves& get(const TensorSpec& op, bool serial_only) {
+    char kb[8 + 2 * MAX_RANK + 4 + 4 * MAX_PHYS];
+    int p = 0;
+    kb[p++] = (char)op.dtype; kb[p++] = (char)serial_only; kb[p++] = (char)op.shape.n; kb[p++] = (char)op.aux.mem;
+    kb[p++] = (char)op.aux.vector_size; kb[p++] = (char)op.aux.layout.n; kb[p++] = (char)op.aux.layout.contig; kb[p++] = 0;
+    for (int i = 0; i < op.shape.n; i++) { kb[p++] = (char)(op.shape[i] & 0xff); kb[p++] = (char)(op.shape[i] >> 8); }
+    for (int j = 0; j < op.aux.layout.n; j++) {
+      kb[p++] = (char)op.aux.layout.d[j].ldim; kb[p++] = (char)op.aux.layout.d[j].kind;
+      kb[p++] = (char)(op.aux.layout.d[j].size & 0xff); kb[p++] = (char)(op.aux.layout.d[j].size >> 8);
+    }
+    std::string key(kb, (size_t)p);
+    auto it = map_.find(key);
+    if (it != map_.end()) return *it->second;
+    std::unique_ptr<OperandMoves> om(new OperandMoves());
+    operand_moves(op, serial_only, *om);
+    OperandMoves& ref = *om;
+    map_.emplace(std::move(key), std::move(om));
+    return ref;
+  }
+  size_t size() const { return map_.size(); }
+
+ private:
+  std::unordered_map<std::string, std::unique_ptr<OperandMoves>> map_;
+};
+
 // ---- the enumeration ----
 // Returns the total number of enumerated actions (applicable or not); [*leaf_first, *leaf_end) =
 // the action numbers of the leaf-kernel section.
 inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& out, u32* leaf_first = nullptr,
-                               u32* leaf_end = nullptr) {
+                               u32* leaf_end = nullptr, MoveMemo* memo = nullptr) {
   if (!spec.serial_only) throw ModelError("only serial-only Specs are tabulated");
   u32 action = 0;
   const int nops = spec.nops();
   TensorSpec ops[MAX_OPS];
   for (int i = 0; i < nops; i++) ops[i] = spec.operand(i);
 
-  // 1. Moves (common_actions.rs:301-376)
-  auto emit_move = [&](int i, Mem mem, const Layout& layout, u32 vs) {
-    u32 this_action = action++;
-    MovePlan p = plan_move(ops[i], mem, layout, vs);
-    if (!p.applies) return;
-    Candidate c;
-    c.action = (u16)this_action;
-    c.kind = CK_MOVE;
-    c.level = (u8)mem;
-    c.units = (u32)p.units;
-    c.imm = move_cost(ops[i]) + move_cost(p.new_spec);
-    Direction dir = kind_direction(spec.kind, i);
-    bool prologue = !p.cache_miss && (dir == DIR_IN || dir == DIR_INOUT);
-    bool epilogue = !p.cache_miss && (dir == DIR_OUT || dir == DIR_INOUT);
-    int n = 0;
-    if (prologue) c.child[n++] = make_move_spec(ops[i], p.new_spec, spec.serial_only);
-    LogicalSpec body = spec;
-    body.aux[i] = p.new_spec.aux;
-    if (body.kind == K_MOVE) canonicalize_matching_contiguous_move_auxes(body);
-    c.child[n++] = body;
-    if (epilogue) c.child[n++] = make_move_spec(p.new_spec, ops[i], spec.serial_only);
-    c.nchild = (u8)n;
-    c.what = ACT_MOVE;
-    c.arg0 = (u8)i;
-    c.arg1 = (u8)mem;
-    c.arg2 = vs;
-    c.lay = layout;
-    out.push_back(c);
-  };
+  // 1. Moves (common_actions.rs:301-376): per operand, from the memo when there is one
   for (int i = 0; i < nops; i++) {
-    std::vector<Layout> dest_layouts = move_destination_layouts(ops[i].shape, ops[i].dtype);
-    std::vector<Mem> dest_mems = possible_destination_memories(ops[i].aux.mem);
-    bool contains_source_layout = false;
-    for (const Layout& layout : dest_layouts) {
-      if (!contains_source_layout && layout == ops[i].aux.layout) contains_source_layout = true;
-      for (Mem mem : dest_mems) {
-        const std::vector<u32>& vb = mem_vector_bytes(mem);
-        if (vb.empty()) emit_move(i, mem, layout, 0);
-        else for (u32 b : vb) emit_move(i, mem, layout, b / dtype_size(ops[i].dtype));
-      }
+    OperandMoves local;
+    OperandMoves* om = &local;
+    if (memo) om = &memo->get(ops[i], spec.serial_only);
+    else operand_moves(ops[i], spec.serial_only, local);
+    const Direction dir = kind_direction(spec.kind, i);
+    for (MoveOption& o : om->opts) {
+      Candidate c;
+      c.action = (u16)(action + o.action_rel);
+      c.kind = CK_MOVE;
+      c.level = o.mem;
+      c.units = o.units;
+      c.imm = o.imm;
+      const bool prologue = !o.cache_miss && (dir == DIR_IN || dir == DIR_INOUT);
+      const bool epilogue = !o.cache_miss && (dir == DIR_OUT || dir == DIR_INOUT);
+      int n = 0;
+      if (prologue) { c.child[n] = o.pro; c.child_id_slot[n] = memo ? &o.pro_id : nullptr; n++; }
+      LogicalSpec body = spec;
+      body.aux[i] = o.new_aux;
+      if (body.kind == K_MOVE) canonicalize_matching_contiguous_move_auxes(body);
+      c.child[n++] = body;
+      if (epilogue) { c.child[n] = o.epi; c.child_id_slot[n] = memo ? &o.epi_id : nullptr; n++; }
+      c.nchild = (u8)n;
+      c.what = ACT_MOVE;
+      c.arg0 = (u8)i;
+      c.arg1 = o.mem;
+      c.arg2 = o.vs;
+      c.lay = o.layout;
+      out.push_back(c);
     }
-    if (!contains_source_layout) {
-      for (Mem mem : dest_mems) {
-        if (mem_is_addressed(mem)) continue;
-        emit_move(i, mem, ops[i].aux.layout, 0);  // caches have no vector sizes
-      }
-    }
+    action += om->n_actions;
   }
 
   // 2. Serial single-loop tile-outs (common_actions.rs:37-121; tiling.rs:132-228)

@@ -7,6 +7,7 @@
 #include <chrono>
 #include <mutex>
 #include <thread>
+#include <memory>
 #include <unordered_map>
 
 namespace mrl {
@@ -425,16 +426,21 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   });
   plan.stats.n_goal_specs = (u64)next_id.load() * (twin ? 2 : 1);
 
+  // Per thread: the Moves of an operand, and the ids of their prologue / epilogue Move Specs, are
+  // worked out once and reused by every Spec that has the operand.
+  std::vector<std::unique_ptr<MoveMemo>> move_memos(n_threads);
+  for (auto& mm : move_memos) mm.reset(new MoveMemo());
   // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
   for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
     struct alignas(128) PerThread { std::vector<Candidate> scratch; };
+    // (the Move memos live across rounds: see move_memos below)
     std::vector<PerThread> per_thread(n_threads);
     parallel_for(round_hi - round_lo, n_threads, [&](size_t fi, int tid) {
       TempSpec& ts = temp[round_lo + (u32)fi];
       std::vector<Candidate>& cs = per_thread[tid].scratch;
       cs.clear();
       u32 leaf_first = 0, leaf_end = 0;
-      tabulate_candidates(ts.ls, cs, &leaf_first, &leaf_end);
+      tabulate_candidates(ts.ls, cs, &leaf_first, &leaf_end, move_memos[tid].get());
       ts.leaf_first = (u16)leaf_first;
       ts.leaf_end = (u16)leaf_end;
       ts.cands.reserve(cs.size());
@@ -442,6 +448,10 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         CandRec r;
         if (!make_rec(c, top_code, r)) continue;
         for (int j = 0; j < c.nchild; j++) {
+          if (c.child_id_slot[j] && *c.child_id_slot[j] != 0xFFFFFFFFu) {
+            r.child[j] = *c.child_id_slot[j];   // this thread met the Move Spec before
+            continue;
+          }
           char kb[LogicalSpec::MAX_KEY];
           const int kl = c.child[j].key_into(kb);
           const u64 h = hash_key(kb, kl);
@@ -453,6 +463,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
             fresh.key.assign(kb, (size_t)kl);
           }
           r.child[j] = id;
+          if (c.child_id_slot[j]) *c.child_id_slot[j] = id;
         }
         ts.cands.push_back(r);
       }
