@@ -316,19 +316,44 @@ inline void operand_moves(const TensorSpec& op, bool serial_only, OperandMoves& 
   }
 }
 
-// Memo of operand_moves by operand (shape, dtype, aux). One per thread; entries never move.
+// What tiling does to one operand: its aux after the layout is updated for the tile shape and
+// canonicalised (tiling.rs:132-228 per operand; tensorspec.rs:232-236,370-377).
+struct TileResult {
+  bool applies = false;  // the layout applies to the tile shape (TensorSpec::is_valid_tile_shape)
+  bool ok = false;       // ... and the tiled operand canonicalises
+  Aux aux;
+};
+inline TileResult tile_operand(const TensorSpec& op, const Shape& tile) {
+  TileResult r;
+  r.aux = op.aux;
+  if (mem_has_layout(op.aux.mem)) {
+    Layout nl;
+    if (!layout_update_for_tiling(op.aux.layout, op.shape, tile, nl)) return r;
+    r.aux.layout = nl;
+  }
+  r.applies = true;
+  if (check_tensor_vector_size(tile, op.dtype, r.aux.mem, r.aux.vector_size) != CANON_OK) return r;
+  if (!aux_canonicalize(r.aux, tile)) return r;
+  r.ok = true;
+  return r;
+}
+
+// Memo of operand_moves and tile_operand by operand (shape, dtype, aux). One per thread;
+// entries never move.
 class MoveMemo {
  public:
+  const TileResult& tile(const TensorSpec& op, const Shape& tile_shape) {
+    char kb[8 + 4 * MAX_RANK + 4 + 4 * MAX_PHYS];
+    int p = operand_key(op, false, kb);
+    for (int i = 0; i < tile_shape.n; i++) { kb[p++] = (char)(tile_shape[i] & 0xff); kb[p++] = (char)(tile_shape[i] >> 8); }
+    std::string key(kb, (size_t)p);
+    auto it = tiles_.find(key);
+    if (it != tiles_.end()) return it->second;
+    return tiles_.emplace(std::move(key), tile_operand(op, tile_shape)).first->second;
+  }
   OperandMoves& get(const TensorSpec& op, bool serial_only) {
     char kb[8 + 2 * MAX_RANK + 4 + 4 * MAX_PHYS];
-    int p = 0;
-    kb[p++] = (char)op.dtype; kb[p++] = (char)serial_only; kb[p++] = (char)op.shape.n; kb[p++] = (char)op.aux.mem;
-    kb[p++] = (char)op.aux.vector_size; kb[p++] = (char)op.aux.layout.n; kb[p++] = (char)op.aux.layout.contig; kb[p++] = 0;
-    for (int i = 0; i < op.shape.n; i++) { kb[p++] = (char)(op.shape[i] & 0xff); kb[p++] = (char)(op.shape[i] >> 8); }
-    for (int j = 0; j < op.aux.layout.n; j++) {
-      kb[p++] = (char)op.aux.layout.d[j].ldim; kb[p++] = (char)op.aux.layout.d[j].kind;
-      kb[p++] = (char)(op.aux.layout.d[j].size & 0xff); kb[p++] = (char)(op.aux.layout.d[j].size >> 8);
-    }
+    const int p = operand_key(op, serial_only, kb);
     std::string key(kb, (size_t)p);
     auto it = map_.find(key);
     if (it != map_.end()) return *it->second;
@@ -341,8 +366,42 @@ class MoveMemo {
   size_t size() const { return map_.size(); }
 
  private:
+  static int operand_key(const TensorSpec& op, bool flag, char* kb) {
+    int p = 0;
+    kb[p++] = (char)op.dtype; kb[p++] = (char)flag; kb[p++] = (char)op.shape.n; kb[p++] = (char)op.aux.mem;
+    kb[p++] = (char)op.aux.vector_size; kb[p++] = (char)op.aux.layout.n; kb[p++] = (char)op.aux.layout.contig; kb[p++] = 0;
+    for (int i = 0; i < op.shape.n; i++) { kb[p++] = (char)(op.shape[i] & 0xff); kb[p++] = (char)(op.shape[i] >> 8); }
+    for (int j = 0; j < op.aux.layout.n; j++) {
+      kb[p++] = (char)op.aux.layout.d[j].ldim; kb[p++] = (char)op.aux.layout.d[j].kind;
+      kb[p++] = (char)(op.aux.layout.d[j].size & 0xff); kb[p++] = (char)(op.aux.layout.d[j].size >> 8);
+    }
+    return p;
+  }
   std::unordered_map<std::string, std::unique_ptr<OperandMoves>> map_;
+  std::unordered_map<std::string, TileResult> tiles_;
 };
+
+// The body Spec of a tile-out or split: `body` comes in with the new spec_shape; every operand's
+// aux is updated for its new shape and canonicalised. False: the action does not apply.
+inline bool tile_body(const LogicalSpec& spec, const TensorSpec* ops, int nops, LogicalSpec& body, MoveMemo* memo) {
+  if (memo) {
+    for (int j = 0; j < nops; j++) {
+      const TileResult& t = memo->tile(ops[j], body.operand_shape(j));
+      if (!t.ok) return false;
+      body.aux[j] = t.aux;
+    }
+    if (body.kind == K_MOVE) canonicalize_matching_contiguous_move_auxes(body);
+    return true;
+  }
+  for (int j = 0; j < nops; j++) {
+    if (!mem_has_layout(ops[j].aux.mem)) continue;
+    Layout nl;
+    if (!layout_update_for_tiling(ops[j].aux.layout, ops[j].shape, body.operand_shape(j), nl)) return false;
+    body.aux[j].layout = nl;
+  }
+  (void)spec;
+  return logicalspec_canonicalize(body) == CANON_OK;
+}
 
 // ---- the enumeration ----
 // Returns the total number of enumerated actions (applicable or not); [*leaf_first, *leaf_end) =
@@ -402,7 +461,7 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
         if (size > out_shape[dim]) continue;   // TileShapeIsLarger
         Shape tile = out_shape;
         tile[dim] = size;
-        if (!tensorspec_valid_tile_shape(ops[oi], tile)) continue;
+        if (memo ? !memo->tile(ops[oi], tile).applies : !tensorspec_valid_tile_shape(ops[oi], tile)) continue;
         if (out_shape[dim] % size != 0) throw ModelError("boundary tile-outs are outside the tabulated space");
         LogicalSpec body = spec;
         if (spec.kind == K_MATMUL || spec.kind == K_MATMUL_ACCUM) {
@@ -410,15 +469,7 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
         } else {
           body.spec_shape = tile;
         }
-        bool ok = true;
-        for (int j = 0; j < nops && ok; j++) {
-          if (!mem_has_layout(ops[j].aux.mem)) continue;
-          Layout nl;
-          if (!layout_update_for_tiling(ops[j].aux.layout, ops[j].shape, body.operand_shape(j), nl)) ok = false;
-          else body.aux[j].layout = nl;
-        }
-        if (!ok) continue;
-        if (logicalspec_canonicalize(body) != CANON_OK) continue;
+        if (!tile_body(spec, ops, nops, body, memo)) continue;
         Candidate c;
         c.action = (u16)this_action;
         c.kind = CK_LOOP;
@@ -464,20 +515,13 @@ inline u32 tabulate_candidates(const LogicalSpec& spec, std::vector<Candidate>& 
   } else if (spec.kind == K_MATMUL_ACCUM) {  // Split (common_actions.rs:123-197; tiling.rs:478-541)
     const u32 b = spec.spec_shape[0], m = spec.spec_shape[1], K = spec.spec_shape[2], n = spec.spec_shape[3];
     for (u32 k : dim_range_pow2(K, false)) {
-      if (!tensorspec_valid_tile_shape(ops[0], Shape{b, m, k}) || !tensorspec_valid_tile_shape(ops[1], Shape{b, k, n})) continue;
+      if (memo ? (!memo->tile(ops[0], Shape{b, m, k}).applies || !memo->tile(ops[1], Shape{b, k, n}).applies)
+               : (!tensorspec_valid_tile_shape(ops[0], Shape{b, m, k}) || !tensorspec_valid_tile_shape(ops[1], Shape{b, k, n}))) continue;
       u32 this_action = action++;
       if (K % k != 0) throw ModelError("boundary splits are outside the tabulated space");
       LogicalSpec body = spec;
       body.spec_shape[2] = k;
-      bool ok = true;
-      for (int j = 0; j < nops && ok; j++) {
-        if (!mem_has_layout(ops[j].aux.mem)) continue;
-        Layout nl;
-        if (!layout_update_for_tiling(ops[j].aux.layout, ops[j].shape, body.operand_shape(j), nl)) ok = false;
-        else body.aux[j].layout = nl;
-      }
-      if (!ok) continue;
-      if (logicalspec_canonicalize(body) != CANON_OK) continue;
+      if (!tile_body(spec, ops, nops, body, memo)) continue;
       Candidate c;
       c.action = (u16)this_action;
       c.kind = CK_LOOP;

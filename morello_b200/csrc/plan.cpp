@@ -429,7 +429,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // Per thread: the Moves of an operand, and the ids of their prologue / epilogue Move Specs, are
   // worked out once and reused by every Spec that has the operand.
   std::vector<std::unique_ptr<MoveMemo>> move_memos(n_threads);
-  for (auto& mm : move_memos) mm.reset(new MoveMemo());
+  if (!getenv("MRL_NO_MEMO"))   // without: every Spec is tabulated from scratch (for cross-checks)
+    for (auto& mm : move_memos) mm.reset(new MoveMemo());
   // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
   for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
     struct alignas(128) PerThread { std::vector<Candidate> scratch; };

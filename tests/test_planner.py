@@ -33,6 +33,25 @@ def test_dtype_twin_plan_equals_direct_plan(m, size, monkeypatch):
     b.close()
 
 
+@pytest.mark.parametrize("size", [2, 4])
+def test_memoised_tabulation_equals_tabulation_from_scratch(m, size, monkeypatch):
+    """The planner reuses, per operand, its Moves and what tiling does to it. The plan must be the
+    one built with every Spec tabulated from scratch."""
+    monkeypatch.setenv("MRL_NO_TWIN", "1")
+    monkeypatch.delenv("MRL_NO_MEMO", raising=False)
+    a = m.SynthesisDatabase(device=-1)
+    a.plan_precompute(size)
+    monkeypatch.setenv("MRL_NO_MEMO", "1")
+    b = m.SynthesisDatabase(device=-1)
+    b.plan_precompute(size)
+    for (pa, na), (pb, nb) in list(zip(a.plan_share(), b.plan_share()))[2:]:
+        assert na == nb and ctypes.string_at(pa, na) == ctypes.string_at(pb, nb)
+    for i in range(0, a.num_specs(), 7 if size < 4 else 101):
+        assert a.spec_blob(i) == b.spec_blob(i)
+    a.close()
+    b.close()
+
+
 def test_single_dtype_and_uneven_goal_sets_are_planned_directly(m):
     """Twins are only used when the two goal sets mirror each other."""
     db = m.SynthesisDatabase(device=-1)
