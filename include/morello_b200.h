@@ -132,7 +132,12 @@ int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world);
  * sizes (mrl_plan_adopt gives the pointers) and finish with mrl_plan_adopt_done. The planning rank
  * must have called mrl_set_shard with the same world size before planning. */
 int mrl_plan_share(mrl_ctx* ctx, void* ptrs[8], uint64_t sizes[8]);
-int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8]);
+int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8], int cands_on_device_only);
+/* The candidate records (range 3, by far the largest) are only ever read on the device. With
+ * cands_on_device_only the adopting rank gets no host pointer for them (ptrs[3] = NULL): after
+ * mrl_upload on every rank the caller copies the planning rank's device records into
+ * mrl_device_cands of the others (e.g. ncclBroadcast over NVLink). */
+int mrl_device_cands(const mrl_ctx* ctx, void** ptr, uint64_t* bytes);
 int mrl_plan_adopt_done(mrl_ctx* ctx, double plan_seconds);
 int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream);
 uint64_t mrl_num_stages(const mrl_ctx* ctx);

@@ -38,7 +38,8 @@ EXPORTS = {
     "mrl_fill": (C.c_int, [C.c_void_p]),
     "mrl_set_shard": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32]),
     "mrl_plan_share": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
-    "mrl_plan_adopt": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_void_p)]),
+    "mrl_plan_adopt": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_void_p), C.c_int]),
+    "mrl_device_cands": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "mrl_plan_adopt_done": (C.c_int, [C.c_void_p, C.c_double]),
     "mrl_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
     "mrl_num_stages": (C.c_uint64, [C.c_void_p]),

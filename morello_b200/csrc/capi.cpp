@@ -17,6 +17,7 @@ struct mrl_ctx {
   mrl_stats stats;
   std::string err;
   uint32_t rank = 0, world = 1;
+  bool cands_elsewhere = false;   // adopted plan whose candidate records only exist on the planning rank
 };
 
 namespace {
@@ -81,6 +82,7 @@ int upload_and_fill(mrl_ctx* ctx) {
 
 int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
   double t0 = now_s();
+  ctx->cands_elsewhere = false;
   ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->rank, ctx->world);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
@@ -216,7 +218,7 @@ int mrl_upload(mrl_ctx* ctx) {
   if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to fill on");
   if (!ctx->planned) return fail(ctx, -1, "nothing planned");
   double t0 = now_s();
-  if (ctx->dev.upload(ctx->plan) != 0) return fail(ctx, -2, ctx->dev.error());
+  if (ctx->dev.upload(ctx->plan, ctx->cands_elsewhere) != 0) return fail(ctx, -2, ctx->dev.error());
   ctx->uploaded = true;
   ctx->filled = false;
   ctx->stats.upload_seconds = now_s() - t0;
@@ -333,7 +335,7 @@ int mrl_plan_share(mrl_ctx* ctx, void* ptrs[8], uint64_t sizes[8]) {
   return 0;
 }
 
-int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8]) {
+int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8], int cands_on_device_only) {
   if (!ctx || !sizes || !ptrs) return -1;
   try {
     u64 sz[Plan::N_BLOBS];
@@ -342,6 +344,8 @@ int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8]) {
     ctx->planned = ctx->uploaded = ctx->filled = false;
     ctx->plan.adopt_alloc(sz);
     ctx->plan.share_blobs(ptrs, sz);
+    ctx->cands_elsewhere = cands_on_device_only != 0;
+    if (ctx->cands_elsewhere) ptrs[3] = nullptr;   // never touched on this host
     return 0;
   } catch (const std::exception& e) {
     return fail(ctx, -1, e.what());
@@ -395,6 +399,13 @@ int mrl_spec_owners(const mrl_ctx* ctx, uint8_t* out, uint64_t n) {
   if (!ctx || !ctx->planned || !out || n != ctx->plan.hdrs.size()) return -1;
   if (ctx->plan.owner.empty()) memset(out, 0, n);
   else memcpy(out, ctx->plan.owner.data(), n);
+  return 0;
+}
+
+int mrl_device_cands(const mrl_ctx* ctx, void** ptr, uint64_t* bytes) {
+  if (!ctx || !ctx->uploaded) return -1;
+  if (ptr) *ptr = ctx->dev.device_cands();
+  if (bytes) *bytes = ctx->dev.device_cand_bytes();
   return 0;
 }
 

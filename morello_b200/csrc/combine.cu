@@ -877,7 +877,7 @@ int DeviceFill::set_stream(cudaStream_t s) {
   return 0;
 }
 
-int DeviceFill::upload(const Plan& plan) {
+int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaSetDevice(device_));
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
   free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
@@ -938,12 +938,13 @@ int DeviceFill::upload(const Plan& plan) {
     if (!h_ctr_) CK(cudaHostAlloc((void**)&h_ctr_, 256, cudaHostAllocDefault));
     if (!h_diag_) CK(cudaHostAlloc((void**)&h_diag_, sizeof(DiagTable), cudaHostAllocDefault));
   }
-  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + plan.cands.size() * sizeof(CandRec) + plan.mine.size();
+  h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + (skip_cands ? 0 : plan.cands.size() * sizeof(CandRec)) + plan.mine.size();
   CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
   if (!plan.hdrs.empty())
     CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
-  if (!plan.cands.empty())
+  if (!plan.cands.empty() && !skip_cands)
     CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), plan.cands.size() * sizeof(CandRec), cudaMemcpyHostToDevice, stream_));
+  n_cand_bytes_ = plan.cands.size() * sizeof(CandRec);
   if (d_mine_) CK(cudaMemcpyAsync(d_mine_, plan.mine.data(), plan.mine.size(), cudaMemcpyHostToDevice, stream_));
   CK(cudaStreamSynchronize(stream_));
   stats_ = FillStats();

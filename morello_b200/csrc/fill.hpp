@@ -26,7 +26,11 @@ class DeviceFill {
   // that is never grown or freed (attach_buffer before upload).
   void attach_buffer(void* base, size_t bytes, cudaStream_t stream, int device);
   // Copies headers and candidate records to the device and sets up the arena.
-  int upload(const Plan& plan);
+  // skip_cands: the candidate records are not on this host; the caller fills device_cands()
+  // itself (e.g. a broadcast from the rank that planned) before the first fill.
+  int upload(const Plan& plan, bool skip_cands = false);
+  void* device_cands() const { return d_cands_; }
+  uint64_t device_cand_bytes() const { return n_cand_bytes_; }
   // Runs every stage.
   int run(const Plan& plan);
   // The same one stage at a time, for callers that exchange tables between stages (multi-GPU):
@@ -92,6 +96,7 @@ class DeviceFill {
   unsigned long long final_top_seen_ = 0, stage_info_seen_[2] = {0, 0};  // last values read back
   uint64_t last_cells_ = 0;             // working cells of the last pass of the stage being solved
   uint64_t h2d_bytes_ = 0;
+  uint64_t n_cand_bytes_ = 0;
   bool filling_ = false;
   // Before the first solve of a stage a Spec's working masks also take the first masks of its
   // same-stage children (shifted), this many hops deep: one hop saves a third of the solve

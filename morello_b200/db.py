@@ -165,11 +165,19 @@ class SynthesisDatabase:
         self._check(self._lib.mrl_plan_share(self._ctx, ptrs, sizes))
         return [(int(ptrs[k] or 0), int(sizes[k])) for k in range(8)]
 
-    def plan_adopt(self, sizes: Sequence[int]):
-        """Allocates an empty plan of the given range sizes; returns the pointers to fill."""
+    def plan_adopt(self, sizes: Sequence[int], cands_on_device_only: bool = False):
+        """Allocates an empty plan of the given range sizes; returns the pointers to fill (0 for
+        the candidate records when they will only be copied device to device)."""
         ptrs, sz = (C.c_void_p * 8)(), (C.c_uint64 * 8)(*sizes)
-        self._check(self._lib.mrl_plan_adopt(self._ctx, sz, ptrs))
+        self._check(self._lib.mrl_plan_adopt(self._ctx, sz, ptrs, int(cands_on_device_only)))
         return [int(ptrs[k] or 0) for k in range(8)]
+
+    def device_cands(self):
+        """(device pointer, bytes) of the uploaded candidate records."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        if self._lib.mrl_device_cands(self._ctx, C.byref(ptr), C.byref(n)) != 0:
+            raise RuntimeError("plan not uploaded")
+        return int(ptr.value or 0), int(n.value)
 
     def plan_adopt_done(self, plan_seconds: float = 0.0):
         self._check(self._lib.mrl_plan_adopt_done(self._ctx, plan_seconds))

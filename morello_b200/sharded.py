@@ -80,11 +80,12 @@ def fill_sharded(db, dist, torch, process_group=None):
 
 
 def plan_on_one_rank(db, plan_fn: Callable[[], None], dist, torch, process_group=None, device="cuda",
-                     chunk_bytes=256 << 20):
+                     chunk_bytes=256 << 20, cands_on_device_only=False):
     """Plans on the first rank only and hands the plan to the others. The ranks of one node share
     its host cores, so planning once with all of them beats every rank planning on a share.
     The plan's eight byte ranges travel by broadcast, staged through `device` memory in chunks
-    ("cuda" for NCCL, "cpu" for gloo)."""
+    ("cuda" for NCCL, "cpu" for gloo). cands_on_device_only: the candidate records (most of the
+    bytes) are left out here; after upload() call broadcast_device_cands()."""
     rank, world = dist.get_rank(process_group), dist.get_world_size(process_group)
     src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
     db.set_shard(rank, world)
@@ -100,7 +101,9 @@ def plan_on_one_rank(db, plan_fn: Callable[[], None], dist, torch, process_group
     dist.broadcast(sizes, src=src, group=process_group)
     if rank != 0:
         want = [int(x) for x in sizes.tolist()]
-        blobs = list(zip(db.plan_adopt(want), want))
+        blobs = list(zip(db.plan_adopt(want, cands_on_device_only), want))
+    if cands_on_device_only:
+        blobs = [b for k, b in enumerate(blobs) if k != 3]
     chunk = max(1, min(chunk_bytes, max(n for _, n in blobs)))
     host = torch.empty(chunk, dtype=torch.uint8, pin_memory=(device == "cuda"))
     stage = torch.empty(chunk, dtype=torch.uint8, device=device) if device == "cuda" else host
@@ -120,8 +123,22 @@ def plan_on_one_rank(db, plan_fn: Callable[[], None], dist, torch, process_group
         db.plan_adopt_done(time.perf_counter() - t0)
 
 
+def broadcast_device_cands(db, dist, torch, process_group=None):
+    """Copies the planning rank's uploaded candidate records into the other ranks' device buffers."""
+    ptr, nbytes = db.device_cands()
+    if nbytes == 0 or dist.get_world_size(process_group) == 1:
+        return
+    src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
+    buf = torch.as_tensor(_DeviceBytes(ptr, nbytes), device="cuda")
+    step = 1 << 30
+    for off in range(0, nbytes, step):
+        dist.broadcast(buf[off:off + step], src=src, group=process_group)
+
+
 def precompute_sharded(db, size, dist, torch, through=2, dtypes=(4, 6), process_group=None):
     """`precompute` on all ranks of the process group."""
-    plan_on_one_rank(db, lambda: db.plan_precompute(size, through, dtypes), dist, torch, process_group)
+    plan_on_one_rank(db, lambda: db.plan_precompute(size, through, dtypes), dist, torch, process_group,
+                     cands_on_device_only=True)
     db.upload()
+    broadcast_device_cands(db, dist, torch, process_group)
     fill_sharded(db, dist, torch, process_group)
