@@ -284,7 +284,10 @@ def cuda_arm(args):
         traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(traffic_path):
             with open(traffic_path) as f:
-                line["roofline"]["traffic"] = json.load(f).get(str(SIZE), {}).get("dram_bytes_per_step")
+                t = json.load(f).get(str(SIZE))
+            if t:  # measured DRAM bytes per algorithmic byte on a small case, scaled to this step (see the file's "how")
+                line["roofline"]["traffic"] = t["dram_over_algorithmic"] * st["algorithmic_bytes"]
+                line["roofline"]["traffic_how"] = "scaled from a small-case ncu capture: profiles/traffic.json"
         print(json.dumps(line))
     db.close()
     if world > 1:
