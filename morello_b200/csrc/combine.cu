@@ -1262,6 +1262,7 @@ int DeviceFill::run(const Plan& plan) {
 }
 
 int DeviceFill::lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t n, MrlRow* out) {
+  std::lock_guard<std::mutex> guard(lookup_mu_);   // callers on several threads share the staging buffer and the stream
   CK(cudaSetDevice(device_));
   if (n == 0) return 0;
   for (size_t i = 0; i < n; i++)

@@ -3,6 +3,7 @@
 #pragma once
 #include "plan.hpp"
 #include <cuda_runtime.h>
+#include <mutex>
 
 namespace mrl {
 
@@ -110,6 +111,7 @@ class DeviceFill {
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
   std::vector<cudaEvent_t> ev_pool_;
   size_t ev_used_ = 0;
+  std::mutex lookup_mu_;
   char err_[256] = {0};
 };
 
