@@ -4,6 +4,7 @@
 #include "model/impl_text.hpp"
 #include <algorithm>
 #include <chrono>
+#include <cstdlib>
 #include <thread>
 
 using namespace mrl;
@@ -80,10 +81,10 @@ int upload_and_fill(mrl_ctx* ctx) {
   return 0;
 }
 
-int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals) {
+int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals, int mirror_dtype = -1) {
   double t0 = now_s();
   ctx->cands_elsewhere = false;
-  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->rank, ctx->world);
+  ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->rank, ctx->world, mirror_dtype);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
   const PlanStats& ps = ctx->plan.stats;
@@ -193,8 +194,15 @@ int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask
     std::vector<Dtype> dts = dtypes_of(dtype_mask);
     if (dts.empty()) return fail(ctx, -1, "empty dtype mask");
     double t0 = now_s();
+    // u32 + f32: the goal sets mirror each other by construction, so only the u32 goals are
+    // enumerated and the planner derives the f32 half (plan.cpp, "dtype twins")
+    int mirror = -1;
+    if (dts.size() == 2 && dts[0] == DT_U32 && dts[1] == DT_F32 && !getenv("MRL_NO_TWIN")) {
+      dts.pop_back();
+      mirror = DT_F32;
+    }
     std::vector<LogicalSpec> goals = precompute_goals(size, (Through)through, dts, ctx->n_threads);
-    int rc = set_plan(ctx, goals);
+    int rc = set_plan(ctx, goals, mirror);
     ctx->stats.plan_seconds = now_s() - t0;
     return rc;
   } catch (const std::exception& e) {

@@ -600,15 +600,17 @@ diag_histogram_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict_
 }
 
 // Pass step 3b: lists the working cells diagonal by diagonal (diag->base set by the host from the
-// histogram). A block counts its own cells per diagonal, reserves that many list slots per
-// diagonal with one atomic each, then writes its cells.
+// histogram). Every warp counts its own cells per diagonal; the block reserves list slots per
+// diagonal with one atomic each and hands every warp a contiguous piece, so that the cells one
+// warp (one Spec) has on a diagonal stay neighbours in the list - and neighbours in a combine warp.
 __global__ void __launch_bounds__(128)
 scatter_cells_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
                      DiagTable* __restrict__ diag, CellRef* __restrict__ cells) {
-  __shared__ uint32_t hist[MRL_MAX_DIAG];
-  __shared__ unsigned long long start[MRL_MAX_DIAG];
-  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) hist[k] = 0;
+  __shared__ uint32_t hist[4][MRL_MAX_DIAG];
+  __shared__ unsigned long long start[4][MRL_MAX_DIAG];
+  for (uint32_t k = threadIdx.x; k < 4 * MRL_MAX_DIAG; k += blockDim.x) hist[k / MRL_MAX_DIAG][k % MRL_MAX_DIAG] = 0;
   __syncthreads();
+  const uint32_t wib = threadIdx.x >> 5;   // warp in block
   const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
   Column c;
@@ -616,12 +618,19 @@ scatter_cells_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__
   if (warp < n_chunks) c = decode_column(hdrs, chunks[warp], lane);
   const uint32_t mF = c.valid ? sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F) : 0u;
   for (uint32_t mrest = mF; mrest; mrest &= mrest - 1)
-    atomicAdd(&hist[(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
+    atomicAdd(&hist[wib][(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
   __syncthreads();
   for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) {
-    const uint32_t n = hist[k];
-    if (n) start[k] = diag->base[k] + atomicAdd(&diag->cursor[k], n);
-    hist[k] = 0;   // becomes the block-local cursor
+    const uint32_t n0 = hist[0][k], n1 = hist[1][k], n2 = hist[2][k], n3 = hist[3][k];
+    const uint32_t n = n0 + n1 + n2 + n3;
+    if (n) {
+      const unsigned long long base = diag->base[k] + atomicAdd(&diag->cursor[k], n);
+      start[0][k] = base;
+      start[1][k] = base + n0;
+      start[2][k] = base + n0 + n1;
+      start[3][k] = base + n0 + n1 + n2;
+    }
+    hist[0][k] = hist[1][k] = hist[2][k] = hist[3][k] = 0;   // become the warps' cursors
   }
   __syncthreads();
   if (!c.valid) return;
@@ -633,11 +642,11 @@ scatter_cells_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__
   uint32_t s = 0;
   for (uint32_t mrest = mF; mrest; mrest &= mrest - 1, s++) {
     const uint32_t d = (c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1);
-    const uint32_t pos = atomicAdd(&hist[d], 1u);
+    const uint32_t pos = atomicAdd(&hist[wib][d], 1u);
     CellRef r;
     r.spec = c.spec;
     r.cell = off0 + s * stF;
-    cells[start[d] + pos] = r;
+    cells[start[wib][d] + pos] = r;
   }
 }
 

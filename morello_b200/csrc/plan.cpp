@@ -358,7 +358,8 @@ std::pair<u64, u64> twin_hash(const LogicalSpec& g0, Dtype as) {
 
 }  // namespace
 
-Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, u32 rank, u32 world) {
+Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, u32 rank, u32 world,
+                int mirror_dtype) {
   if (n_threads < 1) n_threads = 1;
   if (world < 1 || rank >= world) throw ModelError("bad shard rank / world size");
   Plan plan;
@@ -382,7 +383,15 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // tabulated directly afterwards and compared. MRL_NO_TWIN disables this.
   bool twin = false;
   Dtype dt_a = DT_U8, dt_b = DT_U8;
-  {
+  const bool mirrored = mirror_dtype >= 0 && !goals.empty();   // the caller vouches: goals come in one dtype, mirror them
+  if (mirrored) {
+    dt_a = goals[0].dtype;
+    dt_b = (Dtype)mirror_dtype;
+    for (const LogicalSpec& g : goals)
+      if (g.dtype != dt_a) throw ModelError("mirrored goals must come in one dtype");
+    if (dt_b <= dt_a || dtype_size(dt_a) != dtype_size(dt_b)) throw ModelError("cannot mirror goals into this dtype");
+    twin = true;
+  } else {
     int seen[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (const LogicalSpec& g : goals) seen[g.dtype & 7] = 1;
     int n_dt = 0;
@@ -530,8 +539,18 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     }
     i = j;
   }
-  for (size_t gi = 0; gi < goals.size(); gi++)
-    plan.goal_ids[gi] = (twin && goals[gi].dtype == dt_b) ? id_b[plan.goal_ids[gi]] : id_a[plan.goal_ids[gi]];
+  if (mirrored) {   // goals, then their mirror images
+    const size_t ng = goals.size();
+    plan.goal_ids.resize(2 * ng);
+    for (size_t gi = 0; gi < ng; gi++) {
+      const u32 t = plan.goal_ids[gi];
+      plan.goal_ids[gi] = id_a[t];
+      plan.goal_ids[ng + gi] = id_b[t];
+    }
+  } else {
+    for (size_t gi = 0; gi < goals.size(); gi++)
+      plan.goal_ids[gi] = (twin && goals[gi].dtype == dt_b) ? id_b[plan.goal_ids[gi]] : id_a[plan.goal_ids[gi]];
+  }
 
   plan.specs.reset(N);
   plan.hdrs.reset(N);

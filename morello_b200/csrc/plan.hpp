@@ -132,7 +132,7 @@ struct Plan {
   bool pack_limits(const u64 limits[NMEM], u32* out) const;
 
  private:
-  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32);
+  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32, int);
   std::vector<u32> find_tab_;  // open-addressing table of ids by Spec key hash (0xFFFFFFFF = empty)
   struct Meta {                // blob 0
     u32 top_code[NMEM];
@@ -142,9 +142,11 @@ struct Plan {
   void assign_owners_();
 };
 
-// Top limits are Avx2Target::max_mem() unless overridden.
+// Top limits are Avx2Target::max_mem() unless overridden. mirror_dtype >= 0: the goals come in
+// one dtype and the plan also covers their images in that second dtype of the same byte size
+// (what build_plan otherwise detects by itself when handed both goal sets).
 Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr,
-                u32 rank = 0, u32 world = 1);
+                u32 rank = 0, u32 world = 1, int mirror_dtype = -1);
 
 // Goal sets.
 std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes,

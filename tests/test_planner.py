@@ -11,6 +11,21 @@ def m(built_extension):
     return morello_b200
 
 
+def _same_plan(a, b, size):
+    """Headers, candidate records, stages, families and the id lookup table byte for byte; the goal
+    ids as a set (their order follows how the goals were handed in); Specs by their blobs."""
+    import numpy as np
+    ra, rb = a.plan_share(), b.plan_share()
+    for k in (2, 3, 4, 5, 7):
+        (pa, na), (pb, nb) = ra[k], rb[k]
+        assert na == nb and ctypes.string_at(pa, na) == ctypes.string_at(pb, nb), k
+    ga = np.sort(np.frombuffer(ctypes.string_at(*ra[6]), dtype=np.uint32))
+    gb = np.sort(np.frombuffer(ctypes.string_at(*rb[6]), dtype=np.uint32))
+    assert (ga == gb).all()
+    for i in range(0, a.num_specs(), 7 if size < 4 else 101):
+        assert a.spec_blob(i) == b.spec_blob(i)
+
+
 @pytest.mark.parametrize("size", [1, 2, 4])
 def test_dtype_twin_plan_equals_direct_plan(m, size, monkeypatch):
     """u32 and f32 goals: the planner tabulates u32 only and derives the f32 records. The result
@@ -25,10 +40,7 @@ def test_dtype_twin_plan_equals_direct_plan(m, size, monkeypatch):
     keys = ("n_specs", "n_goal_specs", "n_candidates", "n_stages")
     sa, sb = a.stats(), b.stats()
     assert {k: sa[k] for k in keys} == {k: sb[k] for k in keys}
-    for (pa, na), (pb, nb) in list(zip(a.plan_share(), b.plan_share()))[2:]:
-        assert na == nb and ctypes.string_at(pa, na) == ctypes.string_at(pb, nb)
-    for i in range(0, a.num_specs(), 7 if size < 4 else 101):
-        assert a.spec_blob(i) == b.spec_blob(i)
+    _same_plan(a, b, size)
     a.close()
     b.close()
 
@@ -44,10 +56,7 @@ def test_memoised_tabulation_equals_tabulation_from_scratch(m, size, monkeypatch
     monkeypatch.setenv("MRL_NO_MEMO", "1")
     b = m.SynthesisDatabase(device=-1)
     b.plan_precompute(size)
-    for (pa, na), (pb, nb) in list(zip(a.plan_share(), b.plan_share()))[2:]:
-        assert na == nb and ctypes.string_at(pa, na) == ctypes.string_at(pb, nb)
-    for i in range(0, a.num_specs(), 7 if size < 4 else 101):
-        assert a.spec_blob(i) == b.spec_blob(i)
+    _same_plan(a, b, size)
     a.close()
     b.close()
 
@@ -64,3 +73,24 @@ def test_single_dtype_and_uneven_goal_sets_are_planned_directly(m):
     db.plan_goals(goals)       # different shapes per dtype: no twin derivation, still a valid plan
     assert db.stats()["n_goal_specs"] == 2
     db.close()
+
+
+def test_mirrored_goal_lists_are_detected(m, monkeypatch):
+    """top_down_many-style goal lists that contain every goal in both dtypes take the twin path
+    too (detected from the goals themselves) and give the direct plan."""
+    shapes = ([1, 2, 2, 2], [1, 2, 4, 2], [1, 1, 2, 4])
+    goals = [m.simple_spec(m.KIND_MATMUL, dt, sh, m.GL) for dt in (m.DTYPE_F32, m.DTYPE_U32) for sh in shapes]
+    monkeypatch.delenv("MRL_NO_TWIN", raising=False)
+    a = m.SynthesisDatabase(device=-1)
+    a.plan_goals(goals)
+    monkeypatch.setenv("MRL_NO_TWIN", "1")
+    b = m.SynthesisDatabase(device=-1)
+    b.plan_goals(goals)
+    assert a.stats()["n_goal_specs"] == b.stats()["n_goal_specs"] == 6
+    _same_plan(a, b, 2)
+    import numpy as np
+    ga = np.frombuffer(ctypes.string_at(*a.plan_share()[6]), dtype=np.uint32)
+    gb = np.frombuffer(ctypes.string_at(*b.plan_share()[6]), dtype=np.uint32)
+    assert (ga == gb).all()      # here the goal order is the callers' in both
+    a.close()
+    b.close()
