@@ -689,8 +689,10 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   }
 
   // The order the device relies on: a child never lies in a later stage; a child inside its
-  // parent's stage belongs to a Move that consumes memory (so it sits at strictly lower limits)
-  // and to the parent's family.
+  // parent's stage belongs to a Move that consumes memory (so it sits at strictly lower limits),
+  // to the parent's family and - when the fill is sharded - to the rank that solves the parent.
+  if (plan.world > 255) throw ModelError("at most 255 ranks");
+  plan.assign_owners_();
   {
     std::vector<u32> stage_of(N), fam_of(N);
     for (u32 si = 0; si < plan.stages.size(); si++)
@@ -699,17 +701,20 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       for (u32 i = plan.families[fi].spec_lo; i < plan.families[fi].spec_hi; i++) fam_of[i] = fi;
     std::atomic<int> bad{0};
     std::atomic<u64> bad_pair{0};
+    const bool sharded = !plan.owner.empty();
     parallel_for(N, n_threads, [&](size_t i, int) {
       const SpecHdr& h = plan.hdrs[i];
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
         for (int j = 0; j < r.nchild; j++) {
           const u32 ch = r.child[j];
-          if (stage_of[ch] > stage_of[i]) { bad = 1; bad_pair = ((u64)i << 32) | ch; }
-          if (stage_of[ch] == stage_of[i] && (r.kind != MRL_CK_MOVE || r.units == 0 || fam_of[ch] != fam_of[i])) {
-            bad = 2;
-            bad_pair = ((u64)i << 32) | ch;
+          int what = 0;
+          if (stage_of[ch] > stage_of[i]) what = 1;
+          else if (stage_of[ch] == stage_of[i]) {
+            if (r.kind != MRL_CK_MOVE || r.units == 0 || fam_of[ch] != fam_of[i]) what = 2;
+            else if (sharded && plan.owner[ch] != plan.owner[i]) what = 3;
           }
+          if (what) { bad = what; bad_pair = ((u64)i << 32) | ch; }
         }
       }
     });
@@ -717,28 +722,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
                                           plan.specs[bad_pair.load() & 0xFFFFFFFFu].str()) : std::string();
     if (bad.load() == 1) throw ModelError("planner: a child Spec lies in a later stage than its parent" + who);
     if (bad.load() == 2) throw ModelError("planner: a same-stage child is not below its parent in the limits lattice" + who);
-  }
-
-  if (plan.world > 255) throw ModelError("at most 255 ranks");
-  plan.assign_owners_();
-  if (plan.world > 1) {
-    // a same-stage child must be solved by the rank that solves its parent
-    std::atomic<int> split{0};
-    parallel_for(N, n_threads, [&](size_t i, int) {
-      const SpecHdr& h = plan.hdrs[i];
-      for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
-        const CandRec& r = plan.cands[c];
-        if (r.kind != MRL_CK_MOVE) continue;
-        for (int j = 0; j < r.nchild; j++)
-          if (plan.owner[r.child[j]] != plan.owner[i] && r.child[j] >= plan.stages[0].spec_lo) {
-            // children in earlier stages may belong to anyone; same-stage ones may not
-            const LogicalSpec& a = plan.specs[i];
-            const LogicalSpec& b = plan.specs[r.child[j]];
-            if (stage_key(a) == stage_key(b)) split = 1;
-          }
-      }
-    });
-    if (split.load()) throw ModelError("planner: a same-stage child belongs to another rank than its parent");
+    if (bad.load() == 3) throw ModelError("planner: a same-stage child belongs to another rank than its parent" + who);
   }
   if (twin) {
     // Sample check of the twin derivation: tabulate every 2039th Spec (originals and twins alike)
