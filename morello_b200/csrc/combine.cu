@@ -3,15 +3,16 @@
 // Specs are processed stage by stage (plan.hpp). For one stage the device
 //   1. derives each Spec's working limits grid: per memory the lattice codes at which its
 //      result can change - thresholds of its own candidates plus the (shifted) breakpoints of
-//      the finished tables of its children (derive_masks_kernel, place_kernel);
-//   2. solves every cell of those grids directly, one launch per occupied limits diagonal
-//      (combine_argmin_kernel): a thread owns one "column" of a Spec's grid, walks the Spec's
-//      candidate records, gathers the child rows each candidate needs at the child's limits,
-//      combines them into a Cost and keeps the lexicographic minimum;
+//      the finished tables of its children (derive_masks_kernel; totals_kernel, place_kernel);
+//   2. lists the working cells by limits diagonal (diag_histogram_kernel, scatter_cells_kernel)
+//      and solves them directly, one launch per occupied diagonal (combine_argmin_kernel): a
+//      thread (or 4, 8, 32 lanes in small launches) takes one cell, walks the Spec's candidate
+//      records, gathers the child rows each candidate needs at the child's limits, combines
+//      them into a Cost and keeps the lexicographic minimum;
 //   3. finds which breakpoints are real - some pair of neighbouring cells differs
-//      (real_masks_kernel) - and repeats 1-3 while a Spec's grid still lacks a breakpoint that
-//      a same-stage child turned out to have (relayout Moves are the only same-stage
-//      dependency; the first pass ignores them);
+//      (real_masks_kernel) - and repeats 1-3 for the Specs whose grid still lacks a breakpoint
+//      that a same-stage child turned out to have, and for the Specs above them
+//      (spread_dirty_kernel); relayout Moves are the only same-stage dependency;
 //   4. compacts the working grids to the real breakpoints and appends them to the table
 //      (final_count_kernel, scan_block_sums_kernel, compact_kernel).
 // Step 3's fixpoint is exact: when every Spec's grid contains all thresholds and all shifted
