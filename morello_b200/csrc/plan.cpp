@@ -724,6 +724,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (bad.load() == 2) throw ModelError("planner: a same-stage child is not below its parent in the limits lattice" + who);
     if (bad.load() == 3) throw ModelError("planner: a same-stage child belongs to another rank than its parent" + who);
   }
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   stages, owners, order check %.2fs\n", now_s() - t1);
   if (twin) {
     // Sample check of the twin derivation: tabulate every 2039th Spec (originals and twins alike)
     // directly and compare with the records built above, byte for byte.
@@ -751,6 +752,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (bad.load() >= 0)
       throw ModelError("planner: records derived for a dtype twin differ from direct tabulation: " + plan.specs[(u32)bad.load()].str());
   }
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   twin sample check %.2fs\n", now_s() - t1);
   plan.stats.seconds_layout = now_s() - t1;
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 

@@ -94,3 +94,27 @@ def test_mirrored_goal_lists_are_detected(m, monkeypatch):
     assert (ga == gb).all()      # here the goal order is the callers' in both
     a.close()
     b.close()
+
+
+def test_calls_out_of_order_fail_cleanly(m):
+    """Status codes, not crashes: lookups before a fill, shard ranks out of range, a shared plan
+    whose sizes do not describe a plan."""
+    db = m.SynthesisDatabase(device=-1)
+    goal = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
+    with pytest.raises(RuntimeError, match="not filled"):
+        db.get(goal)
+    with pytest.raises(RuntimeError, match="not filled"):
+        db.get_impl(goal)
+    with pytest.raises(RuntimeError, match="not filled"):
+        db.verify(10)
+    with pytest.raises(RuntimeError, match="rank"):
+        db.set_shard(2, 2)
+    with pytest.raises(RuntimeError, match="nothing planned"):
+        db.plan_share()
+    with pytest.raises(RuntimeError, match="sizes"):
+        db.plan_adopt([1, 2, 3, 4, 5, 6, 7, 8])
+    db.plan_goals([goal])
+    with pytest.raises(RuntimeError, match="no device"):
+        db.upload()          # planning-only context
+    assert db.spec_owners() == bytes(db.num_specs())   # not sharded: everything belongs to rank 0
+    db.close()
