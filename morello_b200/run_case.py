@@ -18,6 +18,8 @@ def main():
     ap.add_argument("case", choices=["matmul1", "matmul2", "matmul2_f32", "matmul8", "precompute1", "precompute2", "precompute2_u32",
                                      "precompute4", "precompute4_u32", "precompute8", "precompute8_u32"])
     ap.add_argument("--fills", type=int, default=1, help="fills of the final plan (>= 1)")
+    ap.add_argument("--through", choices=["move", "zero", "matmul"], default="matmul",
+                    help="last phase of a precompute case (move: Move Specs only)")
     args = ap.parse_args()
     db = m.SynthesisDatabase(device=0)
     if args.case.startswith("matmul"):
@@ -27,7 +29,8 @@ def main():
         db.plan_goals([goal])
     else:
         dtypes = (m.DTYPE_U32,) if args.case.endswith("_u32") else (m.DTYPE_U32, m.DTYPE_F32)
-        db.plan_precompute(int(args.case[10]), dtypes=dtypes)
+        db.plan_precompute(int(args.case[10]), through={"move": m.THROUGH_MOVE, "zero": m.THROUGH_ZERO,
+                                                        "matmul": m.THROUGH_MATMUL}[args.through], dtypes=dtypes)
     db.upload()
     for _ in range(args.fills):
         db.fill()
