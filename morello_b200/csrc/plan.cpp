@@ -487,7 +487,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   double t1 = now_s();
   std::vector<u32> order(n);
   std::vector<u32> gkey(n);
-  for (u32 i = 0; i < n; i++) gkey[i] = stage_key(temp[i].ls);
+  parallel_for(n, n_threads, [&](size_t i, int) { gkey[i] = stage_key(temp[(u32)i].ls); });
   {
     // bucket by stage key, then sort every bucket by Spec key on all threads
     std::vector<u32> uniq(gkey);
@@ -495,10 +495,10 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     uniq.erase(std::unique(uniq.begin(), uniq.end()), uniq.end());
     std::vector<u32> start(uniq.size() + 1, 0);
     std::vector<u32> bucket(n);
-    for (u32 i = 0; i < n; i++) {
+    parallel_for(n, n_threads, [&](size_t i, int) {
       bucket[i] = (u32)(std::lower_bound(uniq.begin(), uniq.end(), gkey[i]) - uniq.begin());
-      start[bucket[i] + 1]++;
-    }
+    });
+    for (u32 i = 0; i < n; i++) start[bucket[i] + 1]++;
     for (size_t b = 0; b < uniq.size(); b++) start[b + 1] += start[b];
     std::vector<u32> cur(start.begin(), start.end() - 1);
     for (u32 i = 0; i < n; i++) order[cur[bucket[i]]++] = i;
@@ -646,12 +646,20 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       const int kl = plan.specs[i].key_into(kb);
       hs[i] = hash_key(kb, kl);
     });
+    // claimed slot by slot with compare-and-swap from all threads (which slot of a probe run an
+    // id ends up in depends on the race; lookups do not care)
     const size_t mask = cap - 1;
-    for (u32 i = 0; i < N; i++) {
+    u32* tab = plan.find_tab_.data();
+    parallel_for(N, n_threads, [&](size_t i, int) {
       size_t j = (size_t)hs[i] & mask;
-      while (plan.find_tab_[j] != 0xFFFFFFFFu) j = (j + 1) & mask;
-      plan.find_tab_[j] = i;
-    }
+      for (;;) {
+        u32 expect = 0xFFFFFFFFu;
+        if (__atomic_load_n(&tab[j], __ATOMIC_RELAXED) == expect &&
+            __atomic_compare_exchange_n(&tab[j], &expect, (u32)i, false, __ATOMIC_RELAXED, __ATOMIC_RELAXED))
+          break;
+        j = (j + 1) & mask;
+      }
+    });
   }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   find table %.2fs\n", now_s() - t1);
 
