@@ -36,6 +36,7 @@
 #include <string.h>
 #include <algorithm>
 #include <mutex>
+#include <thread>
 
 #ifndef MRL_MIN_BLOCKS
 #define MRL_MIN_BLOCKS 12
@@ -952,9 +953,37 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
   if (!plan.hdrs.empty())
     CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
-  if (!plan.cands.empty() && !skip_cands)
-    CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), plan.cands.size() * sizeof(CandRec), cudaMemcpyHostToDevice, stream_));
   n_cand_bytes_ = plan.cands.size() * sizeof(CandRec);
+  if (!plan.cands.empty() && !skip_cands) {
+    // A copy from pageable memory is staged by one host thread (about 11 GB/s); the candidate
+    // records are gigabytes, so they go up in four pieces from four threads on their own streams.
+    const size_t total = n_cand_bytes_;
+    const int pieces = (!fixed_ && total >= (size_t(1) << 30)) ? 4 : 1;
+    if (pieces == 1) {
+      CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), total, cudaMemcpyHostToDevice, stream_));
+    } else {
+      const size_t step = ((total / pieces) + 255) & ~size_t(255);
+      std::vector<cudaError_t> errs(pieces, cudaSuccess);
+      std::vector<std::thread> pool;
+      for (int k = 0; k < pieces; k++)
+        pool.emplace_back([&, k]() {
+          const size_t lo = std::min(total, step * k), hi = std::min(total, step * (k + 1));
+          if (hi <= lo) return;
+          cudaError_t e = cudaSetDevice(device_);
+          cudaStream_t st = nullptr;
+          if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+          if (e == cudaSuccess) e = cudaMemcpyAsync(reinterpret_cast<unsigned char*>(d_cands_) + lo,
+                                                    reinterpret_cast<const unsigned char*>(plan.cands.data()) + lo, hi - lo,
+                                                    cudaMemcpyHostToDevice, st);
+          if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+          if (st) cudaStreamDestroy(st);
+          errs[k] = e;
+        });
+      for (auto& th : pool) th.join();
+      for (cudaError_t e : errs)
+        if (e != cudaSuccess) { snprintf(err_, sizeof(err_), "candidate upload failed: %s", cudaGetErrorString(e)); return -1; }
+    }
+  }
   if (d_mine_) CK(cudaMemcpyAsync(d_mine_, plan.mine.data(), plan.mine.size(), cudaMemcpyHostToDevice, stream_));
   CK(cudaStreamSynchronize(stream_));
   stats_ = FillStats();
