@@ -153,8 +153,11 @@ def cuda_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
+    # stdout carries exactly one JSON line: whatever libraries print while the job runs (the NCCL
+    # version banner, for one) goes to stderr
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -290,7 +293,10 @@ def cuda_arm(args):
             if t:  # measured DRAM bytes per algorithmic byte on a small case, scaled to this step (see the file's "how")
                 line["roofline"]["traffic"] = t["dram_over_algorithmic"] * st["algorithmic_bytes"]
                 line["roofline"]["traffic_how"] = "scaled from a small-case ncu capture: profiles/traffic.json"
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     db.close()
     if world > 1:
         dist.destroy_process_group()
