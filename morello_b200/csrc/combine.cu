@@ -30,6 +30,7 @@
 #include "device_types.h"
 #include "fill.hpp"
 #include <cuda_runtime.h>
+#include <cuda_profiler_api.h>
 #include <stddef.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -866,6 +867,9 @@ int DeviceFill::init(int device) {
 int DeviceFill::init_events() {
   stage_log_ = getenv("MRL_STAGE_LOG") != nullptr;
   if (const char* e = getenv("MRL_SEED_HOPS")) seed_hops_ = std::max(0, std::min(8, atoi(e)));
+  // For profilers started with capture off (ncu --profile-from-start off): only combine launches
+  // with at least this many cells are bracketed by cudaProfilerStart / Stop.
+  if (const char* e = getenv("MRL_PROFILE_MIN_CELLS")) profile_min_cells_ = (uint32_t)strtoul(e, nullptr, 10);
   if (!ev0_) CK(cudaEventCreate(&ev0_));
   if (!ev1_) CK(cudaEventCreate(&ev1_));
   return 0;
@@ -1196,6 +1200,8 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
       if (!nd) continue;
       // lanes per cell by launch size: what fills the GPU (227 k threads) runs one lane per cell
       const CellRef* list = d_cells_ + hd->base[d];
+      const bool mark = profile_min_cells_ && nd >= profile_min_cells_;   // MRL_PROFILE_MIN_CELLS: see init_events
+      if (mark) cudaProfilerStart();
       if (nd > 65536)
         combine_argmin_kernel<1><<<(nd + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
       else if (nd > 16384)
@@ -1204,6 +1210,7 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
         combine_argmin_kernel<8><<<(nd + 15) / 16, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
       else
         combine_argmin_kernel<32><<<(nd + 3) / 4, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
+      if (mark) cudaProfilerStop();
       stats_.combine_launches++;
     }
     CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));

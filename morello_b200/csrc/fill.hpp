@@ -104,6 +104,7 @@ class DeviceFill {
   // passes at size 8 for 9 % more cells; two hops cost more cells than they save. MRL_SEED_HOPS
   // overrides (0..8); any value gives the same tables.
   int seed_hops_ = 1;
+  uint32_t profile_min_cells_ = 0;      // MRL_PROFILE_MIN_CELLS
   bool stage_log_ = false;              // MRL_STAGE_LOG: one line per solve pass on stderr
   FillStats stats_;
   cudaStream_t stream_ = nullptr;
