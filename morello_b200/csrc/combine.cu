@@ -262,21 +262,20 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
   CellRef ref;
   ref.spec = 0;
-  ref.cell = 0;
+  ref.cpack = 0;
+  uint32_t cell = 0;
   unsigned long long base = 0;
   if (valid) {
     ref = cells[t];
+    // the cell's place in its Spec's working grid: slot = breakpoints at or below the code, minus one
     const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ref.spec]));
-    const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-    uint32_t rest = ref.cell;
-    const uint32_t i0 = rest % n0; rest /= n0;
-    const uint32_t i1 = rest % n1; rest /= n1;
-    const uint32_t i2 = rest % n2;
-    const uint32_t i3 = rest / n2;
-    const uint32_t cpack = nth_set_bit(m.x, i0) | (nth_set_bit(m.y, i1) << 8) | (nth_set_bit(m.z, i2) << 16) |
-                           (nth_set_bit(m.w, i3) << 24);
+    const uint32_t i0 = __popc(m.x & ((2u << code_of(ref.cpack, 0)) - 1u)) - 1;
+    const uint32_t i1 = __popc(m.y & ((2u << code_of(ref.cpack, 1)) - 1u)) - 1;
+    const uint32_t i2 = __popc(m.z & ((2u << code_of(ref.cpack, 2)) - 1u)) - 1;
+    const uint32_t i3 = __popc(m.w & ((2u << code_of(ref.cpack, 3)) - 1u)) - 1;
+    cell = ((i3 * __popc(m.z) + i2) * __popc(m.y) + i1) * __popc(m.x) + i0;
     base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ref.spec].row_base));
-    best = solve_point(hdrs, cands, rows, temp, ref.spec, cpack, n_specs, error_flag, sub, G);
+    best = solve_point(hdrs, cands, rows, temp, ref.spec, ref.cpack, n_specs, error_flag, sub, G);
   }
   if (G > 1) {
 #pragma unroll
@@ -290,7 +289,7 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   }
   // Specs of the stage being solved always live in the working buffer.
   if (valid && sub == 0)
-    *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + ref.cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
+    *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
 }
 
 // Consistency check of a finished table: at sampled (or all) points of the limits lattice, for
@@ -637,18 +636,15 @@ scatter_cells_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__
   }
   __syncthreads();
   if (!c.valid) return;
-  const uint32_t st[4] = {1u, c.nn[0], c.nn[0] * c.nn[1], c.nn[0] * c.nn[1] * c.nn[2]};
-  const uint32_t stF = sel4(st[0], st[1], st[2], st[3], c.F);
-  uint32_t off0 = 0;
-#pragma unroll
-  for (int k = 0; k < 4; k++) off0 += c.idx[k] * st[k];   // idx[F] is 0
-  uint32_t s = 0;
-  for (uint32_t mrest = mF; mrest; mrest &= mrest - 1, s++) {
-    const uint32_t d = (c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1);
+  // the fixed memories' codes, one per byte (RF in byte 0 .. GL in byte 3); the byte of F is 0
+  const uint32_t fixed = c.code[0] | (c.code[1] << 8) | (c.code[2] << 16) | (c.code[3] << 24);
+  for (uint32_t mrest = mF; mrest; mrest &= mrest - 1) {
+    const uint32_t codeF = __ffs(mrest) - 1;
+    const uint32_t d = (c.others + codeF) & (MRL_MAX_DIAG - 1);
     const uint32_t pos = atomicAdd(&hist[wib][d], 1u);
     CellRef r;
     r.spec = c.spec;
-    r.cell = off0 + s * stF;
+    r.cpack = fixed | (codeF << (8 * c.F));
     cells[start[wib][d] + pos] = r;
   }
 }

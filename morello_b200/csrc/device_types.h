@@ -81,10 +81,11 @@ struct DiagTable {
   unsigned long long base[MRL_MAX_DIAG];
 };
 
-// One working cell: Spec id and the cell's linear index in the Spec's working grid.
+// One working cell: Spec id and the cell's limits as lattice codes, one per byte (RF in byte 0
+// .. GL in byte 3). Its place in the Spec's working grid follows from the masks by popcounts.
 struct CellRef {
   uint32_t spec;
-  uint32_t cell;
+  uint32_t cpack;
 };
 
 #ifdef __cplusplus
