@@ -243,65 +243,6 @@ __device__ __forceinline__ Key solve_point(const SpecHdr* __restrict__ hdrs, con
   return best;
 }
 
-// Lazy Move thresholds. A working grid does not hold the feasibility thresholds of the Spec's Move
-// candidates as breakpoints (few of those candidates ever win, and every breakpoint multiplies
-// the cells). Instead, after a cell is solved at its corner, every Move candidate whose threshold
-// t falls inside the cell (above the corner's code in its memory, below the next breakpoint) is
-// evaluated once at t: between the corner and t nothing else changes - no other breakpoint lies
-// there - so the value at t is min(cell value, that candidate at t). If the candidate wins, t is
-// recorded in `extra` and becomes a breakpoint of the next pass. m = the Spec's working masks.
-// Runs after the whole pass is solved (check_thresholds_kernel).
-__device__ __forceinline__ void check_move_thresholds(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                                                      const MrlRow* __restrict__ rows, const MrlRow* __restrict__ temp,
-                                                      uint32_t spec, uint32_t cpack, const uint4 m, const Key best,
-                                                      uint4* __restrict__ extra, uint32_t first_cand, uint32_t cand_stride) {
-  const uint32_t bm0 = (2u << code_of(cpack, 0)) - 1u, bm1 = (2u << code_of(cpack, 1)) - 1u,
-                 bm2 = (2u << code_of(cpack, 2)) - 1u, bm3 = (2u << code_of(cpack, 3)) - 1u;
-  const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[spec].cand_off));
-  for (uint32_t ci = first_cand; ci < cl.y; ci += cand_stride) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-    const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-    if (kind != MRL_CK_MOVE) continue;
-    const uint32_t imm = a.y, level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, units = a.w;
-    const uint32_t lv = code_of(cpack, level);
-    if (thr <= lv) continue;                        // feasible at the corner: part of the solve
-    const uint32_t above = sel4(m.x, m.y, m.z, m.w, level) >> (lv + 1);   // lv <= 30
-    const uint32_t next = above ? lv + __ffs(above) : 32u;
-    if (thr >= next) continue;                      // inside a later cell, or a breakpoint already
-    if (imm > best.main) continue;                  // costs more than the cell's value whatever its children cost
-    uint32_t ccode;
-    if (level < 2) ccode = thr - units;
-    else ccode = 32 - __clz(cache_value(thr) - units);
-    const uint32_t cb = (2u << ccode) - 1u;
-    const uint32_t c0 = (level == 0) ? cb : bm0, c1 = (level == 1) ? cb : bm1, c2 = (level == 2) ? cb : bm2,
-                   c3 = (level == 3) ? cb : bm3;
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
-    const uint4 r0 = lookup(hdrs, rows, temp, b.x, c0, c1, c2, c3);
-    if (r0.z == MRL_UNSAT) continue;
-    uint4 r1 = r0, r2 = r0;
-    if (nchild > 1) {
-      r1 = lookup(hdrs, rows, temp, b.y, c0, c1, c2, c3);
-      if (r1.z == MRL_UNSAT) continue;
-      if (nchild > 2) {
-        r2 = lookup(hdrs, rows, temp, b.z, c0, c1, c2, c3);
-        if (r2.z == MRL_UNSAT) continue;
-      }
-    }
-    Key k;
-    k.main = sat_add(imm, r0.x);
-    if (nchild > 1) k.main = sat_add(k.main, r1.x);
-    if (nchild > 2) k.main = sat_add(k.main, r2.x);
-    uint32_t peaks = __vmaxu4(__vmaxu4(r0.y, r1.y), r2.y);
-    const uint32_t sh = peak_shift(level);
-    const uint32_t child_code = (peaks >> sh) & 0xFFu;
-    const uint32_t ncode = level < 2 ? units + child_code : cache_code_ceil(units + cache_value(child_code));
-    k.peaks = (peaks & ~(0xFFu << sh)) | (ncode << sh);
-    const uint32_t depth = min(max(max(r0.z >> 16, r1.z >> 16), r2.z >> 16) + 1u, 255u);
-    k.tail = (depth << 16) | action;
-    if (key_less(k, best)) atomicOr(reinterpret_cast<uint32_t*>(&extra[spec]) + level, 1u << thr);
-  }
-}
-
 // One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes),
 // listed by scatter_cells_kernel: every thread has a cell, and neighbouring threads mostly have
 // neighbouring cells of one Spec. G = lanes per cell. A launch with few cells cannot fill the
@@ -349,27 +290,6 @@ combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restric
   // Specs of the stage being solved always live in the working buffer.
   if (valid && sub == 0)
     *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
-}
-
-// The threshold check of a whole pass, after all its diagonals are solved (a candidate evaluated at
-// its threshold may read same-stage child cells on any diagonal). Thread per listed cell.
-__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
-check_thresholds_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                        const CellRef* __restrict__ cells, uint32_t n_cells, const MrlRow* __restrict__ rows,
-                        const MrlRow* __restrict__ temp, uint4* __restrict__ extra) {
-  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_cells) return;
-  const CellRef ref = cells[t];
-  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ref.spec]));
-  const uint32_t i0 = __popc(m.x & ((2u << code_of(ref.cpack, 0)) - 1u)) - 1;
-  const uint32_t i1 = __popc(m.y & ((2u << code_of(ref.cpack, 1)) - 1u)) - 1;
-  const uint32_t i2 = __popc(m.z & ((2u << code_of(ref.cpack, 2)) - 1u)) - 1;
-  const uint32_t i3 = __popc(m.w & ((2u << code_of(ref.cpack, 3)) - 1u)) - 1;
-  const uint32_t cell = ((i3 * __popc(m.z) + i2) * __popc(m.y) + i1) * __popc(m.x) + i0;
-  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ref.spec].row_base));
-  const uint4 own = *reinterpret_cast<const uint4*>(temp + (base & ~MRL_TEMP_FLAG) + cell);
-  const Key best = {own.x, own.y, own.z};
-  check_move_thresholds(hdrs, cands, rows, temp, ref.spec, ref.cpack, m, best, extra, 0, 1);
 }
 
 // Consistency check of a finished table: at sampled (or all) points of the limits lattice, for
@@ -467,8 +387,7 @@ __device__ __forceinline__ uint32_t shift_mask(uint32_t cm, uint32_t level, uint
 __global__ void __launch_bounds__(128)
 derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, uint4* __restrict__ rmask,
                     const uint8_t* __restrict__ mine, uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi,
-                    int first, int child_source, int seed_copy, uint32_t top_pack, int omit_move_thresholds,
-                    const uint4* __restrict__ extra) {
+                    int first, int child_source, int seed_copy, uint32_t top_pack) {
   const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= hi || (mine && !mine[i])) return;
   const uint4 old = *reinterpret_cast<const uint4*>(&hdrs[i]);
@@ -478,7 +397,7 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
     const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
     const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
     const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, units = a.w;
-    if (kind == MRL_CK_LEAF || (kind == MRL_CK_MOVE && !omit_move_thresholds)) or_level(r0, r1, r2, r3, level, 1u << thr);
+    if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
     if (kind == MRL_CK_LEAF) continue;
     const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
     for (uint32_t j = 0; j < nchild; j++) {
@@ -488,9 +407,7 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
       else if (child_source == 0) continue;
       else cm = rmask[child];
       if (kind == MRL_CK_MOVE) {
-        // (experiment: without the Move's own threshold, which is also where the child's code 0 lands)
-        const uint32_t drop0 = omit_move_thresholds ? ~1u : ~0u;
-        const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level) & drop0, level, units, code_of(top_pack, level));
+        const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(top_pack, level));
         r0 |= (level == 0) ? s : cm.x;
         r1 |= (level == 1) ? s : cm.y;
         r2 |= (level == 2) ? s : cm.z;
@@ -499,10 +416,6 @@ derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cand
         r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
       }
     }
-  }
-  if (extra) {   // Move thresholds the solve found to matter (lazy thresholds)
-    const uint4 e = extra[i];
-    r0 |= e.x; r1 |= e.y; r2 |= e.z; r3 |= e.w;
   }
   const uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
   const bool changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
@@ -918,10 +831,10 @@ void DeviceFill::free_(void* p) {
 
 void DeviceFill::release() {
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_); free_(d_extra_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
-  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr; d_extra_ = nullptr;
+  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
   row_cap_ = temp_cap_ = chunk_cap_ = cell_cap_ = 0;
   buf_off_ = 0;
@@ -952,10 +865,6 @@ int DeviceFill::init_events() {
   if (const char* e = getenv("MRL_SEED_HOPS")) seed_hops_ = std::max(0, std::min(8, atoi(e)));
   // For profilers started with capture off (ncu --profile-from-start off): only combine launches
   // with at least this many cells are bracketed by cudaProfilerStart / Stop.
-  // Experiment only, results are NOT exact: working grids without the Move candidates' own
-  // feasibility thresholds (to size what checking those thresholds lazily could save).
-  omit_move_thr_ = getenv("MRL_EXPERIMENT_OMIT_MOVE_THRESHOLDS") != nullptr;
-  if (const char* e = getenv("MRL_LAZY_THRESHOLDS")) lazy_ = atoi(e) != 0;
   if (const char* e = getenv("MRL_PROFILE_MIN_CELLS")) profile_min_cells_ = (uint32_t)strtoul(e, nullptr, 10);
   if (!ev0_) CK(cudaEventCreate(&ev0_));
   if (!ev1_) CK(cudaEventCreate(&ev1_));
@@ -982,10 +891,10 @@ int DeviceFill::set_stream(cudaStream_t s) {
 int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaSetDevice(device_));
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_); free_(d_extra_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
-  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr; d_extra_ = nullptr;
+  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
   buf_off_ = 0;
   n_specs_ = (uint32_t)plan.hdrs.size();
@@ -1000,7 +909,6 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   if ((rc = alloc_((void**)&d_cands_, plan.cands.size() * sizeof(CandRec)))) return rc;
   if ((rc = alloc_((void**)&d_rmask_, plan.hdrs.size() * sizeof(uint4)))) return rc;
   if ((rc = alloc_((void**)&d_dirty_, plan.hdrs.size()))) return rc;
-  if (lazy_ && (rc = alloc_((void**)&d_extra_, plan.hdrs.size() * sizeof(uint4)))) return rc;
   if (!plan.mine.empty() && (rc = alloc_((void**)&d_mine_, plan.mine.size()))) return rc;
   if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage * sizeof(uint32_t)))) return rc;
   if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage / 256 + 1) * sizeof(unsigned long long)))) return rc;
@@ -1215,7 +1123,6 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
   if (n == 0) return 0;
   if (d_mine_) CK(cudaMemsetAsync(d_rmask_ + lo, 0, (size_t)n * sizeof(uint4), stream_));
   CK(cudaMemsetAsync(d_dirty_ + lo, 0, n, stream_));
-  if (lazy_) CK(cudaMemsetAsync(d_extra_ + lo, 0, (size_t)n * sizeof(uint4), stream_));
   const uint32_t top_pack = plan.top_pack();
   const uint32_t nb128 = (n + 127) / 128;
   uint64_t temp_top = 0;   // working rows handed out so far in this stage
@@ -1224,14 +1131,13 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
     // masks: the first pass knows nothing about same-stage children; later passes add the real
     // breakpoints the previous passes found in them. Specs whose masks grew become dirty.
     derive_masks_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, d_dirty_, lo, hi, pass == 0,
-                                                    pass == 0 ? 0 : 1, pass == 0 && seed_hops_ > 0, top_pack, omit_move_thr_ || lazy_,
-                                                    lazy_ ? d_extra_ : nullptr);
+                                                    pass == 0 ? 0 : 1, pass == 0 && seed_hops_ > 0, top_pack);
     stats_.launches++;
     if (pass == 0)
       for (int h = 0; h < seed_hops_; h++) {
         // optional seeding: assume the same-stage children's breakpoints are their own first masks
         derive_masks_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, d_dirty_, lo, hi, 0, 1,
-                                                        h + 1 < seed_hops_, top_pack, omit_move_thr_ || lazy_, lazy_ ? d_extra_ : nullptr);
+                                                        h + 1 < seed_hops_, top_pack);
         stats_.launches++;
       }
     // close the dirty marks under "has a dirty same-stage child", then total the pass
@@ -1302,11 +1208,6 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
         combine_argmin_kernel<32><<<(nd + 3) / 4, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
       if (mark) cudaProfilerStop();
       stats_.combine_launches++;
-    }
-    if (lazy_) {
-      check_thresholds_kernel<<<((uint32_t)c.cells + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_cells_, (uint32_t)c.cells,
-                                                                                 d_rows_, d_temp_, d_extra_);
-      stats_.launches++;
     }
     CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
     real_masks_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_temp_, d_rmask_);

@@ -76,7 +76,6 @@ class DeviceFill {
   uint4* d_rmask_ = nullptr;
   uint8_t* d_mine_ = nullptr;
   uint8_t* d_dirty_ = nullptr;   // by Spec id: to be solved (again) in the coming pass
-  uint4* d_extra_ = nullptr;     // by Spec id: Move thresholds that turned out to be breakpoints (lazy thresholds)
   Chunk* d_chunks_ = nullptr;
   CellRef* d_cells_ = nullptr;   // working cells of the pass, listed diagonal by diagonal
   DiagTable* d_diag_ = nullptr;
@@ -105,8 +104,6 @@ class DeviceFill {
   // passes at size 8 for 9 % more cells; two hops cost more cells than they save. MRL_SEED_HOPS
   // overrides (0..8); any value gives the same tables.
   int seed_hops_ = 1;
-  bool lazy_ = false;                   // MRL_LAZY_THRESHOLDS: Move thresholds are checked, not gridded (combine.cu)
-  int omit_move_thr_ = 0;               // MRL_EXPERIMENT_OMIT_MOVE_THRESHOLDS (inexact; measurement only)
   uint32_t profile_min_cells_ = 0;      // MRL_PROFILE_MIN_CELLS
   bool stage_log_ = false;              // MRL_STAGE_LOG: one line per solve pass on stderr
   FillStats stats_;
