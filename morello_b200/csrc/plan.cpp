@@ -43,7 +43,19 @@ struct KeyShard {
   std::vector<Entry> tab;
   std::string arena;
   size_t count = 0;
-  KeyShard() : tab(256) { for (auto& e : tab) e.used = 0; }
+  // where the table is, for prefetches from outside the lock (may be stale: a prefetch of
+  // memory that has moved on does no harm)
+  std::atomic<const Entry*> peek_ptr{nullptr};
+  std::atomic<size_t> peek_mask{0};
+  KeyShard() : tab(256) {
+    for (auto& e : tab) e.used = 0;
+    peek_ptr = tab.data();
+    peek_mask = tab.size() - 1;
+  }
+  void prefetch(u64 h) const {
+    const Entry* p = peek_ptr.load(std::memory_order_relaxed);
+    __builtin_prefetch(p + ((size_t)(h >> 10) & peek_mask.load(std::memory_order_relaxed)));
+  }
   // Returns the id stored for the key, or inserts `fresh_id()` and returns it with *inserted.
   template <class F>
   u32 find_or_insert(u64 h, const char* key, int len, F fresh_id, bool* inserted) {
@@ -69,6 +81,9 @@ struct KeyShard {
         bigger[j] = e;
       }
       tab.swap(bigger);
+      peek_mask.store(0, std::memory_order_relaxed);
+      peek_ptr.store(tab.data(), std::memory_order_relaxed);
+      peek_mask.store(tab.size() - 1, std::memory_order_relaxed);
       mask = tab.size() - 1;
       i = (size_t)(h >> 10) & mask;
       while (tab[i].used) i = (i + 1) & mask;
@@ -442,7 +457,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     for (auto& mm : move_memos) mm.reset(new MoveMemo());
   // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
   for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
-    struct alignas(128) PerThread { std::vector<Candidate> scratch; };
+    struct ChildKey { u64 h; int len; char bytes[LogicalSpec::MAX_KEY]; };
+    struct alignas(128) PerThread { std::vector<Candidate> scratch; std::vector<ChildKey> keys; std::vector<int> key_of; };
     // (the Move memos live across rounds: see move_memos below)
     std::vector<PerThread> per_thread(n_threads);
     parallel_for(round_hi - round_lo, n_threads, [&](size_t fi, int tid) {
@@ -454,27 +470,45 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       ts.leaf_first = (u16)leaf_first;
       ts.leaf_end = (u16)leaf_end;
       ts.cands.reserve(cs.size());
+      // Keys and hashes of the children first, with a prefetch of each one's table slot: the
+      // probes below then find their cache lines on the way instead of missing one by one.
+      std::vector<ChildKey>& keys = per_thread[tid].keys;
+      std::vector<int>& key_of = per_thread[tid].key_of;   // per (candidate, child) in order: index into keys, or -1
+      keys.clear();
+      key_of.clear();
+      for (const Candidate& c : cs)
+        for (int j = 0; j < c.nchild; j++) {
+          if (c.child_id_slot[j] && *c.child_id_slot[j] != 0xFFFFFFFFu) { key_of.push_back(-1); continue; }
+          key_of.push_back((int)keys.size());
+          keys.emplace_back();
+          ChildKey& k = keys.back();
+          k.len = c.child[j].key_into(k.bytes);
+          k.h = hash_key(k.bytes, k.len);
+          shards[k.h % NSHARD].prefetch(k.h);
+        }
+      size_t next_child = 0;
       for (const Candidate& c : cs) {
         CandRec r;
-        if (!make_rec(c, top_code, r)) continue;
+        const bool keep = make_rec(c, top_code, r);
         for (int j = 0; j < c.nchild; j++) {
+          const int ki = key_of[next_child++];
+          if (!keep) continue;   // the candidate never fits: its children are not part of the closure
           if (c.child_id_slot[j] && *c.child_id_slot[j] != 0xFFFFFFFFu) {
-            r.child[j] = *c.child_id_slot[j];   // this thread met the Move Spec before
+            r.child[j] = *c.child_id_slot[j];   // this thread met the Move Spec before (maybe a moment ago)
             continue;
           }
-          char kb[LogicalSpec::MAX_KEY];
-          const int kl = c.child[j].key_into(kb);
-          const u64 h = hash_key(kb, kl);
+          const ChildKey& k = keys[ki];
           bool inserted = false;
-          const u32 id = shards[h % NSHARD].find_or_insert(h, kb, kl, [&]() { return next_id++; }, &inserted);
+          const u32 id = shards[k.h % NSHARD].find_or_insert(k.h, k.bytes, k.len, [&]() { return next_id++; }, &inserted);
           if (inserted) {
             TempSpec& fresh = temp.construct(id);
             fresh.ls = c.child[j];
-            fresh.key.assign(kb, (size_t)kl);
+            fresh.key.assign(k.bytes, (size_t)k.len);
           }
           r.child[j] = id;
           if (c.child_id_slot[j]) *c.child_id_slot[j] = id;
         }
+        if (!keep) continue;
         ts.cands.push_back(r);
       }
     });
