@@ -84,6 +84,7 @@ int upload_and_fill(mrl_ctx* ctx) {
 int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals, int mirror_dtype = -1) {
   double t0 = now_s();
   ctx->cands_elsewhere = false;
+  ctx->dev.wait_upload();   // a background upload may still be reading the old plan
   ctx->plan = build_plan(goals, ctx->n_threads, nullptr, ctx->rank, ctx->world, mirror_dtype);
   ctx->planned = true;
   ctx->uploaded = ctx->filled = false;
@@ -348,6 +349,7 @@ int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8], int can
   try {
     u64 sz[Plan::N_BLOBS];
     for (int k = 0; k < Plan::N_BLOBS; k++) sz[k] = sizes[k];
+    ctx->dev.wait_upload();   // a background upload may still be reading the old plan
     ctx->plan = Plan();
     ctx->planned = ctx->uploaded = ctx->filled = false;
     ctx->plan.adopt_alloc(sz);
@@ -412,6 +414,7 @@ int mrl_spec_owners(const mrl_ctx* ctx, uint8_t* out, uint64_t n) {
 
 int mrl_device_cands(const mrl_ctx* ctx, void** ptr, uint64_t* bytes) {
   if (!ctx || !ctx->uploaded) return -1;
+  if (const_cast<mrl_ctx*>(ctx)->dev.wait_upload()) return -2;   // the caller is about to read them
   if (ptr) *ptr = ctx->dev.device_cands();
   if (bytes) *bytes = ctx->dev.device_cand_bytes();
   return 0;

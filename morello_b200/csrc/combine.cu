@@ -36,6 +36,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <algorithm>
+#include <chrono>
 #include <mutex>
 #include <thread>
 
@@ -830,6 +831,7 @@ void DeviceFill::free_(void* p) {
 }
 
 void DeviceFill::release() {
+  wait_upload();
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
   free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
@@ -888,8 +890,31 @@ int DeviceFill::set_stream(cudaStream_t s) {
   return 0;
 }
 
+int DeviceFill::wait_cands_(uint64_t upto_bytes) {
+  if (up_threads_.empty()) return 0;
+  const size_t need = std::min<uint64_t>(up_pieces_, (upto_bytes + up_piece_bytes_ - 1) / up_piece_bytes_);
+  while (up_ready_ < need) {
+    if (up_done_[up_ready_].load(std::memory_order_acquire)) up_ready_++;
+    else if (up_err_.load(std::memory_order_relaxed) != 0) break;
+    else std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+  const int e = up_err_.load();
+  if (up_ready_ == up_pieces_ || e != 0) {
+    for (auto& th : up_threads_) th.join();
+    up_threads_.clear();
+  }
+  if (e != 0) {
+    snprintf(err_, sizeof(err_), "candidate upload failed: %s", cudaGetErrorString((cudaError_t)e));
+    return -1;
+  }
+  return 0;
+}
+
+int DeviceFill::wait_upload() { return wait_cands_(~uint64_t(0) >> 1); }
+
 int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaSetDevice(device_));
+  wait_upload();   // of an earlier plan
   free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
   free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
   d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
@@ -956,32 +981,40 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   n_cand_bytes_ = plan.cands.size() * sizeof(CandRec);
   if (!plan.cands.empty() && !skip_cands) {
     // A copy from pageable memory is staged by one host thread (about 11 GB/s); the candidate
-    // records are gigabytes, so they go up in four pieces from four threads on their own streams.
+    // records are gigabytes, so four threads copy them on their own streams, piece by piece in
+    // id order, and go on after this call has returned (wait_cands_).
     const size_t total = n_cand_bytes_;
-    const int pieces = (!fixed_ && total >= (size_t(1) << 30)) ? 4 : 1;
-    if (pieces == 1) {
+    if (fixed_ || total < (size_t(1) << 30)) {
       CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), total, cudaMemcpyHostToDevice, stream_));
     } else {
-      const size_t step = ((total / pieces) + 255) & ~size_t(255);
-      std::vector<cudaError_t> errs(pieces, cudaSuccess);
-      std::vector<std::thread> pool;
-      for (int k = 0; k < pieces; k++)
-        pool.emplace_back([&, k]() {
-          const size_t lo = std::min(total, step * k), hi = std::min(total, step * (k + 1));
-          if (hi <= lo) return;
+      up_piece_bytes_ = size_t(128) << 20;
+      up_pieces_ = (total + up_piece_bytes_ - 1) / up_piece_bytes_;
+      up_done_.reset(new std::atomic<uint8_t>[up_pieces_]);
+      for (size_t k = 0; k < up_pieces_; k++) up_done_[k].store(0, std::memory_order_relaxed);
+      up_next_ = 0;
+      up_err_ = 0;
+      up_ready_ = 0;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(plan.cands.data());
+      unsigned char* dst = reinterpret_cast<unsigned char*>(d_cands_);
+      for (int t = 0; t < 4; t++)
+        up_threads_.emplace_back([this, src, dst, total]() {
           cudaError_t e = cudaSetDevice(device_);
           cudaStream_t st = nullptr;
           if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
-          if (e == cudaSuccess) e = cudaMemcpyAsync(reinterpret_cast<unsigned char*>(d_cands_) + lo,
-                                                    reinterpret_cast<const unsigned char*>(plan.cands.data()) + lo, hi - lo,
-                                                    cudaMemcpyHostToDevice, st);
-          if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+          while (e == cudaSuccess && up_err_.load(std::memory_order_relaxed) == 0) {
+            const size_t k = up_next_.fetch_add(1);
+            if (k >= up_pieces_) break;
+            const size_t lo = k * up_piece_bytes_, hi = std::min(total, lo + up_piece_bytes_);
+            e = cudaMemcpyAsync(dst + lo, src + lo, hi - lo, cudaMemcpyHostToDevice, st);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+            if (e == cudaSuccess) up_done_[k].store(1, std::memory_order_release);
+          }
           if (st) cudaStreamDestroy(st);
-          errs[k] = e;
+          if (e != cudaSuccess) {
+            int expect = 0;
+            up_err_.compare_exchange_strong(expect, (int)e);
+          }
         });
-      for (auto& th : pool) th.join();
-      for (cudaError_t e : errs)
-        if (e != cudaSuccess) { snprintf(err_, sizeof(err_), "candidate upload failed: %s", cudaGetErrorString(e)); return -1; }
     }
   }
   if (d_mine_) CK(cudaMemcpyAsync(d_mine_, plan.mine.data(), plan.mine.size(), cudaMemcpyHostToDevice, stream_));
@@ -1121,6 +1154,13 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
   const uint32_t lo = st.spec_lo, hi = st.spec_hi, n = hi - lo;
   last_cells_ = 0;
   if (n == 0) return 0;
+  {
+    // the stage reads its own Specs' candidate records (ids, and with them the records, are in
+    // stage order): wait for that much of a background upload
+    const SpecHdr& last = plan.hdrs[hi - 1];
+    int rc = wait_cands_(((uint64_t)last.cand_off + last.ncand) * sizeof(CandRec));
+    if (rc) return rc;
+  }
   if (d_mine_) CK(cudaMemsetAsync(d_rmask_ + lo, 0, (size_t)n * sizeof(uint4), stream_));
   CK(cudaMemsetAsync(d_dirty_ + lo, 0, n, stream_));
   const uint32_t top_pack = plan.top_pack();
@@ -1341,6 +1381,7 @@ int DeviceFill::lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t 
 int DeviceFill::verify(const Plan& plan, uint64_t n_samples, uint64_t seed, uint64_t* checked, uint64_t* mismatches,
                        uint64_t* first_bad) {
   CK(cudaSetDevice(device_));
+  if (wait_upload()) return -1;
   const uint32_t top = plan.top_pack();
   unsigned long long per_spec = 1;
   for (int k = 0; k < 4; k++) per_spec *= ((top >> (8 * k)) & 0xFFu) + 1u;

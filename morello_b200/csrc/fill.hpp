@@ -3,7 +3,10 @@
 #pragma once
 #include "plan.hpp"
 #include <cuda_runtime.h>
+#include <atomic>
+#include <memory>
 #include <mutex>
+#include <thread>
 
 namespace mrl {
 
@@ -27,9 +30,14 @@ class DeviceFill {
   // that is never grown or freed (attach_buffer before upload).
   void attach_buffer(void* base, size_t bytes, cudaStream_t stream, int device);
   // Copies headers and candidate records to the device and sets up the arena.
+  // Gigabytes of candidate records keep going up in the background, in id order, after upload()
+  // has returned: the plan must stay as it is until wait_upload() (a fill waits stage by stage
+  // for the records it is about to read, so its first stages overlap the copy).
   // skip_cands: the candidate records are not on this host; the caller fills device_cands()
   // itself (e.g. a broadcast from the rank that planned) before the first fill.
   int upload(const Plan& plan, bool skip_cands = false);
+  // Blocks until every candidate record is on the device.
+  int wait_upload();
   void* device_cands() const { return d_cands_; }
   uint64_t device_cand_bytes() const { return n_cand_bytes_; }
   // Runs every stage.
@@ -66,6 +74,7 @@ class DeviceFill {
   int ensure_chunks_(uint64_t need);
   int ensure_cells_(uint64_t need);
   int read_counters_(PassCounters* out);
+  int wait_cands_(uint64_t upto_bytes);   // until the candidate bytes [0, upto_bytes) are on the device
 
   int device_ = 0;
   bool fixed_ = false;            // carved from an attached buffer: no growth
@@ -113,6 +122,12 @@ class DeviceFill {
   std::vector<cudaEvent_t> ev_pool_;
   size_t ev_used_ = 0;
   std::mutex lookup_mu_;
+  // background candidate upload: pieces handed out in order to a few copying threads
+  std::vector<std::thread> up_threads_;
+  std::unique_ptr<std::atomic<uint8_t>[]> up_done_;   // by piece
+  std::atomic<size_t> up_next_{0};
+  std::atomic<int> up_err_{0};                        // cudaError_t of the first failed copy
+  size_t up_pieces_ = 0, up_piece_bytes_ = 0, up_ready_ = 0;   // up_ready_: pieces known complete, a prefix
   char err_[256] = {0};
 };
 

@@ -107,6 +107,7 @@ struct TempSpec {
   std::string key;
   std::vector<CandRec> cands;  // child[] holds temporary ids
   u16 leaf_first = 0, leaf_end = 0;  // action numbers of the leaf-kernel section [first, end)
+  u16 n_leaf = 0;                    // leaf records among cands
 };
 
 // Growing array of TempSpec in fixed blocks: elements never move, blocks are allocated on demand
@@ -428,7 +429,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // ---- 1. discovery: closure of the goals under "is a sub-Spec of some candidate" ----
   double t0 = now_s();
   std::vector<KeyShard> shards(NSHARD);
-  TempSpecs temp;
+  std::shared_ptr<TempSpecs> temp_owner = std::make_shared<TempSpecs>();
+  TempSpecs& temp = *temp_owner;
   std::atomic<u32> next_id{0};
 
   plan.goal_ids.assign(goals.size(), 0);
@@ -509,8 +511,11 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
           if (c.child_id_slot[j]) *c.child_id_slot[j] = id;
         }
         if (!keep) continue;
+        ts.n_leaf += r.kind == MRL_CK_LEAF;
         ts.cands.push_back(r);
       }
+      // final record order, while the records are still in cache
+      std::stable_sort(ts.cands.begin(), ts.cands.end(), cand_before);
     });
   }
   { std::vector<KeyShard>().swap(shards); }
@@ -594,8 +599,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     const TempSpec& ts = temp[order[i]];
     offs[pos_a[i] + 1] = ts.cands.size();
     if (twin) {
-      size_t nleaf_a = 0;
-      for (const CandRec& r : ts.cands) nleaf_a += r.kind == MRL_CK_LEAF;
+      const size_t nleaf_a = ts.n_leaf;
       LogicalSpec sb = ts.ls;
       sb.dtype = dt_b;
       std::vector<Candidate> lv;
@@ -614,8 +618,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   {
     std::vector<u64> kids_t(1, 0);
     parallel_for(n, n_threads, [&](size_t i, int) {
-      TempSpec& ts = temp[order[i]];
-      std::stable_sort(ts.cands.begin(), ts.cands.end(), cand_before);
+      const TempSpec& ts = temp[order[i]];
       u64 kids = 0;
       {
         const u32 id = pos_a[i];
@@ -665,7 +668,19 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     plan.stats.n_children += kids_t[0];
   }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   move specs+cands %.2fs\n", now_s() - t1);
-  parallel_for(n, n_threads, [&](size_t i, int) { temp.destroy((u32)i); });
+  // The temporary Specs are taken apart by a few threads of their own while the rest of the
+  // plan is built; whoever drops the plan's handle last (normally the end of this function)
+  // waits for them.
+  {
+    TempSpecs* tp = temp_owner.get();
+    const int nt = std::max(1, n_threads / 3);
+    std::thread* bg = new std::thread([tp, n, nt]() { parallel_for(n, nt, [tp](size_t i, int) { tp->destroy((u32)i); }); });
+    plan.cleanup_ = std::shared_ptr<void>(nullptr, [bg, temp_owner](void*) mutable {
+      bg->join();
+      delete bg;
+      temp_owner.reset();
+    });
+  }
   // from here on everything is about the final arrays (N Specs)
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   free temp %.2fs\n", now_s() - t1);
   // id lookup table for find(): open addressing over the Spec key hash, ids only (equality is
@@ -699,35 +714,43 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 
   // stages, and inside them families: maximal runs with equal dtype and shape (ids are
   // key-sorted, and the key starts with kind, dtype, serial flag, rank, shape)
-  for (u32 i = 0; i < N;) {
-    const u32 sk = stage_key(plan.specs[i]);
-    u32 j = i;
-    while (j < N && stage_key(plan.specs[j]) == sk) j++;
-    Stage st;
-    st.spec_lo = i;
-    st.spec_hi = j;
-    st.phase = (u8)(sk >> 16);
-    st.shape_sum = (u8)((sk >> 8) & 0xff);
-    st.level_rank = (u8)(sk & 0xff);
-    st.fam_lo = (u32)plan.families.size();
-    for (u32 a = i; a < j;) {
-      u32 b = a;
-      u64 w = 0;
-      while (b < j && plan.specs[b].dtype == plan.specs[a].dtype && plan.specs[b].spec_shape == plan.specs[a].spec_shape) {
-        w += plan.hdrs[b].ncand + 1;
-        b++;
+  {
+    std::vector<u32> skey(N);
+    std::vector<u8> fam_start(N);   // dtype or shape differs from the Spec before
+    parallel_for(N, n_threads, [&](size_t i, int) {
+      skey[i] = stage_key(plan.specs[i]);
+      fam_start[i] = i == 0 || plan.specs[i].dtype != plan.specs[i - 1].dtype || plan.specs[i].spec_shape != plan.specs[i - 1].spec_shape;
+    });
+    for (u32 i = 0; i < N;) {
+      const u32 sk = skey[i];
+      u32 j = i;
+      while (j < N && skey[j] == sk) j++;
+      Stage st;
+      st.spec_lo = i;
+      st.spec_hi = j;
+      st.phase = (u8)(sk >> 16);
+      st.shape_sum = (u8)((sk >> 8) & 0xff);
+      st.level_rank = (u8)(sk & 0xff);
+      st.fam_lo = (u32)plan.families.size();
+      for (u32 a = i; a < j;) {
+        u32 b = a;
+        u64 w = 0;
+        do {
+          w += plan.hdrs[b].ncand + 1;
+          b++;
+        } while (b < j && !fam_start[b]);
+        Family f;
+        f.spec_lo = a;
+        f.spec_hi = b;
+        f.stage = (u32)plan.stages.size();
+        f.weight = w;
+        plan.families.push_back(f);
+        a = b;
       }
-      Family f;
-      f.spec_lo = a;
-      f.spec_hi = b;
-      f.stage = (u32)plan.stages.size();
-      f.weight = w;
-      plan.families.push_back(f);
-      a = b;
+      st.fam_hi = (u32)plan.families.size();
+      plan.stages.push_back(st);
+      i = j;
     }
-    st.fam_hi = (u32)plan.families.size();
-    plan.stages.push_back(st);
-    i = j;
   }
 
   // The order the device relies on: a child never lies in a later stage; a child inside its
@@ -795,6 +818,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       throw ModelError("planner: records derived for a dtype twin differ from direct tabulation: " + plan.specs[(u32)bad.load()].str());
   }
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   twin sample check %.2fs\n", now_s() - t1);
+  plan.cleanup_.reset();   // waits for the release of the temporaries
+  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   temporaries released %.2fs\n", now_s() - t1);
   plan.stats.seconds_layout = now_s() - t1;
   if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 

@@ -18,8 +18,10 @@
 #include "model/space.hpp"
 #include "device_types.h"
 #include <cstdlib>
+#include <sys/mman.h>
 #include <new>
 #include <string>
+#include <memory>
 #include <vector>
 
 namespace mrl {
@@ -43,7 +45,18 @@ class RawVec {
     p_ = nullptr;
     n_ = 0;
     if (n) {
-      p_ = static_cast<T*>(malloc(n * sizeof(T)));
+      const size_t bytes = n * sizeof(T);
+      if (bytes >= (size_t(64) << 20)) {
+        // large arrays are 2 MiB-aligned; with MRL_HUGEPAGE set they are advised for huge pages
+        // (one page fault per 2 MiB for the threads that first touch them; off by default:
+        // where the kernel has to compact memory to grant them the faults get slower, not faster)
+        void* q = nullptr;
+        if (posix_memalign(&q, size_t(2) << 20, bytes) != 0) throw std::bad_alloc();
+        if (getenv("MRL_HUGEPAGE")) madvise(q, bytes, MADV_HUGEPAGE);
+        p_ = static_cast<T*>(q);
+      } else {
+        p_ = static_cast<T*>(malloc(bytes));
+      }
       if (!p_) throw std::bad_alloc();
       n_ = n;
     }
@@ -133,6 +146,7 @@ struct Plan {
 
  private:
   friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32, int);
+  std::shared_ptr<void> cleanup_;  // background release of planning temporaries; joined when dropped
   std::vector<u32> find_tab_;  // open-addressing table of ids by Spec key hash (0xFFFFFFFF = empty)
   struct Meta {                // blob 0
     u32 top_code[NMEM];
