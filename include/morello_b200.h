@@ -107,7 +107,10 @@ int mrl_top_down_many_noalloc(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t
 int mrl_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask);
 
 /* The three steps of the two calls above, exposed separately for measurement: plan on the
- * host, copy the plan to the device, fill (may be repeated). */
+ * host, copy the plan to the device, fill (may be repeated). Gigabytes of candidate records keep
+ * going up in the background after mrl_upload has returned, in stage order; a fill waits stage by
+ * stage for the records it needs, so its first stages overlap the copy. Calls that replace the
+ * plan or read the device records (mrl_plan_*, mrl_verify, mrl_device_cands) wait for the copy. */
 int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask);
 int mrl_plan_goals(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n);
 int mrl_upload(mrl_ctx* ctx);

@@ -88,14 +88,19 @@ inline LeafInfo leaf_kernel_info(LeafKernel k, const LogicalSpec& spec) {
   LeafInfo r;
   TensorSpec op[MAX_OPS];
   for (int i = 0; i < spec.nops(); i++) op[i] = spec.operand(i);
-  u32 io = 0;
-  for (int i = 0; i < spec.nops(); i++) io += move_cost(op[i]);
+  // cost of touching every operand once; only the scalar kernels charge it, and it is the
+  // expensive part (a layout expansion per operand), so it is computed where it is used
+  auto io_cost = [&]() {
+    u32 io = 0;
+    for (int i = 0; i < spec.nops(); i++) io += move_cost(op[i]);
+    return io;
+  };
   switch (k) {
     case LK_MULTADD: {  // cpu.rs:914-921, 2315-2340
       if (spec.kind != K_MATMUL_ACCUM) return r;
       for (int i = 0; i < 3; i++) if (!is_rf_or_l1(op[i].aux.mem) || !op[i].shape.all_ones()) return r;
       r.applies = true;
-      r.main = (spec.dtype == DT_F32 ? 1 : (spec.dtype == DT_BF16 ? 30 : 2)) + io;
+      r.main = (spec.dtype == DT_F32 ? 1 : (spec.dtype == DT_BF16 ? 30 : 2)) + io_cost();
       return r;
     }
     case LK_BCAST_VEC_MULTADD: {  // cpu.rs:922-943, 1884-1897, 2010-2036
@@ -132,7 +137,7 @@ inline LeafInfo leaf_kernel_info(LeafKernel k, const LogicalSpec& spec) {
         if (op[0].aux.layout != op[1].aux.layout) return r;
         if (!is_rf_or_l1(op[0].aux.mem) || !is_rf_or_l1(op[1].aux.mem)) return r;
         r.applies = true;
-        r.main = io + 1;
+        r.main = io_cost() + 1;
         return r;
       }
       if (!op[0].is_contiguous() || !op[1].is_contiguous()) return r;
@@ -159,7 +164,7 @@ inline LeafInfo leaf_kernel_info(LeafKernel k, const LogicalSpec& spec) {
     case LK_VALUE_ZERO: {  // cpu.rs:1822-1831, 2057-2069
       if (spec.kind != K_FILL_ZERO) return r;
       if (op[0].volume() != 1 || !is_rf_or_l1(op[0].aux.mem)) return r;
-      r.applies = true; r.main = io + 1;
+      r.applies = true; r.main = io_cost() + 1;
       return r;
     }
     case LK_VECTOR_ZERO: {  // cpu.rs:1832-1856, 2372-2378

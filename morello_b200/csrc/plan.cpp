@@ -108,6 +108,8 @@ struct TempSpec {
   std::vector<CandRec> cands;  // child[] holds temporary ids
   u16 leaf_first = 0, leaf_end = 0;  // action numbers of the leaf-kernel section [first, end)
   u16 n_leaf = 0;                    // leaf records among cands
+  u16 twin_leaf_end = 0;             // the dtype twin's leaf_end and leaf records (set when ids are laid out)
+  std::vector<CandRec> twin_leaf;
 };
 
 // Growing array of TempSpec in fixed blocks: elements never move, blocks are allocated on demand
@@ -596,18 +598,18 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // candidate records per final id; a twin swaps the leaf records for its own
   std::vector<u64> offs((size_t)N + 1, 0);
   parallel_for(n, n_threads, [&](size_t i, int) {
-    const TempSpec& ts = temp[order[i]];
+    TempSpec& ts = temp[order[i]];
     offs[pos_a[i] + 1] = ts.cands.size();
     if (twin) {
-      const size_t nleaf_a = ts.n_leaf;
+      // the twin's own leaf kernels, kept for the pass that writes the records
       LogicalSpec sb = ts.ls;
       sb.dtype = dt_b;
       std::vector<Candidate> lv;
-      tabulate_leaves(sb, ts.leaf_first, lv);
-      size_t nleaf_b = 0;
+      ts.twin_leaf_end = (u16)tabulate_leaves(sb, ts.leaf_first, lv);
       CandRec r;
-      for (const Candidate& c : lv) nleaf_b += make_rec(c, top_code, r);
-      offs[pos_b[i] + 1] = ts.cands.size() - nleaf_a + nleaf_b;
+      for (const Candidate& c : lv)
+        if (make_rec(c, top_code, r)) ts.twin_leaf.push_back(r);
+      offs[pos_b[i] + 1] = ts.cands.size() - ts.n_leaf + ts.twin_leaf.size();
     }
   });
   for (u32 i = 0; i < N; i++) offs[i + 1] += offs[i];
@@ -645,12 +647,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         h.cand_off = (u32)off;
         h.ncand = (u32)(offs[id + 1] - offs[id]);
         // its own leaf kernels, numbered from where the leaf section starts ...
-        std::vector<Candidate> lv;
-        const u32 leaf_end_b = tabulate_leaves(sb, ts.leaf_first, lv);
-        for (const Candidate& c : lv) {
-          CandRec r;
-          if (make_rec(c, top_code, r)) plan.cands[off++] = r;
-        }
+        const u32 leaf_end_b = ts.twin_leaf_end;
+        for (const CandRec& r : ts.twin_leaf) plan.cands[off++] = r;
         // ... then the first dtype's other records; what is numbered after the leaf section
         // (ToAccum, splits) moves by the difference in applicable kernels
         const int shift = (int)leaf_end_b - (int)ts.leaf_end;
