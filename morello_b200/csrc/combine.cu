@@ -980,9 +980,9 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
     CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
   n_cand_bytes_ = plan.cands.size() * sizeof(CandRec);
   if (!plan.cands.empty() && !skip_cands) {
-    // A copy from pageable memory is staged by one host thread (about 11 GB/s); the candidate
-    // records are gigabytes, so four threads copy them on their own streams, piece by piece in
-    // id order, and go on after this call has returned (wait_cands_).
+    // The candidate records are gigabytes of pageable memory and one host thread stages about
+    // 11 GB/s, so four threads copy them on their own streams, piece by piece in id order, and
+    // go on after this call has returned (wait_cands_).
     const size_t total = n_cand_bytes_;
     if (fixed_ || total < (size_t(1) << 30)) {
       CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), total, cudaMemcpyHostToDevice, stream_));
@@ -998,18 +998,44 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
       unsigned char* dst = reinterpret_cast<unsigned char*>(d_cands_);
       for (int t = 0; t < 4; t++)
         up_threads_.emplace_back([this, src, dst, total]() {
+          // Each thread stages through two small pinned buffers of its own: the copy into them
+          // is a plain memcpy outside the driver, and the transfer out of them is asynchronous,
+          // so the thread that launches the fill's kernels is not held up behind driver-side
+          // staging of pageable memory.
+          const size_t sub = size_t(8) << 20;
+          unsigned char* pin[2] = {nullptr, nullptr};
+          cudaEvent_t ev[2] = {nullptr, nullptr};
+          bool used[2] = {false, false};
           cudaError_t e = cudaSetDevice(device_);
           cudaStream_t st = nullptr;
           if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+          for (int b = 0; b < 2 && e == cudaSuccess; b++) {
+            e = cudaHostAlloc((void**)&pin[b], sub, cudaHostAllocDefault);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev[b], cudaEventDisableTiming);
+          }
+          unsigned turn = 0;
           while (e == cudaSuccess && up_err_.load(std::memory_order_relaxed) == 0) {
             const size_t k = up_next_.fetch_add(1);
             if (k >= up_pieces_) break;
             const size_t lo = k * up_piece_bytes_, hi = std::min(total, lo + up_piece_bytes_);
-            e = cudaMemcpyAsync(dst + lo, src + lo, hi - lo, cudaMemcpyHostToDevice, st);
+            for (size_t off = lo; off < hi && e == cudaSuccess; off += sub, turn++) {
+              const int b = turn & 1;
+              const size_t len = std::min(sub, hi - off);
+              if (used[b]) e = cudaEventSynchronize(ev[b]);   // the buffer's last transfer is done
+              if (e != cudaSuccess) break;
+              memcpy(pin[b], src + off, len);
+              e = cudaMemcpyAsync(dst + off, pin[b], len, cudaMemcpyHostToDevice, st);
+              if (e == cudaSuccess) e = cudaEventRecord(ev[b], st);
+              used[b] = true;
+            }
             if (e == cudaSuccess) e = cudaStreamSynchronize(st);
             if (e == cudaSuccess) up_done_[k].store(1, std::memory_order_release);
           }
-          if (st) cudaStreamDestroy(st);
+          if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+          for (int b = 0; b < 2; b++) {
+            if (ev[b]) cudaEventDestroy(ev[b]);
+            if (pin[b]) cudaFreeHost(pin[b]);
+          }
           if (e != cudaSuccess) {
             int expect = 0;
             up_err_.compare_exchange_strong(expect, (int)e);
