@@ -260,6 +260,9 @@ def cuda_arm(args):
                    "logical_specs_with_closure": st["n_specs"], "candidate_records": st["n_candidates"],
                    "stages": st["n_stages"], "table_rows": st["n_rows"], "cells_solved_per_step": st["n_cells_solved"],
                    "solve_passes_per_step": st["n_passes"],
+                   "candidates_evaluated_per_step": st["n_candidates_evaluated"],
+                   "rows_gathered_per_step": st["n_rows_gathered"], "grid_syncs_per_step": st["n_grid_syncs"],
+                   "combine_phase_ms_per_step": st["combine_ms"],
                    "l2": ("candidate records and headers %.1f GB + table %.2f GB, larger than L2; L2 also flushed "
                           "between fills" % (plan_gb, table_gb)),
                    "multi_gpu": ("families of each stage sharded over %d ranks; masks and rows summed over the ranks "
@@ -273,7 +276,7 @@ def cuda_arm(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "combine_argmin_kernel",
                      "algorithmic_bytes_per_step": st["algorithmic_bytes"], "kernel_ms_per_step": combine_ms_per_step,
-                     "kernel_launches_per_step": st["n_combine_launches"],
+                     "kernel_launches_per_step": st["n_launches"],
                      "whole_fill_GBps": alg_bytes / (ms_per_step * 1e-3) / 1e9},
         "clocks": clocks,
     }

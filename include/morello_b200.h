@@ -42,18 +42,33 @@ typedef struct mrl_stats {
   uint64_t n_candidates;       /* candidate records */
   uint64_t n_stages;           /* stages of the fill (plan order) */
   uint64_t n_rows;             /* rows of the finished tables: cells of the Specs' final limits grids */
-  uint64_t n_cells_solved;     /* working-grid cells the last fill solved directly (all passes) */
+  uint64_t n_cells_solved;     /* working-grid cells the last fill solved (all passes) */
+  uint64_t n_candidates_evaluated; /* candidate records evaluated by those solves */
+  uint64_t n_rows_gathered;    /* child rows they read */
   uint64_t n_passes;           /* solve passes of the last fill, summed over stages */
-  uint64_t n_launches;         /* kernel launches of the last fill */
-  uint64_t n_combine_launches; /* of which combine launches */
-  uint64_t algorithmic_bytes;  /* bytes those solves must move (rows out, candidate headers, child rows in) */
+  uint64_t n_launches;         /* kernel launches of the last fill (one cooperative launch per stage) */
+  uint64_t n_grid_syncs;       /* grid-wide barriers inside those launches */
+  uint64_t algorithmic_bytes;  /* of the finished table: per final row 12 bytes out, 16 per candidate record of
+                                * its Spec, 16 per child of each candidate that fits the row's limits */
   uint64_t h2d_bytes;          /* bytes copied host->device by the last upload */
   uint64_t d2h_bytes;          /* bytes copied device->host by the last query */
   double plan_seconds;         /* host: closure, candidate tabulation, stage order */
   double upload_seconds;
   double fill_ms;              /* device time of the last fill (CUDA events on the launch stream) */
-  double combine_ms;           /* of which inside the combine launches */
+  double combine_ms;           /* of which inside the solve phases (device timer) */
+  double early_ms;             /* of which the phase that needs no order: candidates whose children lie in earlier stages */
 } mrl_stats;
+
+/* One row of the device table as mrl_export_all hands it out: main cost; peak memory as lattice
+ * codes, RF in the top byte .. GL in the low byte (registers raw, caches as bit length of the
+ * line count: MemoryLimitsBimap, morello/src/memorylimits.rs:696-734); depth << 16 | ActionNum,
+ * all ones when the cell has no implementation. */
+typedef struct mrl_row {
+  uint32_t main_cost;
+  uint32_t peak_codes;
+  uint32_t depth_action;
+  uint32_t reserved;
+} mrl_row;
 
 enum { MRL_KIND_MOVE = 0, MRL_KIND_FILL_ZERO = 1, MRL_KIND_MATMUL_ACCUM = 2, MRL_KIND_MATMUL = 3 };
 enum { MRL_DTYPE_U32 = 4, MRL_DTYPE_F32 = 6 };
@@ -86,14 +101,20 @@ void mrl_max_mem(uint64_t limits[4]);
 int mrl_top_down_many(mrl_ctx* ctx, const uint8_t* blobs, const uint64_t* blob_off, size_t n, const uint64_t* limits,
                       mrl_decision* out);
 
+/* Cross-check modes of the host planner (tests): same plan, built the slow way. Bit 0: tabulate
+ * both dtypes of a mirrored goal set instead of deriving f32 records from u32 ones; bit 1:
+ * tabulate every Spec from scratch instead of re-using per-operand results. */
+int mrl_set_plan_flags(mrl_ctx* ctx, uint32_t flags);
+
 /* No counterpart in the reference. Same inputs, outputs and results as mrl_top_down_many, for
  * callers that must not allocate device memory: a process that handed all of HBM to its tables
  * at start-up has none left to give, and worker threads that call in concurrently would be
  * serialised by the device-wide synchronisation of every cudaMalloc / cudaFree. This call makes
  * neither; the device working set of the fill (plan arrays, working grids, row table, lookup staging) lives in
  * one fixed array of MRL_NOALLOC_MAX_BYTES that each GPU loading the library holds until the
- * process exits. A goal set whose fill needs more is refused with status -4 and a message; use
- * mrl_top_down_many for it. The context's own tables are not touched.
+ * process exits. A goal set whose fill needs more is refused with status -5 and a message; use
+ * mrl_top_down_many for it (a goal that cannot be canonicalised is status -4, as in mrl_plan_goals).
+ * The context's own tables are not touched.
  * The first call on a device resolves the array's device address; make that call before any
  * stream capture. All calls share the array, so calls that overlap on one GPU race - issue them
  * one at a time per device. */
@@ -139,8 +160,11 @@ int mrl_plan_adopt(mrl_ctx* ctx, const uint64_t sizes[8], void* ptrs[8], int can
 /* The candidate records (range 3, by far the largest) are only ever read on the device. With
  * cands_on_device_only the adopting rank gets no host pointer for them (ptrs[3] = NULL): after
  * mrl_upload on every rank the caller copies the planning rank's device records into
- * mrl_device_cands of the others (e.g. ncclBroadcast over NVLink). */
+ * mrl_device_cands of the others (e.g. ncclBroadcast over NVLink) and then calls mrl_cands_arrived
+ * on every rank: it checks on the device that every record the kernels will index with is in
+ * range; until it has succeeded a fill is refused with a status. */
 int mrl_device_cands(const mrl_ctx* ctx, void** ptr, uint64_t* bytes);
+int mrl_cands_arrived(mrl_ctx* ctx);
 int mrl_plan_adopt_done(mrl_ctx* ctx, double plan_seconds);
 int mrl_set_stream(mrl_ctx* ctx, void* cuda_stream);
 uint64_t mrl_num_stages(const mrl_ctx* ctx);
@@ -177,6 +201,11 @@ long mrl_get_impl(mrl_ctx* ctx, const uint8_t* blob, size_t len, const uint64_t 
  * recurrence that defines the database at every checked point. */
 int mrl_verify(mrl_ctx* ctx, uint64_t n_samples, uint64_t seed, uint64_t* n_checked, uint64_t* n_mismatch);
 
+/* 64-bit checksum of the filled tables, no counterpart in the reference: a sum over all Specs of a
+ * hash of (Spec id, breakpoint masks, rows in cell order). Independent of where rows lie in device
+ * memory, so a sharded fill and a single-GPU fill of one plan must agree. */
+int mrl_checksum(mrl_ctx* ctx, uint64_t* out);
+
 int mrl_get_stats(const mrl_ctx* ctx, mrl_stats* out);
 
 /* Table export (the data a FilesDatabase::put stream would have produced,
@@ -186,6 +215,34 @@ uint64_t mrl_num_specs(const mrl_ctx* ctx);
 int mrl_spec_blob(const mrl_ctx* ctx, uint64_t spec_id, uint8_t* out, size_t cap);
 int mrl_spec_grid(mrl_ctx* ctx, uint64_t spec_id, uint32_t masks[4], uint64_t* n_cells);
 int mrl_export_rows(mrl_ctx* ctx, uint64_t spec_id, mrl_decision* out, size_t cap);
+/* The whole table in two device-to-host copies: per Spec its four masks (masks, 4 * n_specs words)
+ * and the index of its first row (first_row, n_specs + 1 entries), and all rows (rows, n_rows
+ * entries: mrl_get_stats.n_rows). mrl_decode_row turns a row into a decision. */
+int mrl_export_all(mrl_ctx* ctx, uint32_t* masks, uint64_t* first_row, mrl_row* rows, uint64_t rows_cap);
+void mrl_decode_row(const mrl_row* row, mrl_decision* out);
+/* The reference's logical table contents for one Spec (what FilesDatabase::put leaves behind,
+ * morello/src/db/mod.rs:650-766, morello/src/db/pagecontents.rs:125-184): rectangles over the four
+ * limit dimensions, each with one decision. Neighbouring cells of the Spec's grid with equal
+ * decisions are merged along RF, then VRF, L1, GL. lo / hi: 4 lattice codes per rectangle,
+ * inclusive. Returns the number of rectangles (-3: cap too small). */
+long mrl_export_rects(mrl_ctx* ctx, uint64_t spec_id, uint8_t* lo, uint8_t* hi, mrl_decision* out, size_t cap);
+
+/* Replaces FilesDatabase::save (morello/src/db/mod.rs:769-775) and the reopening of a database
+ * directory (FilesDatabase::new on an existing path, :350-380, with its TARGET / TILESCALE guards,
+ * :2091-2153). One file: target and tile-scale tags, the top limits, every Spec blob, the masks
+ * and rows. Written to `path`.tmp and renamed. mrl_load checks tags, sizes and a checksum of the
+ * contents and answers lookups afterwards; when the context already holds the plan of the same job
+ * (same Specs in the same order) its candidate records stay usable (mrl_verify, mrl_fill).
+ * Status -7: not a database of this library / target; -8: truncated or corrupt. */
+int mrl_save(mrl_ctx* ctx, const char* path);
+int mrl_load(mrl_ctx* ctx, const char* path);
+
+/* FilesDatabase::put (morello/src/db/mod.rs:637-766) has no writing counterpart here: every cell of
+ * these tables is a direct solve from the children's cells, so a decision from elsewhere cannot be
+ * stored without breaking that. What the reference debug-asserts on overlapping puts (equal cost,
+ * morello/src/db/pagecontents.rs:194-198) is what this checks: 0 when the tables hold exactly this
+ * decision at (Spec, limits), -9 when they hold another one, -3 when the Spec is not in the tables. */
+int mrl_put(mrl_ctx* ctx, const uint8_t* blob, size_t len, const uint64_t limits[4], const mrl_decision* decision);
 
 #ifdef __cplusplus
 }

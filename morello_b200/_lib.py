@@ -10,13 +10,19 @@ class Decision(C.Structure):
                 ("peaks", C.c_uint64 * 4)]
 
 
+class Row(C.Structure):
+    _fields_ = [("main_cost", C.c_uint32), ("peak_codes", C.c_uint32), ("depth_action", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
 class Stats(C.Structure):
     _fields_ = [("n_specs", C.c_uint64), ("n_goal_specs", C.c_uint64), ("n_candidates", C.c_uint64),
                 ("n_stages", C.c_uint64), ("n_rows", C.c_uint64), ("n_cells_solved", C.c_uint64),
-                ("n_passes", C.c_uint64), ("n_launches", C.c_uint64), ("n_combine_launches", C.c_uint64),
+                ("n_candidates_evaluated", C.c_uint64), ("n_rows_gathered", C.c_uint64),
+                ("n_passes", C.c_uint64), ("n_launches", C.c_uint64), ("n_grid_syncs", C.c_uint64),
                 ("algorithmic_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
                 ("plan_seconds", C.c_double), ("upload_seconds", C.c_double), ("fill_ms", C.c_double),
-                ("combine_ms", C.c_double)]
+                ("combine_ms", C.c_double), ("early_ms", C.c_double)]
 
 
 EXPORTS = {
@@ -64,6 +70,15 @@ EXPORTS = {
     "mrl_spec_blob": (C.c_int, [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t]),
     "mrl_spec_grid": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
     "mrl_export_rows": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(Decision), C.c_size_t]),
+    "mrl_set_plan_flags": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "mrl_cands_arrived": (C.c_int, [C.c_void_p]),
+    "mrl_checksum": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "mrl_export_all": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "mrl_decode_row": (None, [C.POINTER(Row), C.POINTER(Decision)]),
+    "mrl_export_rects": (C.c_long, [C.c_void_p, C.c_uint64, C.c_char_p, C.c_char_p, C.POINTER(Decision), C.c_size_t]),
+    "mrl_save": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "mrl_load": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "mrl_put": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_uint64), C.POINTER(Decision)]),
 }
 
 _lib = None
@@ -74,7 +89,7 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = os.environ.get("MRL_LIB_PATH", LIB_PATH)  # override: an alternative build of the same library
+    path = LIB_PATH
     if not os.path.exists(path):
         raise RuntimeError(
             f"{path} is missing: build the CUDA extension first (python -c 'import __graft_entry__ as g; g.build()')")

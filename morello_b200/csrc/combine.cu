@@ -1,23 +1,28 @@
 // The CUDA side of the synthesis-database fill (sm_100a).
 //
-// Specs are processed stage by stage (plan.hpp). For one stage the device
-//   1. derives each Spec's working limits grid: per memory the lattice codes at which its
+// Specs are processed stage by stage (plan.hpp). One cooperative launch solves a whole stage
+// on the device, with grid-wide barriers between its phases and nothing for the host to decide:
+//   1. every Spec gets its working limits grid: per memory the lattice codes at which its
 //      result can change - thresholds of its own candidates plus the (shifted) breakpoints of
-//      the finished tables of its children (derive_masks_kernel; totals_kernel, place_kernel);
-//   2. lists the working cells by limits diagonal (diag_histogram_kernel, scatter_cells_kernel)
-//      and solves them directly, one launch per occupied diagonal (combine_argmin_kernel): a
-//      thread (or 4, 8, 32 lanes in small launches) takes one cell, walks the Spec's candidate
-//      records, gathers the child rows each candidate needs at the child's limits, combines
-//      them into a Cost and keeps the lexicographic minimum;
-//   3. finds which breakpoints are real - some pair of neighbouring cells differs
-//      (real_masks_kernel) - and repeats 1-3 for the Specs whose grid still lacks a breakpoint
-//      that a same-stage child turned out to have, and for the Specs above them
-//      (spread_dirty_kernel); relayout Moves are the only same-stage dependency;
-//   4. compacts the working grids to the real breakpoints and appends them to the table
-//      (final_count_kernel, scan_block_sums_kernel, compact_kernel).
-// Step 3's fixpoint is exact: when every Spec's grid contains all thresholds and all shifted
+//      the finished tables of its children (phase_derive);
+//   2. the Specs to solve get working rows, and the working cells are listed by limits diagonal
+//      (sum of the four codes) (phase_place, phase_histogram, phase_scatter);
+//   3. every working cell is solved. Evaluating a candidate at a cell = feasibility under the
+//      cell's limits, gather of the child rows at the children's limits, combine into a Cost,
+//      lexicographic minimum. Candidates whose children all lie in earlier stages need no order:
+//      a warp takes a Spec, its lanes take 32 cells at a time and walk those candidate records
+//      together, so record and child-header loads are warp-uniform (phase_early). The rest -
+//      relayout Moves, whose body is a Spec of the same stage at strictly lower limits - are
+//      evaluated diagonal by diagonal in ascending order, one thread per listed cell, starting
+//      from the optimum of the first group (phase_combine);
+//   4. breakpoints at which some pair of neighbouring cells differs are real
+//      (phase_real_masks); 1-4 repeat for the Specs whose grid still lacks a breakpoint that a
+//      same-stage child turned out to have, and for the Specs above them;
+//   5. the working grids are compacted to the real breakpoints and appended to the table
+//      (phase_final_count, phase_scan_sums, phase_compact).
+// Step 4's fixpoint is exact: when every Spec's grid contains all thresholds and all shifted
 // breakpoints of the computed tables of its children, induction over the limits lattice shows
-// every computed cell equals the direct solve at every limit inside the cell.
+// every computed cell equals the direct solve at every limit inside it.
 //
 // What the combine replaces in the reference (paths inside the Morello repository):
 //   morello/src/scheduling/mod.rs:286-368     ActionSolver::compute_cost
@@ -26,11 +31,13 @@
 //   morello/src/scheduling/select.rs:34-47    kernel-allocation feasibility
 //   morello/src/search/reducer.rs:40-99       argmin on (Cost, ActionNum)
 //   morello/src/db/pagecontents.rs:103-123    child lookup (here: an index computation)
-// Integer-only work bounded by HBM/L2 bandwidth; no tensor cores.
+//   precompute/src/main.rs:304-385            the stage loop (here: on the device)
+// Integer-only work; no tensor cores.
 #include "device_types.h"
 #include "fill.hpp"
+#include "../../include/morello_b200.h"
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
-#include <cuda_profiler_api.h>
 #include <stddef.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -40,11 +47,16 @@
 #include <mutex>
 #include <thread>
 
-#ifndef MRL_MIN_BLOCKS
-#define MRL_MIN_BLOCKS 12
-#endif
+namespace cg = cooperative_groups;
+
+static_assert(MRL_STATIC_SCRATCH_BYTES == MRL_NOALLOC_MAX_BYTES,
+              "the fixed device array and the limit the header promises are one number");
 
 namespace {
+
+constexpr int kBlock = 128;      // threads per block of every kernel here
+constexpr int kMinBlocks = 8;   // resident blocks per SM the stage kernel is compiled for
+constexpr int kMaxPasses = 128;
 
 __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
   uint32_t s = a + b;
@@ -67,6 +79,13 @@ __device__ __forceinline__ uint32_t cache_code_ceil(uint32_t x) {
 }
 __device__ __forceinline__ uint32_t cache_value(uint32_t code) { return code ? (1u << (code - 1)) : 0u; }
 
+// The limit code a Move's children see in the memory it allocates in, given the parent's code
+// there (at or above the Move's threshold): registers subtract, caches subtract and snap down
+// to a power of two (morello/src/memorylimits.rs:409-436).
+__device__ __forceinline__ uint32_t child_code(uint32_t level, uint32_t lv, uint32_t units) {
+  return level < 2 ? lv - units : 32 - __clz(cache_value(lv) - units);
+}
+
 // Position of the n-th (0-based) set bit of m; m has more than n bits set.
 __device__ __forceinline__ uint32_t nth_set_bit(uint32_t m, uint32_t n) {
   uint32_t pos = 0;
@@ -84,251 +103,153 @@ __device__ __forceinline__ uint32_t nth_set_bit(uint32_t m, uint32_t n) {
 __device__ __forceinline__ uint32_t sel4(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t k) {
   return k == 0 ? a0 : (k == 1 ? a1 : (k == 2 ? a2 : a3));
 }
+__device__ __forceinline__ uint32_t below(uint32_t code) { return (2u << code) - 1u; }   // codes <= code
 
-struct Key {
-  uint32_t main, peaks, tail;
+// The running optimum of a cell: the row's three key words and the index of the winning
+// candidate record within its Spec.
+struct Best {
+  uint32_t main, peaks, tail, ci;
 };
-__device__ __forceinline__ bool key_less(const Key& a, const Key& b) {
-  if (a.main != b.main) return a.main < b.main;
-  if (a.peaks != b.peaks) return a.peaks < b.peaks;
-  return a.tail < b.tail;
+__device__ __forceinline__ bool key_less(uint32_t m, uint32_t p, uint32_t t, const Best& b) {
+  if (m != b.main) return m < b.main;
+  if (p != b.peaks) return p < b.peaks;
+  return t < b.tail;
 }
 
-// Row of a child Spec at given limits: the cell whose breakpoints are the largest ones not
-// above the limits. b_k = mask of the codes <= the limit's code in memory k. One 32-byte
-// header (two loads) and one 16-byte row.
-// Row `base` of the table: bit 63 set = a working row of the stage being solved (temp buffer).
+struct Tally {   // what a thread's solves touched
+  uint32_t cands, lookups;
+};
+
+// Row `base` of the table: bit 63 set = a working row of the stage being solved.
 #define MRL_TEMP_FLAG (1ull << 63)
 __device__ __forceinline__ const MrlRow* row_at(const MrlRow* rows, const MrlRow* temp, unsigned long long base) {
   return ((base & MRL_TEMP_FLAG) ? temp : rows) + (base & ~MRL_TEMP_FLAG);
 }
 
-__device__ __forceinline__ uint4 lookup(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
-                                        const MrlRow* __restrict__ temp, uint32_t child, uint32_t b0, uint32_t b1,
-                                        uint32_t b2, uint32_t b3) {
-  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[child]));
-  const unsigned long long base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[child].row_base));
+// Row of a child Spec at given limits: the cell whose breakpoints are the largest ones not
+// above the limits. b_k = mask of the codes <= the limit's code in memory k. One 32-byte
+// header and one 16-byte row. Plain loads: headers and working rows of the stage being solved
+// are written by earlier phases of the same launch.
+__device__ __forceinline__ const MrlRow* row_of(const MrlRow* rows, const MrlRow* temp, const uint4 m,
+                                                unsigned long long base, uint32_t b0, uint32_t b1, uint32_t b2,
+                                                uint32_t b3) {
   const uint32_t i0 = __popc(m.x & b0) - 1;
   const uint32_t i1 = __popc(m.y & b1) - 1;
   const uint32_t i2 = __popc(m.z & b2) - 1;
   const uint32_t i3 = __popc(m.w & b3) - 1;
   const uint32_t off = ((i3 * __popc(m.z) + i2) * __popc(m.y) + i1) * __popc(m.x) + i0;  // cells per Spec < 2^32
-  // Rows read here were written by earlier launches (lower diagonal or earlier stage), never by
-  // this one, so the read-only path is safe.
-  return __ldg(reinterpret_cast<const uint4*>(row_at(rows, temp, base) + off));
+  return row_at(rows, temp, base) + off;
+}
+__device__ __forceinline__ uint4 lookup(const SpecHdr* hdrs, const MrlRow* rows, const MrlRow* temp, uint32_t child,
+                                        uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+  const uint4 m = *reinterpret_cast<const uint4*>(&hdrs[child]);
+  const unsigned long long base = hdrs[child].row_base;
+  return *reinterpret_cast<const uint4*>(row_of(rows, temp, m, base, b0, b1, b2, b3));
 }
 
-// Geometry of one thread's column. A column fixes the slot index in the three memories other
-// than the Spec's free memory F.
-struct Column {
-  uint32_t spec, F;
-  uint32_t mm[4], nn[4], idx[4], code[4];
-  uint32_t others;  // sum of the codes of the fixed memories
-  bool valid;
-};
-__device__ __forceinline__ Column decode_column(const SpecHdr* __restrict__ hdrs, const Chunk ch, uint32_t lane) {
-  Column c;
-  c.spec = ch.spec;
-  c.F = ch.col_start >> 30;
-  const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch.spec]));
-  c.mm[0] = m.x; c.mm[1] = m.y; c.mm[2] = m.z; c.mm[3] = m.w;
-  uint32_t rest = (ch.col_start & 0x3FFFFFFFu) + lane;
-  c.others = 0;
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    c.nn[k] = (uint32_t)__popc(c.mm[k]);
-    const uint32_t nk = ((uint32_t)k == c.F) ? 1u : c.nn[k];
-    c.idx[k] = rest % nk;
-    rest /= nk;
-    c.code[k] = nth_set_bit(c.mm[k], c.idx[k]);  // for F: slot 0, code 0
-    c.others += c.code[k];
-  }
-  c.valid = rest == 0;  // false: column index beyond this Spec's grid
-  return c;
-}
-
-// The direct solve of one (Spec, limits) point from the tables of the Spec's children: walks the
-// candidate records, applies the limits-dependent feasibility tests, gathers the child rows at
-// the children's limits, combines them and keeps the lexicographic minimum. cpack = the limits
-// as lattice codes (RF in byte 0 .. GL in byte 3).
-__device__ __forceinline__ Key solve_point(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                                           const MrlRow* __restrict__ rows, const MrlRow* __restrict__ temp,
-                                           uint32_t spec, uint32_t cpack, uint32_t n_specs,
-                                           uint32_t* __restrict__ error_flag, uint32_t first_cand = 0,
-                                           uint32_t cand_stride = 1) {
-  // "codes at or below this point's limit", per memory: what a child lookup at the same limits needs
-  const uint32_t bm0 = (2u << code_of(cpack, 0)) - 1u, bm1 = (2u << code_of(cpack, 1)) - 1u,
-                 bm2 = (2u << code_of(cpack, 2)) - 1u, bm3 = (2u << code_of(cpack, 3)) - 1u;
-  const uint2 cl = __ldg(reinterpret_cast<const uint2*>(&hdrs[spec].cand_off));
-  const uint32_t cand_off = cl.x, ncand = cl.y;
-
-  Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-  for (uint32_t ci = first_cand; ci < ncand; ci += cand_stride) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]));
-    const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-    const uint32_t imm = a.y;
-    const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, pcode = (a.z >> 16) & 0xFFu;
-    const uint32_t units = a.w;
-    const uint32_t lv = code_of(cpack, level);  // the cell's limit in `level`
-    Key k;
-    if (kind == MRL_CK_LEAF) {
-      if (lv < thr) continue;
-      k.main = imm;
-      k.peaks = pcode << peak_shift(level);
-      k.tail = (1u << 16) | action;
-    } else {
-      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cand_off + ci]) + 1);
-      uint32_t c0 = bm0, c1 = bm1, c2 = bm2, c3 = bm3;
-      const uint32_t sh = peak_shift(level);
-      if (kind == MRL_CK_MOVE) {
-        if (lv < thr) continue;
-        // Branch and bound: a Move costs at least its own base cost. Candidates are stored
-        // cheapest-first (kernels, loops, then Moves by base cost), so most Moves end here.
-        if (imm > best.main) continue;
-        uint32_t ccode;
-        if (level < 2) ccode = lv - units;                      // registers: exact
-        else ccode = 32 - __clz(cache_value(lv) - units);       // caches: snap down to 2^k
-        const uint32_t cb = (2u << ccode) - 1u;
-        c0 = (level == 0) ? cb : c0;
-        c1 = (level == 1) ? cb : c1;
-        c2 = (level == 2) ? cb : c2;
-        c3 = (level == 3) ? cb : c3;
-      }
-#ifdef MRL_CHECK_CHILD_IDS
-      if (b.x >= n_specs || (nchild > 1 && b.y >= n_specs) || (nchild > 2 && b.z >= n_specs)) {
-        if (error_flag) atomicExch(error_flag, 1u);
-        continue;
-      }
-#endif
-      // Children one at a time: a child without an implementation, or a partial sum that already
-      // exceeds the best main cost, ends the candidate before the remaining rows are fetched.
-      const uint4 r0 = lookup(hdrs, rows, temp, b.x, c0, c1, c2, c3);
-      if (r0.z == MRL_UNSAT) continue;
-      uint4 r1 = r0, r2 = r0;
-      if (nchild > 1) {
-        if (kind == MRL_CK_MOVE && sat_add(imm, r0.x) > best.main) continue;
-        r1 = lookup(hdrs, rows, temp, b.y, c0, c1, c2, c3);
-        if (r1.z == MRL_UNSAT) continue;
-        if (nchild > 2) {
-          r2 = lookup(hdrs, rows, temp, b.z, c0, c1, c2, c3);
-          if (r2.z == MRL_UNSAT) continue;
-        }
-      }
-      uint32_t main, peaks, depth;
-      if (kind == MRL_CK_LOOP) {
-        main = sat_mul(r0.x, imm);
-        peaks = r0.y;
-        depth = 1u;  // a single-body tile loop has depth 1 whatever its body's depth
-      } else {
-        main = (kind == MRL_CK_MOVE) ? sat_add(imm, r0.x) : r0.x;
-        if (nchild > 1) main = sat_add(main, r1.x);
-        if (nchild > 2) main = sat_add(main, r2.x);
-        peaks = __vmaxu4(__vmaxu4(r0.y, r1.y), r2.y);
-        if (kind == MRL_CK_MOVE) {
-          // own allocation sits on top of the deepest child's peak in `level`; rounding to the
-          // lattice is monotone, so max-then-round equals the reference's round-per-child
-          const uint32_t child_code = (peaks >> sh) & 0xFFu;
-          uint32_t ncode;
-          if (level < 2) ncode = units + child_code;
-          else ncode = cache_code_ceil(units + cache_value(child_code));
-          peaks = (peaks & ~(0xFFu << sh)) | (ncode << sh);
-        }
-        depth = min(max(max(r0.z >> 16, r1.z >> 16), r2.z >> 16) + 1u, 255u);
-      }
-      k.main = main;
-      k.peaks = peaks;
-      k.tail = (depth << 16) | action;
+// One candidate record of a Spec at one limits point: feasibility under the limits, the child
+// rows at the children's limits, the combined Cost, and the running minimum. The fill is bound by
+// the latency of dependent loads (record -> child header -> child row), so the headers of all
+// children are requested together, then all rows: two round trips per candidate whatever the
+// number of children.
+// kFinished: every child lies in a finished stage, so headers and rows are read-only for the whole
+// launch and may take the non-coherent load path.
+template <bool kFinished>
+__device__ __forceinline__ void eval_candidate(const SpecHdr* hdrs, const CandRec* __restrict__ cands, const MrlRow* rows,
+                                               const MrlRow* temp, uint32_t rec, const uint4 a, uint32_t ci, uint32_t cpack,
+                                               uint32_t bm0, uint32_t bm1, uint32_t bm2, uint32_t bm3, Best& best,
+                                               Tally& tally) {
+  const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
+  const uint32_t imm = a.y;
+  const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, pcode = (a.z >> 16) & 0xFFu;
+  const uint32_t units = a.w;
+  const uint32_t lv = code_of(cpack, level);  // the cell's limit in `level`
+  tally.cands++;
+  uint32_t k_main, k_peaks, k_tail;
+  if (kind == MRL_CK_LEAF) {
+    if (lv < thr) return;
+    k_main = imm;
+    k_peaks = pcode << peak_shift(level);
+    k_tail = (1u << 16) | action;
+  } else {
+    uint32_t c0 = bm0, c1 = bm1, c2 = bm2, c3 = bm3;
+    const uint32_t sh = peak_shift(level);
+    if (kind == MRL_CK_MOVE) {
+      if (lv < thr) return;
+      // Branch and bound: a Move costs at least its own base cost.
+      if (imm > best.main) return;
+      const uint32_t cb = below(child_code(level, lv, units));
+      c0 = (level == 0) ? cb : c0;
+      c1 = (level == 1) ? cb : c1;
+      c2 = (level == 2) ? cb : c2;
+      c3 = (level == 3) ? cb : c3;
     }
-    if (key_less(k, best)) best = k;
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[rec]) + 1);
+    const uint32_t ch1 = nchild > 1 ? b.y : b.x, ch2 = nchild > 2 ? b.z : b.x;   // absent children repeat the first
+    uint4 m0, m1, m2, r0, r1, r2;
+    unsigned long long base0, base1, base2;
+    if (kFinished) {
+      m0 = __ldg(reinterpret_cast<const uint4*>(&hdrs[b.x]));
+      m1 = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch1]));
+      m2 = __ldg(reinterpret_cast<const uint4*>(&hdrs[ch2]));
+      base0 = __ldg(&hdrs[b.x].row_base); base1 = __ldg(&hdrs[ch1].row_base); base2 = __ldg(&hdrs[ch2].row_base);
+      r0 = __ldg(reinterpret_cast<const uint4*>(row_of(rows, temp, m0, base0, c0, c1, c2, c3)));
+      r1 = __ldg(reinterpret_cast<const uint4*>(row_of(rows, temp, m1, base1, c0, c1, c2, c3)));
+      r2 = __ldg(reinterpret_cast<const uint4*>(row_of(rows, temp, m2, base2, c0, c1, c2, c3)));
+    } else {
+      m0 = *reinterpret_cast<const uint4*>(&hdrs[b.x]);
+      m1 = *reinterpret_cast<const uint4*>(&hdrs[ch1]);
+      m2 = *reinterpret_cast<const uint4*>(&hdrs[ch2]);
+      base0 = hdrs[b.x].row_base; base1 = hdrs[ch1].row_base; base2 = hdrs[ch2].row_base;
+      r0 = *reinterpret_cast<const uint4*>(row_of(rows, temp, m0, base0, c0, c1, c2, c3));
+      r1 = *reinterpret_cast<const uint4*>(row_of(rows, temp, m1, base1, c0, c1, c2, c3));
+      r2 = *reinterpret_cast<const uint4*>(row_of(rows, temp, m2, base2, c0, c1, c2, c3));
+    }
+    tally.lookups += nchild;
+    if (r0.z == MRL_UNSAT || r1.z == MRL_UNSAT || r2.z == MRL_UNSAT) return;
+    uint32_t depth;
+    if (kind == MRL_CK_LOOP) {
+      k_main = sat_mul(r0.x, imm);
+      k_peaks = r0.y;
+      depth = 1u;  // a single-body tile loop has depth 1 whatever its body's depth
+    } else {
+      k_main = (kind == MRL_CK_MOVE) ? sat_add(imm, r0.x) : r0.x;
+      if (nchild > 1) k_main = sat_add(k_main, r1.x);
+      if (nchild > 2) k_main = sat_add(k_main, r2.x);
+      if (k_main > best.main) return;
+      k_peaks = __vmaxu4(__vmaxu4(r0.y, r1.y), r2.y);
+      if (kind == MRL_CK_MOVE) {
+        // own allocation sits on top of the deepest child's peak in `level`; rounding to the
+        // lattice is monotone, so max-then-round equals the reference's round-per-child
+        const uint32_t cc = (k_peaks >> sh) & 0xFFu;
+        const uint32_t ncode = level < 2 ? units + cc : cache_code_ceil(units + cache_value(cc));
+        k_peaks = (k_peaks & ~(0xFFu << sh)) | (ncode << sh);
+      }
+      depth = min(max(max(r0.z >> 16, r1.z >> 16), r2.z >> 16) + 1u, 255u);
+    }
+    k_tail = (depth << 16) | action;
+  }
+  if (key_less(k_main, k_peaks, k_tail, best)) {
+    best.main = k_main;
+    best.peaks = k_peaks;
+    best.tail = k_tail;
+    best.ci = ci;
+  }
+}
+
+// The direct solve of one (Spec, limits) point from the tables of the Spec's children: every
+// candidate record of the Spec. cpack = the limits as lattice codes.
+__device__ __forceinline__ Best solve_point(const SpecHdr* hdrs, const CandRec* __restrict__ cands, const MrlRow* rows,
+                                            const MrlRow* temp, uint32_t spec, uint32_t cpack, Tally& tally) {
+  const uint32_t bm0 = below(code_of(cpack, 0)), bm1 = below(code_of(cpack, 1)), bm2 = below(code_of(cpack, 2)),
+                 bm3 = below(code_of(cpack, 3));
+  const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[spec].cand_off);
+  Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+  for (uint32_t ci = 0; ci < cl.y; ci++) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
+    eval_candidate<false>(hdrs, cands, rows, temp, cl.x + ci, a, ci, cpack, bm0, bm1, bm2, bm3, best, tally);
   }
   return best;
-}
-
-// One launch = the cells of one stage that lie on one limits diagonal (sum of the four codes),
-// listed by scatter_cells_kernel: every thread has a cell, and neighbouring threads mostly have
-// neighbouring cells of one Spec. G = lanes per cell. A launch with few cells cannot fill the
-// GPU and lasts as long as one cell's chain of dependent loads (tens of microseconds with ~30
-// candidates); there the G lanes of a cell take every G-th candidate each and min-reduce their
-// keys with shuffles, which shortens the chain G-fold. Large launches use G = 1, which keeps the
-// lower-bound cut across all candidates of a cell.
-template <int G>
-__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
-combine_argmin_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                      const CellRef* __restrict__ cells, uint32_t n_cells,
-                      const MrlRow* __restrict__ rows, MrlRow* __restrict__ temp, uint32_t n_specs,
-                      uint32_t* __restrict__ error_flag) {
-  const uint32_t t = (blockIdx.x * blockDim.x + threadIdx.x) / G;
-  const uint32_t sub = threadIdx.x % G;
-  const bool valid = t < n_cells;   // the G lanes of a cell agree; no lane leaves before the shuffles
-  Key best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-  CellRef ref;
-  ref.spec = 0;
-  ref.cpack = 0;
-  uint32_t cell = 0;
-  unsigned long long base = 0;
-  if (valid) {
-    ref = cells[t];
-    // the cell's place in its Spec's working grid: slot = breakpoints at or below the code, minus one
-    const uint4 m = __ldg(reinterpret_cast<const uint4*>(&hdrs[ref.spec]));
-    const uint32_t i0 = __popc(m.x & ((2u << code_of(ref.cpack, 0)) - 1u)) - 1;
-    const uint32_t i1 = __popc(m.y & ((2u << code_of(ref.cpack, 1)) - 1u)) - 1;
-    const uint32_t i2 = __popc(m.z & ((2u << code_of(ref.cpack, 2)) - 1u)) - 1;
-    const uint32_t i3 = __popc(m.w & ((2u << code_of(ref.cpack, 3)) - 1u)) - 1;
-    cell = ((i3 * __popc(m.z) + i2) * __popc(m.y) + i1) * __popc(m.x) + i0;
-    base = __ldg(reinterpret_cast<const unsigned long long*>(&hdrs[ref.spec].row_base));
-    best = solve_point(hdrs, cands, rows, temp, ref.spec, ref.cpack, n_specs, error_flag, sub, G);
-  }
-  if (G > 1) {
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) {
-      Key other;
-      other.main = __shfl_xor_sync(0xFFFFFFFFu, best.main, o);
-      other.peaks = __shfl_xor_sync(0xFFFFFFFFu, best.peaks, o);
-      other.tail = __shfl_xor_sync(0xFFFFFFFFu, best.tail, o);
-      if (key_less(other, best)) best = other;
-    }
-  }
-  // Specs of the stage being solved always live in the working buffer.
-  if (valid && sub == 0)
-    *reinterpret_cast<uint4*>(temp + (base & ~MRL_TEMP_FLAG) + cell) = make_uint4(best.main, best.peaks, best.tail, 0u);
-}
-
-// Consistency check of a finished table: at sampled (or all) points of the limits lattice, for
-// sampled (or all) Specs, the direct solve from the children's tables must equal what the Spec's
-// own table returns there. Every point where that holds is a point where the table satisfies
-// the defining recurrence of the fill, whatever grid the table is stored on.
-__global__ void __launch_bounds__(128, MRL_MIN_BLOCKS)
-verify_points_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                     const MrlRow* __restrict__ rows, uint32_t n_specs, uint32_t top_pack, unsigned long long first,
-                     unsigned long long count, unsigned long long total_points, unsigned long long seed, int exhaustive,
-                     unsigned long long* __restrict__ out /* [0] mismatches, [1] first bad sample + 1 */) {
-  const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= count) return;
-  const uint32_t e0 = code_of(top_pack, 0) + 1, e1 = code_of(top_pack, 1) + 1, e2 = code_of(top_pack, 2) + 1,
-                 e3 = code_of(top_pack, 3) + 1;
-  const unsigned long long per_spec = (unsigned long long)e0 * e1 * e2 * e3;
-  unsigned long long s = first + i;
-  if (!exhaustive) {
-    // splitmix64 of (seed, sample index): a point of the (Spec x lattice) product
-    unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (s + 1);
-    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-    z ^= z >> 31;
-    s = z % total_points;
-  }
-  const uint32_t spec = (uint32_t)(s / per_spec);
-  uint32_t p = (uint32_t)(s % per_spec);
-  const uint32_t c0 = p % e0; p /= e0;
-  const uint32_t c1 = p % e1; p /= e1;
-  const uint32_t c2 = p % e2;
-  const uint32_t c3 = p / e2;
-  const uint32_t cpack = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
-  const Key k = solve_point(hdrs, cands, rows, rows, spec, cpack, n_specs, nullptr);
-  const uint4 r = lookup(hdrs, rows, rows, spec, (2u << c0) - 1u, (2u << c1) - 1u, (2u << c2) - 1u, (2u << c3) - 1u);
-  if (k.main != r.x || k.peaks != r.y || k.tail != r.z) {
-    atomicAdd(&out[0], 1ull);
-    atomicMin(&out[1], first + i);
-  }
 }
 
 // ---- working grids ---------------------------------------------------------------------
@@ -352,6 +273,35 @@ __device__ __forceinline__ Grid grid_of(const uint4 m) {
   g.cols = (uint32_t)(g.cells / best);
   g.warps = (g.cols + 31u) / 32u;
   return g;
+}
+
+// Geometry of one thread's column. A column fixes the slot index in the three memories other
+// than the Spec's free memory F.
+struct Column {
+  uint32_t spec, F;
+  uint32_t mm[4], nn[4], idx[4], code[4];
+  uint32_t others;  // sum of the codes of the fixed memories
+  bool valid;
+};
+__device__ __forceinline__ Column decode_column(const SpecHdr* hdrs, const Chunk ch, uint32_t lane) {
+  Column c;
+  c.spec = ch.spec;
+  c.F = ch.col_start >> 30;
+  const uint4 m = *reinterpret_cast<const uint4*>(&hdrs[ch.spec]);
+  c.mm[0] = m.x; c.mm[1] = m.y; c.mm[2] = m.z; c.mm[3] = m.w;
+  uint32_t rest = (ch.col_start & 0x3FFFFFFFu) + lane;
+  c.others = 0;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    c.nn[k] = (uint32_t)__popc(c.mm[k]);
+    const uint32_t nk = ((uint32_t)k == c.F) ? 1u : c.nn[k];
+    c.idx[k] = rest % nk;
+    rest /= nk;
+    c.code[k] = nth_set_bit(c.mm[k], c.idx[k]);  // for F: slot 0, code 0
+    c.others += c.code[k];
+  }
+  c.valid = rest == 0;  // false: column index beyond this Spec's grid
+  return c;
 }
 
 __device__ __forceinline__ void or_level(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t level,
@@ -380,146 +330,9 @@ __device__ __forceinline__ uint32_t shift_mask(uint32_t cm, uint32_t level, uint
   return out;
 }
 
-// Pass step 1: per Spec of the stage, the masks its working grid needs. child_source says what
-// is known about same-stage children: 0 = nothing (first pass: they are ignored), 1 = the
-// breakpoints in rmask (found real by the previous pass; or, when seeding, the children's own
-// first working masks). A Spec whose masks grew is marked dirty. seed_copy: also copy the new
-// masks to rmask (so that a following launch can read them as the children's breakpoints).
-__global__ void __launch_bounds__(128)
-derive_masks_kernel(SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, uint4* __restrict__ rmask,
-                    const uint8_t* __restrict__ mine, uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi,
-                    int first, int child_source, int seed_copy, uint32_t top_pack) {
-  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= hi || (mine && !mine[i])) return;
-  const uint4 old = *reinterpret_cast<const uint4*>(&hdrs[i]);
-  const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
-  uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
-  for (uint32_t ci = 0; ci < cl.y; ci++) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-    const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-    const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, units = a.w;
-    if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
-    if (kind == MRL_CK_LEAF) continue;
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
-    for (uint32_t j = 0; j < nchild; j++) {
-      const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
-      uint4 cm;
-      if (child < lo) cm = *reinterpret_cast<const uint4*>(&hdrs[child]);   // finished stage: final masks
-      else if (child_source == 0) continue;
-      else cm = rmask[child];
-      if (kind == MRL_CK_MOVE) {
-        const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(top_pack, level));
-        r0 |= (level == 0) ? s : cm.x;
-        r1 |= (level == 1) ? s : cm.y;
-        r2 |= (level == 2) ? s : cm.z;
-        r3 |= (level == 3) ? s : cm.w;
-      } else {
-        r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
-      }
-    }
-  }
-  const uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
-  const bool changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
-  if (changed) {
-    *reinterpret_cast<uint4*>(&hdrs[i]) = nm;
-    dirty[i] = 1;
-  }
-  if (seed_copy) rmask[i] = nm;
-}
-
-// A Spec with a dirty same-stage child has to be solved again too (its lookups may change).
-// Monotone, so racing with other threads' marks is harmless; run until totals_kernel reports
-// no unmarked Spec with a dirty child.
-__global__ void __launch_bounds__(128)
-spread_dirty_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands,
-                    const uint8_t* __restrict__ mine, uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi) {
-  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= hi || (mine && !mine[i]) || dirty[i]) return;
-  const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
-  for (uint32_t ci = 0; ci < cl.y; ci++) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-    const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-    if (kind != MRL_CK_MOVE) continue;   // only Moves have same-stage children
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
-    for (uint32_t j = 0; j < nchild; j++) {
-      const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
-      if (child >= lo && dirty[child]) { dirty[i] = 1; return; }
-    }
-  }
-}
-
-// Totals of what the coming solve takes (dirty Specs only), the working cells of the whole stage,
-// and whether the dirty marks are closed under "has a dirty same-stage child".
-__global__ void __launch_bounds__(128)
-totals_kernel(const SpecHdr* __restrict__ hdrs, const CandRec* __restrict__ cands, const uint8_t* __restrict__ mine,
-              uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi, PassCounters* __restrict__ ctr) {
-  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  const bool active = i < hi && (!mine || mine[i]);
-  unsigned long long cells = 0, warps = 0, bytes = 0, all_cells = 0;
-  uint32_t open_marks = 0;
-  if (active) {
-    const uint4 nm = *reinterpret_cast<const uint4*>(&hdrs[i]);
-    const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
-    const Grid g = grid_of(nm);
-    all_cells = g.cells;
-    bool is_dirty = dirty[i] != 0;
-    if (!is_dirty) {
-      for (uint32_t ci = 0; ci < cl.y && !is_dirty; ci++) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-        const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-        if (kind != MRL_CK_MOVE) continue;
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]) + 1);
-        for (uint32_t j = 0; j < nchild; j++) {
-          const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
-          if (child >= lo && dirty[child]) is_dirty = true;
-        }
-      }
-      if (is_dirty) { dirty[i] = 1; open_marks = 1; }
-    }
-    if (is_dirty) {
-      cells = g.cells;
-      warps = g.warps;
-      // algorithmic bytes of one solve: a 12-byte row out; per candidate a 16-byte header; per
-      // child of a candidate that fits the cell's limits a 4-byte index and a 12-byte row in
-      bytes = cells * 12ull;
-      for (uint32_t ci = 0; ci < cl.y; ci++) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(&cands[cl.x + ci]));
-        const uint32_t kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;
-        const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu;
-        bytes += cells * 16ull;
-        if (nchild) {
-          unsigned long long feasible = cells;
-          if (kind == MRL_CK_MOVE) {
-            const uint32_t ml = sel4(nm.x, nm.y, nm.z, nm.w, level);
-            feasible = cells / (uint32_t)__popc(ml) * (uint32_t)__popc(ml >> thr);
-          }
-          bytes += feasible * nchild * 16ull;
-        }
-      }
-    }
-  }
-  // warp totals, then one atomic per warp and counter
-  for (int o = 16; o > 0; o >>= 1) {
-    cells += __shfl_xor_sync(0xFFFFFFFFu, cells, o);
-    warps += __shfl_xor_sync(0xFFFFFFFFu, warps, o);
-    bytes += __shfl_xor_sync(0xFFFFFFFFu, bytes, o);
-    all_cells += __shfl_xor_sync(0xFFFFFFFFu, all_cells, o);
-  }
-  open_marks = __reduce_or_sync(0xFFFFFFFFu, open_marks);
-  if ((threadIdx.x & 31) == 0) {
-    if (cells) {
-      atomicAdd(&ctr->cells, cells);
-      atomicAdd(&ctr->warps, warps);
-      atomicAdd(&ctr->alg_bytes, bytes);
-    }
-    if (all_cells) atomicAdd(&ctr->all_cells, all_cells);
-    if (open_marks) atomicOr(&ctr->changed, 1u);
-  }
-}
-
-// Exclusive prefix of v over the block (blockDim.x == 256); *total = the block's sum.
+// Exclusive prefix of v over the block (kBlock threads); *total = the block's sum.
 __device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long v, unsigned long long* total) {
-  __shared__ unsigned long long warp_sum[8];
+  __shared__ unsigned long long warp_sum[kBlock / 32];
   __shared__ unsigned long long block_total;
   const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   unsigned long long inc = v;
@@ -532,7 +345,7 @@ __device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned long long run = 0;
-    for (int k = 0; k < 8; k++) { const unsigned long long t = warp_sum[k]; warp_sum[k] = run; run += t; }
+    for (int k = 0; k < kBlock / 32; k++) { const unsigned long long t = warp_sum[k]; warp_sum[k] = run; run += t; }
     block_total = run;
   }
   __syncthreads();
@@ -540,255 +353,806 @@ __device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long
   return warp_sum[w] + inc - v;
 }
 
-// Pass step 2: gives every dirty Spec of the stage fresh working rows (in the temp buffer, from
-// temp_top up; Specs that are not solved again keep theirs) and its chunks, and resets its
-// real-breakpoint masks.
-__global__ void __launch_bounds__(256)
-place_kernel(SpecHdr* __restrict__ hdrs, uint4* __restrict__ rmask, const uint8_t* __restrict__ mine,
-             uint8_t* __restrict__ dirty, uint32_t lo, uint32_t hi, unsigned long long temp_top,
-             unsigned long long temp_cap, Chunk* __restrict__ chunks, unsigned long long chunk_cap,
-             PassCounters* __restrict__ ctr) {
-  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  const bool active = i < hi && (!mine || mine[i]) && dirty[i];
-  Grid g;
-  g.cells = 0; g.warps = 0; g.F = 0;
-  if (active) g = grid_of(*reinterpret_cast<const uint4*>(&hdrs[i]));
-  unsigned long long tot_cells, tot_warps;
-  const unsigned long long my_row = block_excl_scan(g.cells, &tot_cells);
-  const unsigned long long my_chunk = block_excl_scan(active ? g.warps : 0ull, &tot_warps);
-  __shared__ unsigned long long row0, chunk0;
-  if (threadIdx.x == 0) {
-    row0 = atomicAdd(&ctr->temp_rows, tot_cells);
-    chunk0 = atomicAdd(&ctr->n_chunks, (uint32_t)tot_warps);
-  }
-  __syncthreads();
-  if (!active) return;
-  const unsigned long long rb = temp_top + row0 + my_row;
-  const unsigned long long cb = chunk0 + my_chunk;
-  if (rb + g.cells > temp_cap || cb + g.warps > chunk_cap) { atomicOr(&ctr->error, 2u); return; }
-  hdrs[i].row_base = rb | MRL_TEMP_FLAG;
-  rmask[i] = make_uint4(1u, 1u, 1u, 1u);
-  dirty[i] = 0;   // solved by this pass
-  for (uint32_t w = 0; w < g.warps; w++) {
-    Chunk c;
-    c.spec = i;
-    c.col_start = (w * 32u) | (g.F << 30);
-    chunks[cb + w] = c;
+// Everything a stage kernel needs; passed by value.
+struct StageArgs {
+  SpecHdr* hdrs;
+  const CandRec* cands;
+  uint4* rmask;
+  const uint8_t* mine;    // null: every Spec is computed here
+  uint8_t* dirty;         // by Spec id: 0 keep, 1 solve in the coming pass, 2 being solved in this pass
+  Chunk* chunks;
+  WorkItem* items;
+  CellRef* cells;
+  DiagTable* diag;
+  MrlRow* rows;
+  MrlRow* temp;
+  uint32_t* fcount;
+  unsigned long long* block_sums;
+  FillCtl* ctl;
+  uint32_t lo, hi;                // the stage's Spec ids
+  uint32_t top_pack;
+  uint32_t stage;
+  unsigned long long temp_cap, chunk_cap, item_cap, cell_cap, row_cap;
+  int solve, place;               // which halves to run
+};
+
+__device__ __forceinline__ bool computed_here(const StageArgs& a, uint32_t i) { return !a.mine || a.mine[i]; }
+
+// Pass step 1: per Spec of the stage, the masks its working grid needs. child_source says what
+// is known about same-stage children: 0 = nothing (first pass: they are ignored), 1 = the
+// breakpoints in rmask (found real by the previous pass; or, when seeding, the children's own
+// first working masks). A Spec whose masks grew is marked for solving. seed_copy: also copy the
+// new masks to rmask (so that a following phase can read them as the children's breakpoints).
+__device__ __noinline__ void phase_derive(const StageArgs& a, uint32_t gtid, uint32_t gthreads, int first, int child_source,
+                             int seed_copy) {
+  for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
+    if (!computed_here(a, i)) continue;
+    const uint4 old = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+    const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+    uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
+    for (uint32_t ci = 0; ci < cl.y; ci++) {
+      const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+      const uint32_t kind = (c.x >> 16) & 0xFFu, nchild = c.x >> 24;
+      const uint32_t level = c.z & 0xFFu, thr = (c.z >> 8) & 0xFFu, units = c.w;
+      if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
+      if (kind == MRL_CK_LEAF) continue;
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]) + 1);
+      for (uint32_t j = 0; j < nchild; j++) {
+        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+        uint4 cm;
+        if (child < a.lo) cm = *reinterpret_cast<const uint4*>(&a.hdrs[child]);   // finished stage: final masks
+        else if (child_source == 0) continue;
+        else cm = a.rmask[child];
+        if (kind == MRL_CK_MOVE) {
+          const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(a.top_pack, level));
+          r0 |= (level == 0) ? s : cm.x;
+          r1 |= (level == 1) ? s : cm.y;
+          r2 |= (level == 2) ? s : cm.z;
+          r3 |= (level == 3) ? s : cm.w;
+        } else {
+          r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
+        }
+      }
+    }
+    const uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
+    const bool changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
+    if (changed) {
+      *reinterpret_cast<uint4*>(&a.hdrs[i]) = nm;
+      a.dirty[i] = 1;
+    }
+    if (seed_copy) a.rmask[i] = nm;
   }
 }
 
-// Pass step 3a: how many working cells lie on each limits diagonal. Thread per column.
-__global__ void __launch_bounds__(128)
-diag_histogram_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
-                      DiagTable* __restrict__ diag) {
+// A Spec with a marked same-stage child has to be solved again too (its lookups may change).
+// Monotone, so racing with other threads' marks is harmless; repeated until a round marks nothing.
+__device__ __noinline__ void phase_spread(const StageArgs& a, uint32_t gtid, uint32_t gthreads, uint32_t epoch) {
+  for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
+    if (!computed_here(a, i) || a.dirty[i]) continue;
+    const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+    bool hit = false;
+    for (uint32_t ci = 0; ci < cl.y && !hit; ci++) {
+      const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+      const uint32_t kind = (c.x >> 16) & 0xFFu, nchild = c.x >> 24;
+      if (kind != MRL_CK_MOVE) continue;   // only Moves have same-stage children
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]) + 1);
+      for (uint32_t j = 0; j < nchild; j++) {
+        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+        if (child >= a.lo && a.dirty[child]) hit = true;
+      }
+    }
+    if (hit) {
+      a.dirty[i] = 1;
+      a.ctl->spread_epoch = epoch;   // every writer of a round stores the same value
+    }
+  }
+}
+
+// Totals of what the coming solve takes (marked Specs only) and the working cells of the whole stage.
+__device__ __noinline__ void phase_totals(const StageArgs& a, uint32_t gtid, uint32_t gthreads) {
+  unsigned long long cells = 0, warps = 0, all_cells = 0;
+  for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
+    if (!computed_here(a, i)) continue;
+    const Grid g = grid_of(*reinterpret_cast<const uint4*>(&a.hdrs[i]));
+    all_cells += g.cells;
+    if (a.dirty[i]) {
+      cells += g.cells;
+      warps += g.warps;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    cells += __shfl_xor_sync(0xFFFFFFFFu, cells, o);
+    warps += __shfl_xor_sync(0xFFFFFFFFu, warps, o);
+    all_cells += __shfl_xor_sync(0xFFFFFFFFu, all_cells, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (cells) {
+      atomicAdd(&a.ctl->cells, cells);
+      atomicAdd(&a.ctl->warps, warps);
+    }
+    if (all_cells) atomicAdd(&a.ctl->all_cells, all_cells);
+  }
+}
+
+// Pass step 2: gives every marked Spec of the stage fresh working rows (from temp_top up; Specs
+// that are not solved again keep theirs) and its chunks, and resets its real-breakpoint masks.
+// Capacities were checked against the pass totals before.
+__device__ __noinline__ void phase_place(const StageArgs& a, unsigned long long temp_top, uint32_t item_cells) {
+  __shared__ unsigned long long row0, chunk0, item0;
+  for (uint32_t base = a.lo + blockIdx.x * kBlock; base < a.hi; base += gridDim.x * kBlock) {
+    const uint32_t i = base + threadIdx.x;
+    const bool active = i < a.hi && computed_here(a, i) && a.dirty[i] == 1;
+    Grid g;
+    g.cells = 0; g.warps = 0; g.F = 0;
+    if (active) g = grid_of(*reinterpret_cast<const uint4*>(&a.hdrs[i]));
+    const uint32_t n_items = (uint32_t)((g.cells + item_cells - 1) / item_cells);
+    unsigned long long tot_cells, tot_warps, tot_items;
+    const unsigned long long my_row = block_excl_scan(g.cells, &tot_cells);
+    const unsigned long long my_chunk = block_excl_scan(active ? g.warps : 0ull, &tot_warps);
+    const unsigned long long my_item = block_excl_scan(n_items, &tot_items);
+    if (threadIdx.x == 0) {
+      row0 = atomicAdd(&a.ctl->row_cursor, tot_cells);
+      chunk0 = atomicAdd(&a.ctl->chunk_cursor, (uint32_t)tot_warps);
+      item0 = atomicAdd(&a.ctl->item_cursor, (uint32_t)tot_items);
+    }
+    __syncthreads();
+    if (active) {
+      const unsigned long long cb = chunk0 + my_chunk;
+      for (uint32_t w = 0; w < n_items; w++) {
+        WorkItem it;
+        it.spec = i;
+        it.first_cell = w * item_cells;
+        a.items[item0 + my_item + w] = it;
+      }
+      a.hdrs[i].row_base = (temp_top + row0 + my_row) | MRL_TEMP_FLAG;
+      a.rmask[i] = make_uint4(1u, 1u, 1u, 1u);
+      a.dirty[i] = 2;   // solved by this pass
+      for (uint32_t w = 0; w < g.warps; w++) {
+        Chunk c;
+        c.spec = i;
+        c.col_start = (w * 32u) | (g.F << 30);
+        a.chunks[cb + w] = c;
+      }
+    }
+    __syncthreads();   // row0 / chunk0 / item0 are rewritten by the next round
+  }
+}
+
+// Pass step 3a: how many working cells lie on each limits diagonal. Warp per chunk, thread per column.
+__device__ __noinline__ void phase_histogram(const StageArgs& a, uint32_t n_chunks) {
   __shared__ uint32_t hist[MRL_MAX_DIAG];
-  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) hist[k] = 0;
+  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += kBlock) hist[k] = 0;
   __syncthreads();
-  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  if (warp < n_chunks) {
-    const Column c = decode_column(hdrs, chunks[warp], lane);
+  const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_chunks; w += gwarps) {
+    const Column c = decode_column(a.hdrs, a.chunks[w], lane);
+    if (!c.valid) continue;
+    for (uint32_t mrest = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F); mrest; mrest &= mrest - 1)
+      atomicAdd(&hist[(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
+  }
+  __syncthreads();
+  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += kBlock)
+    if (hist[k]) atomicAdd(&a.diag->count[k], hist[k]);
+}
+
+// Pass step 3b (one thread): where each diagonal's cells start in the list, and which diagonals
+// are occupied.
+__device__ void diag_layout(DiagTable* diag) {
+  unsigned long long run = 0;
+  uint32_t n = 0;
+  for (uint32_t d = 0; d < MRL_MAX_DIAG; d++) {
+    diag->base[d] = run;
+    diag->cursor[d] = 0;
+    diag->work[d] = 0;
+    const uint32_t c = diag->count[d];
+    if (c) diag->order[n++] = d;
+    run += c;
+  }
+  diag->n_occupied = n;
+}
+
+// Pass step 3c: lists the working cells diagonal by diagonal. Every warp counts its own cells
+// per diagonal; the block reserves list slots per diagonal with one atomic each and hands every
+// warp a contiguous piece, so that the cells one warp (one Spec) has on a diagonal stay
+// neighbours in the list - and neighbours in a combine warp.
+__device__ __noinline__ void phase_scatter(const StageArgs& a, uint32_t n_chunks) {
+  constexpr int W = kBlock / 32;
+  __shared__ uint32_t hist[W][MRL_MAX_DIAG];
+  __shared__ unsigned long long start[W][MRL_MAX_DIAG];
+  const uint32_t wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t n_groups = (n_chunks + W - 1) / W;
+  for (uint32_t g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    for (uint32_t k = threadIdx.x; k < W * MRL_MAX_DIAG; k += kBlock) hist[k / MRL_MAX_DIAG][k % MRL_MAX_DIAG] = 0;
+    __syncthreads();
+    const uint32_t warp = g * W + wib;
+    Column c;
+    c.valid = false;
+    if (warp < n_chunks) c = decode_column(a.hdrs, a.chunks[warp], lane);
+    const uint32_t mF = c.valid ? sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F) : 0u;
+    for (uint32_t mrest = mF; mrest; mrest &= mrest - 1)
+      atomicAdd(&hist[wib][(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
+    __syncthreads();
+    for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += kBlock) {
+      uint32_t n = 0;
+      for (int w = 0; w < W; w++) n += hist[w][k];
+      if (n) {
+        unsigned long long at = a.diag->base[k] + atomicAdd(&a.diag->cursor[k], n);
+        for (int w = 0; w < W; w++) { start[w][k] = at; at += hist[w][k]; }
+      }
+      for (int w = 0; w < W; w++) hist[w][k] = 0;   // become the warps' cursors
+    }
+    __syncthreads();
     if (c.valid) {
-      uint32_t mrest = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
-      while (mrest) {
+      // the fixed memories' codes, one per byte (RF in byte 0 .. GL in byte 3); the byte of F is 0
+      const uint32_t fixed = c.code[0] | (c.code[1] << 8) | (c.code[2] << 16) | (c.code[3] << 24);
+      for (uint32_t mrest = mF; mrest; mrest &= mrest - 1) {
+        const uint32_t codeF = __ffs(mrest) - 1;
+        const uint32_t d = (c.others + codeF) & (MRL_MAX_DIAG - 1);
+        const uint32_t pos = atomicAdd(&hist[wib][d], 1u);
+        CellRef r;
+        r.spec = c.spec;
+        r.cpack = fixed | (codeF << (8 * c.F));
+        a.cells[start[wib][d] + pos] = r;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// A candidate record whose body is a Spec of the same stage (a relayout Move): the planner flags
+// it and stores these records after all others, dearest first.
+__device__ __forceinline__ bool is_late(const uint4 a) { return (a.z >> 24) & 1u; }
+
+// Pass step 4a: the candidates whose children all lie in earlier stages, for every cell of every
+// Spec being solved. No order is needed. A warp takes a work item (up to MRL_ITEM_CELLS cells of one
+// Spec) at a time as it finishes others; its lanes take 32 cells at a time and walk the records
+// together: one record, the same child headers, neighbouring child rows.
+struct HotArgs {   // what the two solve phases read, by value: registers instead of the argument block in local memory
+  const SpecHdr* hdrs;
+  const CandRec* cands;
+  const MrlRow* rows;
+  MrlRow* temp;
+};
+__device__ __forceinline__ HotArgs hot_args(const StageArgs& s) {
+  HotArgs h;
+  h.hdrs = s.hdrs; h.cands = s.cands; h.rows = s.rows; h.temp = s.temp;
+  return h;
+}
+
+__device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items, uint32_t n_items, uint32_t item_cells,
+                                         uint32_t* next_item, unsigned long long* block_stats) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  Tally tally = {0, 0};
+  // every warp starts with the item of its own number; further items are handed out by a counter
+  // (no atomics at all when there are fewer items than warps)
+  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_items;) {
+    const WorkItem it = items[w];
+    const uint32_t i = it.spec;
+    const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+    const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+    MrlRow* const grid = a.temp + (a.hdrs[i].row_base & ~MRL_TEMP_FLAG);
+    const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
+    const uint32_t cells = n0 * n1 * n2 * n3;
+    const uint32_t c_end = min(cells, it.first_cell + item_cells);
+    for (uint32_t c0 = it.first_cell; c0 < c_end; c0 += 32) {
+      const uint32_t cell = c0 + lane;
+      const bool valid = cell < c_end;
+      uint32_t rest = valid ? cell : 0u;
+      const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
+      const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
+      const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
+      const uint32_t k3 = nth_set_bit(m.w, rest);
+      const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
+      const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
+      Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+      for (uint32_t ci = 0; ci < cl.y; ci++) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));   // the same for all lanes
+        if (is_late(c)) break;
+        if (valid) eval_candidate<true>(a.hdrs, a.cands, a.rows, a.temp, cl.x + ci, c, ci, cpack, bm0, bm1, bm2, bm3, best, tally);
+      }
+      if (valid) *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+    }
+    if (n_items <= gwarps) break;
+    if (lane == 0) w = gwarps + atomicAdd(next_item, 1u);
+    w = __shfl_sync(0xFFFFFFFFu, w, 0);
+  }
+  uint32_t tc = tally.cands, tl = tally.lookups;
+  for (int o = 16; o > 0; o >>= 1) {
+    tc += __shfl_xor_sync(0xFFFFFFFFu, tc, o);
+    tl += __shfl_xor_sync(0xFFFFFFFFu, tl, o);
+  }
+  if (lane == 0 && (tc | tl)) {
+    atomicAdd(&block_stats[0], (unsigned long long)tc);
+    atomicAdd(&block_stats[1], (unsigned long long)tl);
+  }
+}
+
+// Pass step 4b, one diagonal: the candidates with a same-stage child, one thread per listed cell,
+// on top of what phase_early left in the cell. Every cell such a candidate reads lies on a lower
+// diagonal. The records come dearest first and are walked from the end, so the cheapest Move is
+// tried first and a Move whose base cost alone exceeds the cell's optimum ends the walk.
+__device__ __noinline__ void phase_combine(const HotArgs a, const CellRef* list, uint32_t n_cells, uint32_t* next_cell,
+                                           unsigned long long* block_stats) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  const uint32_t gwarp = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
+  Tally tally = {0, 0};
+  if (n_cells <= gwarps * 4u) {
+    // A small diagonal lasts as long as one cell's chain of dependent loads: 8 lanes share a cell,
+    // each takes every 8th record of the walk, and the group min-reduces with shuffles.
+    const uint32_t t = gwarp * 4u + (lane >> 3), sub = lane & 7u;
+    const bool valid = t < n_cells;
+    Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+    MrlRow* out = nullptr;
+    uint32_t was = MRL_UNSAT;
+    if (valid) {
+      const CellRef ref = list[t];
+      const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[ref.spec].cand_off);
+      const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[ref.spec]);
+      MrlRow* const grid = a.temp + (a.hdrs[ref.spec].row_base & ~MRL_TEMP_FLAG);
+      const uint32_t bm0 = below(code_of(ref.cpack, 0)), bm1 = below(code_of(ref.cpack, 1)),
+                     bm2 = below(code_of(ref.cpack, 2)), bm3 = below(code_of(ref.cpack, 3));
+      const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+      const uint32_t i0 = __popc(m.x & bm0) - 1, i1 = __popc(m.y & bm1) - 1, i2 = __popc(m.z & bm2) - 1,
+                     i3 = __popc(m.w & bm3) - 1;
+      out = grid + (((i3 * n2 + i2) * n1 + i1) * n0 + i0);
+      const uint4 r = *reinterpret_cast<const uint4*>(out);
+      best.main = r.x; best.peaks = r.y; best.tail = r.z; best.ci = r.w;
+      was = r.w;
+      for (uint32_t back = sub; back < cl.y; back += 8) {
+        const uint32_t ci = cl.y - 1 - back;
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+        if (!is_late(c) || c.y > best.main) break;   // later steps of this lane's walk are dearer still, or not late
+        eval_candidate<false>(a.hdrs, a.cands, a.rows, a.temp, cl.x + ci, c, ci, ref.cpack, bm0, bm1, bm2, bm3, best, tally);
+      }
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      Best other;
+      other.main = __shfl_xor_sync(0xFFFFFFFFu, best.main, o);
+      other.peaks = __shfl_xor_sync(0xFFFFFFFFu, best.peaks, o);
+      other.tail = __shfl_xor_sync(0xFFFFFFFFu, best.tail, o);
+      other.ci = __shfl_xor_sync(0xFFFFFFFFu, best.ci, o);
+      if (key_less(other.main, other.peaks, other.tail, best)) best = other;
+    }
+    if (valid && sub == 0 && best.ci != was) *reinterpret_cast<uint4*>(out) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+  } else {
+    // Cells a warp takes at a time: an even share of the diagonal in whole warp-wide steps, at most
+    // 64. Every warp starts with the piece of its own number; what a large diagonal has beyond
+    // that is handed out by a counter.
+    const uint32_t grab = min(64u, max(32u, ((n_cells + gwarps - 1) / gwarps + 31u) & ~31u));
+    const bool more = (unsigned long long)gwarps * grab < n_cells;
+    for (uint32_t g0 = gwarp * grab; g0 < n_cells;) {
+      const uint32_t g1 = min(n_cells, g0 + grab);
+      for (uint32_t t = g0 + lane; t < g1; t += 32) {
+        const CellRef ref = list[t];
+        const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[ref.spec].cand_off);
+        if (cl.y == 0) continue;
+        uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + cl.y - 1]));
+        if (!is_late(c)) continue;   // nothing in this Spec depends on the stage itself
+        const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[ref.spec]);
+        MrlRow* const grid = a.temp + (a.hdrs[ref.spec].row_base & ~MRL_TEMP_FLAG);   // Specs being solved live in the working rows
+        const uint32_t bm0 = below(code_of(ref.cpack, 0)), bm1 = below(code_of(ref.cpack, 1)),
+                       bm2 = below(code_of(ref.cpack, 2)), bm3 = below(code_of(ref.cpack, 3));
+        // the cell's place in its Spec's working grid: slot = breakpoints at or below the code, minus one
+        const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
+        const uint32_t i0 = __popc(m.x & bm0) - 1, i1 = __popc(m.y & bm1) - 1, i2 = __popc(m.z & bm2) - 1,
+                       i3 = __popc(m.w & bm3) - 1;
+        const uint32_t cell = ((i3 * n2 + i2) * n1 + i1) * n0 + i0;
+        const uint4 r = *reinterpret_cast<const uint4*>(grid + cell);
+        Best best = {r.x, r.y, r.z, r.w};
+        for (uint32_t ci = cl.y - 1;;) {
+          if (c.y > best.main) break;   // base cost of this Move and of every one before it in the records
+          eval_candidate<false>(a.hdrs, a.cands, a.rows, a.temp, cl.x + ci, c, ci, ref.cpack, bm0, bm1, bm2, bm3, best, tally);
+          if (ci == 0) break;
+          ci--;
+          c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+          if (!is_late(c)) break;
+        }
+        if (best.ci != r.w) *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+      }
+      if (!more) break;
+      if (lane == 0) g0 = gwarps * grab + atomicAdd(next_cell, grab);
+      g0 = __shfl_sync(0xFFFFFFFFu, g0, 0);
+    }
+  }
+  uint32_t tc = tally.cands, tl = tally.lookups;
+  for (int o = 16; o > 0; o >>= 1) {
+    tc += __shfl_xor_sync(0xFFFFFFFFu, tc, o);
+    tl += __shfl_xor_sync(0xFFFFFFFFu, tl, o);
+  }
+  if (lane == 0 && (tc | tl)) {
+    atomicAdd(&block_stats[0], (unsigned long long)tc);
+    atomicAdd(&block_stats[1], (unsigned long long)tl);
+  }
+}
+
+// Pass step 5: which breakpoints of the working grids are real. A breakpoint (memory k, code c)
+// is real when some cell starting at c differs from its neighbour one slot lower in k.
+__device__ __noinline__ void phase_real_masks(const StageArgs& a, uint32_t n_chunks) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_chunks; w += gwarps) {
+    const Chunk ch = a.chunks[w];
+    const Column c = decode_column(a.hdrs, ch, lane);
+    uint32_t bits[4] = {0, 0, 0, 0};
+    if (c.valid) {
+      const unsigned long long base = a.hdrs[ch.spec].row_base & ~MRL_TEMP_FLAG;
+      const uint32_t st[4] = {1u, c.nn[0], c.nn[0] * c.nn[1], c.nn[0] * c.nn[1] * c.nn[2]};
+      const uint32_t mF = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
+      const uint32_t nF = sel4(c.nn[0], c.nn[1], c.nn[2], c.nn[3], c.F);
+      const uint32_t stF = sel4(st[0], st[1], st[2], st[3], c.F);
+      uint32_t off0 = 0;
+#pragma unroll
+      for (int k = 0; k < 4; k++) off0 += c.idx[k] * st[k];   // idx[F] is 0
+      uint4 prev = make_uint4(0, 0, 0, 0);
+      uint32_t fbits = 0, mrest = mF;
+      for (uint32_t s = 0; s < nF; s++) {
         const uint32_t codeF = __ffs(mrest) - 1;
         mrest &= mrest - 1;
-        atomicAdd(&hist[(c.others + codeF) & (MRL_MAX_DIAG - 1)], 1u);
+        const unsigned long long r_at = base + off0 + (unsigned long long)s * stF;
+        const uint4 r = *reinterpret_cast<const uint4*>(a.temp + r_at);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          if ((uint32_t)k == c.F || c.idx[k] == 0) continue;
+          const uint4 nb = *reinterpret_cast<const uint4*>(a.temp + r_at - st[k]);
+          if (nb.x != r.x || nb.y != r.y || nb.z != r.z) bits[k] |= 1u << c.code[k];
+        }
+        if (s > 0 && (prev.x != r.x || prev.y != r.y || prev.z != r.z)) fbits |= 1u << codeF;
+        prev = r;
       }
-    }
-  }
-  __syncthreads();
-  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x)
-    if (hist[k]) atomicAdd(&diag->count[k], hist[k]);
-}
-
-// Pass step 3b: lists the working cells diagonal by diagonal (diag->base set by the host from the
-// histogram). Every warp counts its own cells per diagonal; the block reserves list slots per
-// diagonal with one atomic each and hands every warp a contiguous piece, so that the cells one
-// warp (one Spec) has on a diagonal stay neighbours in the list - and neighbours in a combine warp.
-__global__ void __launch_bounds__(128)
-scatter_cells_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
-                     DiagTable* __restrict__ diag, CellRef* __restrict__ cells) {
-  __shared__ uint32_t hist[4][MRL_MAX_DIAG];
-  __shared__ unsigned long long start[4][MRL_MAX_DIAG];
-  for (uint32_t k = threadIdx.x; k < 4 * MRL_MAX_DIAG; k += blockDim.x) hist[k / MRL_MAX_DIAG][k % MRL_MAX_DIAG] = 0;
-  __syncthreads();
-  const uint32_t wib = threadIdx.x >> 5;   // warp in block
-  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const uint32_t lane = threadIdx.x & 31;
-  Column c;
-  c.valid = false;
-  if (warp < n_chunks) c = decode_column(hdrs, chunks[warp], lane);
-  const uint32_t mF = c.valid ? sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F) : 0u;
-  for (uint32_t mrest = mF; mrest; mrest &= mrest - 1)
-    atomicAdd(&hist[wib][(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
-  __syncthreads();
-  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += blockDim.x) {
-    const uint32_t n0 = hist[0][k], n1 = hist[1][k], n2 = hist[2][k], n3 = hist[3][k];
-    const uint32_t n = n0 + n1 + n2 + n3;
-    if (n) {
-      const unsigned long long base = diag->base[k] + atomicAdd(&diag->cursor[k], n);
-      start[0][k] = base;
-      start[1][k] = base + n0;
-      start[2][k] = base + n0 + n1;
-      start[3][k] = base + n0 + n1 + n2;
-    }
-    hist[0][k] = hist[1][k] = hist[2][k] = hist[3][k] = 0;   // become the warps' cursors
-  }
-  __syncthreads();
-  if (!c.valid) return;
-  // the fixed memories' codes, one per byte (RF in byte 0 .. GL in byte 3); the byte of F is 0
-  const uint32_t fixed = c.code[0] | (c.code[1] << 8) | (c.code[2] << 16) | (c.code[3] << 24);
-  for (uint32_t mrest = mF; mrest; mrest &= mrest - 1) {
-    const uint32_t codeF = __ffs(mrest) - 1;
-    const uint32_t d = (c.others + codeF) & (MRL_MAX_DIAG - 1);
-    const uint32_t pos = atomicAdd(&hist[wib][d], 1u);
-    CellRef r;
-    r.spec = c.spec;
-    r.cpack = fixed | (codeF << (8 * c.F));
-    cells[start[wib][d] + pos] = r;
-  }
-}
-
-// Pass step 4: which breakpoints of the working grids are real. A breakpoint (memory k, code c)
-// is real when some cell starting at c differs from its neighbour one slot lower in k.
-__global__ void __launch_bounds__(128)
-real_masks_kernel(const SpecHdr* __restrict__ hdrs, const Chunk* __restrict__ chunks, uint32_t n_chunks,
-                  const MrlRow* __restrict__ temp, uint4* __restrict__ rmask) {
-  const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const uint32_t lane = threadIdx.x & 31;
-  if (warp >= n_chunks) return;   // whole warps leave together
-  const Chunk ch = chunks[warp];
-  const Column c = decode_column(hdrs, ch, lane);
-  uint32_t bits[4] = {0, 0, 0, 0};
-  if (c.valid) {
-    const unsigned long long base = hdrs[ch.spec].row_base & ~MRL_TEMP_FLAG;
-    const uint32_t st[4] = {1u, c.nn[0], c.nn[0] * c.nn[1], c.nn[0] * c.nn[1] * c.nn[2]};
-    const uint32_t mF = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
-    const uint32_t nF = sel4(c.nn[0], c.nn[1], c.nn[2], c.nn[3], c.F);
-    const uint32_t stF = sel4(st[0], st[1], st[2], st[3], c.F);
-    uint32_t off0 = 0;
 #pragma unroll
-    for (int k = 0; k < 4; k++) off0 += c.idx[k] * st[k];   // idx[F] is 0
-    uint4 prev = make_uint4(0, 0, 0, 0);
-    uint32_t fbits = 0, mrest = mF;
-    for (uint32_t s = 0; s < nF; s++) {
-      const uint32_t codeF = __ffs(mrest) - 1;
-      mrest &= mrest - 1;
-      const unsigned long long r_at = base + off0 + (unsigned long long)s * stF;
-      const uint4 r = *reinterpret_cast<const uint4*>(temp + r_at);
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        if ((uint32_t)k == c.F || c.idx[k] == 0) continue;
-        const uint4 nb = *reinterpret_cast<const uint4*>(temp + r_at - st[k]);
-        if (nb.x != r.x || nb.y != r.y || nb.z != r.z) bits[k] |= 1u << c.code[k];
-      }
-      if (s > 0 && (prev.x != r.x || prev.y != r.y || prev.z != r.z)) fbits |= 1u << codeF;
-      prev = r;
+      for (int k = 0; k < 4; k++)
+        if ((uint32_t)k == c.F) bits[k] = fbits;
     }
 #pragma unroll
-    for (int k = 0; k < 4; k++)
-      if ((uint32_t)k == c.F) bits[k] = fbits;
-  }
+    for (int k = 0; k < 4; k++) bits[k] = __reduce_or_sync(0xFFFFFFFFu, bits[k]);
+    if (lane == 0) {
+      uint32_t* out = reinterpret_cast<uint32_t*>(&a.rmask[ch.spec]);
 #pragma unroll
-  for (int k = 0; k < 4; k++) bits[k] = __reduce_or_sync(0xFFFFFFFFu, bits[k]);
-  if (lane == 0) {
-    uint32_t* out = reinterpret_cast<uint32_t*>(&rmask[ch.spec]);
-#pragma unroll
-    for (int k = 0; k < 4; k++)
-      if (bits[k]) atomicOr(out + k, bits[k]);
+      for (int k = 0; k < 4; k++)
+        if (bits[k]) atomicOr(out + k, bits[k]);
+    }
   }
 }
 
 // ---- compaction: working grids -> final table ---------------------------------------------
 
-// Final cell count per Spec of the stage and the sum per block of 256 Specs.
-__global__ void __launch_bounds__(256)
-final_count_kernel(const uint4* __restrict__ rmask, uint32_t lo, uint32_t hi, uint32_t* __restrict__ fcount,
-                   unsigned long long* __restrict__ block_sums) {
-  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  unsigned long long n = 0;
-  if (i < hi) {
-    const uint4 m = rmask[i];
-    n = (unsigned long long)__popc(m.x) * __popc(m.y) * __popc(m.z) * __popc(m.w);
-    fcount[i - lo] = (uint32_t)n;
+// Final cell count per Spec of the stage, the sum per run of kBlock Specs, and the algorithmic
+// bytes of the stage's final rows.
+__device__ __noinline__ void phase_final_count(const StageArgs& a) {
+  unsigned long long bytes = 0;
+  for (uint32_t base = a.lo + blockIdx.x * kBlock; base < a.hi; base += gridDim.x * kBlock) {
+    const uint32_t i = base + threadIdx.x;
+    unsigned long long n = 0;
+    if (i < a.hi) {
+      const uint4 m = a.rmask[i];
+      n = (unsigned long long)__popc(m.x) * __popc(m.y) * __popc(m.z) * __popc(m.w);
+      a.fcount[i - a.lo] = (uint32_t)n;
+      if (computed_here(a, i)) {
+        const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+        bytes += n * (12ull + 16ull * cl.y);
+        for (uint32_t ci = 0; ci < cl.y; ci++) {
+          const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+          const uint32_t kind = (c.x >> 16) & 0xFFu, nchild = c.x >> 24;
+          if (!nchild) continue;
+          unsigned long long feasible = n;
+          if (kind == MRL_CK_MOVE) {
+            const uint32_t ml = sel4(m.x, m.y, m.z, m.w, c.z & 0xFFu), thr = (c.z >> 8) & 0xFFu;
+            feasible = n / (uint32_t)__popc(ml) * (uint32_t)__popc(ml >> thr);   // final cells at or above the threshold
+          }
+          bytes += feasible * nchild * 16ull;
+        }
+      }
+    }
+    unsigned long long total;
+    block_excl_scan(n, &total);
+    if (threadIdx.x == 0) a.block_sums[(base - a.lo) / kBlock] = total;
   }
-  unsigned long long total;
-  block_excl_scan(n, &total);
-  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+  for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xFFFFFFFFu, bytes, o);
+  if ((threadIdx.x & 31) == 0 && bytes) atomicAdd(&a.ctl->st_final_bytes, bytes);
 }
 
-// Exclusive scan of the block sums (one block), and the stage's place in the table:
-// stage_info[0] = first final row of the stage, stage_info[1] = its row count.
-__global__ void __launch_bounds__(256)
-scan_block_sums_kernel(unsigned long long* __restrict__ block_sums, uint32_t n_blocks,
-                       unsigned long long* __restrict__ final_top, unsigned long long* __restrict__ stage_info) {
+// Exclusive scan of the run sums (one block), and the stage's place in the table.
+__device__ __noinline__ void phase_scan_sums(const StageArgs& a) {
+  const uint32_t n_runs = (a.hi - a.lo + kBlock - 1) / kBlock;
   unsigned long long carry = 0;
-  for (uint32_t b0 = 0; b0 < n_blocks; b0 += 256) {
+  for (uint32_t b0 = 0; b0 < n_runs; b0 += kBlock) {
     const uint32_t b = b0 + threadIdx.x;
-    const unsigned long long v = b < n_blocks ? block_sums[b] : 0ull;
+    const unsigned long long v = b < n_runs ? a.block_sums[b] : 0ull;
     unsigned long long total;
     const unsigned long long ex = block_excl_scan(v, &total);
-    if (b < n_blocks) block_sums[b] = carry + ex;
+    if (b < n_runs) a.block_sums[b] = carry + ex;
     carry += total;
   }
   if (threadIdx.x == 0) {
-    stage_info[0] = *final_top;
-    stage_info[1] = carry;
-    *final_top += carry;
+    FillCtl* ctl = a.ctl;
+    ctl->stage_first_row = ctl->final_top;
+    ctl->stage_rows = carry;
+    if (ctl->final_top + carry > a.row_cap) {
+      if (!ctl->error) ctl->failed_stage = a.stage;
+      ctl->error |= MRL_ERR_TABLE;
+      ctl->need_rows = ctl->final_top + carry;
+    } else {
+      ctl->final_top += carry;
+    }
   }
 }
 
 // Copies each Spec's real cells from its working grid to its final rows and repoints the header.
 // Specs computed by another rank get zero rows (the exchange adds the owner's rows onto them).
-__global__ void __launch_bounds__(256)
-compact_kernel(SpecHdr* __restrict__ hdrs, const uint4* __restrict__ rmask, const uint8_t* __restrict__ mine,
-               uint32_t lo, uint32_t hi, const uint32_t* __restrict__ fcount,
-               const unsigned long long* __restrict__ block_sums, const unsigned long long* __restrict__ stage_info,
-               MrlRow* __restrict__ rows, unsigned long long row_cap, const MrlRow* __restrict__ temp,
-               PassCounters* __restrict__ ctr) {
-  const uint32_t i = lo + blockIdx.x * blockDim.x + threadIdx.x;
-  const unsigned long long n = i < hi ? fcount[i - lo] : 0u;
-  unsigned long long total;
-  const unsigned long long ex = block_excl_scan(n, &total);
-  if (i >= hi) return;
-  const unsigned long long fbase = stage_info[0] + block_sums[blockIdx.x] + ex;
-  if (fbase + n > row_cap) { atomicOr(&ctr->error, 4u); return; }
-  const uint4 fm = rmask[i];
-  if (!mine || mine[i]) {
-    const uint4 tm = *reinterpret_cast<const uint4*>(&hdrs[i]);
-    const unsigned long long tbase = hdrs[i].row_base & ~MRL_TEMP_FLAG;
-    const uint32_t f0 = __popc(fm.x), f1 = __popc(fm.y), f2 = __popc(fm.z);
-    const uint32_t t0 = __popc(tm.x), t1 = __popc(tm.y), t2 = __popc(tm.z);
-    for (uint32_t j = 0; j < (uint32_t)n; j++) {
-      uint32_t rest = j;
-      const uint32_t j0 = rest % f0; rest /= f0;
-      const uint32_t j1 = rest % f1; rest /= f1;
-      const uint32_t j2 = rest % f2; rest /= f2;
-      const uint32_t j3 = rest;
-      const uint32_t i0 = __popc(tm.x & ((2u << nth_set_bit(fm.x, j0)) - 1u)) - 1;
-      const uint32_t i1 = __popc(tm.y & ((2u << nth_set_bit(fm.y, j1)) - 1u)) - 1;
-      const uint32_t i2 = __popc(tm.z & ((2u << nth_set_bit(fm.z, j2)) - 1u)) - 1;
-      const uint32_t i3 = __popc(tm.w & ((2u << nth_set_bit(fm.w, j3)) - 1u)) - 1;
-      const uint32_t toff = ((i3 * t2 + i2) * t1 + i1) * t0 + i0;
-      *reinterpret_cast<uint4*>(rows + fbase + j) = *reinterpret_cast<const uint4*>(temp + tbase + toff);
+__device__ __noinline__ void phase_compact(const StageArgs& a) {
+  const unsigned long long first_row = a.ctl->stage_first_row;
+  for (uint32_t base = a.lo + blockIdx.x * kBlock; base < a.hi; base += gridDim.x * kBlock) {
+    const uint32_t i = base + threadIdx.x;
+    const unsigned long long n = i < a.hi ? a.fcount[i - a.lo] : 0u;
+    unsigned long long total;
+    const unsigned long long ex = block_excl_scan(n, &total);
+    if (i >= a.hi) continue;
+    const unsigned long long fbase = first_row + a.block_sums[(base - a.lo) / kBlock] + ex;
+    const uint4 fm = a.rmask[i];
+    if (computed_here(a, i)) {
+      const uint4 tm = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+      const unsigned long long tbase = a.hdrs[i].row_base & ~MRL_TEMP_FLAG;
+      const uint32_t f0 = __popc(fm.x), f1 = __popc(fm.y), f2 = __popc(fm.z);
+      const uint32_t t0 = __popc(tm.x), t1 = __popc(tm.y), t2 = __popc(tm.z);
+      for (uint32_t j = 0; j < (uint32_t)n; j++) {
+        uint32_t rest = j;
+        const uint32_t j0 = rest % f0; rest /= f0;
+        const uint32_t j1 = rest % f1; rest /= f1;
+        const uint32_t j2 = rest % f2; rest /= f2;
+        const uint32_t j3 = rest;
+        const uint32_t i0 = __popc(tm.x & below(nth_set_bit(fm.x, j0))) - 1;
+        const uint32_t i1 = __popc(tm.y & below(nth_set_bit(fm.y, j1))) - 1;
+        const uint32_t i2 = __popc(tm.z & below(nth_set_bit(fm.z, j2))) - 1;
+        const uint32_t i3 = __popc(tm.w & below(nth_set_bit(fm.w, j3))) - 1;
+        const uint32_t toff = ((i3 * t2 + i2) * t1 + i1) * t0 + i0;
+        uint4 r = *reinterpret_cast<const uint4*>(a.temp + tbase + toff);
+        r.w = 0;
+        *reinterpret_cast<uint4*>(a.rows + fbase + j) = r;
+      }
+    } else {
+      for (uint32_t j = 0; j < (uint32_t)n; j++) *reinterpret_cast<uint4*>(a.rows + fbase + j) = make_uint4(0, 0, 0, 0);
     }
-  } else {
-    for (uint32_t j = 0; j < (uint32_t)n; j++) *reinterpret_cast<uint4*>(rows + fbase + j) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(&a.hdrs[i]) = fm;
+    a.hdrs[i].row_base = fbase;
   }
-  *reinterpret_cast<uint4*>(&hdrs[i]) = fm;
-  hdrs[i].row_base = fbase;
+}
+
+// One stage, start to finish, in one cooperative launch. Every thread of the grid reaches every
+// barrier: what decides the control flow (pass totals, the closure epoch, the occupied
+// diagonals, the error word) is read from device memory after a barrier and written again only
+// after a later one, so all threads take the same branches.
+__global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  const uint32_t gtid = blockIdx.x * kBlock + threadIdx.x;
+  const uint32_t gthreads = gridDim.x * kBlock;
+  FillCtl* const ctl = a.ctl;
+  uint32_t syncs = 0;
+#define GRID_SYNC() do { grid.sync(); syncs++; } while (0)
+  if (ctl->error) return;   // an earlier stage failed: the host repairs and resumes (uniform: nothing writes it before the first barrier)
+  __shared__ unsigned long long block_stats[2];   // candidates evaluated, rows gathered
+  if (threadIdx.x < 2) block_stats[threadIdx.x] = 0;
+  __syncthreads();
+  if (a.solve) {
+    if (gtid == 0) {
+      ctl->cells = ctl->warps = ctl->row_cursor = 0;
+      ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
+      ctl->spread_epoch = 0;
+      ctl->temp_top = 0;
+      ctl->all_cells = 0;
+    }
+    if (a.mine)
+      for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) a.rmask[i] = make_uint4(0, 0, 0, 0);   // other ranks' Specs: zero until the exchange
+    for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) a.dirty[i] = 0;
+    GRID_SYNC();
+    uint32_t epoch = 0;
+    unsigned long long combine_ns = 0, early_ns = 0;
+    bool failed = false;
+    for (int pass = 0;; pass++) {
+      if (pass >= kMaxPasses) { failed = true; if (gtid == 0) { ctl->failed_stage = a.stage; ctl->error |= MRL_ERR_PASSES; } break; }
+      // masks: the first pass knows nothing about same-stage children and seeds their breakpoints
+      // one hop deep with their own first masks (a third fewer passes for a tenth more cells);
+      // later passes add the real breakpoints the previous passes found in them.
+      phase_derive(a, gtid, gthreads, pass == 0, pass == 0 ? 0 : 1, pass == 0);
+      GRID_SYNC();
+      if (pass == 0) {
+        phase_derive(a, gtid, gthreads, 0, 1, 0);
+        GRID_SYNC();
+      } else {
+        // close the marks under "has a marked same-stage child"
+        for (;;) {
+          epoch++;
+          phase_spread(a, gtid, gthreads, epoch);
+          GRID_SYNC();
+          if (ctl->spread_epoch != epoch) break;
+        }
+      }
+      phase_totals(a, gtid, gthreads);
+      GRID_SYNC();
+      const unsigned long long cells = ctl->cells, warps = ctl->warps, temp_top = ctl->temp_top;
+      // Work items of the unordered phase: an even share of the pass's cells per warp, in whole
+      // warp-wide steps, at most MRL_ITEM_CELLS; every Spec adds at most one partial item.
+      const uint32_t gwarps = gridDim.x * (kBlock / 32);
+      const uint32_t item_cells = (uint32_t)min((unsigned long long)MRL_ITEM_CELLS, max(32ull, ((cells + gwarps - 1) / gwarps + 31ull) & ~31ull));
+      const unsigned long long max_items = cells / item_cells + (a.hi - a.lo);
+      if (cells == 0) break;   // nothing left to solve: every working grid is consistent
+      if (temp_top + cells > a.temp_cap || warps > a.chunk_cap || max_items > a.item_cap || cells > a.cell_cap ||
+          cells >= 0xFFFFFFF0ull || warps >= 0xFFFFFFF0ull) {
+        failed = true;
+        if (gtid == 0) {
+          ctl->failed_stage = a.stage;
+          ctl->error |= MRL_ERR_WORKING;
+          ctl->need_temp = temp_top + cells;
+          ctl->need_chunks = warps;
+          ctl->need_items = max_items;
+          ctl->need_cells = cells;
+        }
+        break;
+      }
+      phase_place(a, temp_top, item_cells);
+      for (uint32_t k = gtid; k < MRL_MAX_DIAG; k += gthreads) a.diag->count[k] = 0;
+      GRID_SYNC();
+      const uint32_t n_chunks = (uint32_t)warps;
+      phase_histogram(a, n_chunks);
+      GRID_SYNC();
+      if (gtid == 0) diag_layout(a.diag);
+      GRID_SYNC();
+      unsigned long long t0 = 0;
+      if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      phase_scatter(a, n_chunks);
+      phase_early(hot_args(a), a.items, ctl->item_cursor, item_cells, &ctl->item_next, block_stats);
+      GRID_SYNC();
+      if (gtid == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        early_ns += t1 - t0;
+      }
+      const uint32_t n_occ = a.diag->n_occupied;
+      for (uint32_t q = 0; q < n_occ; q++) {
+        const uint32_t d = a.diag->order[q];
+        phase_combine(hot_args(a), a.cells + a.diag->base[d], a.diag->count[d], &a.diag->work[d], block_stats);
+        GRID_SYNC();
+      }
+      if (gtid == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        combine_ns += t1 - t0;
+      }
+      phase_real_masks(a, n_chunks);
+      for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads)
+        if (a.dirty[i] == 2) a.dirty[i] = 0;
+      if (gtid == 0) {
+        ctl->temp_top = temp_top + cells;
+        ctl->st_cells += cells;
+        ctl->st_passes += 1;
+        ctl->cells = ctl->warps = ctl->row_cursor = 0;
+        ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
+        ctl->all_cells = 0;
+      }
+      GRID_SYNC();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && (block_stats[0] | block_stats[1])) {
+      atomicAdd(&ctl->st_cands, block_stats[0]);
+      atomicAdd(&ctl->st_lookups, block_stats[1]);
+    }
+    if (gtid == 0) { ctl->st_combine_ns += combine_ns; ctl->st_early_ns += early_ns; }
+    if (failed) {
+      if (gtid == 0) ctl->st_syncs += syncs;
+      return;   // uniform
+    }
+  }
+  if (a.place) {
+    phase_final_count(a);
+    GRID_SYNC();
+    if (blockIdx.x == 0) phase_scan_sums(a);
+    GRID_SYNC();
+    if (!(ctl->error & MRL_ERR_TABLE)) phase_compact(a);   // uniform: set by phase_scan_sums only
+  }
+  if (gtid == 0) ctl->st_syncs += syncs;
+#undef GRID_SYNC
+}
+
+// Consistency check of a finished table: at sampled (or all) points of the limits lattice, for
+// sampled (or all) Specs, the direct solve from the children's tables - every candidate record,
+// no re-use of neighbouring cells - must equal what the Spec's own table returns there. Every
+// point where that holds is a point where the table satisfies the defining recurrence of the
+// fill, whatever grid the table is stored on.
+__global__ void __launch_bounds__(kBlock)
+verify_points_kernel(const SpecHdr* hdrs, const CandRec* __restrict__ cands, const MrlRow* rows, uint32_t n_specs,
+                     uint32_t top_pack, unsigned long long first, unsigned long long count,
+                     unsigned long long total_points, unsigned long long seed, int exhaustive,
+                     unsigned long long* out /* [0] mismatches, [1] first bad sample */) {
+  const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const uint32_t e0 = code_of(top_pack, 0) + 1, e1 = code_of(top_pack, 1) + 1, e2 = code_of(top_pack, 2) + 1,
+                 e3 = code_of(top_pack, 3) + 1;
+  const unsigned long long per_spec = (unsigned long long)e0 * e1 * e2 * e3;
+  unsigned long long s = first + i;
+  if (!exhaustive) {
+    // splitmix64 of (seed, sample index): a point of the (Spec x lattice) product
+    unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (s + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    s = z % total_points;
+  }
+  const uint32_t spec = (uint32_t)(s / per_spec);
+  uint32_t p = (uint32_t)(s % per_spec);
+  const uint32_t c0 = p % e0; p /= e0;
+  const uint32_t c1 = p % e1; p /= e1;
+  const uint32_t c2 = p % e2;
+  const uint32_t c3 = p / e2;
+  const uint32_t cpack = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+  Tally tally = {0, 0};
+  const Best k = solve_point(hdrs, cands, rows, rows, spec, cpack, tally);
+  const uint4 r = lookup(hdrs, rows, rows, spec, below(c0), below(c1), below(c2), below(c3));
+  if (k.main != r.x || k.peaks != r.y || k.tail != r.z) {
+    atomicAdd(&out[0], 1ull);
+    atomicMin(&out[1], first + i);
+  }
 }
 
 // Point lookups for get: the row of (Spec id, packed limit codes), into a dense buffer.
-__global__ void lookup_rows_kernel(const SpecHdr* __restrict__ hdrs, const MrlRow* __restrict__ rows,
-                                   const uint2* __restrict__ queries, unsigned long long n, MrlRow* __restrict__ out) {
+__global__ void lookup_rows_kernel(const SpecHdr* hdrs, const MrlRow* rows, const uint2* __restrict__ queries,
+                                   unsigned long long n, MrlRow* __restrict__ out) {
   const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const uint2 q = queries[i];
-  const uint4 r = lookup(hdrs, rows, rows, q.x, (2u << code_of(q.y, 0)) - 1u, (2u << code_of(q.y, 1)) - 1u,
-                         (2u << code_of(q.y, 2)) - 1u, (2u << code_of(q.y, 3)) - 1u);
+  const uint4 r = lookup(hdrs, rows, rows, q.x, below(code_of(q.y, 0)), below(code_of(q.y, 1)), below(code_of(q.y, 2)),
+                         below(code_of(q.y, 3)));
   *reinterpret_cast<uint4*>(out + i) = r;
+}
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+// Sum over all Specs of a hash of (id, masks, rows in cell order). The sum commutes, and where a
+// Spec's rows lie in the table does not enter, so two fills of one plan agree however their
+// tables are laid out.
+__global__ void __launch_bounds__(kBlock)
+checksum_kernel(const SpecHdr* hdrs, const MrlRow* rows, uint32_t n_specs, unsigned long long* out) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned long long h = 0;
+  if (i < n_specs) {
+    const uint4 m = *reinterpret_cast<const uint4*>(&hdrs[i]);
+    const unsigned long long base = hdrs[i].row_base;
+    const unsigned long long n = (unsigned long long)__popc(m.x) * __popc(m.y) * __popc(m.z) * __popc(m.w);
+    h = mix64(0x9E3779B97F4A7C15ull * (i + 1ull));
+    h = mix64(h ^ (((unsigned long long)m.x << 32) | m.y));
+    h = mix64(h ^ (((unsigned long long)m.z << 32) | m.w));
+    for (unsigned long long j = 0; j < n; j++) {
+      const uint4 r = *reinterpret_cast<const uint4*>(rows + base + j);
+      h = mix64(h ^ (((unsigned long long)r.x << 32) | r.y));
+      h = mix64(h ^ r.z);
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) h += __shfl_xor_sync(0xFFFFFFFFu, h, o);
+  if ((threadIdx.x & 31) == 0 && h) atomicAdd(out, h);
+}
+
+// Candidate records that arrived on the device without passing through this host's planner:
+// every field a kernel indexes with must be in range.
+__global__ void __launch_bounds__(kBlock)
+check_records_kernel(const SpecHdr* hdrs, const CandRec* __restrict__ cands, uint32_t n_specs, unsigned long long n_cands,
+                     uint32_t* error) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_specs) return;
+  const uint2 cl = *reinterpret_cast<const uint2*>(&hdrs[i].cand_off);
+  bool bad = (unsigned long long)cl.x + cl.y > n_cands;
+  for (uint32_t ci = 0; ci < cl.y && !bad; ci++) {
+    const CandRec c = cands[cl.x + ci];
+    bad = c.kind > MRL_CK_BLOCK || c.nchild > 3 || c.level > 3 || c.thr_code > 30 || c.peak_code > 31 || c.late > 1 ||
+          (c.kind == MRL_CK_LEAF) != (c.nchild == 0);
+    for (uint32_t j = 0; j < c.nchild && !bad; j++) bad = c.child[j] >= n_specs;
+  }
+  if (bad) atomicOr(error, (uint32_t)MRL_ERR_CHILD);
 }
 
 }  // namespace
@@ -808,21 +1172,28 @@ static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 DeviceFill::~DeviceFill() { release(); }
 
+int DeviceFill::too_large_() {
+  snprintf(err_, sizeof(err_),
+           "this fill needs more than the %zu bytes of device memory the no-allocation entry point has; "
+           "use mrl_top_down_many for it", buf_bytes_);
+  return -5;
+}
+
 int DeviceFill::alloc_(void** p, size_t bytes) {
   bytes = std::max<size_t>(bytes, 256);
   if (fixed_) {
     const size_t off = align256(buf_off_);
-    if (off + bytes > buf_bytes_) {
-      snprintf(err_, sizeof(err_),
-               "this fill needs more than the %zu bytes of device memory the no-allocation entry point has; "
-               "use mrl_top_down_many for it", buf_bytes_);
-      return -4;
-    }
+    if (off + bytes > buf_bytes_) return too_large_();
     *p = buf_ + off;
     buf_off_ = off + bytes;
     return 0;
   }
-  CK(cudaMalloc(p, bytes));
+  cudaError_t e = cudaMalloc(p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    snprintf(err_, sizeof(err_), "out of device memory: cudaMalloc of %zu bytes failed (%s)", bytes, cudaGetErrorString(e));
+    return -6;
+  }
   return 0;
 }
 
@@ -832,18 +1203,18 @@ void DeviceFill::free_(void* p) {
 
 void DeviceFill::release() {
   wait_upload();
-  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
-  d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_rows_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_); free_(d_cells_);
+  free_(d_diag_); free_(d_dirty_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr;
+  d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctl_ = nullptr;
   d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
-  row_cap_ = temp_cap_ = chunk_cap_ = cell_cap_ = 0;
+  row_cap_ = temp_cap_ = chunk_cap_ = item_cap_ = cell_cap_ = 0;
   buf_off_ = 0;
-  if (h_ctr_) { cudaFreeHost(h_ctr_); h_ctr_ = nullptr; }
-  if (h_diag_) { cudaFreeHost(h_diag_); h_diag_ = nullptr; }
-  for (cudaEvent_t e : ev_pool_) cudaEventDestroy(e);
-  ev_pool_.clear();
+  cands_present_ = false;
+  if (h_ctl_ && h_ctl_ != &ctl_pageable_) cudaFreeHost(h_ctl_);
+  h_ctl_ = nullptr;
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
   ev0_ = ev1_ = nullptr;
@@ -863,13 +1234,15 @@ int DeviceFill::init(int device) {
 }
 
 int DeviceFill::init_events() {
-  stage_log_ = getenv("MRL_STAGE_LOG") != nullptr;
-  if (const char* e = getenv("MRL_SEED_HOPS")) seed_hops_ = std::max(0, std::min(8, atoi(e)));
-  // For profilers started with capture off (ncu --profile-from-start off): only combine launches
-  // with at least this many cells are bracketed by cudaProfilerStart / Stop.
-  if (const char* e = getenv("MRL_PROFILE_MIN_CELLS")) profile_min_cells_ = (uint32_t)strtoul(e, nullptr, 10);
   if (!ev0_) CK(cudaEventCreate(&ev0_));
   if (!ev1_) CK(cudaEventCreate(&ev1_));
+  int coop = 0, per_sm = 0;
+  CK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device_));
+  CK(cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, device_));
+  if (!coop) { snprintf(err_, sizeof(err_), "the device does not support cooperative launches"); return -1; }
+  CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stage_kernel, kBlock, 0));
+  if (per_sm < 1) { snprintf(err_, sizeof(err_), "the stage kernel does not fit an SM"); return -1; }
+  coop_blocks_ = per_sm * n_sm_;
   return 0;
 }
 
@@ -915,377 +1288,272 @@ int DeviceFill::wait_upload() { return wait_cands_(~uint64_t(0) >> 1); }
 int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaSetDevice(device_));
   wait_upload();   // of an earlier plan
-  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctr_); free_(d_stage_); free_(d_cells_); free_(d_diag_); free_(d_dirty_);
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr;
-  d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctr_ = nullptr;
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_rows_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_); free_(d_cells_);
+  free_(d_diag_); free_(d_dirty_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr;
+  d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctl_ = nullptr;
   d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
   buf_off_ = 0;
+  cands_present_ = false;
   n_specs_ = (uint32_t)plan.hdrs.size();
-  uint32_t max_stage = 1;
-  for (const Stage& st : plan.stages) max_stage = std::max(max_stage, st.spec_hi - st.spec_lo);
+  max_stage_ = 1;
+  for (const Stage& st : plan.stages) max_stage_ = std::max(max_stage_, st.spec_hi - st.spec_lo);
   int rc;
-  if ((rc = alloc_((void**)&d_ctr_, 256))) return rc;
+  if ((rc = alloc_((void**)&d_ctl_, 512))) return rc;
   if ((rc = alloc_((void**)&d_diag_, sizeof(DiagTable)))) return rc;
-  d_final_top_ = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(d_ctr_) + 64);
-  d_stage_info_ = d_final_top_ + 1;
   if ((rc = alloc_((void**)&d_hdrs_, plan.hdrs.size() * sizeof(SpecHdr)))) return rc;
   if ((rc = alloc_((void**)&d_cands_, plan.cands.size() * sizeof(CandRec)))) return rc;
   if ((rc = alloc_((void**)&d_rmask_, plan.hdrs.size() * sizeof(uint4)))) return rc;
   if ((rc = alloc_((void**)&d_dirty_, plan.hdrs.size()))) return rc;
   if (!plan.mine.empty() && (rc = alloc_((void**)&d_mine_, plan.mine.size()))) return rc;
-  if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage * sizeof(uint32_t)))) return rc;
-  if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage / 256 + 1) * sizeof(unsigned long long)))) return rc;
+  if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
+  if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage_ / kBlock + 1) * sizeof(unsigned long long)))) return rc;
   if (fixed_) {
-    // Everything left is split once: lookup staging, chunks, working rows and final rows.
+    // Everything left is split once: lookup staging, chunks, cell list, working rows and final rows.
     stage_bytes_ = 64 << 10;
     if ((rc = alloc_(&d_stage_, stage_bytes_))) return rc;
-    const size_t left = buf_bytes_ > align256(buf_off_) + 1024 ? buf_bytes_ - align256(buf_off_) - 1024 : 0;
+    const size_t left = buf_bytes_ > align256(buf_off_) + 2048 ? buf_bytes_ - align256(buf_off_) - 2048 : 0;
     // per working cell: 16 bytes of row, 8 of cell list, under 1 of chunks; the rest is the table
-    chunk_cap_ = left / 32 / sizeof(Chunk);
+    chunk_cap_ = left / 64 / sizeof(Chunk);
     temp_cap_ = left * 14 / 32 / sizeof(MrlRow);
     cell_cap_ = left * 7 / 32 / sizeof(CellRef);
     row_cap_ = (left - left / 32 - left * 14 / 32 - left * 7 / 32) / sizeof(MrlRow);
-    if (chunk_cap_ == 0 || row_cap_ == 0) {
-      snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
-               "entry point has; use mrl_top_down_many for it", buf_bytes_);
-      return -4;
-    }
-    if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
-    if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
-    if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
-    if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
+    if (chunk_cap_ == 0 || row_cap_ == 0) return too_large_();
+    h_ctl_ = &ctl_pageable_;
   } else {
-    // Starting sizes from what fills of this kind ended with (about 40 table rows per Spec and
-    // 700 working cells per Spec of the largest stage at size 8), within a quarter of the free
-    // memory each; every buffer still grows on demand.
+    // Starting sizes from what fills of this kind ended with (about 40 table rows per Spec and 700
+    // working cells per Spec of the largest stage at size 8), within a share of the free memory
+    // each. A stage that needs more reports what it needs and is run again with larger buffers.
     size_t free_b = 0, total_b = 0;
     CK(cudaMemGetInfo(&free_b, &total_b));
-    const uint64_t quarter = free_b / 4;
-    chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)max_stage * 32);
-    temp_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage * 700, quarter / sizeof(MrlRow)));
-    cell_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage * 400, quarter / sizeof(CellRef)));
-    row_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)n_specs_ * 40, quarter / sizeof(MrlRow)));
-    if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
-    if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
-    if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
-    if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
-    if (!h_ctr_) CK(cudaHostAlloc((void**)&h_ctr_, 256, cudaHostAllocDefault));
-    if (!h_diag_) CK(cudaHostAlloc((void**)&h_diag_, sizeof(DiagTable), cudaHostAllocDefault));
+    const uint64_t share = free_b / 5;
+    chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)max_stage_ * 32);
+    temp_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage_ * 1000, share / sizeof(MrlRow)));
+    cell_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage_ * 600, share / sizeof(CellRef)));
+    row_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)n_specs_ * 40, share / sizeof(MrlRow)));
+    if (!h_ctl_) CK(cudaHostAlloc((void**)&h_ctl_, sizeof(FillCtl), cudaHostAllocDefault));
   }
+  if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
+  item_cap_ = chunk_cap_ * 2 + max_stage_;
+  if ((rc = alloc_((void**)&d_items_, item_cap_ * sizeof(WorkItem)))) return rc;
+  if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
+  if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
+  if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
   h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + (skip_cands ? 0 : plan.cands.size() * sizeof(CandRec)) + plan.mine.size();
-  CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
+  CK(cudaMemsetAsync(d_ctl_, 0, 512, stream_));
   if (!plan.hdrs.empty())
     CK(cudaMemcpyAsync(d_hdrs_, plan.hdrs.data(), plan.hdrs.size() * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
   n_cand_bytes_ = plan.cands.size() * sizeof(CandRec);
-  if (!plan.cands.empty() && !skip_cands) {
-    // The candidate records are gigabytes of pageable memory and one host thread stages about
-    // 11 GB/s, so four threads copy them on their own streams, piece by piece in id order, and
-    // go on after this call has returned (wait_cands_).
-    const size_t total = n_cand_bytes_;
-    if (fixed_ || total < (size_t(1) << 30)) {
-      CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), total, cudaMemcpyHostToDevice, stream_));
-    } else {
-      up_piece_bytes_ = size_t(128) << 20;
-      up_pieces_ = (total + up_piece_bytes_ - 1) / up_piece_bytes_;
-      up_done_.reset(new std::atomic<uint8_t>[up_pieces_]);
-      for (size_t k = 0; k < up_pieces_; k++) up_done_[k].store(0, std::memory_order_relaxed);
-      up_next_ = 0;
-      up_err_ = 0;
-      up_ready_ = 0;
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(plan.cands.data());
-      unsigned char* dst = reinterpret_cast<unsigned char*>(d_cands_);
-      for (int t = 0; t < 4; t++)
-        up_threads_.emplace_back([this, src, dst, total]() {
-          // Each thread stages through two small pinned buffers of its own: the copy into them
-          // is a plain memcpy outside the driver, and the transfer out of them is asynchronous,
-          // so the thread that launches the fill's kernels is not held up behind driver-side
-          // staging of pageable memory.
-          const size_t sub = size_t(8) << 20;
-          unsigned char* pin[2] = {nullptr, nullptr};
-          cudaEvent_t ev[2] = {nullptr, nullptr};
-          bool used[2] = {false, false};
-          cudaError_t e = cudaSetDevice(device_);
-          cudaStream_t st = nullptr;
-          if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
-          for (int b = 0; b < 2 && e == cudaSuccess; b++) {
-            e = cudaHostAlloc((void**)&pin[b], sub, cudaHostAllocDefault);
-            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev[b], cudaEventDisableTiming);
-          }
-          unsigned turn = 0;
-          while (e == cudaSuccess && up_err_.load(std::memory_order_relaxed) == 0) {
-            const size_t k = up_next_.fetch_add(1);
-            if (k >= up_pieces_) break;
-            const size_t lo = k * up_piece_bytes_, hi = std::min(total, lo + up_piece_bytes_);
-            for (size_t off = lo; off < hi && e == cudaSuccess; off += sub, turn++) {
-              const int b = turn & 1;
-              const size_t len = std::min(sub, hi - off);
-              if (used[b]) e = cudaEventSynchronize(ev[b]);   // the buffer's last transfer is done
-              if (e != cudaSuccess) break;
-              memcpy(pin[b], src + off, len);
-              e = cudaMemcpyAsync(dst + off, pin[b], len, cudaMemcpyHostToDevice, st);
-              if (e == cudaSuccess) e = cudaEventRecord(ev[b], st);
-              used[b] = true;
+  if (skip_cands) {
+    if (n_cand_bytes_) CK(cudaMemsetAsync(d_cands_, 0, n_cand_bytes_, stream_));   // defined until the caller's records arrive
+  } else {
+    cands_present_ = true;
+    if (!plan.cands.empty()) {
+      // The candidate records are gigabytes of pageable memory and one host thread stages about
+      // 11 GB/s, so four threads copy them on their own streams, piece by piece in id order, and
+      // go on after this call has returned (wait_cands_).
+      const size_t total = n_cand_bytes_;
+      if (fixed_ || total < (size_t(1) << 30)) {
+        CK(cudaMemcpyAsync(d_cands_, plan.cands.data(), total, cudaMemcpyHostToDevice, stream_));
+      } else {
+        up_piece_bytes_ = size_t(128) << 20;
+        up_pieces_ = (total + up_piece_bytes_ - 1) / up_piece_bytes_;
+        up_done_.reset(new std::atomic<uint8_t>[up_pieces_]);
+        for (size_t k = 0; k < up_pieces_; k++) up_done_[k].store(0, std::memory_order_relaxed);
+        up_next_ = 0;
+        up_err_ = 0;
+        up_ready_ = 0;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(plan.cands.data());
+        unsigned char* dst = reinterpret_cast<unsigned char*>(d_cands_);
+        for (int t = 0; t < 4; t++)
+          up_threads_.emplace_back([this, src, dst, total]() {
+            // Each thread stages through two small pinned buffers of its own: the copy into them
+            // is a plain memcpy outside the driver, and the transfer out of them is asynchronous,
+            // so the thread that launches the fill's kernels is not held up behind driver-side
+            // staging of pageable memory.
+            const size_t sub = size_t(8) << 20;
+            unsigned char* pin[2] = {nullptr, nullptr};
+            cudaEvent_t ev[2] = {nullptr, nullptr};
+            bool used[2] = {false, false};
+            cudaError_t e = cudaSetDevice(device_);
+            cudaStream_t st = nullptr;
+            if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+            for (int b = 0; b < 2 && e == cudaSuccess; b++) {
+              e = cudaHostAlloc((void**)&pin[b], sub, cudaHostAllocDefault);
+              if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev[b], cudaEventDisableTiming);
             }
-            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-            if (e == cudaSuccess) up_done_[k].store(1, std::memory_order_release);
-          }
-          if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
-          for (int b = 0; b < 2; b++) {
-            if (ev[b]) cudaEventDestroy(ev[b]);
-            if (pin[b]) cudaFreeHost(pin[b]);
-          }
-          if (e != cudaSuccess) {
-            int expect = 0;
-            up_err_.compare_exchange_strong(expect, (int)e);
-          }
-        });
+            unsigned turn = 0;
+            while (e == cudaSuccess && up_err_.load(std::memory_order_relaxed) == 0) {
+              const size_t k = up_next_.fetch_add(1);
+              if (k >= up_pieces_) break;
+              const size_t lo = k * up_piece_bytes_, hi = std::min(total, lo + up_piece_bytes_);
+              for (size_t off = lo; off < hi && e == cudaSuccess; off += sub, turn++) {
+                const int b = turn & 1;
+                const size_t len = std::min(sub, hi - off);
+                if (used[b]) e = cudaEventSynchronize(ev[b]);   // the buffer's last transfer is done
+                if (e != cudaSuccess) break;
+                memcpy(pin[b], src + off, len);
+                e = cudaMemcpyAsync(dst + off, pin[b], len, cudaMemcpyHostToDevice, st);
+                if (e == cudaSuccess) e = cudaEventRecord(ev[b], st);
+                used[b] = true;
+              }
+              if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+              if (e == cudaSuccess) up_done_[k].store(1, std::memory_order_release);
+            }
+            if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+            for (int b = 0; b < 2; b++) {
+              if (ev[b]) cudaEventDestroy(ev[b]);
+              if (pin[b]) cudaFreeHost(pin[b]);
+            }
+            if (e != cudaSuccess) {
+              int expect = 0;
+              up_err_.compare_exchange_strong(expect, (int)e);
+            }
+          });
+      }
     }
   }
   if (d_mine_) CK(cudaMemcpyAsync(d_mine_, plan.mine.data(), plan.mine.size(), cudaMemcpyHostToDevice, stream_));
   CK(cudaStreamSynchronize(stream_));
   stats_ = FillStats();
-  final_bound_ = 0;
   return 0;
 }
 
-int DeviceFill::read_counters_(PassCounters* out) {
-  if (h_ctr_) {
-    CK(cudaMemcpyAsync(h_ctr_, d_ctr_, sizeof(PassCounters) + 24, cudaMemcpyDeviceToHost, stream_));
+int DeviceFill::cands_arrived() {
+  CK(cudaSetDevice(device_));
+  if (cands_present_) return 0;
+  if (n_specs_) {
+    check_records_kernel<<<(n_specs_ + kBlock - 1) / kBlock, kBlock, 0, stream_>>>(d_hdrs_, d_cands_, n_specs_,
+                                                                                   n_cand_bytes_ / sizeof(CandRec), &d_ctl_->error);
+    CK(cudaGetLastError());
+  }
+  if (read_ctl_() != 0) return -1;
+  if (h_ctl_->error) {
+    CK(cudaMemsetAsync(&d_ctl_->error, 0, sizeof(uint32_t), stream_));
+    snprintf(err_, sizeof(err_), "the candidate records on the device do not describe this plan (a field is out of range)");
+    return -2;
+  }
+  cands_present_ = true;
+  return 0;
+}
+
+int DeviceFill::read_ctl_() {
+  CK(cudaMemcpyAsync(h_ctl_, d_ctl_, sizeof(FillCtl), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  return 0;
+}
+
+// After a stage asked for more room than a buffer had: enlarges what it named. Working buffers
+// hold nothing worth keeping between stages; the rows placed so far move along.
+int DeviceFill::grow_after_error_(uint32_t bits) {
+  if (fixed_) return too_large_();
+  CK(cudaStreamSynchronize(stream_));
+  auto regrow = [&](void** p, uint64_t* cap, uint64_t need, size_t elem) -> int {
+    if (need <= *cap) return 0;
+    cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    const uint64_t want = need + need / 4;
+    int rc = alloc_(p, want * elem);
+    if (rc) return rc;
+    *cap = want;
+    return 0;
+  };
+  int rc;
+  if (bits & MRL_ERR_WORKING) {
+    if ((rc = regrow((void**)&d_temp_, &temp_cap_, h_ctl_->need_temp, sizeof(MrlRow)))) return rc;
+    if ((rc = regrow((void**)&d_chunks_, &chunk_cap_, h_ctl_->need_chunks, sizeof(Chunk)))) return rc;
+    if ((rc = regrow((void**)&d_items_, &item_cap_, h_ctl_->need_items, sizeof(WorkItem)))) return rc;
+    if ((rc = regrow((void**)&d_cells_, &cell_cap_, h_ctl_->need_cells, sizeof(CellRef)))) return rc;
+  }
+  if (bits & MRL_ERR_TABLE) {
+    const uint64_t need = h_ctl_->need_rows;
+    size_t free_b = 0, total_b = 0;
+    CK(cudaMemGetInfo(&free_b, &total_b));
+    uint64_t cap = std::max<uint64_t>(need + need / 8, row_cap_ * 2);
+    if (cap * sizeof(MrlRow) + (1ull << 30) > free_b) cap = need + need / 16;
+    MrlRow* nr = nullptr;
+    if ((rc = alloc_((void**)&nr, cap * sizeof(MrlRow)))) {
+      snprintf(err_, sizeof(err_), "out of device memory: the table needs %llu rows", (unsigned long long)need);
+      return -6;
+    }
+    if (h_ctl_->final_top) CK(cudaMemcpyAsync(nr, d_rows_, h_ctl_->final_top * sizeof(MrlRow), cudaMemcpyDeviceToDevice, stream_));
     CK(cudaStreamSynchronize(stream_));
-    *out = *h_ctr_;
-    final_top_seen_ = reinterpret_cast<const unsigned long long*>(h_ctr_ + 1)[0];
-    stage_info_seen_[0] = reinterpret_cast<const unsigned long long*>(h_ctr_ + 1)[1];
-    stage_info_seen_[1] = reinterpret_cast<const unsigned long long*>(h_ctr_ + 1)[2];
-  } else {
-    unsigned char tmp[sizeof(PassCounters) + 24];
-    CK(cudaMemcpyAsync(tmp, d_ctr_, sizeof(tmp), cudaMemcpyDeviceToHost, stream_));
-    CK(cudaStreamSynchronize(stream_));
-    memcpy(out, tmp, sizeof(PassCounters));
-    unsigned long long v[3];
-    memcpy(v, tmp + sizeof(PassCounters), 24);
-    final_top_seen_ = v[0];
-    stage_info_seen_[0] = v[1];
-    stage_info_seen_[1] = v[2];
+    cudaFree(d_rows_);
+    d_rows_ = nr;
+    row_cap_ = cap;
   }
-  return 0;
-}
-
-// Makes room for `need` final rows; the rows placed so far move along.
-int DeviceFill::ensure_rows_(uint64_t need, bool refresh) {
-  if (need <= row_cap_) return 0;
-  if (refresh) {
-    // The bound on the rows placed so far may be loose: use the exact count before growing.
-    PassCounters c;
-    if (read_counters_(&c) != 0) return -1;
-    need = need - final_bound_ + final_top_seen_;
-    final_bound_ = final_top_seen_;
-    if (need <= row_cap_) return 0;
-  }
-  if (fixed_) {
-    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
-             "entry point has; use mrl_top_down_many for it", buf_bytes_);
-    return -4;
-  }
-  size_t free_b = 0, total_b = 0;
-  CK(cudaMemGetInfo(&free_b, &total_b));
-  uint64_t cap = std::max<uint64_t>(need, row_cap_ * 2);
-  if (cap * sizeof(MrlRow) + (1ull << 30) > free_b) cap = need;
-  if (cap * sizeof(MrlRow) + (256ull << 20) > free_b) {
-    snprintf(err_, sizeof(err_), "out of device memory: the table needs %llu rows", (unsigned long long)need);
-    return -6;
-  }
-  MrlRow* nr = nullptr;
-  CK(cudaMalloc((void**)&nr, cap * sizeof(MrlRow)));
-  if (final_bound_) CK(cudaMemcpyAsync(nr, d_rows_, final_bound_ * sizeof(MrlRow), cudaMemcpyDeviceToDevice, stream_));
-  CK(cudaStreamSynchronize(stream_));
-  cudaFree(d_rows_);
-  d_rows_ = nr;
-  row_cap_ = cap;
-  return 0;
-}
-
-// Room for `need` working rows; the first `keep` rows (grids of Specs that are not solved again
-// in this pass) move along.
-int DeviceFill::ensure_temp_(uint64_t need, uint64_t keep) {
-  if (need <= temp_cap_) return 0;
-  if (fixed_) {
-    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
-             "entry point has; use mrl_top_down_many for it", buf_bytes_);
-    return -4;
-  }
-  const uint64_t cap = need + need / 4;
-  MrlRow* nt = nullptr;
-  CK(cudaMalloc((void**)&nt, cap * sizeof(MrlRow)));
-  if (keep) CK(cudaMemcpyAsync(nt, d_temp_, keep * sizeof(MrlRow), cudaMemcpyDeviceToDevice, stream_));
-  CK(cudaStreamSynchronize(stream_));
-  cudaFree(d_temp_);
-  d_temp_ = nt;
-  temp_cap_ = cap;
-  return 0;
-}
-
-int DeviceFill::ensure_cells_(uint64_t need) {
-  if (need <= cell_cap_) return 0;
-  if (fixed_) {
-    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
-             "entry point has; use mrl_top_down_many for it", buf_bytes_);
-    return -4;
-  }
-  CK(cudaStreamSynchronize(stream_));
-  cudaFree(d_cells_);
-  d_cells_ = nullptr;
-  cell_cap_ = 0;
-  const uint64_t cap = need + need / 4;
-  CK(cudaMalloc((void**)&d_cells_, cap * sizeof(CellRef)));
-  cell_cap_ = cap;
-  return 0;
-}
-
-int DeviceFill::ensure_chunks_(uint64_t need) {
-  if (need <= chunk_cap_) return 0;
-  if (need > 0xFFFFFFF0ull) { snprintf(err_, sizeof(err_), "stage too large: %llu chunks", (unsigned long long)need); return -6; }
-  if (fixed_) {
-    snprintf(err_, sizeof(err_), "this fill needs more than the %zu bytes of device memory the no-allocation "
-             "entry point has; use mrl_top_down_many for it", buf_bytes_);
-    return -4;
-  }
-  CK(cudaStreamSynchronize(stream_));
-  cudaFree(d_chunks_);
-  d_chunks_ = nullptr;
-  chunk_cap_ = 0;
-  const uint64_t cap = need + need / 4;
-  CK(cudaMalloc((void**)&d_chunks_, cap * sizeof(Chunk)));
-  chunk_cap_ = cap;
   return 0;
 }
 
 int DeviceFill::begin_fill() {
   CK(cudaSetDevice(device_));
+  if (!cands_present_) {
+    snprintf(err_, sizeof(err_), "the candidate records are not on the device yet (mrl_device_cands hands out the buffer; "
+             "mrl_cands_arrived checks what was written)");
+    return -3;
+  }
   stats_ = FillStats();
-  final_bound_ = 0;
-  ev_used_ = 0;
-  CK(cudaMemsetAsync(d_ctr_, 0, 256, stream_));
+  CK(cudaMemsetAsync(d_ctl_, 0, 512, stream_));
   CK(cudaEventRecord(ev0_, stream_));
   filling_ = true;
   return 0;
 }
 
-// Solves one stage: passes of (derive masks, place, one combine launch per occupied diagonal,
-// find real breakpoints) until no working grid lacks a breakpoint of a same-stage child.
-int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
-  if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
+int DeviceFill::launch_solve_(const Plan& plan, uint32_t si, bool place_too) {
   const Stage& st = plan.stages[si];
-  const uint32_t lo = st.spec_lo, hi = st.spec_hi, n = hi - lo;
-  last_cells_ = 0;
+  const uint32_t n = st.spec_hi - st.spec_lo;
   if (n == 0) return 0;
   {
     // the stage reads its own Specs' candidate records (ids, and with them the records, are in
     // stage order): wait for that much of a background upload
-    const SpecHdr& last = plan.hdrs[hi - 1];
+    const SpecHdr& last = plan.hdrs[st.spec_hi - 1];
     int rc = wait_cands_(((uint64_t)last.cand_off + last.ncand) * sizeof(CandRec));
     if (rc) return rc;
   }
-  if (d_mine_) CK(cudaMemsetAsync(d_rmask_ + lo, 0, (size_t)n * sizeof(uint4), stream_));
-  CK(cudaMemsetAsync(d_dirty_ + lo, 0, n, stream_));
-  const uint32_t top_pack = plan.top_pack();
-  const uint32_t nb128 = (n + 127) / 128;
-  uint64_t temp_top = 0;   // working rows handed out so far in this stage
-  for (int pass = 0;; pass++) {
-    if (pass >= 128) { snprintf(err_, sizeof(err_), "stage %u did not reach a consistent limits grid", si); return -2; }
-    // masks: the first pass knows nothing about same-stage children; later passes add the real
-    // breakpoints the previous passes found in them. Specs whose masks grew become dirty.
-    derive_masks_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, d_dirty_, lo, hi, pass == 0,
-                                                    pass == 0 ? 0 : 1, pass == 0 && seed_hops_ > 0, top_pack);
-    stats_.launches++;
-    if (pass == 0)
-      for (int h = 0; h < seed_hops_; h++) {
-        // optional seeding: assume the same-stage children's breakpoints are their own first masks
-        derive_masks_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rmask_, d_mine_, d_dirty_, lo, hi, 0, 1,
-                                                        h + 1 < seed_hops_, top_pack);
-        stats_.launches++;
-      }
-    // close the dirty marks under "has a dirty same-stage child", then total the pass
-    PassCounters c;
-    for (int round = 0;; round++) {
-      if (round >= 4096) { snprintf(err_, sizeof(err_), "stage %u: dirty marks did not settle", si); return -2; }
-      if (pass > 0)
-        for (int k = 0; k < 3; k++) {
-          spread_dirty_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_mine_, d_dirty_, lo, hi);
-          stats_.launches++;
-        }
-      CK(cudaMemsetAsync(d_ctr_, 0, offsetof(PassCounters, error), stream_));   // the error word is sticky
-      totals_kernel<<<nb128, 128, 0, stream_>>>(d_hdrs_, d_cands_, d_mine_, d_dirty_, lo, hi, d_ctr_);
-      stats_.launches++;
-      if (read_counters_(&c) != 0) return -1;
-      if (c.error) {
-        snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u (1: bad child index, 2: working "
-                 "buffers too small, 4: row arena too small)", c.error, si);
-        return -2;
-      }
-      if (pass == 0 || !c.changed) break;
-    }
-    last_cells_ = c.all_cells;
-    if (c.cells == 0) break;   // nothing left to solve: every working grid is consistent
-    int rc;
-    if ((rc = ensure_chunks_(c.warps))) return rc;
-    if ((rc = ensure_temp_(temp_top + c.cells, temp_top))) return rc;
-    if (c.cells >= 0xFFFFFFF0ull) { snprintf(err_, sizeof(err_), "stage %u too large: %llu working cells", si, (unsigned long long)c.cells); return -6; }
-    if ((rc = ensure_cells_(c.cells))) return rc;
-    place_kernel<<<(n + 255) / 256, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, d_dirty_, lo, hi, temp_top, temp_cap_,
-                                                       d_chunks_, chunk_cap_, d_ctr_);
-    temp_top += c.cells;
-    const uint32_t n_chunks = (uint32_t)c.warps;
-    const uint32_t blocks = (n_chunks + 3) / 4;
-    // cells per limits diagonal, then the cell lists
-    CK(cudaMemsetAsync(d_diag_, 0, sizeof(DiagTable), stream_));
-    diag_histogram_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_diag_);
-    DiagTable* hd = h_diag_ ? h_diag_ : &diag_pageable_;
-    CK(cudaMemcpyAsync(hd->count, d_diag_->count, sizeof(hd->count), cudaMemcpyDeviceToHost, stream_));
-    CK(cudaStreamSynchronize(stream_));
-    unsigned long long run = 0;
-    for (int d = 0; d < MRL_MAX_DIAG; d++) { hd->base[d] = run; run += hd->count[d]; }
-    if (run != c.cells) { snprintf(err_, sizeof(err_), "stage %u: diagonal histogram counts %llu cells, expected %llu", si, run, (unsigned long long)c.cells); return -2; }
-    CK(cudaMemcpyAsync(d_diag_->base, hd->base, sizeof(hd->base), cudaMemcpyHostToDevice, stream_));
-    scatter_cells_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_diag_, d_cells_);
-    if (ev_used_ + 2 > ev_pool_.size()) {
-      for (int k = 0; k < 64; k++) {
-        cudaEvent_t e;
-        CK(cudaEventCreate(&e));
-        ev_pool_.push_back(e);
-      }
-    }
-    CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
-    for (uint32_t d = 0; d < MRL_MAX_DIAG; d++) {
-      const uint32_t nd = hd->count[d];
-      if (!nd) continue;
-      // lanes per cell by launch size: what fills the GPU (227 k threads) runs one lane per cell
-      const CellRef* list = d_cells_ + hd->base[d];
-      const bool mark = profile_min_cells_ && nd >= profile_min_cells_;   // MRL_PROFILE_MIN_CELLS: see init_events
-      if (mark) cudaProfilerStart();
-      if (nd > 65536)
-        combine_argmin_kernel<1><<<(nd + 127) / 128, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
-      else if (nd > 16384)
-        combine_argmin_kernel<4><<<(nd + 31) / 32, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
-      else if (nd > 4096)
-        combine_argmin_kernel<8><<<(nd + 15) / 16, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
-      else
-        combine_argmin_kernel<32><<<(nd + 3) / 4, 128, 0, stream_>>>(d_hdrs_, d_cands_, list, nd, d_rows_, d_temp_, n_specs_, &d_ctr_->error);
-      if (mark) cudaProfilerStop();
-      stats_.combine_launches++;
-    }
-    CK(cudaEventRecord(ev_pool_[ev_used_++], stream_));
-    real_masks_kernel<<<blocks, 128, 0, stream_>>>(d_hdrs_, d_chunks_, n_chunks, d_temp_, d_rmask_);
-    CK(cudaGetLastError());
-    if (stage_log_) fprintf(stderr, "[fill] stage %u (phase %u, shape %u, level %u, %u Specs) pass %d: %llu cells, %u chunks\n", si,
-                            st.phase, st.shape_sum, st.level_rank, n, pass, (unsigned long long)c.cells, n_chunks);
-    stats_.launches += 4;
-    stats_.passes++;
-    stats_.cells_solved += c.cells;
-    stats_.alg_bytes += c.alg_bytes;
-  }
+  StageArgs a;
+  a.hdrs = d_hdrs_; a.cands = d_cands_; a.rmask = d_rmask_; a.mine = d_mine_; a.dirty = d_dirty_;
+  a.chunks = d_chunks_; a.items = d_items_; a.cells = d_cells_; a.diag = d_diag_; a.rows = d_rows_; a.temp = d_temp_;
+  a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.ctl = d_ctl_;
+  a.lo = st.spec_lo; a.hi = st.spec_hi; a.top_pack = plan.top_pack(); a.stage = si;
+  a.temp_cap = temp_cap_; a.chunk_cap = chunk_cap_; a.item_cap = item_cap_; a.cell_cap = cell_cap_; a.row_cap = row_cap_;
+  a.solve = 1;
+  a.place = place_too ? 1 : 0;
+  // Small stages run on fewer blocks: a grid-wide barrier costs less, and there is no work for more.
+  const uint64_t want = ((uint64_t)n * 24 + kBlock - 1) / kBlock;
+  const int blocks = (int)std::min<uint64_t>((uint64_t)coop_blocks_, std::max<uint64_t>((uint64_t)n_sm_, want));
+  void* args[] = {&a};
+  CK(cudaLaunchCooperativeKernel((const void*)stage_kernel, dim3(blocks), dim3(kBlock), args, 0, stream_));
+  stats_.launches++;
   return 0;
+}
+
+int DeviceFill::launch_place_(const Plan& plan, uint32_t si) {
+  const Stage& st = plan.stages[si];
+  const uint32_t n = st.spec_hi - st.spec_lo;
+  if (n == 0) return 0;
+  StageArgs a;
+  a.hdrs = d_hdrs_; a.cands = d_cands_; a.rmask = d_rmask_; a.mine = d_mine_; a.dirty = d_dirty_;
+  a.chunks = d_chunks_; a.items = d_items_; a.cells = d_cells_; a.diag = d_diag_; a.rows = d_rows_; a.temp = d_temp_;
+  a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.ctl = d_ctl_;
+  a.lo = st.spec_lo; a.hi = st.spec_hi; a.top_pack = plan.top_pack(); a.stage = si;
+  a.temp_cap = temp_cap_; a.chunk_cap = chunk_cap_; a.item_cap = item_cap_; a.cell_cap = cell_cap_; a.row_cap = row_cap_;
+  a.solve = 0;
+  a.place = 1;
+  const uint64_t want = ((uint64_t)n + kBlock - 1) / kBlock;
+  const int blocks = (int)std::min<uint64_t>((uint64_t)coop_blocks_, std::max<uint64_t>(1, want));
+  void* args[] = {&a};
+  CK(cudaLaunchCooperativeKernel((const void*)stage_kernel, dim3(blocks), dim3(kBlock), args, 0, stream_));
+  stats_.launches++;
+  return 0;
+}
+
+int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
+  if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
+  if (!filling_) { snprintf(err_, sizeof(err_), "no fill in progress"); return -3; }
+  return launch_solve_(plan, si, false);
 }
 
 int DeviceFill::stage_masks(const Plan& plan, uint32_t si, void** ptr, uint64_t* bytes) {
@@ -1296,77 +1564,100 @@ int DeviceFill::stage_masks(const Plan& plan, uint32_t si, void** ptr, uint64_t*
   return 0;
 }
 
-// Appends the stage's compacted grids to the table. With rows_ptr: also reports where they
-// went (the slice other ranks need), which costs one synchronisation.
+static const char* kErrorBits = "(1: candidate record out of range, 2: working buffers too small, 4: row table too small, "
+                                "8: no consistent limits grid)";
+
+// Appends the stage's compacted grids to the table and reports where they went (the slice other
+// ranks need), which costs the one synchronisation of the stage. A stage that ran out of room is
+// run again here, whole, after its buffers have grown: its masks cannot have been exchanged yet.
 int DeviceFill::place_stage(const Plan& plan, uint32_t si, void** rows_ptr, uint64_t* bytes) {
   if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
-  const Stage& st = plan.stages[si];
-  const uint32_t lo = st.spec_lo, hi = st.spec_hi, n = hi - lo;
+  if (!filling_) { snprintf(err_, sizeof(err_), "no fill in progress"); return -3; }
   if (rows_ptr) *rows_ptr = d_rows_;
   if (bytes) *bytes = 0;
-  if (n == 0) return 0;
-  const uint32_t nb = (n + 255) / 256;
+  const Stage& st = plan.stages[si];
+  if (st.spec_hi == st.spec_lo) return 0;
   int rc;
-  const bool exact = d_mine_ || rows_ptr;
-  if (!exact) {
-    // final cells <= working cells of the last pass: room for that many is enough
-    if ((rc = ensure_rows_(final_bound_ + last_cells_, true))) return rc;
-    final_bound_ += last_cells_;
+  if ((rc = launch_place_(plan, si))) return rc;
+  if (read_ctl_() != 0) return -1;
+  if (h_ctl_->error) {
+    const uint32_t bits = h_ctl_->error;
+    if (bits & MRL_ERR_WORKING) {
+      snprintf(err_, sizeof(err_), "stage %u needs larger working buffers than a sharded fill starts with "
+               "(%llu working rows, %llu cells); fill once unsharded, or with fewer Specs per stage", si,
+               (unsigned long long)h_ctl_->need_temp, (unsigned long long)h_ctl_->need_cells);
+      return -6;
+    }
+    if (bits & ~(uint32_t)MRL_ERR_TABLE) {
+      snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u %s", bits, h_ctl_->failed_stage, kErrorBits);
+      return -2;
+    }
+    if ((rc = grow_after_error_(bits))) return rc;
+    CK(cudaMemsetAsync(&d_ctl_->error, 0, sizeof(uint32_t), stream_));
+    if ((rc = launch_place_(plan, si))) return rc;
+    if (read_ctl_() != 0) return -1;
+    if (h_ctl_->error) { snprintf(err_, sizeof(err_), "stage %u failed again after its buffers were enlarged (0x%x)", si, h_ctl_->error); return -2; }
   }
-  final_count_kernel<<<nb, 256, 0, stream_>>>(d_rmask_, lo, hi, d_fcount_, d_block_sums_);
-  scan_block_sums_kernel<<<1, 256, 0, stream_>>>(d_block_sums_, nb, d_final_top_, d_stage_info_);
-  stats_.launches += 2;
-  if (exact) {
-    // other ranks' Specs count too: ask the device how many rows the stage takes
-    PassCounters c;
-    if (read_counters_(&c) != 0) return -1;
-    final_bound_ = stage_info_seen_[0];   // rows to keep if the arena has to grow
-    if ((rc = ensure_rows_(final_bound_ + stage_info_seen_[1], false))) return rc;
-    final_bound_ += stage_info_seen_[1];
-  }
-  compact_kernel<<<nb, 256, 0, stream_>>>(d_hdrs_, d_rmask_, d_mine_, lo, hi, d_fcount_, d_block_sums_, d_stage_info_,
-                                          d_rows_, row_cap_, d_temp_, d_ctr_);
-  CK(cudaGetLastError());
-  stats_.launches++;
-  if (rows_ptr) {
-    *rows_ptr = d_rows_ + stage_info_seen_[0];
-    if (bytes) *bytes = stage_info_seen_[1] * sizeof(MrlRow);
-  }
+  if (rows_ptr) *rows_ptr = d_rows_ + h_ctl_->stage_first_row;
+  if (bytes) *bytes = h_ctl_->stage_rows * sizeof(MrlRow);
   return 0;
+}
+
+void DeviceFill::take_stats_() {
+  const FillCtl& c = *h_ctl_;
+  stats_.n_rows = c.final_top;
+  stats_.cells_solved = c.st_cells;
+  stats_.cands_evaluated = c.st_cands;
+  stats_.lookups = c.st_lookups;
+  stats_.alg_bytes = c.st_final_bytes;
+  stats_.passes = c.st_passes;
+  stats_.grid_syncs = c.st_syncs;
+  stats_.combine_ms = (float)(c.st_combine_ns * 1e-6);
+  stats_.early_ms = (float)(c.st_early_ns * 1e-6);
 }
 
 int DeviceFill::end_fill() {
   CK(cudaEventRecord(ev1_, stream_));
-  PassCounters c;
-  if (read_counters_(&c) != 0) return -1;
+  if (read_ctl_() != 0) return -1;
   filling_ = false;
   CK(cudaEventElapsedTime(&stats_.fill_ms, ev0_, ev1_));
-  float cms = 0;
-  for (size_t k = 0; k + 1 < ev_used_; k += 2) {
-    float t = 0;
-    CK(cudaEventElapsedTime(&t, ev_pool_[k], ev_pool_[k + 1]));
-    cms += t;
-  }
-  stats_.combine_ms = cms;
-  stats_.launches += stats_.combine_launches;
-  stats_.n_rows = final_top_seen_;
-  final_bound_ = final_top_seen_;
-  if (c.error) {
-    snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x (1: bad child index, 2: working buffers too small, "
-             "4: row arena too small)", c.error);
+  take_stats_();
+  if (h_ctl_->error) {
+    snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u %s", h_ctl_->error, h_ctl_->failed_stage, kErrorBits);
     return -2;
   }
   return 0;
 }
 
+// Every stage is enqueued without waiting for the one before: sizes, pass counts and launch
+// geometry are all decided on the device. A stage that runs out of room raises an error word
+// that turns the stages behind it into no-ops; the host then enlarges the buffers it named and
+// resumes from that stage.
 int DeviceFill::run(const Plan& plan) {
   int rc;
   if ((rc = begin_fill())) return rc;
-  for (uint32_t s = 0; s < plan.stages.size(); s++) {
-    if ((rc = solve_stage(plan, s))) return rc;
-    if ((rc = place_stage(plan, s, nullptr, nullptr))) return rc;
+  uint32_t from = 0;
+  for (int attempt = 0;; attempt++) {
+    for (uint32_t s = from; s < plan.stages.size(); s++)
+      if ((rc = launch_solve_(plan, s, true))) return rc;
+    CK(cudaEventRecord(ev1_, stream_));
+    if (read_ctl_() != 0) return -1;
+    const uint32_t bits = h_ctl_->error;
+    if (!bits) break;
+    if ((bits & ~(uint32_t)(MRL_ERR_WORKING | MRL_ERR_TABLE)) || attempt >= 64) {
+      filling_ = false;
+      take_stats_();
+      snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u %s", bits, h_ctl_->failed_stage, kErrorBits);
+      return -2;
+    }
+    from = h_ctl_->failed_stage;
+    if ((rc = grow_after_error_(bits))) { filling_ = false; return rc; }
+    CK(cudaMemsetAsync(&d_ctl_->error, 0, sizeof(uint32_t), stream_));
   }
-  return end_fill();
+  filling_ = false;
+  CK(cudaEventElapsedTime(&stats_.fill_ms, ev0_, ev1_));
+  take_stats_();
+  return 0;
 }
 
 int DeviceFill::lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t n, MrlRow* out) {
@@ -1376,17 +1667,18 @@ int DeviceFill::lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t 
   for (size_t i = 0; i < n; i++)
     if (spec_ids[i] >= n_specs_) { snprintf(err_, sizeof(err_), "Spec id out of range"); return -3; }
   const size_t per = sizeof(uint2) + sizeof(MrlRow);
-  size_t batch = n;
+  size_t batch = std::min<size_t>(n, size_t(1) << 22);
   if (fixed_) batch = std::min(n, stage_bytes_ / 2 / per);
-  else if (stage_bytes_ < 2 * align256(n * sizeof(MrlRow))) {
+  else if (stage_bytes_ < 2 * align256(batch * sizeof(MrlRow))) {
     CK(cudaStreamSynchronize(stream_));
     if (d_stage_) cudaFree(d_stage_);
     d_stage_ = nullptr;
     stage_bytes_ = 0;
-    CK(cudaMalloc(&d_stage_, 2 * align256(n * sizeof(MrlRow))));
-    stage_bytes_ = 2 * align256(n * sizeof(MrlRow));
+    int rc = alloc_(&d_stage_, 2 * align256(batch * sizeof(MrlRow)));
+    if (rc) return rc;
+    stage_bytes_ = 2 * align256(batch * sizeof(MrlRow));
   }
-  if (batch == 0) { snprintf(err_, sizeof(err_), "lookup staging too small"); return -4; }
+  if (batch == 0) { snprintf(err_, sizeof(err_), "lookup staging too small"); return -5; }
   std::vector<uint2> q(batch);
   for (size_t done = 0; done < n; done += batch) {
     const size_t m = std::min(batch, n - done);
@@ -1414,15 +1706,15 @@ int DeviceFill::verify(const Plan& plan, uint64_t n_samples, uint64_t seed, uint
   const unsigned long long total = per_spec * n_specs_;
   const bool exhaustive = n_samples == 0;
   const unsigned long long count = exhaustive ? total : n_samples;
-  unsigned long long* d_out = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(d_ctr_) + 96);
+  unsigned long long* d_out = d_ctl_->scratch;
   const unsigned long long init[2] = {0ull, ~0ull};
   CK(cudaMemcpyAsync(d_out, init, sizeof(init), cudaMemcpyHostToDevice, stream_));
   CK(cudaStreamSynchronize(stream_));
   const unsigned long long batch = 1ull << 28;
   for (unsigned long long first = 0; first < count && total; first += batch) {
     const unsigned long long n = std::min(batch, count - first);
-    verify_points_kernel<<<(unsigned)((n + 127) / 128), 128, 0, stream_>>>(d_hdrs_, d_cands_, d_rows_, n_specs_, top, first, n,
-                                                                          total, seed, exhaustive ? 1 : 0, d_out);
+    verify_points_kernel<<<(unsigned)((n + kBlock - 1) / kBlock), kBlock, 0, stream_>>>(d_hdrs_, d_cands_, d_rows_, n_specs_, top, first, n,
+                                                                                       total, seed, exhaustive ? 1 : 0, d_out);
     CK(cudaGetLastError());
   }
   unsigned long long res[2] = {0, 0};
@@ -1431,6 +1723,50 @@ int DeviceFill::verify(const Plan& plan, uint64_t n_samples, uint64_t seed, uint
   if (checked) *checked = total ? count : 0;
   if (mismatches) *mismatches = res[0];
   if (first_bad) *first_bad = res[1];
+  return 0;
+}
+
+int DeviceFill::checksum(uint64_t* out) {
+  CK(cudaSetDevice(device_));
+  unsigned long long* d_out = d_ctl_->scratch + 2;
+  CK(cudaMemsetAsync(d_out, 0, sizeof(unsigned long long), stream_));
+  if (n_specs_) {
+    checksum_kernel<<<(n_specs_ + kBlock - 1) / kBlock, kBlock, 0, stream_>>>(d_hdrs_, d_rows_, n_specs_, d_out);
+    CK(cudaGetLastError());
+  }
+  unsigned long long v = 0;
+  CK(cudaMemcpyAsync(&v, d_out, sizeof(v), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  *out = v;
+  return 0;
+}
+
+int DeviceFill::read_table(SpecHdr* hdrs_out, MrlRow* rows_out) {
+  CK(cudaSetDevice(device_));
+  if (n_specs_) CK(cudaMemcpyAsync(hdrs_out, d_hdrs_, (size_t)n_specs_ * sizeof(SpecHdr), cudaMemcpyDeviceToHost, stream_));
+  if (stats_.n_rows) CK(cudaMemcpyAsync(rows_out, d_rows_, stats_.n_rows * sizeof(MrlRow), cudaMemcpyDeviceToHost, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  return 0;
+}
+
+int DeviceFill::load_table(const Plan& plan, const SpecHdr* hdrs, const MrlRow* rows, uint64_t n_rows) {
+  CK(cudaSetDevice(device_));
+  if (plan.hdrs.size() != n_specs_) { snprintf(err_, sizeof(err_), "the saved table belongs to another plan"); return -3; }
+  if (n_rows > row_cap_) {
+    if (fixed_) return too_large_();
+    CK(cudaStreamSynchronize(stream_));
+    cudaFree(d_rows_);
+    d_rows_ = nullptr;
+    row_cap_ = 0;
+    int rc = alloc_((void**)&d_rows_, n_rows * sizeof(MrlRow));
+    if (rc) return rc;
+    row_cap_ = n_rows;
+  }
+  if (n_specs_) CK(cudaMemcpyAsync(d_hdrs_, hdrs, (size_t)n_specs_ * sizeof(SpecHdr), cudaMemcpyHostToDevice, stream_));
+  if (n_rows) CK(cudaMemcpyAsync(d_rows_, rows, n_rows * sizeof(MrlRow), cudaMemcpyHostToDevice, stream_));
+  CK(cudaStreamSynchronize(stream_));
+  stats_ = FillStats();
+  stats_.n_rows = n_rows;
   return 0;
 }
 
@@ -1472,15 +1808,20 @@ constexpr int kMaxDevices = 64;
 void* g_scratch_addr[kMaxDevices] = {nullptr};
 std::mutex g_scratch_mu;
 
-// Device address of the static array on `device`, resolved on first use.
+// Device address of the static array on `device`, resolved on first use. The caller's current
+// device is left as it was.
 cudaError_t static_scratch_address(int device, void** out) {
   if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> g(g_scratch_mu);
   if (!g_scratch_addr[device]) {
-    cudaError_t e = cudaSetDevice(device);
+    int before = -1;
+    cudaError_t e = cudaGetDevice(&before);
+    if (e != cudaSuccess) return e;
+    e = cudaSetDevice(device);
     if (e != cudaSuccess) return e;
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (before != device) cudaSetDevice(before);
     if (e != cudaSuccess) return e;
     g_scratch_addr[device] = p;
   }
@@ -1490,7 +1831,7 @@ cudaError_t static_scratch_address(int device, void** out) {
 }  // namespace
 
 // Runs `plan` entirely inside the static array and copies the rows of the given (Spec id,
-// packed limit codes) queries to `out` (host). No cudaMalloc / cudaFree. Returns -4 with a
+// packed limit codes) queries to `out` (host). No cudaMalloc / cudaFree. Returns -5 with a
 // message when the fill does not fit.
 int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint32_t* spec_ids, const uint32_t* cpacks,
                 size_t n, MrlRow* out, char* err, size_t err_len) {

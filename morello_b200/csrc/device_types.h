@@ -1,4 +1,4 @@
-// Plain-data records shared by the host planner and the CUDA combine kernel.
+// Plain-data records shared by the host planner and the CUDA fill kernels.
 //
 // Limits lattice: one integer "code" per memory, in the reference's own database
 // coordinates (MemoryLimitsBimap, morello/src/memorylimits.rs:696-734): registers (RF, VRF)
@@ -16,15 +16,17 @@ struct MrlRow {
   uint32_t main;   // saturating u32 main cost
   uint32_t peaks;  // RF<<24 | VRF<<16 | L1 code<<8 | GL code   (peak memory, as lattice codes)
   uint32_t tail;   // depth<<16 | action number; 0xFFFFFFFF = no implementation
-  uint32_t pad;    // 12 bytes of payload kept in a 16-byte slot: one aligned vector load per gather
+  uint32_t aux;    // finished table: 0. Working rows of the stage being solved: index of the winning
+                   // candidate record within its Spec (0xFFFFFFFF when there is none).
+                   // 12 bytes of payload in a 16-byte slot: one aligned vector load per gather.
 };
 #define MRL_UNSAT 0xFFFFFFFFu
 
 // Per logical Spec: breakpoint masks of its limits grid (bit c set = code c starts a new
 // cell; bit 0 always set), the first row of its dense cell block and its candidates.
 // Cell (i0,i1,i2,i3) has row ((i3*n2 + i2)*n1 + i1)*n0 + i0 with n_k = popcount(mask[k]).
-// While a stage is being solved its Specs point at a working grid in the scratch end of the
-// row arena; once the stage is consistent they point at the compacted final grid.
+// While a stage is being solved its Specs point at a working grid in the working-row buffer;
+// once the stage is consistent they point at the compacted final grid.
 struct SpecHdr {
   uint32_t mask[4];
   uint64_t row_base;
@@ -44,7 +46,7 @@ struct CandRec {
   uint8_t level;     // memory the action allocates in (MOVE, LEAF)
   uint8_t thr_code;  // smallest limit code in `level` at which the action applies
   uint8_t peak_code; // LEAF: the kernel's own peak in `level`, as a code
-  uint8_t pad0;
+  uint8_t late;      // 1: a child lies in the Spec's own stage (a relayout Move); such records come last
   uint32_t units;    // MOVE: units consumed in `level` (registers or cache lines)
   uint32_t child[3]; // Spec ids, in request order
   uint32_t pad1;
@@ -58,27 +60,27 @@ struct Chunk {
   uint32_t col_start;
 };
 
-// Counters one solve pass of a stage leaves for the host (zeroed before every pass).
-struct PassCounters {
-  uint32_t changed;             // a Spec was marked for solving by totals_kernel itself (marks were not closed)
-  uint32_t n_chunks;            // chunk cursor (place kernel)
-  unsigned long long cells;     // working cells of the Specs to solve in this pass
-  unsigned long long warps;     // chunks those cells need
-  unsigned long long temp_rows; // row cursor (place kernel)
-  unsigned long long alg_bytes; // algorithmic bytes of one solve of those cells
-  unsigned long long all_cells; // working cells of all the stage's Specs under the current masks
-  uint32_t pad0[2];
-  uint32_t error;               // bad child index / capacity overrun seen by a kernel (sticky over a fill)
-  uint32_t pad;
-};
-
-// Per limits diagonal (sum of the four codes, < 128) of the stage being solved: how many working
-// cells lie on it, and where their descriptors start in the cell list.
+// Per limits diagonal (sum of the four codes, < 128) of the pass being solved: how many working
+// cells lie on it, where their descriptors start in the cell list, and the occupied diagonals in
+// ascending order.
 #define MRL_MAX_DIAG 128
 struct DiagTable {
   uint32_t count[MRL_MAX_DIAG];
   uint32_t cursor[MRL_MAX_DIAG];
   unsigned long long base[MRL_MAX_DIAG];
+  uint32_t order[MRL_MAX_DIAG];
+  uint32_t work[MRL_MAX_DIAG];    // how many of a diagonal's cells have been handed to a warp
+  uint32_t n_occupied;
+  uint32_t pad[3];
+};
+
+// A piece of one Spec's working grid for the unordered solve phase: consecutive cells from
+// first_cell on, at most MRL_ITEM_CELLS of them (a pass picks the size). Warps take items as they
+// finish others.
+#define MRL_ITEM_CELLS 1024u
+struct WorkItem {
+  uint32_t spec;
+  uint32_t first_cell;
 };
 
 // One working cell: Spec id and the cell's limits as lattice codes, one per byte (RF in byte 0
@@ -88,9 +90,51 @@ struct CellRef {
   uint32_t cpack;
 };
 
+// Error bits a fill kernel can raise (sticky until the host clears them).
+enum {
+  MRL_ERR_CHILD = 1,      // a candidate record names a Spec id outside the plan
+  MRL_ERR_WORKING = 2,    // a working buffer (rows, chunks, cell list) is too small
+  MRL_ERR_TABLE = 4,      // the row table is too small
+  MRL_ERR_PASSES = 8,     // a stage did not reach a consistent limits grid
+};
+
+// Control block of a fill, in device memory. The stage kernels read their sizes and cursors
+// here and leave the host nothing to decide between launches; the host reads it once per fill
+// (once per stage when the fill is sharded).
+struct FillCtl {
+  // -- one solve pass (zeroed by the kernel before every pass)
+  unsigned long long cells;          // working cells of the Specs solved in this pass
+  unsigned long long warps;          // chunks those cells need
+  unsigned long long row_cursor;     // placement cursors of the pass
+  uint32_t chunk_cursor;
+  uint32_t item_cursor;
+  uint32_t item_next;                // next work item to hand out
+  uint32_t spread_epoch;             // closure of the re-solve marks: last round that marked a Spec
+  // -- one stage
+  unsigned long long temp_top;       // working rows handed out so far in this stage
+  unsigned long long all_cells;      // working cells of all the stage's Specs under the final masks
+  // -- sticky over a fill
+  uint32_t error;                    // MRL_ERR_* bits
+  uint32_t failed_stage;             // first stage that raised one
+  unsigned long long need_temp, need_chunks, need_items, need_cells, need_rows;   // what it would have taken
+  unsigned long long final_top;      // rows of the finished table
+  unsigned long long stage_first_row, stage_rows;   // the last placed stage's slice of the table
+  // -- statistics of a fill
+  unsigned long long st_cells;       // working cells solved, all passes
+  unsigned long long st_cands;       // candidate records evaluated
+  unsigned long long st_lookups;     // child rows gathered
+  unsigned long long st_passes;
+  unsigned long long st_combine_ns;  // device time inside the solve phases (globaltimer)
+  unsigned long long st_early_ns;    // of which the unordered phase (with the cell listing)
+  unsigned long long st_final_bytes; // algorithmic bytes of the finished rows (see fill.hpp)
+  unsigned long long st_syncs;       // grid-wide barriers executed
+  // -- scratch of verify and checksum
+  unsigned long long scratch[4];
+};
+
 #ifdef __cplusplus
 static_assert(sizeof(MrlRow) == 16, "row slot is 16 bytes");
 static_assert(sizeof(SpecHdr) == 32, "spec header is 32 bytes");
 static_assert(sizeof(CandRec) == 32, "candidate record is 32 bytes");
-static_assert(sizeof(PassCounters) == 64, "pass counters are 64 bytes");
+static_assert(sizeof(FillCtl) % 8 == 0 && sizeof(FillCtl) <= 512, "control block");
 #endif

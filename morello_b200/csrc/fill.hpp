@@ -1,4 +1,4 @@
-// Device side of the fill: owns the device copies of a Plan and the row arena, and runs the
+// Device side of the fill: owns the device copies of a Plan and the row table, and runs the
 // stages. Callers hand in host data only.
 #pragma once
 #include "plan.hpp"
@@ -13,12 +13,18 @@ namespace mrl {
 struct FillStats {
   uint64_t n_rows = 0;          // final table rows
   uint64_t cells_solved = 0;    // working-grid cells solved, all passes
-  uint64_t alg_bytes = 0;       // algorithmic bytes of those solves
+  uint64_t cands_evaluated = 0; // candidate records evaluated
+  uint64_t lookups = 0;         // child rows gathered
+  // Algorithmic bytes of the finished table: per final row 12 bytes out, 16 per candidate record
+  // of its Spec and 16 (index + row) per child of every candidate that fits the row's limits.
+  // Working cells that do not survive compaction do not count.
+  uint64_t alg_bytes = 0;
   uint64_t passes = 0;          // solve passes over all stages
   uint64_t launches = 0;        // kernel launches
-  uint64_t combine_launches = 0;
+  uint64_t grid_syncs = 0;      // grid-wide barriers inside the stage kernels
   float fill_ms = 0;            // device time of the whole fill (CUDA events on the launch stream)
-  float combine_ms = 0;         // device time inside the combine launches only
+  float combine_ms = 0;         // device time inside the solve phases (device timer)
+  float early_ms = 0;           // of which the unordered phase
 };
 
 class DeviceFill {
@@ -29,22 +35,25 @@ class DeviceFill {
   // Memory from cudaMalloc (the default), or carved out of one caller-supplied device buffer
   // that is never grown or freed (attach_buffer before upload).
   void attach_buffer(void* base, size_t bytes, cudaStream_t stream, int device);
-  // Copies headers and candidate records to the device and sets up the arena.
+  // Copies headers and candidate records to the device and sets up the buffers.
   // Gigabytes of candidate records keep going up in the background, in id order, after upload()
   // has returned: the plan must stay as it is until wait_upload() (a fill waits stage by stage
   // for the records it is about to read, so its first stages overlap the copy).
   // skip_cands: the candidate records are not on this host; the caller fills device_cands()
-  // itself (e.g. a broadcast from the rank that planned) before the first fill.
+  // itself (e.g. a broadcast from the rank that planned) and then calls cands_arrived().
   int upload(const Plan& plan, bool skip_cands = false);
   // Blocks until every candidate record is on the device.
   int wait_upload();
   void* device_cands() const { return d_cands_; }
   uint64_t device_cand_bytes() const { return n_cand_bytes_; }
-  // Runs every stage.
+  // After the caller has written device_cands(): checks every record on the device (child ids
+  // inside the plan, kinds and levels in range) and lets fills run.
+  int cands_arrived();
+  // Runs every stage: two launches per stage, no host synchronisation before the end.
   int run(const Plan& plan);
   // The same one stage at a time, for callers that exchange tables between stages (multi-GPU):
   // begin_fill; per stage solve_stage, [exchange stage_masks], place_stage, [exchange rows];
-  // end_fill. All work is enqueued on the stream; solve_stage and place_stage synchronise it.
+  // end_fill. All work is enqueued on the stream; place_stage synchronises it once.
   int begin_fill();
   int solve_stage(const Plan& plan, uint32_t stage);
   int stage_masks(const Plan& plan, uint32_t stage, void** ptr, uint64_t* bytes);
@@ -56,6 +65,13 @@ class DeviceFill {
   int lookup(const uint32_t* spec_ids, const uint32_t* cpacks, size_t n, MrlRow* out);
   int verify(const Plan& plan, uint64_t n_samples, uint64_t seed, uint64_t* checked, uint64_t* mismatches,
              uint64_t* first_bad);
+  // Order-independent 64-bit checksum of the logical table: per Spec its id, masks and rows in
+  // cell order; where the rows lie in the table does not enter.
+  int checksum(uint64_t* out);
+  // The whole finished table in two copies: headers (masks, first row) and rows.
+  int read_table(SpecHdr* hdrs_out, MrlRow* rows_out);
+  // Replaces the table by a saved one (hdrs as read_table gave them).
+  int load_table(const Plan& plan, const SpecHdr* hdrs, const MrlRow* rows, uint64_t n_rows);
   int read_hdr(uint32_t spec, SpecHdr* out);
   int read_rows(uint64_t first, uint64_t n, MrlRow* out);
   void release();
@@ -65,16 +81,18 @@ class DeviceFill {
   MrlRow* device_rows() const { return d_rows_; }
   cudaStream_t stream() const { return stream_; }
   int device() const { return device_; }
+  uint32_t n_specs() const { return n_specs_; }
 
  private:
   int alloc_(void** p, size_t bytes);
   void free_(void* p);
-  int ensure_rows_(uint64_t need, bool refresh);
-  int ensure_temp_(uint64_t need, uint64_t keep);
-  int ensure_chunks_(uint64_t need);
-  int ensure_cells_(uint64_t need);
-  int read_counters_(PassCounters* out);
-  int wait_cands_(uint64_t upto_bytes);   // until the candidate bytes [0, upto_bytes) are on the device
+  int launch_solve_(const Plan& plan, uint32_t stage, bool place_too);
+  int launch_place_(const Plan& plan, uint32_t stage);
+  int read_ctl_();                       // device control block -> h_ctl_ (synchronises the stream)
+  int grow_after_error_(uint32_t bits);  // enlarges the buffers a failed stage asked for
+  int wait_cands_(uint64_t upto_bytes);  // until the candidate bytes [0, upto_bytes) are on the device
+  void take_stats_();
+  int too_large_();
 
   int device_ = 0;
   bool fixed_ = false;            // carved from an attached buffer: no growth
@@ -86,41 +104,30 @@ class DeviceFill {
   uint8_t* d_mine_ = nullptr;
   uint8_t* d_dirty_ = nullptr;   // by Spec id: to be solved (again) in the coming pass
   Chunk* d_chunks_ = nullptr;
+  WorkItem* d_items_ = nullptr;  // pieces of working grids for the unordered solve phase
   CellRef* d_cells_ = nullptr;   // working cells of the pass, listed diagonal by diagonal
   DiagTable* d_diag_ = nullptr;
-  DiagTable* h_diag_ = nullptr;  // pinned
-  DiagTable diag_pageable_;      // used instead when nothing may be allocated
-  MrlRow* d_rows_ = nullptr;   // the table
-  MrlRow* d_temp_ = nullptr;   // working grids of the stage being solved
+  MrlRow* d_rows_ = nullptr;     // the table
+  MrlRow* d_temp_ = nullptr;     // working grids of the stage being solved
   uint32_t* d_fcount_ = nullptr;
   unsigned long long* d_block_sums_ = nullptr;
-  PassCounters* d_ctr_ = nullptr;       // [0]: pass counters; then final_top, stage_info[2]
-  unsigned long long* d_final_top_ = nullptr;
-  unsigned long long* d_stage_info_ = nullptr;
-  void* d_stage_ = nullptr;             // lookup staging
+  FillCtl* d_ctl_ = nullptr;
+  void* d_stage_ = nullptr;      // lookup staging
   size_t stage_bytes_ = 0;
-  PassCounters* h_ctr_ = nullptr;       // pinned
-  uint32_t n_specs_ = 0;
-  uint64_t row_cap_ = 0, temp_cap_ = 0, chunk_cap_ = 0, cell_cap_ = 0;
-  uint64_t final_bound_ = 0;            // upper bound of the final rows placed so far
-  unsigned long long final_top_seen_ = 0, stage_info_seen_[2] = {0, 0};  // last values read back
-  uint64_t last_cells_ = 0;             // working cells of the last pass of the stage being solved
+  FillCtl* h_ctl_ = nullptr;     // pinned, or &ctl_pageable_ when nothing may be allocated
+  FillCtl ctl_pageable_;
+  uint32_t n_specs_ = 0, max_stage_ = 1;
+  uint64_t row_cap_ = 0, temp_cap_ = 0, chunk_cap_ = 0, item_cap_ = 0, cell_cap_ = 0;
   uint64_t h2d_bytes_ = 0;
   uint64_t n_cand_bytes_ = 0;
+  bool cands_present_ = false;   // the device candidate records are complete and checked
   bool filling_ = false;
-  // Before the first solve of a stage a Spec's working masks also take the first masks of its
-  // same-stage children (shifted), this many hops deep: one hop saves a third of the solve
-  // passes at size 8 for 9 % more cells; two hops cost more cells than they save. MRL_SEED_HOPS
-  // overrides (0..8); any value gives the same tables.
-  int seed_hops_ = 1;
-  uint32_t profile_min_cells_ = 0;      // MRL_PROFILE_MIN_CELLS
-  bool stage_log_ = false;              // MRL_STAGE_LOG: one line per solve pass on stderr
+  int coop_blocks_ = 0;          // co-resident blocks of the stage kernel on this device
+  int n_sm_ = 0;
   FillStats stats_;
   cudaStream_t stream_ = nullptr;
   bool own_stream_ = false;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
-  std::vector<cudaEvent_t> ev_pool_;
-  size_t ev_used_ = 0;
   std::mutex lookup_mu_;
   // background candidate upload: pieces handed out in order to a few copying threads
   std::vector<std::thread> up_threads_;
@@ -134,8 +141,8 @@ class DeviceFill {
 // Size of the fixed device array behind the no-allocation entry point (32 MiB per GPU).
 #define MRL_STATIC_SCRATCH_BYTES (32u << 20)
 
-// One whole small fill inside the fixed device array: plan arrays, row arena and lookup
-// staging; no device allocation. See combine.cu.
+// One whole small fill inside the fixed device array: plan arrays, working buffers, row table
+// and lookup staging; no device allocation. See combine.cu.
 int fill_static(int device, cudaStream_t stream, const Plan& plan, const uint32_t* spec_ids, const uint32_t* cpacks,
                 size_t n, MrlRow* out, char* err, size_t err_len);
 

@@ -306,20 +306,79 @@ void Plan::assign_owners_() {
   for (u32 i = 0; i < n; i++) mine[i] = owner[i] == rank;
 }
 
-void Plan::adopt_done(u32 rank_, u32 world_, int n_threads_) {
+void Plan::adopt_done(u32 rank_, u32 world_, int n_threads_, bool have_cands) {
   if (meta_.world != world_) throw ModelError("shared plan was made for another world size");
   if (world_ < 1 || rank_ >= world_) throw ModelError("bad shard rank / world size");
-  for (int k = 0; k < NMEM; k++) top_code[k] = meta_.top_code[k];
+  for (int k = 0; k < NMEM; k++) {
+    top_code[k] = meta_.top_code[k];
+    if (top_code[k] > 30) throw ModelError("shared plan: bad top limits");
+  }
   stats = meta_.stats;
   rank = rank_;
   world = world_;
   n_threads = n_threads_;
-  if (stats.n_specs != hdrs.size() || stats.n_cands != cands.size() || stats.n_stages != stages.size() ||
+  const u64 n = hdrs.size();
+  if (stats.n_specs != n || stats.n_cands != cands.size() || stats.n_stages != stages.size() ||
       stats.n_families != families.size())
     throw ModelError("shared plan: contents do not match their description");
-  for (const Family& f : families)
-    if (f.spec_hi > hdrs.size() || f.spec_lo > f.spec_hi) throw ModelError("shared plan: bad family");
+  // Everything a kernel or a lookup indexes with: stages and families tile the ids in order, every
+  // Spec's candidate range lies inside the records, goal ids and the id table point at Specs.
+  u32 pos = 0, fam = 0;
+  for (size_t si = 0; si < stages.size(); si++) {
+    const Stage& st = stages[si];
+    if (st.spec_lo != pos || st.spec_hi < st.spec_lo || st.spec_hi > n || st.fam_lo != fam || st.fam_hi < st.fam_lo ||
+        st.fam_hi > families.size())
+      throw ModelError("shared plan: bad stage");
+    for (u32 f = st.fam_lo; f < st.fam_hi; f++) {
+      const Family& fm = families[f];
+      if (fm.spec_lo != pos || fm.spec_hi <= fm.spec_lo || fm.spec_hi > st.spec_hi || fm.stage != si)
+        throw ModelError("shared plan: bad family");
+      pos = fm.spec_hi;
+    }
+    if (pos != st.spec_hi) throw ModelError("shared plan: families do not tile their stage");
+    fam = st.fam_hi;
+  }
+  if (pos != n || fam != families.size()) throw ModelError("shared plan: stages do not cover the Specs");
+  for (u32 g : goal_ids)
+    if (g >= n) throw ModelError("shared plan: bad goal id");
+  if (find_tab_.empty() || (find_tab_.size() & (find_tab_.size() - 1)) || find_tab_.size() < n)
+    throw ModelError("shared plan: bad id table");
+  for (u32 id : find_tab_)
+    if (id != 0xFFFFFFFFu && id >= n) throw ModelError("shared plan: bad id table");
+  const u64 ncand = stats.n_cands;
+  std::atomic<int> bad{0};
+  parallel_for(n, n_threads_, [&](size_t i, int) {
+    const SpecHdr& h = hdrs[i];
+    if ((u64)h.cand_off + h.ncand > ncand) { bad = 1; return; }
+    if (specs[i].kind > K_MATMUL || specs[i].spec_shape.n > MAX_RANK) { bad = 2; return; }
+    for (int o = 0; o < specs[i].nops(); o++)
+      if (specs[i].aux[o].mem > GL || specs[i].aux[o].layout.n > MAX_PHYS) { bad = 2; return; }
+    if (!have_cands) return;
+    for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
+      const CandRec& r = cands[c];
+      if (r.kind > MRL_CK_BLOCK || r.nchild > 3 || r.level >= NMEM || r.thr_code > 30 || r.late > 1 || (r.kind == MRL_CK_LEAF) != (r.nchild == 0)) { bad = 3; return; }
+      for (int j = 0; j < r.nchild; j++)
+        if (r.child[j] >= n) { bad = 3; return; }
+    }
+  });
+  if (bad.load() == 1) throw ModelError("shared plan: a Spec's candidate range lies outside the records");
+  if (bad.load() == 2) throw ModelError("shared plan: bad Spec");
+  if (bad.load() == 3) throw ModelError("shared plan: bad candidate record");
   assign_owners_();
+}
+
+u64 Plan::fingerprint(int n_threads_) const {
+  const size_t n = specs.size();
+  std::vector<u64> hs(n);
+  parallel_for(n, n_threads_, [&](size_t i, int) {
+    char kb[LogicalSpec::MAX_KEY];
+    const int kl = specs[i].key_into(kb);
+    hs[i] = hash_key(kb, kl) * (2 * (u64)i + 1);
+  });
+  u64 h = 0x243F6A8885A308D3ull ^ (u64)n;
+  for (size_t i = 0; i < n; i++) h = (h ^ hs[i]) * 0x9E3779B97F4A7C15ull + (h >> 29);
+  for (int k = 0; k < NMEM; k++) h = (h ^ top_code[k]) * 0xD6E8FEB86659FD93ull;
+  return h ^ (h >> 31);
 }
 
 bool Plan::pack_limits(const u64 limits[NMEM], u32* out) const {
@@ -353,12 +412,22 @@ bool make_rec(const Candidate& c, const u32* top_code, CandRec& r) {
   return true;
 }
 
-// Evaluation order of a Spec's records is free (the argmin carries the action number): kernels
-// first, then loops and blocks, then Moves by ascending base cost, so that the kernel's
-// lower-bound test on a Move's base cost cuts as early as possible.
+// Evaluation order of a Spec's records is free (the argmin carries the action number). Records
+// whose children all lie in earlier stages come first: kernels, then loops and blocks, then Moves
+// by ascending base cost. Records with a child in the Spec's own stage (relayout Moves) come
+// last, dearest first: the device walks them from the end, cheapest first, and stops at the first
+// one whose base cost alone exceeds the cell's optimum so far.
 u64 cand_rank(const CandRec& c) {
+  if (c.late) return (u64(1) << 40) | (0xFFFFFFFFu - c.imm);
   const u64 k = c.kind == MRL_CK_LEAF ? 0 : (c.kind == MRL_CK_LOOP ? 1 : (c.kind == MRL_CK_BLOCK ? 2 : 3));
   return (k << 32) | (c.kind == MRL_CK_MOVE ? c.imm : 0u);
+}
+// Whether a candidate of `parent` has a child in the parent's own stage.
+bool has_same_stage_child(const LogicalSpec& parent, const Candidate& c) {
+  const u32 sk = stage_key(parent);
+  for (int j = 0; j < c.nchild; j++)
+    if (stage_key(c.child[j]) == sk) return true;
+  return false;
 }
 bool cand_before(const CandRec& a, const CandRec& b) { return cand_rank(a) < cand_rank(b); }
 
@@ -377,7 +446,7 @@ std::pair<u64, u64> twin_hash(const LogicalSpec& g0, Dtype as) {
 }  // namespace
 
 Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits, u32 rank, u32 world,
-                int mirror_dtype) {
+                int mirror_dtype, u32 flags) {
   if (n_threads < 1) n_threads = 1;
   if (world < 1 || rank >= world) throw ModelError("bad shard rank / world size");
   Plan plan;
@@ -398,7 +467,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // each other's images under swapping the dtype, only the first dtype is discovered and
   // tabulated: a Spec's Moves, tile-outs and splits depend on the dtype's size only, so the twin's
   // records are the same with its own leaf kernels put in (step 2). A sample of the twins is
-  // tabulated directly afterwards and compared. MRL_NO_TWIN disables this.
+  // tabulated directly afterwards and compared. PLAN_NO_TWINS disables this.
   bool twin = false;
   Dtype dt_a = DT_U8, dt_b = DT_U8;
   const bool mirrored = mirror_dtype >= 0 && !goals.empty();   // the caller vouches: goals come in one dtype, mirror them
@@ -415,7 +484,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     int n_dt = 0;
     for (int d = 0; d < 8; d++)
       if (seen[d]) { if (n_dt == 0) dt_a = (Dtype)d; else dt_b = (Dtype)d; n_dt++; }
-    if (n_dt == 2 && dtype_size(dt_a) == dtype_size(dt_b) && !getenv("MRL_NO_TWIN")) {
+    if (n_dt == 2 && dtype_size(dt_a) == dtype_size(dt_b) && !(flags & PLAN_NO_TWINS)) {
       std::vector<std::pair<u64, u64>> ha, hb;
       std::vector<std::pair<u64, u64>> all(goals.size());
       parallel_for(goals.size(), n_threads, [&](size_t i, int) { all[i] = twin_hash(goals[i], dt_a); });
@@ -457,7 +526,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // Per thread: the Moves of an operand, and the ids of their prologue / epilogue Move Specs, are
   // worked out once and reused by every Spec that has the operand.
   std::vector<std::unique_ptr<MoveMemo>> move_memos(n_threads);
-  if (!getenv("MRL_NO_MEMO"))   // without: every Spec is tabulated from scratch (for cross-checks)
+  if (!(flags & PLAN_NO_MEMO))   // without: every Spec is tabulated from scratch (for cross-checks)
     for (auto& mm : move_memos) mm.reset(new MoveMemo());
   // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
   for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
@@ -494,6 +563,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       for (const Candidate& c : cs) {
         CandRec r;
         const bool keep = make_rec(c, top_code, r);
+        if (keep) r.late = has_same_stage_child(ts.ls, c) ? 1 : 0;
         for (int j = 0; j < c.nchild; j++) {
           const int ki = key_of[next_child++];
           if (!keep) continue;   // the candidate never fits: its children are not part of the closure
@@ -560,7 +630,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       });
     for (auto& th : pool) th.join();
   }
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   sort ids %.2fs\n", now_s() - t1);
   // Final ids. Without twins: the sorted position. With twins every stage holds its discovered
   // Specs followed by their twins (the key orders by dtype right after the kind, and dt_a < dt_b):
   // position i of a stage that starts at sorted position lo and has cnt Specs becomes id i + lo,
@@ -616,7 +685,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   const u64 ncand = offs[N];
   if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
   plan.cands.reset(ncand);
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]     counted cands %.2fs\n", now_s() - t1);
   {
     std::vector<u64> kids_t(1, 0);
     parallel_for(n, n_threads, [&](size_t i, int) {
@@ -665,7 +733,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     });
     plan.stats.n_children += kids_t[0];
   }
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   move specs+cands %.2fs\n", now_s() - t1);
   // The temporary Specs are taken apart by a few threads of their own while the rest of the
   // plan is built; whoever drops the plan's handle last (normally the end of this function)
   // waits for them.
@@ -680,7 +747,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     });
   }
   // from here on everything is about the final arrays (N Specs)
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   free temp %.2fs\n", now_s() - t1);
   // id lookup table for find(): open addressing over the Spec key hash, ids only (equality is
   // checked on the Spec itself)
   {
@@ -708,7 +774,6 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       }
     });
   }
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   find table %.2fs\n", now_s() - t1);
 
   // stages, and inside them families: maximal runs with equal dtype and shape (ids are
   // key-sorted, and the key starts with kind, dtype, serial flag, rank, shape)
@@ -769,12 +834,17 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       const SpecHdr& h = plan.hdrs[i];
       for (u32 c = h.cand_off; c < h.cand_off + h.ncand; c++) {
         const CandRec& r = plan.cands[c];
+        if (c > h.cand_off && plan.cands[c - 1].late && (!r.late || r.imm > plan.cands[c - 1].imm)) { bad = 4; bad_pair = ((u64)i << 32) | i; }
+        bool any_same = false;
+        for (int j = 0; j < r.nchild; j++) any_same |= stage_of[r.child[j]] == stage_of[i];
+        if (any_same != (r.late != 0)) { bad = 4; bad_pair = ((u64)i << 32) | i; }
         for (int j = 0; j < r.nchild; j++) {
           const u32 ch = r.child[j];
           int what = 0;
           if (stage_of[ch] > stage_of[i]) what = 1;
+          else if (stage_of[ch] < stage_of[i]) { /* finished before the parent's stage starts */ }
           else if (stage_of[ch] == stage_of[i]) {
-            if (r.kind != MRL_CK_MOVE || r.units == 0 || fam_of[ch] != fam_of[i]) what = 2;
+            if (r.kind != MRL_CK_MOVE || r.units == 0 || fam_of[ch] != fam_of[i] || !r.late) what = 2;
             else if (sharded && plan.owner[ch] != plan.owner[i]) what = 3;
           }
           if (what) { bad = what; bad_pair = ((u64)i << 32) | ch; }
@@ -786,8 +856,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (bad.load() == 1) throw ModelError("planner: a child Spec lies in a later stage than its parent" + who);
     if (bad.load() == 2) throw ModelError("planner: a same-stage child is not below its parent in the limits lattice" + who);
     if (bad.load() == 3) throw ModelError("planner: a same-stage child belongs to another rank than its parent" + who);
+    if (bad.load() == 4) throw ModelError("planner: records with a same-stage child are not flagged or not stored last, dearest first" + who);
   }
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   stages, owners, order check %.2fs\n", now_s() - t1);
   if (twin) {
     // Sample check of the twin derivation: tabulate every 2039th Spec (originals and twins alike)
     // directly and compare with the records built above, byte for byte.
@@ -801,6 +871,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       for (const Candidate& c : cs) {
         CandRec r;
         if (!make_rec(c, top_code, r)) continue;
+        r.late = has_same_stage_child(plan.specs[id], c) ? 1 : 0;
         for (int j = 0; j < c.nchild; j++) {
           const long ch = plan.find(c.child[j]);
           if (ch < 0) { bad = id; return; }
@@ -815,16 +886,46 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (bad.load() >= 0)
       throw ModelError("planner: records derived for a dtype twin differ from direct tabulation: " + plan.specs[(u32)bad.load()].str());
   }
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   twin sample check %.2fs\n", now_s() - t1);
   plan.cleanup_.reset();   // waits for the release of the temporaries
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan]   temporaries released %.2fs\n", now_s() - t1);
   plan.stats.seconds_layout = now_s() - t1;
-  if (getenv("MRL_PLAN_TIMING")) fprintf(stderr, "[plan] discover %.2fs, ids/stages/families %.2fs\n", plan.stats.seconds_discover, plan.stats.seconds_layout);
 
   plan.stats.n_specs = N;
   plan.stats.n_cands = ncand;
   plan.stats.n_stages = plan.stages.size();
   plan.stats.n_families = plan.families.size();
+  return plan;
+}
+
+Plan table_only_plan(RawVec<LogicalSpec>&& specs, RawVec<SpecHdr>&& hdrs, const u32* top_code, int n_threads) {
+  if (specs.size() != hdrs.size()) throw ModelError("saved table: Specs and headers differ in number");
+  if (n_threads < 1) n_threads = 1;
+  Plan plan;
+  plan.n_threads = n_threads;
+  for (int k = 0; k < NMEM; k++) {
+    if (top_code[k] > 30) throw ModelError("saved table: bad top limits");
+    plan.top_code[k] = top_code[k];
+  }
+  plan.specs = std::move(specs);
+  plan.hdrs = std::move(hdrs);
+  const u32 N = (u32)plan.specs.size();
+  size_t cap = 64;
+  while (cap < (size_t)N * 2) cap *= 2;
+  plan.find_tab_.assign(cap, 0xFFFFFFFFu);
+  const size_t mask = cap - 1;
+  u32* tab = plan.find_tab_.data();
+  parallel_for(N, n_threads, [&](size_t i, int) {
+    char kb[LogicalSpec::MAX_KEY];
+    const int kl = plan.specs[i].key_into(kb);
+    size_t j = (size_t)hash_key(kb, kl) & mask;
+    for (;;) {
+      u32 expect = 0xFFFFFFFFu;
+      if (__atomic_load_n(&tab[j], __ATOMIC_RELAXED) == expect &&
+          __atomic_compare_exchange_n(&tab[j], &expect, (u32)i, false, __ATOMIC_RELAXED, __ATOMIC_RELAXED))
+        break;
+      j = (j + 1) & mask;
+    }
+  });
+  plan.stats.n_specs = N;
   return plan;
 }
 

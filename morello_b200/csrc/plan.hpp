@@ -18,7 +18,6 @@
 #include "model/space.hpp"
 #include "device_types.h"
 #include <cstdlib>
-#include <sys/mman.h>
 #include <new>
 #include <string>
 #include <memory>
@@ -47,12 +46,10 @@ class RawVec {
     if (n) {
       const size_t bytes = n * sizeof(T);
       if (bytes >= (size_t(64) << 20)) {
-        // large arrays are 2 MiB-aligned; with MRL_HUGEPAGE set they are advised for huge pages
-        // (one page fault per 2 MiB for the threads that first touch them; off by default:
-        // where the kernel has to compact memory to grant them the faults get slower, not faster)
+        // large arrays are 2 MiB-aligned (huge-page advice was measured: no gain on a GPU host,
+        // eight times slower page faults where the kernel has to compact memory to grant them)
         void* q = nullptr;
         if (posix_memalign(&q, size_t(2) << 20, bytes) != 0) throw std::bad_alloc();
-        if (getenv("MRL_HUGEPAGE")) madvise(q, bytes, MADV_HUGEPAGE);
         p_ = static_cast<T*>(q);
       } else {
         p_ = static_cast<T*>(malloc(bytes));
@@ -136,7 +133,11 @@ struct Plan {
   // Receiving side: allocate by size, let the caller fill the ranges (share_blobs gives the
   // pointers), then adopt_done() for this rank of `world`.
   void adopt_alloc(const u64 sizes[N_BLOBS]);
-  void adopt_done(u32 rank, u32 world, int n_threads);
+  // have_cands: the candidate records were received too (they are checked as well).
+  void adopt_done(u32 rank, u32 world, int n_threads, bool have_cands);
+  // 64-bit fingerprint of the job: every Spec key in id order, the candidate count, the top
+  // limits. Two plans with one fingerprint address one table layout.
+  u64 fingerprint(int n_threads) const;
 
   // id of a logical Spec (canonical form), or -1.
   long find(const LogicalSpec& ls) const;
@@ -145,7 +146,8 @@ struct Plan {
   bool pack_limits(const u64 limits[NMEM], u32* out) const;
 
  private:
-  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32, int);
+  friend Plan build_plan(const std::vector<LogicalSpec>&, int, const u64*, u32, u32, int, u32);
+  friend Plan table_only_plan(RawVec<LogicalSpec>&&, RawVec<SpecHdr>&&, const u32*, int);
   std::shared_ptr<void> cleanup_;  // background release of planning temporaries; joined when dropped
   std::vector<u32> find_tab_;  // open-addressing table of ids by Spec key hash (0xFFFFFFFF = empty)
   struct Meta {                // blob 0
@@ -156,11 +158,21 @@ struct Plan {
   void assign_owners_();
 };
 
+// Cross-check modes of the planner: slower, same plan (tests compare).
+enum : u32 {
+  PLAN_NO_TWINS = 1,   // tabulate both dtypes of a mirrored goal set instead of deriving one from the other
+  PLAN_NO_MEMO = 2,    // tabulate every Spec from scratch instead of re-using per-operand results
+};
+
 // Top limits are Avx2Target::max_mem() unless overridden. mirror_dtype >= 0: the goals come in
 // one dtype and the plan also covers their images in that second dtype of the same byte size
 // (what build_plan otherwise detects by itself when handed both goal sets).
 Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64* top_limits = nullptr,
-                u32 rank = 0, u32 world = 1, int mirror_dtype = -1);
+                u32 rank = 0, u32 world = 1, int mirror_dtype = -1, u32 flags = 0);
+
+// A plan that can only answer lookups: Specs and their table headers as a saved database holds
+// them; no candidate records, no stages.
+Plan table_only_plan(RawVec<LogicalSpec>&& specs, RawVec<SpecHdr>&& hdrs, const u32* top_code, int n_threads);
 
 // Goal sets.
 std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::vector<Dtype>& dtypes,

@@ -100,7 +100,13 @@ class SynthesisDatabase:
 
     def _check(self, rc):
         if rc != 0:
-            raise RuntimeError(self._lib.mrl_last_error(self._ctx).decode() or f"status {rc}")
+            err = RuntimeError(self._lib.mrl_last_error(self._ctx).decode() or f"status {rc}")
+            err.status = rc
+            raise err
+
+    def set_plan_flags(self, no_twins: bool = False, no_memo: bool = False):
+        """Cross-check modes of the host planner: the same plan built the slow way."""
+        self._check(self._lib.mrl_set_plan_flags(self._ctx, int(no_twins) | (int(no_memo) << 1)))
 
     # --- search::top_down_many / top_down ---
     def top_down_many(self, goals: Sequence[bytes], limits: Optional[Sequence[Sequence[int]]] = None) -> List[Decision]:
@@ -178,6 +184,10 @@ class SynthesisDatabase:
         if self._lib.mrl_device_cands(self._ctx, C.byref(ptr), C.byref(n)) != 0:
             raise RuntimeError("plan not uploaded")
         return int(ptr.value or 0), int(n.value)
+
+    def cands_arrived(self):
+        """After the candidate records were written into device_cands(): checks them on the device."""
+        self._check(self._lib.mrl_cands_arrived(self._ctx))
 
     def plan_adopt_done(self, plan_seconds: float = 0.0):
         self._check(self._lib.mrl_plan_adopt_done(self._ctx, plan_seconds))
@@ -287,6 +297,54 @@ class SynthesisDatabase:
         out = (L.Decision * n)()
         self._check(self._lib.mrl_export_rows(self._ctx, spec_id, out, n))
         return [Decision.from_c(d) for d in out]
+
+    def checksum(self) -> int:
+        """64-bit checksum of the filled tables (Spec ids, masks, rows in cell order)."""
+        out = C.c_uint64()
+        self._check(self._lib.mrl_checksum(self._ctx, C.byref(out)))
+        return int(out.value)
+
+    def export_all(self):
+        """The whole table in two device-to-host copies: (masks[n_specs, 4] uint32,
+        first_row[n_specs + 1] uint64, rows[n_rows, 4] uint32 = main, peak codes, depth << 16 | action, 0)."""
+        import numpy as np
+        n, n_rows = self.num_specs(), int(self.stats()["n_rows"])
+        masks = np.zeros((n, 4), dtype=np.uint32)
+        first = np.zeros(n + 1, dtype=np.uint64)
+        rows = np.zeros((max(n_rows, 1), 4), dtype=np.uint32)
+        self._check(self._lib.mrl_export_all(self._ctx, masks.ctypes.data, first.ctypes.data, rows.ctypes.data, n_rows))
+        return masks, first, rows[:n_rows]
+
+    def export_rects(self, spec_id: int):
+        """[(lo codes, hi codes, Decision)]: the Spec's table as rectangles over the four limit
+        dimensions, equal neighbours merged (the reference's logical page contents)."""
+        _, cells = self.spec_grid(spec_id)
+        lo = C.create_string_buffer(4 * cells)
+        hi = C.create_string_buffer(4 * cells)
+        out = (L.Decision * cells)()
+        n = self._lib.mrl_export_rects(self._ctx, spec_id, lo, hi, out, cells)
+        if n < 0:
+            self._check(int(n))
+        return [(tuple(lo.raw[4 * i:4 * i + 4]), tuple(hi.raw[4 * i:4 * i + 4]), Decision.from_c(out[i])) for i in range(n)]
+
+    def save(self, path: str):
+        """FilesDatabase::save: the filled tables to one file (written to a temporary, then renamed)."""
+        self._check(self._lib.mrl_save(self._ctx, path.encode()))
+
+    def load(self, path: str):
+        """Reopens a saved database. Lookups work afterwards; with the job's plan already in this
+        context (plan_precompute / plan_goals of the same job) so do verify and fill."""
+        self._check(self._lib.mrl_load(self._ctx, path.encode()))
+
+    def put(self, spec: bytes, limits: Sequence[int], decision: "Decision"):
+        """FilesDatabase::put as a check: succeeds when the tables hold exactly this decision."""
+        d = L.Decision()
+        d.found = 1 if decision.found == 1 else 0
+        d.action, d.main_cost, d.depth = decision.action, decision.main_cost, decision.depth
+        for k in range(4):
+            d.peaks[k] = decision.peaks[k]
+        lim = (C.c_uint64 * 4)(*limits)
+        self._check(self._lib.mrl_put(self._ctx, spec, len(spec), lim, C.byref(d)))
 
     @staticmethod
     def _dtype_mask(dtypes):

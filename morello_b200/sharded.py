@@ -127,12 +127,14 @@ def broadcast_device_cands(db, dist, torch, process_group=None):
     """Copies the planning rank's uploaded candidate records into the other ranks' device buffers."""
     ptr, nbytes = db.device_cands()
     if nbytes == 0 or dist.get_world_size(process_group) == 1:
+        db.cands_arrived()
         return
     src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
     buf = torch.as_tensor(_DeviceBytes(ptr, nbytes), device="cuda")
     step = 1 << 30
     for off in range(0, nbytes, step):
         dist.broadcast(buf[off:off + step], src=src, group=process_group)
+    db.cands_arrived()
 
 
 def precompute_sharded(db, size, dist, torch, through=2, dtypes=(4, 6), process_group=None):

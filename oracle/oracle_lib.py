@@ -9,7 +9,6 @@ import numpy as np
 ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(ORACLE_DIR, "_build", "liboracle.so")
 KAT = os.path.join(ORACLE_DIR, "_build", "kat")
-CLI = os.path.join(ORACLE_DIR, "_build", "oracle_cli")
 
 
 class OrcDecision(C.Structure):
@@ -106,7 +105,6 @@ def load():
         def new(self):
             return Oracle(lib)
         kat_path = KAT
-        cli_path = CLI
     return _Factory()
 
 

@@ -29,15 +29,14 @@ def _same_plan(a, b, size):
 
 
 @pytest.mark.parametrize("size", [1, 2, 4])
-def test_dtype_twin_plan_equals_direct_plan(m, size, monkeypatch):
+def test_dtype_twin_plan_equals_direct_plan(m, size):
     """u32 and f32 goals: the planner tabulates u32 only and derives the f32 records. The result
     must be the plan it builds when both dtypes are tabulated - headers, candidate records,
     stages, families, goal ids and the id lookup table byte for byte, Specs by their blobs."""
-    monkeypatch.delenv("MRL_NO_TWIN", raising=False)
     a = m.SynthesisDatabase(device=-1)
     a.plan_precompute(size)
-    monkeypatch.setenv("MRL_NO_TWIN", "1")
     b = m.SynthesisDatabase(device=-1)
+    b.set_plan_flags(no_twins=True)
     b.plan_precompute(size)
     keys = ("n_specs", "n_goal_specs", "n_candidates", "n_stages")
     sa, sb = a.stats(), b.stats()
@@ -48,15 +47,14 @@ def test_dtype_twin_plan_equals_direct_plan(m, size, monkeypatch):
 
 
 @pytest.mark.parametrize("size", [2, 4])
-def test_memoised_tabulation_equals_tabulation_from_scratch(m, size, monkeypatch):
+def test_memoised_tabulation_equals_tabulation_from_scratch(m, size):
     """The planner reuses, per operand, its Moves and what tiling does to it. The plan must be the
     one built with every Spec tabulated from scratch."""
-    monkeypatch.setenv("MRL_NO_TWIN", "1")
-    monkeypatch.delenv("MRL_NO_MEMO", raising=False)
     a = m.SynthesisDatabase(device=-1)
+    a.set_plan_flags(no_twins=True)
     a.plan_precompute(size)
-    monkeypatch.setenv("MRL_NO_MEMO", "1")
     b = m.SynthesisDatabase(device=-1)
+    b.set_plan_flags(no_twins=True, no_memo=True)
     b.plan_precompute(size)
     _same_plan(a, b, size)
     a.close()
@@ -77,16 +75,15 @@ def test_single_dtype_and_uneven_goal_sets_are_planned_directly(m):
     db.close()
 
 
-def test_mirrored_goal_lists_are_detected(m, monkeypatch):
+def test_mirrored_goal_lists_are_detected(m):
     """top_down_many-style goal lists that contain every goal in both dtypes take the twin path
     too (detected from the goals themselves) and give the direct plan."""
     shapes = ([1, 2, 2, 2], [1, 2, 4, 2], [1, 1, 2, 4])
     goals = [m.simple_spec(m.KIND_MATMUL, dt, sh, m.GL) for dt in (m.DTYPE_F32, m.DTYPE_U32) for sh in shapes]
-    monkeypatch.delenv("MRL_NO_TWIN", raising=False)
     a = m.SynthesisDatabase(device=-1)
     a.plan_goals(goals)
-    monkeypatch.setenv("MRL_NO_TWIN", "1")
     b = m.SynthesisDatabase(device=-1)
+    b.set_plan_flags(no_twins=True)
     b.plan_goals(goals)
     assert a.stats()["n_goal_specs"] == b.stats()["n_goal_specs"] == 6
     _same_plan(a, b, 2)
