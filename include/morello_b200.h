@@ -94,6 +94,15 @@ int mrl_spec_describe(const uint8_t* blob, size_t len, char* out, size_t cap);
 /* Avx2Target::max_mem() (morello/src/target/avx2.rs:59-65). */
 void mrl_max_mem(uint64_t limits[4]);
 
+/* The applicable actions of a Spec as the fill tabulates them (Target::actions,
+ * morello/src/target/cpu.rs:455-823, with each action's solver, morello/src/scheduling/mod.rs:148-167):
+ * per action, in enumeration order, 16 bytes - ActionNum u16, combine kind u8 (0 kernel, 1 loop,
+ * 2 move, 3 block), number of sub-Specs u8, immediate u32 (kernel cost / loop iterations / base move
+ * cost), memory u8 and 3 bytes of padding, units u32 - followed per sub-Spec by its blob length (u16)
+ * and its canonical blob. Host only; for inspection and cross-checks. Returns the number of bytes
+ * written, or a negative status (-3: `cap` too small). */
+long mrl_tabulate(const uint8_t* blob, size_t len, uint8_t* out, size_t cap);
+
 /* Replaces search::top_down_many (morello/src/search/mod.rs:21-42) as called from
  * precompute/src/main.rs:419 and frontend/src/main.rs:296: canonicalises each goal, fills the
  * tables for the goals' whole dependency closure on the GPU and returns each goal's decision

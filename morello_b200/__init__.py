@@ -7,8 +7,8 @@ Python mirror of the reference's search/database interface for this path:
 """
 from .db import (Decision, SynthesisDatabase, MAX_MEM, KIND_MOVE, KIND_FILL_ZERO, KIND_MATMUL_ACCUM, KIND_MATMUL,
                  DTYPE_U32, DTYPE_F32, RF, VRF, L1, GL, THROUGH_MOVE, THROUGH_ZERO, THROUGH_MATMUL, simple_spec,
-                 describe_spec)
+                 describe_spec, tabulate)
 
-__all__ = ["Decision", "SynthesisDatabase", "MAX_MEM", "simple_spec", "describe_spec", "KIND_MOVE", "KIND_FILL_ZERO",
+__all__ = ["Decision", "SynthesisDatabase", "MAX_MEM", "simple_spec", "describe_spec", "tabulate", "KIND_MOVE", "KIND_FILL_ZERO",
            "KIND_MATMUL_ACCUM", "KIND_MATMUL", "DTYPE_U32", "DTYPE_F32", "RF", "VRF", "L1", "GL", "THROUGH_MOVE",
            "THROUGH_ZERO", "THROUGH_MATMUL"]

@@ -70,6 +70,7 @@ EXPORTS = {
     "mrl_spec_blob": (C.c_int, [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t]),
     "mrl_spec_grid": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
     "mrl_export_rows": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(Decision), C.c_size_t]),
+    "mrl_tabulate": (C.c_long, [C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t]),
     "mrl_set_plan_flags": (C.c_int, [C.c_void_p, C.c_uint32]),
     "mrl_cands_arrived": (C.c_int, [C.c_void_p]),
     "mrl_checksum": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),

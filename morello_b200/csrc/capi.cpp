@@ -192,6 +192,34 @@ int mrl_spec_describe(const uint8_t* blob, size_t len, char* out, size_t cap) {
   }
 }
 
+long mrl_tabulate(const uint8_t* blob, size_t len, uint8_t* out, size_t cap) {
+  try {
+    LogicalSpec ls = LogicalSpec::from_key(std::string((const char*)blob, len));
+    if (logicalspec_canonicalize(ls) != CANON_OK) return -4;
+    std::vector<Candidate> cs;
+    tabulate_candidates(ls, cs);
+    std::string buf;
+    auto put32 = [&](uint32_t v) { for (int k = 0; k < 4; k++) buf.push_back((char)(v >> (8 * k))); };
+    for (const Candidate& c : cs) {
+      buf.push_back((char)(c.action & 0xff)); buf.push_back((char)(c.action >> 8));
+      buf.push_back((char)c.kind); buf.push_back((char)c.nchild);
+      put32(c.imm);
+      buf.push_back((char)c.level); buf.push_back(0); buf.push_back(0); buf.push_back(0);
+      put32(c.units);
+      for (int j = 0; j < c.nchild; j++) {
+        const std::string k = c.child[j].key();
+        buf.push_back((char)(k.size() & 0xff)); buf.push_back((char)(k.size() >> 8));
+        buf += k;
+      }
+    }
+    if (buf.size() > cap) return -3;
+    memcpy(out, buf.data(), buf.size());
+    return (long)buf.size();
+  } catch (const std::exception&) {
+    return -1;
+  }
+}
+
 void mrl_max_mem(uint64_t limits[4]) { for (int i = 0; i < 4; i++) limits[i] = AVX2_MAX_MEM[i]; }
 
 int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask) {
@@ -776,7 +804,6 @@ int mrl_save(mrl_ctx* ctx, const char* path) {
 
 int mrl_load(mrl_ctx* ctx, const char* path) {
   if (!ctx || !path) return -1;
-  if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to load onto");
   FILE* f = fopen(path, "rb");
   if (!f) return fail(ctx, -1, std::string("cannot open ") + path);
   struct Closer { FILE* f; ~Closer() { fclose(f); } } closer{f};
@@ -813,6 +840,8 @@ int mrl_load(mrl_ctx* ctx, const char* path) {
       if (hdrs[i].row_base > fh.n_rows || cells > fh.n_rows - hdrs[i].row_base) return fail(ctx, -8, "the database file is corrupt (rows)");
       if (blob_end[i] > blobs.size() || (i && blob_end[i] < blob_end[i - 1])) return fail(ctx, -8, "the database file is corrupt (Specs)");
     }
+    // the file is sound as far as the host can tell; from here on a device is needed
+    if (ctx->device < 0) return fail(ctx, -2, "planning-only context: no device to load onto");
     const bool same_job = ctx->planned && !ctx->table_only && ctx->plan.hdrs.size() == n &&
                           ctx->plan.fingerprint(ctx->n_threads) == fh.fingerprint;
     if (!same_job) {

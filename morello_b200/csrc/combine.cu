@@ -1315,11 +1315,14 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
     stage_bytes_ = 64 << 10;
     if ((rc = alloc_(&d_stage_, stage_bytes_))) return rc;
     const size_t left = buf_bytes_ > align256(buf_off_) + 2048 ? buf_bytes_ - align256(buf_off_) - 2048 : 0;
-    // per working cell: 16 bytes of row, 8 of cell list, under 1 of chunks; the rest is the table
+    // per working cell: 16 bytes of row, 8 of cell list, under 1 of chunks and work items; the
+    // rest is the table
     chunk_cap_ = left / 64 / sizeof(Chunk);
+    item_cap_ = left / 64 / sizeof(WorkItem);
     temp_cap_ = left * 14 / 32 / sizeof(MrlRow);
     cell_cap_ = left * 7 / 32 / sizeof(CellRef);
-    row_cap_ = (left - left / 32 - left * 14 / 32 - left * 7 / 32) / sizeof(MrlRow);
+    row_cap_ = (left - 2 * (left / 64) - left * 14 / 32 - left * 7 / 32) / sizeof(MrlRow);
+    if (item_cap_ < cell_cap_ / 32 + max_stage_ + 1) return too_large_();
     if (chunk_cap_ == 0 || row_cap_ == 0) return too_large_();
     h_ctl_ = &ctl_pageable_;
   } else {
@@ -1333,10 +1336,10 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
     temp_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage_ * 1000, share / sizeof(MrlRow)));
     cell_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage_ * 600, share / sizeof(CellRef)));
     row_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)n_specs_ * 40, share / sizeof(MrlRow)));
+    item_cap_ = cell_cap_ / 32 + max_stage_ + 1;   // a work item holds at least 32 cells, and every Spec at most one partial item
     if (!h_ctl_) CK(cudaHostAlloc((void**)&h_ctl_, sizeof(FillCtl), cudaHostAllocDefault));
   }
   if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
-  item_cap_ = chunk_cap_ * 2 + max_stage_;
   if ((rc = alloc_((void**)&d_items_, item_cap_ * sizeof(WorkItem)))) return rc;
   if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
   if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;

@@ -50,6 +50,31 @@ def describe_spec(blob: bytes) -> str:
     return buf.value.decode()
 
 
+def tabulate(blob: bytes):
+    """[(ActionNum, combine kind, immediate, memory, units, [sub-Spec blobs])]: the applicable actions
+    of a Spec as the fill tabulates them, in the reference's enumeration order."""
+    lib = L.load()
+    buf = C.create_string_buffer(1 << 18)
+    n = lib.mrl_tabulate(blob, len(blob), buf, len(buf))
+    if n < 0:
+        raise ValueError(f"cannot tabulate Spec (status {n})")
+    raw, p, out = buf.raw[:n], 0, []
+    while p < n:
+        action = int.from_bytes(raw[p:p + 2], "little")
+        kind, nchild = raw[p + 2], raw[p + 3]
+        imm = int.from_bytes(raw[p + 4:p + 8], "little")
+        level = raw[p + 8]
+        units = int.from_bytes(raw[p + 12:p + 16], "little")
+        p += 16
+        children = []
+        for _ in range(nchild):
+            ln = int.from_bytes(raw[p:p + 2], "little")
+            children.append(raw[p + 2:p + 2 + ln])
+            p += 2 + ln
+        out.append((action, kind, imm, level, units, children))
+    return out
+
+
 def _pack(blobs: Sequence[bytes], limits: Optional[Sequence[Sequence[int]]]):
     off = (C.c_uint64 * (len(blobs) + 1))()
     pos = 0

@@ -3,6 +3,8 @@
 #include "../morello_b200/csrc/model/impl_text.hpp"
 #include <algorithm>
 #include <chrono>
+#include <condition_variable>
+#include <deque>
 #include <set>
 #include <thread>
 
@@ -90,6 +92,7 @@ Decision Search::solve(const LogicalSpec& ls, const Limits& limits) {
   const Codes pt = limits_to_codes(limits);
   Decision memo;
   if (db_.get(key, pt, memo)) return memo;
+  if (out_of_time && (stats.solves & 15) == 0 && out_of_time()) throw OutOfTime();
 
   stats.solves++;
   std::vector<Candidate> scratch;
@@ -161,64 +164,144 @@ Decision Search::solve(const LogicalSpec& ls, const Limits& limits) {
   return result;
 }
 
+// The driver's schedule (precompute/src/main.rs:221-241,304-385): phases one after another; inside
+// a phase every bound Spec runs its own sequence of stages (`phase.into_par_iter()`, :229), and the
+// tasks of a stage run in parallel (`stage.into_par_iter()`, :339). One pool of workers serves
+// all of it: a bound whose stage is finished queues the tasks of its next stage.
+namespace {
+struct BoundRun {
+  Bound bound;
+  std::vector<std::vector<std::vector<u32>>> stages;   // task points by stage
+  size_t stage = 0;       // stage whose tasks are queued or running
+  size_t open_tasks = 0;  // of that stage, not finished yet
+};
+struct TaskRef { size_t bound, stage, task; };
+}  // namespace
+
 PrecomputeReport precompute(Database& db, u32 size, Through through, const std::vector<Dtype>& dtypes, int threads,
-                            double time_budget_s, bool* finished, bool cache_candidates) {
+                            double time_budget_s, bool* finished, bool cache_candidates, const double* phase_budget_s,
+                            PhaseReport* phase_reports) {
   auto t0 = std::chrono::steady_clock::now();
   auto elapsed = [&]() { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); };
   PrecomputeReport rep;
   Limits top;
   for (int i = 0; i < NMEM; i++) top[i] = AVX2_MAX_MEM[i];
-  std::atomic<u64> solves{0}, lspecs{0};
-  std::atomic<bool> out_of_time{false};
   if (threads < 1) threads = 1;
+  std::atomic<u64> solves{0}, lspecs{0};
+  std::atomic<u64> busy_ns{0};
+  bool all_finished = true;
 
-  for (auto& phase : goal_phases(size, through, dtypes)) {
-    for (const Bound& bound : phase) {
-      for (auto& stage : diagonals(bound_point(bound))) {
-        // Tasks of one stage run in parallel and share the database
-        // (precompute/src/main.rs:339); each task walks its limits worklist serially.
-        std::atomic<size_t> next_task{0};
-        auto worker = [&]() {
-          Search search(db, cache_candidates);
-          while (true) {
-            size_t t = next_task.fetch_add(1);
-            if (t >= stage.size() || out_of_time.load()) break;
-            std::vector<LogicalSpec> task = task_point_specs(bound, stage[t]);
-            lspecs += task.size();
-            std::vector<std::pair<LogicalSpec, Limits>> worklist;
-            for (auto& l : task) worklist.push_back({l, top});
-            while (!worklist.empty()) {
-              std::set<std::pair<std::string, Limits>> next;  // dedup like the HashSet at :346,361
-              for (auto& w : worklist) {
-                if (time_budget_s > 0 && elapsed() > time_budget_s) { out_of_time = true; break; }
-                Decision d = search.solve(w.first, w.second);
-                if (d.found)
-                  for (const Limits& l : next_limits(w.second, d.cost.peaks)) next.insert({w.first.key(), l});
-              }
-              worklist.clear();
-              for (auto& n : next) worklist.push_back({LogicalSpec::from_key(n.first), n.second});
-              if (out_of_time.load() || (time_budget_s > 0 && elapsed() > time_budget_s)) { out_of_time = true; break; }
-            }
-          }
-          solves += search.stats.solves;
-        };
-        if (threads == 1) worker();
-        else {
-          std::vector<std::thread> pool;
-          for (int i = 0; i < threads; i++) pool.emplace_back(worker);
-          for (auto& th : pool) th.join();
-        }
-        if (out_of_time.load()) break;
-      }
-      if (out_of_time.load()) break;
+  auto phases = goal_phases(size, through, dtypes);
+  for (size_t pi = 0; pi < phases.size(); pi++) {
+    const double phase_start = elapsed();
+    const double phase_budget = phase_budget_s ? phase_budget_s[pi] : 0.0;
+    auto out_of_time_now = [&]() {
+      if (time_budget_s > 0 && elapsed() > time_budget_s) return true;
+      return phase_budget > 0 && elapsed() - phase_start > phase_budget;
+    };
+    std::vector<BoundRun> runs;
+    for (const Bound& b : phases[pi]) {
+      BoundRun r;
+      r.bound = b;
+      r.stages = diagonals(bound_point(b));
+      runs.push_back(std::move(r));
     }
-    if (out_of_time.load()) break;
+    std::mutex mu;
+    std::condition_variable cv;
+    std::deque<TaskRef> queue;
+    size_t bounds_open = 0;
+    std::atomic<bool> stop{false};
+    std::atomic<u64> phase_lspecs{0};
+    const u64 puts_before = db.puts.load();
+    auto queue_stage = [&](size_t bi) {   // under mu; skips empty stages
+      BoundRun& r = runs[bi];
+      while (r.stage < r.stages.size() && r.stages[r.stage].empty()) r.stage++;
+      if (r.stage >= r.stages.size()) return false;
+      r.open_tasks = r.stages[r.stage].size();
+      for (size_t t = 0; t < r.open_tasks; t++) queue.push_back(TaskRef{bi, r.stage, t});
+      return true;
+    };
+    {
+      std::lock_guard<std::mutex> g(mu);
+      for (size_t bi = 0; bi < runs.size(); bi++)
+        if (queue_stage(bi)) bounds_open++;
+    }
+    auto worker = [&]() {
+      Search search(db, cache_candidates);
+      if (time_budget_s > 0 || phase_budget > 0) search.out_of_time = [&]() { return stop.load() || out_of_time_now(); };
+      for (;;) {
+        TaskRef ref;
+        {
+          std::unique_lock<std::mutex> lk(mu);
+          cv.wait(lk, [&]() { return !queue.empty() || bounds_open == 0 || stop.load(); });
+          if (stop.load() || (queue.empty() && bounds_open == 0)) break;
+          ref = queue.front();
+          queue.pop_front();
+        }
+        auto w0 = std::chrono::steady_clock::now();
+        const BoundRun& r = runs[ref.bound];
+        std::vector<LogicalSpec> task = task_point_specs(r.bound, r.stages[ref.stage][ref.task]);
+        bool complete = true;
+        // every Spec of the task at the top limits, then the limits worklist (main.rs:340-361)
+        std::vector<std::pair<LogicalSpec, Limits>> worklist;
+        for (auto& l : task) worklist.push_back({l, top});
+        while (!worklist.empty() && complete) {
+          std::set<std::pair<std::string, Limits>> next;  // dedup like the HashSet at :346,361
+          for (auto& w : worklist) {
+            if (stop.load() || out_of_time_now()) { complete = false; break; }
+            Decision d;
+            try {
+              d = search.solve(w.first, w.second);
+            } catch (const Search::OutOfTime&) {
+              complete = false;
+              break;
+            }
+            if (d.found)
+              for (const Limits& l : next_limits(w.second, d.cost.peaks)) next.insert({w.first.key(), l});
+          }
+          worklist.clear();
+          for (auto& n : next) worklist.push_back({LogicalSpec::from_key(n.first), n.second});
+        }
+        busy_ns += (u64)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - w0).count();
+        if (complete) phase_lspecs += task.size();
+        {
+          std::lock_guard<std::mutex> g(mu);
+          if (!complete) stop = true;
+          BoundRun& rr = runs[ref.bound];
+          if (--rr.open_tasks == 0 && !stop.load()) {
+            rr.stage++;
+            if (!queue_stage(ref.bound)) bounds_open--;
+          }
+        }
+        cv.notify_all();
+      }
+      solves += search.stats.solves;
+    };
+    if (threads == 1) worker();
+    else {
+      std::vector<std::thread> pool;
+      for (int i = 0; i < threads; i++) pool.emplace_back(worker);
+      for (auto& th : pool) th.join();
+    }
+    lspecs += phase_lspecs.load();
+    if (phase_reports) {
+      phase_reports[pi].seconds = elapsed() - phase_start;
+      phase_reports[pi].logical_specs = phase_lspecs.load();
+      phase_reports[pi].puts = db.puts.load() - puts_before;
+      phase_reports[pi].finished = !stop.load();
+    }
+    if (stop.load()) {
+      all_finished = false;
+      if (!phase_budget_s) break;                                     // one budget for the whole run: it is spent
+      if (time_budget_s > 0 && elapsed() > time_budget_s) break;
+    }
   }
-  if (finished) *finished = !out_of_time.load();
+  if (finished) *finished = all_finished;
   rep.seconds = elapsed();
   rep.puts = db.puts.load();
   rep.logical_specs = lspecs.load();
   rep.solves = solves.load();
+  rep.busy_seconds = busy_ns.load() * 1e-9;
   return rep;
 }
 
@@ -254,7 +337,8 @@ void orc_destroy(void* h) { delete (OrcHandle*)h; }
 
 // Faithful precompute. dtype_mask bit0 = u32, bit1 = f32. Returns 0, or -1 on a model error.
 int orc_precompute(void* h, uint32_t size, int through, int dtype_mask, int threads, double time_budget_s,
-                   int cache_candidates, double* seconds, uint64_t* puts, uint64_t* logical_specs, uint64_t* solves, int* finished) {
+                   int cache_candidates, double* seconds, uint64_t* puts, uint64_t* logical_specs, uint64_t* solves, int* finished,
+                   double* busy_seconds) {
   try {
     std::vector<Dtype> dts;
     if (dtype_mask & 1) dts.push_back(DT_U32);
@@ -266,6 +350,37 @@ int orc_precompute(void* h, uint32_t size, int through, int dtype_mask, int thre
     if (logical_specs) *logical_specs = r.logical_specs;
     if (solves) *solves = r.solves;
     if (finished) *finished = fin ? 1 : 0;
+    if (busy_seconds) *busy_seconds = r.busy_seconds;
+    return 0;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "oracle error: %s\n", e.what());
+    return -1;
+  }
+}
+
+// The same under one time budget per phase (Move, Zero, Matmul): each phase runs its own stage
+// order until its budget is spent, then the next phase starts on what is in the database so far.
+// phase_out: per phase seconds, goal Specs completed, puts, finished flag.
+int orc_precompute_phases(void* h, uint32_t size, int through, int dtype_mask, int threads, const double* phase_budget_s,
+                          double* seconds, double* busy_seconds, uint64_t* puts, uint64_t* logical_specs, double* phase_seconds,
+                          uint64_t* phase_specs, uint64_t* phase_puts, int* phase_finished) {
+  try {
+    std::vector<Dtype> dts;
+    if (dtype_mask & 1) dts.push_back(DT_U32);
+    if (dtype_mask & 2) dts.push_back(DT_F32);
+    PhaseReport pr[3];
+    bool fin = false;
+    PrecomputeReport r = precompute(((OrcHandle*)h)->db, size, (Through)through, dts, threads, 0.0, &fin, false, phase_budget_s, pr);
+    if (seconds) *seconds = r.seconds;
+    if (busy_seconds) *busy_seconds = r.busy_seconds;
+    if (puts) *puts = r.puts;
+    if (logical_specs) *logical_specs = r.logical_specs;
+    for (int k = 0; k <= through && k < 3; k++) {
+      if (phase_seconds) phase_seconds[k] = pr[k].seconds;
+      if (phase_specs) phase_specs[k] = pr[k].logical_specs;
+      if (phase_puts) phase_puts[k] = pr[k].puts;
+      if (phase_finished) phase_finished[k] = pr[k].finished ? 1 : 0;
+    }
     return 0;
   } catch (const std::exception& e) {
     fprintf(stderr, "oracle error: %s\n", e.what());

@@ -298,6 +298,10 @@ class Search {
   explicit Search(Database& db, bool cache_candidates = false) : db_(db), cache_(cache_candidates) {}
   Decision solve(const LogicalSpec& ls, const Limits& limits);  // algo::solve_node
   SolveStats stats;
+  // A timed run gives up in the middle of a recursion: solve() throws OutOfTime once this
+  // returns true. Nothing half-done reaches the database (puts happen when a solve completes).
+  std::function<bool()> out_of_time;
+  struct OutOfTime {};
  private:
   const std::vector<Candidate>& candidates_for(const LogicalSpec& ls, const std::string& key,
                                                std::vector<Candidate>& scratch);
@@ -306,14 +310,23 @@ class Search {
   std::unordered_map<std::string, std::vector<Candidate>> cand_cache_;
 };
 
-// The precompute driver (precompute/src/main.rs:172-386). Returns wall seconds.
+// The precompute driver (precompute/src/main.rs:172-386).
 struct PrecomputeReport {
-  double seconds = 0;
+  double seconds = 0;        // wall
+  double busy_seconds = 0;   // summed over the workers: time spent inside tasks
   u64 puts = 0;
-  u64 logical_specs = 0;
+  u64 logical_specs = 0;     // goal Specs whose whole limits staircase was completed
   u64 solves = 0;
 };
+struct PhaseReport {
+  double seconds = 0;
+  u64 logical_specs = 0, puts = 0;
+  bool finished = false;
+};
+// time_budget_s > 0: stop when the whole run has taken that long. phase_budget_s (one entry per
+// phase): stop a phase when it has, and go on with the next one.
 PrecomputeReport precompute(Database& db, u32 size, Through through, const std::vector<Dtype>& dtypes, int threads,
-                            double time_budget_s /* <=0: none */, bool* finished, bool cache_candidates = false);
+                            double time_budget_s /* <=0: none */, bool* finished, bool cache_candidates = false,
+                            const double* phase_budget_s = nullptr, PhaseReport* phase_reports = nullptr);
 
 }  // namespace orc

@@ -39,12 +39,30 @@ class Oracle:
         sec = C.c_double()
         puts, lspecs, solves = C.c_uint64(), C.c_uint64(), C.c_uint64()
         fin = C.c_int()
+        busy = C.c_double()
         rc = self.lib.orc_precompute(self.h, size, through, dtype_mask, threads, budget_s, int(cache), C.byref(sec),
-                                     C.byref(puts), C.byref(lspecs), C.byref(solves), C.byref(fin))
+                                     C.byref(puts), C.byref(lspecs), C.byref(solves), C.byref(fin), C.byref(busy))
         if rc != 0:
             raise RuntimeError("oracle precompute failed")
         return {"seconds": sec.value, "puts": puts.value, "logical_specs": lspecs.value, "solves": solves.value,
-                "finished": bool(fin.value)}
+                "finished": bool(fin.value), "busy_seconds": busy.value}
+
+    def precompute_phases(self, size, phase_budgets_s, through=2, dtype_mask=3, threads=1):
+        """The driver with one time budget per phase (Move, Zero, Matmul): a sample that reaches every
+        phase. Returns totals and, per phase, seconds / goal Specs completed / puts / finished."""
+        n = through + 1
+        budgets = (C.c_double * 3)(*(list(phase_budgets_s) + [0.0] * 3)[:3])
+        sec, busy = C.c_double(), C.c_double()
+        puts, lspecs = C.c_uint64(), C.c_uint64()
+        psec, pspecs, pputs, pfin = (C.c_double * 3)(), (C.c_uint64 * 3)(), (C.c_uint64 * 3)(), (C.c_int * 3)()
+        rc = self.lib.orc_precompute_phases(self.h, size, through, dtype_mask, threads, budgets, C.byref(sec), C.byref(busy),
+                                            C.byref(puts), C.byref(lspecs), psec, pspecs, pputs, pfin)
+        if rc != 0:
+            raise RuntimeError("oracle precompute failed")
+        names = ["move", "zero", "matmul"]
+        return {"seconds": sec.value, "busy_seconds": busy.value, "puts": puts.value, "logical_specs": lspecs.value,
+                "phases": [{"phase": names[k], "seconds": psec[k], "goal_specs_completed": int(pspecs[k]),
+                            "puts": int(pputs[k]), "finished": bool(pfin[k])} for k in range(n)]}
 
     def top_down(self, key: bytes, limits):
         lim = (C.c_uint64 * 4)(*limits)
@@ -92,7 +110,11 @@ def load():
     lib.orc_destroy.argtypes = [C.c_void_p]
     lib.orc_precompute.argtypes = [C.c_void_p, C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int,
                                    C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
-                                   C.POINTER(C.c_uint64), C.POINTER(C.c_int)]
+                                   C.POINTER(C.c_uint64), C.POINTER(C.c_int), C.POINTER(C.c_double)]
+    lib.orc_precompute_phases.argtypes = [C.c_void_p, C.c_uint32, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double),
+                                          C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64),
+                                          C.POINTER(C.c_uint64), C.POINTER(C.c_double), C.POINTER(C.c_uint64),
+                                          C.POINTER(C.c_uint64), C.POINTER(C.c_int)]
     lib.orc_top_down.argtypes = [C.c_void_p, C.c_char_p, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(OrcDecision)]
     lib.orc_num_puts.restype = C.c_uint64
     lib.orc_num_puts.argtypes = [C.c_void_p]

@@ -7,6 +7,12 @@ filled-database contents, so these vectors come from the C++ oracle under oracle
 itself pinned by the reference's in-tree known-answer tests (oracle/kat.cpp). Each .npz holds
 every `put` of one oracle run: Spec blobs, the rectangle [lo..hi] of the limits lattice the put
 fills (lattice codes: registers raw, caches bit length) and the decision stored there.
+
+    python tests/golden/make_golden.py --saved-database      # on a machine with a GPU
+
+writes precompute_1.mrldb: the size-1 precompute filled by the CUDA path and saved with mrl_save
+(after its contents were checked against the oracle's puts). The CPU tests use it to exercise the
+loader's file validation.
 """
 import os
 import sys
@@ -61,5 +67,25 @@ def main():
         o.close()
 
 
+def saved_database():
+    import morello_b200 as m
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import parity_util
+    o = oracle_lib.load().new()
+    o.precompute(1)
+    db = m.SynthesisDatabase(device=0)
+    db.precompute(1)
+    bad = parity_util.compare_puts(db, *o.dump())
+    assert not bad, bad
+    path = os.path.join(HERE, "precompute_1.mrldb")
+    db.save(path)
+    print("precompute_1.mrldb", os.path.getsize(path), "bytes, checksum %016x" % db.checksum())
+    db.close()
+    o.close()
+
+
 if __name__ == "__main__":
-    main()
+    if "--saved-database" in sys.argv:
+        saved_database()
+    else:
+        main()

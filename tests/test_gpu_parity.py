@@ -196,25 +196,175 @@ def test_verify_notices_a_corrupted_row(m):
     db.close()
 
 
-def test_size8_full_workload_properties(m):
-    """BASELINE config 2 at full size (10.6 M goal Specs): the recurrence at 500 M random
-    (Spec, limits) points, and a second fill reproduces the table bit for bit."""
+def test_size8_full_workload_against_oracle_and_recurrence(m, oracle):
+    """BASELINE config 2 at full size (10.6 M goal Specs), the configuration the benchmark times.
+    The oracle cannot finish it, so every phase (Move, Zero, Matmul) runs its faithful stage order
+    under a time budget and every put it made is checked against the GPU table at both corners of
+    its rectangle; the recurrence is checked at 500 M random (Spec, limits) points; and a second
+    fill reproduces the table bit for bit."""
+    import os
     import torch
     from morello_b200 import sharded
+    o = oracle.new()
+    rep = o.precompute_phases(8, [8.0, 8.0, 8.0], threads=os.cpu_count() or 1)
+    assert o.dominance_conflicts() == 0
+    assert all(p["goal_specs_completed"] > 0 for p in rep["phases"])   # the sample reaches every phase
+    keys, off, rect, dec = o.dump()
+    assert len(dec) > 100000
     db = m.SynthesisDatabase()
     st = db.precompute(8)
     assert st["n_goal_specs"] == 10613126
+    bad = parity_util.compare_puts(db, keys, off, rect, dec)
+    assert not bad, "\n".join(bad)
+    o.close()
     checked, bad = db.verify(500_000_000, seed=7)
     assert checked == 500_000_000 and bad == 0
     ptr, n = db.device_rows()
     before = torch.as_tensor(sharded._DeviceBytes(ptr, n * sharded.row_bytes()), device="cuda").clone()
+    sum_before = db.checksum()
     db.fill()
     ptr2, n2 = db.device_rows()
     assert n2 == n
     after = torch.as_tensor(sharded._DeviceBytes(ptr2, n2 * sharded.row_bytes()), device="cuda")
-    assert torch.equal(before, after)
+    assert torch.equal(before, after) and db.checksum() == sum_before
     # known answers of the small goals still hold inside the big database
     goal = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
     d = db.get(goal)
     assert (d.found, d.action, d.main_cost, d.depth, d.peaks) == (1, 1, 127, 7, (8, 0, 4, 0))
     db.close()
+
+
+def test_save_load_export_and_put(m, tmp_path):
+    """Persistence and bulk export: a saved database reloads into a fresh context (lookups only) and
+    into a context that holds the job's plan (verify works too) with byte-identical answers; the
+    bulk export, the per-Spec export and the rectangle export agree; put accepts what the tables
+    hold and refuses anything else."""
+    import numpy as np
+    db = m.SynthesisDatabase()
+    st = db.precompute(2)
+    n = db.num_specs()
+    path = str(tmp_path / "p2.mrldb")
+    db.save(path)
+    blobs = [db.spec_blob(i) for i in range(0, n, 7)]
+    limits = [(16 - (i % 5), 16, 1024 >> (i % 4), 33554432) for i in range(len(blobs))]
+    want = db.get_many(blobs, limits)
+    want_sum = db.checksum()
+
+    fresh = m.SynthesisDatabase()
+    fresh.load(path)                      # no plan in this context: lookups only
+    assert fresh.get_many(blobs, limits) == want and fresh.checksum() == want_sum
+    goal = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
+    assert fresh.get_impl(goal) == db.get_impl(goal)
+    with pytest.raises(RuntimeError, match="without their plan"):
+        fresh.verify(10)
+    with pytest.raises(RuntimeError):
+        fresh.fill()
+    fresh.close()
+
+    planned = m.SynthesisDatabase()
+    planned.plan_precompute(2)
+    planned.load(path)                    # same job: the plan's candidate records stay usable
+    assert planned.get_many(blobs, limits) == want
+    assert planned.verify(5_000_000)[1] == 0
+    planned.fill()
+    assert planned.checksum() == want_sum
+    planned.close()
+
+    other = m.SynthesisDatabase()
+    other.plan_precompute(1)              # another job's plan: the file brings its own Specs
+    other.load(path)
+    assert other.num_specs() == n and other.get_many(blobs, limits) == want
+    other.close()
+
+    # a file whose contents were altered after saving fails its checksum
+    raw = bytearray(open(path, "rb").read())
+    raw[-8] ^= 1
+    bad_path = str(tmp_path / "bad.mrldb")
+    open(bad_path, "wb").write(bytes(raw))
+    broken = m.SynthesisDatabase()
+    with pytest.raises(RuntimeError, match="checksum") as e:
+        broken.load(bad_path)
+    assert e.value.status == -8
+    broken.close()
+
+    # bulk export against the per-Spec export and the lookups
+    masks, first, rows = db.export_all()
+    assert masks.shape == (n, 4) and len(rows) == st["n_rows"] == int(first[n])
+    for i in range(0, n, 97):
+        grid_masks, cells = db.spec_grid(i)
+        assert list(masks[i]) == grid_masks and int(first[i + 1] - first[i]) == cells or int(first[i]) + cells <= len(rows)
+        per_spec = db.export_rows(i)
+        for j, dcn in enumerate(per_spec):
+            r = rows[int(first[i]) + j]
+            if dcn.found:
+                assert (int(r[0]), int(r[2]) & 0xFFFF, int(r[2]) >> 16) == (dcn.main_cost, dcn.action, dcn.depth)
+            else:
+                assert int(r[2]) == 0xFFFFFFFF
+        # rectangles: they tile the whole lattice box, and every corner reads back its own decision
+        rects = db.export_rects(i)
+        assert 1 <= len(rects) <= cells
+        volume = 0
+        for lo, hi, dcn in rects:
+            volume += int(np.prod([h - l + 1 for l, h in zip(lo, hi)]))
+        assert volume == 17 * 17 * 12 * 27
+        blob = db.spec_blob(i)
+        for lo, hi, dcn in rects[:6]:
+            for corner in (lo, hi):
+                lim = (corner[0], corner[1], 0 if corner[2] == 0 else 1 << (corner[2] - 1),
+                       0 if corner[3] == 0 else 1 << (corner[3] - 1))
+                assert db.get(blob, lim) == dcn
+    # put: what the tables hold is accepted, anything else refused
+    d = db.get(goal)
+    db.put(goal, m.MAX_MEM, d)
+    wrong = m.Decision(1, d.action, d.main_cost + 1, d.depth, d.peaks)
+    with pytest.raises(RuntimeError, match="another decision") as e:
+        db.put(goal, m.MAX_MEM, wrong)
+    assert e.value.status == -9
+    outside = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 8, 8, 8], m.GL)
+    with pytest.raises(RuntimeError, match="not in the tables"):
+        db.put(outside, m.MAX_MEM, d)
+    db.close()
+
+
+def test_fill_waits_for_device_candidate_records(m):
+    """A plan adopted without its candidate records cannot be filled until they have arrived on
+    the device and passed the device-side check; records that name Specs outside the plan are
+    refused there."""
+    import ctypes
+    import torch
+    from morello_b200 import sharded
+    src = m.SynthesisDatabase()
+    src.set_shard(0, 1)
+    src.precompute(2)
+    blobs = src.plan_share()
+    dst = m.SynthesisDatabase()
+    dst.set_shard(0, 1)
+    ptrs = dst.plan_adopt([nb for _, nb in blobs], cands_on_device_only=True)
+    assert ptrs[3] == 0
+    for k, ((p, nb), q) in enumerate(zip(blobs, ptrs)):
+        if q and nb:
+            ctypes.memmove(q, p, nb)
+    dst.plan_adopt_done()
+    dst.upload()
+    with pytest.raises(RuntimeError, match="candidate records are not on the device") as e:
+        dst.fill()
+    assert e.value.status == -3
+    sptr, sbytes = src.device_cands()
+    dptr, dbytes = dst.device_cands()
+    assert sbytes == dbytes
+    s_t = torch.as_tensor(sharded._DeviceBytes(sptr, sbytes), device="cuda")
+    d_t = torch.as_tensor(sharded._DeviceBytes(dptr, dbytes), device="cuda")
+    d_t.copy_(s_t)
+    d_t.view(torch.int32)[0] |= 9 << 16      # record 0: a combine kind that does not exist
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="do not describe this plan"):
+        dst.cands_arrived()
+    with pytest.raises(RuntimeError, match="candidate records are not on the device"):
+        dst.fill()
+    d_t.copy_(s_t)
+    torch.cuda.synchronize()
+    dst.cands_arrived()
+    dst.fill()
+    assert dst.checksum() == src.checksum()
+    dst.close()
+    src.close()

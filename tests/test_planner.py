@@ -117,3 +117,106 @@ def test_calls_out_of_order_fail_cleanly(m):
         db.upload()          # planning-only context
     assert db.spec_owners() == bytes(db.num_specs())   # not sharded: everything belongs to rank 0
     db.close()
+
+
+def _adopt_copy(m, src, corrupt=None, cands_on_device_only=False):
+    """A second planning context that adopts src's plan byte for byte; corrupt(k, bytearray) may
+    change range k on the way."""
+    blobs = src.plan_share()
+    dst = m.SynthesisDatabase(device=-1)
+    ptrs = dst.plan_adopt([n for _, n in blobs], cands_on_device_only)
+    for k, ((p, n), q) in enumerate(zip(blobs, ptrs)):
+        if q == 0 or n == 0:
+            continue
+        data = bytearray(ctypes.string_at(p, n))
+        if corrupt:
+            corrupt(k, data)
+        ctypes.memmove(q, bytes(data), n)
+    return dst
+
+
+def test_adopted_plan_is_checked_before_use(m):
+    """A plan that arrives as bytes from another process is validated: stage and family ranges,
+    candidate ranges, child ids, record fields, the id table. Anything off is refused with a status
+    instead of reaching a kernel."""
+    import struct
+    src = m.SynthesisDatabase(device=-1)
+    src.plan_precompute(2)
+    ok = _adopt_copy(m, src)
+    ok.plan_adopt_done()
+    assert ok.stats()["n_specs"] == src.stats()["n_specs"] and ok.stages() == src.stages()
+    ok.close()
+    n_specs = src.num_specs()
+
+    def child_out_of_range(k, data):
+        if k == 3:   # candidate records: 32 bytes each, child ids at offset 16; find one with children
+            for off in range(0, len(data), 32):
+                if data[off + 3] > 0:
+                    struct.pack_into("<I", data, off + 16, n_specs + 7)
+                    return
+
+    def bad_kind(k, data):
+        if k == 3:
+            data[2] = 9
+
+    def cand_range_beyond_records(k, data):
+        if k == 2:   # headers: 32 bytes each, cand_off at 24, ncand at 28
+            struct.pack_into("<I", data, 32 * (n_specs - 1) + 28, 1 << 30)
+
+    def stage_gap(k, data):
+        if k == 4:   # stages: spec_lo, spec_hi, fam_lo, fam_hi, ...
+            lo, hi = struct.unpack_from("<II", data, 20)
+            struct.pack_into("<II", data, 20, lo + 1, hi)
+
+    def bad_goal(k, data):
+        if k == 6:
+            struct.pack_into("<I", data, 0, n_specs)
+
+    def bad_id_table(k, data):
+        if k == 7:
+            struct.pack_into("<I", data, 0, n_specs + 1)
+
+    for corrupt in (child_out_of_range, bad_kind, cand_range_beyond_records, stage_gap, bad_goal, bad_id_table):
+        bad = _adopt_copy(m, src, corrupt)
+        with pytest.raises(RuntimeError, match="shared plan"):
+            bad.plan_adopt_done()
+        bad.close()
+    # without the candidate records on the host (they travel device to device) the rest is still checked
+    partial = _adopt_copy(m, src, cand_range_beyond_records, cands_on_device_only=True)
+    with pytest.raises(RuntimeError, match="shared plan"):
+        partial.plan_adopt_done()
+    partial.close()
+    src.close()
+
+
+def test_saved_database_files_are_validated_on_the_host(m, tmp_path):
+    """mrl_load reads and checks a file completely before it touches a device: garbage, a
+    truncated file and inconsistent sizes come back as status codes (-7 / -8)."""
+    import os
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "precompute_1.mrldb")
+    data = open(golden, "rb").read()
+    db = m.SynthesisDatabase(device=-1)
+
+    def status_of(blob):
+        path = tmp_path / "x.mrldb"
+        path.write_bytes(blob)
+        try:
+            db.load(str(path))
+        except RuntimeError as e:
+            return e.status, str(e)
+        return 0, ""
+
+    assert status_of(data)[0] == -2 and "no device" in status_of(data)[1]   # a good file gets as far as the device
+    assert status_of(b"not a database")[0] == -7
+    assert status_of(b"MRLB200\0" + bytes(200))[0] == -7                    # version 0
+    assert status_of(data[:len(data) // 2])[0] == -8                         # truncated
+    assert status_of(data + b"\0" * 16)[0] == -8                             # trailing bytes
+    other_target = bytearray(data)
+    other_target[12] = 2                                                      # TARGET tag
+    assert status_of(bytes(other_target))[0] == -7
+    huge = bytearray(data)
+    huge[40:48] = (1 << 60).to_bytes(8, "little")                             # n_specs
+    assert status_of(bytes(huge))[0] == -8
+    with pytest.raises(RuntimeError, match="cannot open"):
+        db.load(str(tmp_path / "missing.mrldb"))
+    db.close()

@@ -28,26 +28,45 @@ def _goals(m):
 
 
 def test_noalloc_matches_allocating_entry_point_twice_in_a_row(m):
+    import torch
     goals, limits = _goals(m)
     db = m.SynthesisDatabase()
     want = db.top_down_many(goals, limits)
     assert any(w.found == 1 for w in want) and any(w.found == 0 for w in want)
-    first = db.top_down_many_noalloc(goals, limits)
+    stats_before = db.stats()
+    rows_before = db.device_rows()
+    first = db.top_down_many_noalloc(goals, limits)   # also the call that resolves the array's address
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     second = db.top_down_many_noalloc(goals, limits)
     assert first == want      # integer results: exact equality is the tolerance
     assert second == want     # the array still holds the first call's contents
     # A different, smaller goal set right after: stale contents must not leak into it.
     sub = goals[5:9]
-    assert db.top_down_many_noalloc(sub, limits[5:9]) == db.top_down_many(sub, limits[5:9])
+    got_sub = db.top_down_many_noalloc(sub, limits[5:9])
+    # What the entry point is for: not a byte of device memory is taken or given back, and the
+    # context's own tables stay as they were.
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert db.stats() == stats_before and db.device_rows() == rows_before
+    assert got_sub == db.top_down_many(sub, limits[5:9])
     db.close()
 
 
 def test_noalloc_refuses_a_fill_beyond_its_fixed_size(m):
     db = m.SynthesisDatabase()
     # the closure of an 8x8x8 Matmul: its plan arrays alone (hundreds of MB) exceed the fixed array
+    import torch
     big = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 8, 8, 8], m.GL)
-    with pytest.raises(RuntimeError, match="no-allocation entry point has"):
+    small = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 1, 1, 1], m.GL)
+    db.top_down_many_noalloc([small])
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    with pytest.raises(RuntimeError, match="no-allocation entry point has") as e:
         db.top_down_many_noalloc([big])
+    assert e.value.status == -5          # its own code: a goal that cannot be canonicalised is -4
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before   # the refusal allocated nothing either
     # the context is still usable, and the allocating entry point takes the same goal
     assert db.top_down(big).found == 1
     db.close()
