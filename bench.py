@@ -41,11 +41,18 @@ LATTICE_POINTS = 17 * 17 * 12 * 27  # RF 0..16, VRF 0..16, L1 and GL as bit leng
 SIZE = 8
 THROUGH = 2
 THROUGH_NAMES = ["move", "zero", "matmul"]
+DTYPES = (4, 6)   # u32, f32: DTYPES of precompute/src/main.rs:55
+DTYPE_NAMES = {4: "u32", 6: "f32"}
 
 
 def workload_name():
-    return ("precompute --target avx2 --through %s %d: Move%s phases only, u32+f32, serial-only bounds"
-            % (THROUGH_NAMES[THROUGH], SIZE, ["", "+Zero", "+Zero+Matmul"][THROUGH]))
+    return ("precompute --target avx2 --through %s %d: Move%s phases only, %s, serial-only bounds"
+            % (THROUGH_NAMES[THROUGH], SIZE, ["", "+Zero", "+Zero+Matmul"][THROUGH],
+               "+".join(DTYPE_NAMES[d] for d in DTYPES)))
+
+
+def dtype_mask():
+    return sum({4: 1, 6: 2}[d] for d in DTYPES)
 
 
 def measured_peaks():
@@ -112,10 +119,10 @@ def run_oracle(threads, budget_s):
     o = oracle_lib.load().new()
     n_phases = THROUGH + 1
     if SIZE <= 2:
-        r = o.precompute(SIZE, through=THROUGH, dtype_mask=3, threads=threads)
+        r = o.precompute(SIZE, through=THROUGH, dtype_mask=dtype_mask(), threads=threads)
         r["phases"] = None
     else:
-        r = o.precompute_phases(SIZE, [budget_s / n_phases] * n_phases, through=THROUGH, dtype_mask=3, threads=threads)
+        r = o.precompute_phases(SIZE, [budget_s / n_phases] * n_phases, through=THROUGH, dtype_mask=dtype_mask(), threads=threads)
         r["finished"] = all(p["finished"] for p in r["phases"])
     r["utilisation"] = r["busy_seconds"] / (r["seconds"] * threads) if r["seconds"] > 0 else None
     return r, o
@@ -218,9 +225,9 @@ def cuda_arm(args):
             db.fill()
 
     if world > 1:
-        sharded.precompute_sharded(db, SIZE, dist, torch, through=THROUGH)
+        sharded.precompute_sharded(db, SIZE, dist, torch, through=THROUGH, dtypes=DTYPES)
     else:
-        db.precompute(SIZE, through=THROUGH)  # plans, uploads, fills: leaves plan and tables on the device
+        db.precompute(SIZE, through=THROUGH, dtypes=DTYPES)  # plans, uploads, fills: leaves plan and tables on the device
     for _ in range(max(args.warmup, 3) - 1):
         one_fill()
 
@@ -236,9 +243,9 @@ def cuda_arm(args):
             dist.barrier()
         t0 = time.perf_counter()
         if world > 1:
-            sharded.precompute_sharded(fresh, SIZE, dist, torch, through=THROUGH)
+            sharded.precompute_sharded(fresh, SIZE, dist, torch, through=THROUGH, dtypes=DTYPES)
         else:
-            fresh.precompute(SIZE, through=THROUGH)
+            fresh.precompute(SIZE, through=THROUGH, dtypes=DTYPES)
         got = fresh.get_many(goal_blobs, [m.MAX_MEM] * len(goal_blobs))
         dt = time.perf_counter() - t0
         e2e_s.append(dt)
@@ -303,7 +310,7 @@ def cuda_arm(args):
         solo_sum = None
         if rank == 0:   # the same workload filled by this GPU alone
             solo = m.SynthesisDatabase(device=local_rank)
-            solo.precompute(SIZE, through=THROUGH)
+            solo.precompute(SIZE, through=THROUGH, dtypes=DTYPES)
             solo_sum = solo.checksum()
             solo.close()
             parity["equals_single_gpu"] = solo_sum == my_sum
@@ -363,7 +370,7 @@ def cuda_arm(args):
         if os.path.exists(traffic_path):
             with open(traffic_path) as f:
                 t = json.load(f).get(str(SIZE) if THROUGH == 2 else "")
-            if t:  # measured DRAM bytes per solved working cell on a small case, scaled to this step (see the file's "how")
+            if t and "dram_bytes_per_cell" in t:  # measured DRAM bytes per solved working cell on a small case, scaled to this step (see the file's "how")
                 traffic = t["dram_bytes_per_cell"] * sum(cells_by_rank)
                 line["roofline"]["traffic"] = traffic
                 line["roofline"]["traffic_how"] = "scaled from a small-case ncu capture: profiles/traffic.json"
@@ -385,15 +392,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--size", type=int, default=8, choices=[1, 2, 4, 8], help="largest Spec dimension of the workload")
+    ap.add_argument("--size", type=int, default=8, choices=[1, 2, 4, 8, 16], help="largest Spec dimension of the workload")
+    ap.add_argument("--dtypes", default="u32,f32", help="u32,f32 (the reference's DTYPES) or one of them")
     ap.add_argument("--through", default="matmul", choices=THROUGH_NAMES, help="last phase of the workload")
     ap.add_argument("--cpu-budget", type=float, default=21.0, help="seconds of CPU work per reference sample")
     ap.add_argument("--verify-samples", type=int, default=100_000_000,
                     help="(Spec, limits) points at which the timed table is checked against its recurrence")
     args = ap.parse_args()
-    global SIZE, THROUGH
+    global SIZE, THROUGH, DTYPES
     SIZE = args.size
     THROUGH = THROUGH_NAMES.index(args.through)
+    DTYPES = tuple({"u32": 4, "f32": 6}[d] for d in args.dtypes.split(","))
     if args.impl == "reference":
         reference_arm(args)
     else:
