@@ -57,6 +57,7 @@ typedef struct mrl_stats {
   double fill_ms;              /* device time of the last fill (CUDA events on the launch stream) */
   double combine_ms;           /* of which inside the solve phases (device timer) */
   double early_ms;             /* of which the phase that needs no order: candidates whose children lie in earlier stages */
+  uint64_t n_sweeps;           /* relaxation sweeps over the candidates with a same-stage child, all passes */
 } mrl_stats;
 
 /* One row of the device table as mrl_export_all hands it out: main cost; peak memory as lattice

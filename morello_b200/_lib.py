@@ -22,7 +22,7 @@ class Stats(C.Structure):
                 ("n_passes", C.c_uint64), ("n_launches", C.c_uint64), ("n_grid_syncs", C.c_uint64),
                 ("algorithmic_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
                 ("plan_seconds", C.c_double), ("upload_seconds", C.c_double), ("fill_ms", C.c_double),
-                ("combine_ms", C.c_double), ("early_ms", C.c_double)]
+                ("combine_ms", C.c_double), ("early_ms", C.c_double), ("n_sweeps", C.c_uint64)]
 
 
 EXPORTS = {

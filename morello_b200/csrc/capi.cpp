@@ -68,6 +68,7 @@ void copy_fill_stats(mrl_ctx* ctx) {
   ctx->stats.fill_ms = fs.fill_ms;
   ctx->stats.combine_ms = fs.combine_ms;
   ctx->stats.early_ms = fs.early_ms;
+  ctx->stats.n_sweeps = fs.sweeps;
 }
 
 // Upload + fill of the planned tables.

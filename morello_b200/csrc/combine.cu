@@ -55,7 +55,10 @@ static_assert(MRL_STATIC_SCRATCH_BYTES == MRL_NOALLOC_MAX_BYTES,
 namespace {
 
 constexpr int kBlock = 128;      // threads per block of every kernel here
-constexpr int kMinBlocks = 8;   // resident blocks per SM the stage kernel is compiled for
+#ifndef MRL_MIN_BLOCKS
+#define MRL_MIN_BLOCKS 8
+#endif
+constexpr int kMinBlocks = MRL_MIN_BLOCKS;   // resident blocks per SM the stage kernel is compiled for
 constexpr int kMaxPasses = 128;
 
 __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
@@ -362,21 +365,60 @@ struct StageArgs {
   uint8_t* dirty;         // by Spec id: 0 keep, 1 solve in the coming pass, 2 being solved in this pass
   Chunk* chunks;
   WorkItem* items;
-  CellRef* cells;
-  DiagTable* diag;
   MrlRow* rows;
   MrlRow* temp;
+  MrlRow* base;                   // as many rows again: what the unordered phase found for each working cell
   uint32_t* fcount;
   unsigned long long* block_sums;
+  uint32_t* minsat;               // by Spec id: lower corner of the satisfiable region (see phase_minsat)
+  uint32_t* corner;               // by position in the stage: the corner its working grids are clipped at
+  uint32_t* stamp;                // by position in the stage: last relaxation sweep that improved a cell of the Spec
   FillCtl* ctl;
   uint32_t lo, hi;                // the stage's Spec ids
+  uint32_t prev_lo, prev_hi;      // the stage before it
   uint32_t top_pack;
   uint32_t stage;
-  unsigned long long temp_cap, chunk_cap, item_cap, cell_cap, row_cap;
+  unsigned long long temp_cap, chunk_cap, item_cap, row_cap;
   int solve, place;               // which halves to run
 };
 
 __device__ __forceinline__ bool computed_here(const StageArgs& a, uint32_t i) { return !a.mine || a.mine[i]; }
+
+// Lower corner of a Spec's satisfiable region: per memory the smallest limit code at which any
+// implementation exists at all, 5 bits each (RF in the low bits); 31 = none anywhere. More memory
+// never loses an implementation, so every limits point with a coordinate below the corner is
+// unsatisfiable. For a finished Spec the corner is exact (read off its table); for a Spec of the
+// stage being solved it is a lower bound worked out from its candidates before anything is solved.
+#define MRL_NEVER 31u
+__device__ __forceinline__ uint32_t corner_of(uint32_t pack, uint32_t k) { return (pack >> (5 * k)) & 31u; }
+
+// Exact corners of the Specs of the stage before this one (their rows are complete, also where
+// another rank computed them). Along memory k the cell with the top slot in every other memory is
+// satisfiable as soon as any cell with that slot in k is.
+__device__ __noinline__ void phase_minsat(const StageArgs& a, uint32_t gtid, uint32_t gthreads) {
+  for (uint32_t i = a.prev_lo + gtid; i < a.prev_hi; i += gthreads) {
+    const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+    const MrlRow* grid = a.rows + a.hdrs[i].row_base;
+    const uint32_t mm[4] = {m.x, m.y, m.z, m.w};
+    uint32_t nn[4], st[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) nn[k] = __popc(mm[k]);
+    st[0] = 1; st[1] = nn[0]; st[2] = nn[0] * nn[1]; st[3] = nn[0] * nn[1] * nn[2];
+    uint32_t top = 0;
+#pragma unroll
+    for (int k = 0; k < 4; k++) top += (nn[k] - 1) * st[k];
+    uint32_t pack = 0;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      uint32_t code = MRL_NEVER;
+      for (uint32_t sl = 0; sl < nn[k]; sl++) {
+        if (grid[top - (nn[k] - 1 - sl) * st[k]].tail != MRL_UNSAT) { code = nth_set_bit(mm[k], sl); break; }
+      }
+      pack |= code << (5 * k);
+    }
+    a.minsat[i] = pack;
+  }
+}
 
 // Pass step 1: per Spec of the stage, the masks its working grid needs. child_source says what
 // is known about same-stage children: 0 = nothing (first pass: they are ignored), 1 = the
@@ -384,19 +426,49 @@ __device__ __forceinline__ bool computed_here(const StageArgs& a, uint32_t i) { 
 // first working masks). A Spec whose masks grew is marked for solving. seed_copy: also copy the
 // new masks to rmask (so that a following phase can read them as the children's breakpoints).
 __device__ __noinline__ void phase_derive(const StageArgs& a, uint32_t gtid, uint32_t gthreads, int first, int child_source,
-                             int seed_copy) {
+                                          int seed_copy, int pass0) {
   for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
     if (!computed_here(a, i)) continue;
     const uint4 old = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
     const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
     uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
+    // lower corner of the Spec's satisfiable region: per memory the minimum over its candidates of
+    // what each needs at least (its threshold; its children's corners, shifted by what a Move takes)
+    uint32_t l0 = MRL_NEVER, l1 = MRL_NEVER, l2 = MRL_NEVER, l3 = MRL_NEVER;
     for (uint32_t ci = 0; ci < cl.y; ci++) {
       const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
       const uint32_t kind = (c.x >> 16) & 0xFFu, nchild = c.x >> 24;
       const uint32_t level = c.z & 0xFFu, thr = (c.z >> 8) & 0xFFu, units = c.w;
       if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
-      if (kind == MRL_CK_LEAF) continue;
+      uint32_t q0 = 0, q1 = 0, q2 = 0, q3 = 0;   // this candidate's corner
+      if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) {
+        q0 = level == 0 ? thr : 0u; q1 = level == 1 ? thr : 0u; q2 = level == 2 ? thr : 0u; q3 = level == 3 ? thr : 0u;
+      }
+      if (kind == MRL_CK_LEAF) {
+        l0 = min(l0, q0); l1 = min(l1, q1); l2 = min(l2, q2); l3 = min(l3, q3);
+        continue;
+      }
       const uint4 b = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]) + 1);
+      bool never = false;
+      for (uint32_t j = 0; j < nchild; j++) {
+        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+        // a finished child's exact corner; a same-stage child's bound so far (zero before the first round)
+        const uint32_t cp = (child < a.lo || !first) ? a.minsat[child] : 0u;
+        uint32_t e0 = corner_of(cp, 0), e1 = corner_of(cp, 1), e2 = corner_of(cp, 2), e3 = corner_of(cp, 3);
+        if (e0 == MRL_NEVER || e1 == MRL_NEVER || e2 == MRL_NEVER || e3 == MRL_NEVER) { never = true; break; }
+        if (kind == MRL_CK_MOVE) {
+          const uint32_t e = sel4(e0, e1, e2, e3, level);
+          uint32_t sh = 0;
+          if (e) {
+            const uint32_t bit = shift_mask(1u << e, level, units, code_of(a.top_pack, level));
+            if (!bit) { never = true; break; }
+            sh = __ffs(bit) - 1;
+          }
+          e0 = level == 0 ? sh : e0; e1 = level == 1 ? sh : e1; e2 = level == 2 ? sh : e2; e3 = level == 3 ? sh : e3;
+        }
+        q0 = max(q0, e0); q1 = max(q1, e1); q2 = max(q2, e2); q3 = max(q3, e3);
+      }
+      if (!never) { l0 = min(l0, q0); l1 = min(l1, q1); l2 = min(l2, q2); l3 = min(l3, q3); }
       for (uint32_t j = 0; j < nchild; j++) {
         const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
         uint4 cm;
@@ -414,7 +486,33 @@ __device__ __noinline__ void phase_derive(const StageArgs& a, uint32_t gtid, uin
         }
       }
     }
-    const uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
+    uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
+    // Clip the grid at the corner: below it everything is unsatisfiable, so one cell [0, corner)
+    // per memory is enough. The corner is settled in the first pass (its two rounds let a bound
+    // travel two relayouts deep) and kept afterwards, so that grids only ever grow.
+    uint32_t corner;
+    if (pass0) {
+      const uint32_t t0 = code_of(a.top_pack, 0), t1 = code_of(a.top_pack, 1), t2 = code_of(a.top_pack, 2), t3 = code_of(a.top_pack, 3);
+      if (l0 > t0 || l1 > t1 || l2 > t2 || l3 > t3) l0 = l1 = l2 = l3 = MRL_NEVER;   // no limits inside the lattice reach it
+      corner = l0 | (l1 << 5) | (l2 << 10) | (l3 << 15);
+      // the first round's bound is what the second round reads for same-stage children; the
+      // second round's goes to an array of its own, so that no thread reads what another writes
+      if (first) a.minsat[i] = corner;
+      a.corner[i - a.lo] = corner;
+    } else {
+      corner = a.corner[i - a.lo];
+    }
+    {
+      const uint32_t k0 = corner_of(corner, 0), k1 = corner_of(corner, 1), k2 = corner_of(corner, 2), k3 = corner_of(corner, 3);
+      if (k0 == MRL_NEVER) {
+        nm = make_uint4(1u, 1u, 1u, 1u);   // unsatisfiable at every limit: a single cell
+      } else {
+        if (k0) nm.x = (nm.x & ~((1u << k0) - 1u)) | 1u | (1u << k0);
+        if (k1) nm.y = (nm.y & ~((1u << k1) - 1u)) | 1u | (1u << k1);
+        if (k2) nm.z = (nm.z & ~((1u << k2) - 1u)) | 1u | (1u << k2);
+        if (k3) nm.w = (nm.w & ~((1u << k3) - 1u)) | 1u | (1u << k3);
+      }
+    }
     const bool changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
     if (changed) {
       *reinterpret_cast<uint4*>(&a.hdrs[i]) = nm;
@@ -518,112 +616,118 @@ __device__ __noinline__ void phase_place(const StageArgs& a, unsigned long long 
   }
 }
 
-// Pass step 3a: how many working cells lie on each limits diagonal. Warp per chunk, thread per column.
-__device__ __noinline__ void phase_histogram(const StageArgs& a, uint32_t n_chunks) {
-  __shared__ uint32_t hist[MRL_MAX_DIAG];
-  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += kBlock) hist[k] = 0;
-  __syncthreads();
-  const uint32_t lane = threadIdx.x & 31;
-  const uint32_t gwarps = gridDim.x * (kBlock / 32);
-  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_chunks; w += gwarps) {
-    const Column c = decode_column(a.hdrs, a.chunks[w], lane);
-    if (!c.valid) continue;
-    for (uint32_t mrest = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F); mrest; mrest &= mrest - 1)
-      atomicAdd(&hist[(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
-  }
-  __syncthreads();
-  for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += kBlock)
-    if (hist[k]) atomicAdd(&a.diag->count[k], hist[k]);
-}
-
-// Pass step 3b (one thread): where each diagonal's cells start in the list, and which diagonals
-// are occupied.
-__device__ void diag_layout(DiagTable* diag) {
-  unsigned long long run = 0;
-  uint32_t n = 0;
-  for (uint32_t d = 0; d < MRL_MAX_DIAG; d++) {
-    diag->base[d] = run;
-    diag->cursor[d] = 0;
-    diag->work[d] = 0;
-    const uint32_t c = diag->count[d];
-    if (c) diag->order[n++] = d;
-    run += c;
-  }
-  diag->n_occupied = n;
-}
-
-// Pass step 3c: lists the working cells diagonal by diagonal. Every warp counts its own cells
-// per diagonal; the block reserves list slots per diagonal with one atomic each and hands every
-// warp a contiguous piece, so that the cells one warp (one Spec) has on a diagonal stay
-// neighbours in the list - and neighbours in a combine warp.
-__device__ __noinline__ void phase_scatter(const StageArgs& a, uint32_t n_chunks) {
-  constexpr int W = kBlock / 32;
-  __shared__ uint32_t hist[W][MRL_MAX_DIAG];
-  __shared__ unsigned long long start[W][MRL_MAX_DIAG];
-  const uint32_t wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t n_groups = (n_chunks + W - 1) / W;
-  for (uint32_t g = blockIdx.x; g < n_groups; g += gridDim.x) {
-    for (uint32_t k = threadIdx.x; k < W * MRL_MAX_DIAG; k += kBlock) hist[k / MRL_MAX_DIAG][k % MRL_MAX_DIAG] = 0;
-    __syncthreads();
-    const uint32_t warp = g * W + wib;
-    Column c;
-    c.valid = false;
-    if (warp < n_chunks) c = decode_column(a.hdrs, a.chunks[warp], lane);
-    const uint32_t mF = c.valid ? sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F) : 0u;
-    for (uint32_t mrest = mF; mrest; mrest &= mrest - 1)
-      atomicAdd(&hist[wib][(c.others + __ffs(mrest) - 1) & (MRL_MAX_DIAG - 1)], 1u);
-    __syncthreads();
-    for (uint32_t k = threadIdx.x; k < MRL_MAX_DIAG; k += kBlock) {
-      uint32_t n = 0;
-      for (int w = 0; w < W; w++) n += hist[w][k];
-      if (n) {
-        unsigned long long at = a.diag->base[k] + atomicAdd(&a.diag->cursor[k], n);
-        for (int w = 0; w < W; w++) { start[w][k] = at; at += hist[w][k]; }
-      }
-      for (int w = 0; w < W; w++) hist[w][k] = 0;   // become the warps' cursors
-    }
-    __syncthreads();
-    if (c.valid) {
-      // the fixed memories' codes, one per byte (RF in byte 0 .. GL in byte 3); the byte of F is 0
-      const uint32_t fixed = c.code[0] | (c.code[1] << 8) | (c.code[2] << 16) | (c.code[3] << 24);
-      for (uint32_t mrest = mF; mrest; mrest &= mrest - 1) {
-        const uint32_t codeF = __ffs(mrest) - 1;
-        const uint32_t d = (c.others + codeF) & (MRL_MAX_DIAG - 1);
-        const uint32_t pos = atomicAdd(&hist[wib][d], 1u);
-        CellRef r;
-        r.spec = c.spec;
-        r.cpack = fixed | (codeF << (8 * c.F));
-        a.cells[start[wib][d] + pos] = r;
-      }
-    }
-    __syncthreads();
-  }
-}
-
 // A candidate record whose body is a Spec of the same stage (a relayout Move): the planner flags
 // it and stores these records after all others, dearest first.
 __device__ __forceinline__ bool is_late(const uint4 a) { return (a.z >> 24) & 1u; }
 
 // Pass step 4a: the candidates whose children all lie in earlier stages, for every cell of every
 // Spec being solved. No order is needed. A warp takes a work item (up to MRL_ITEM_CELLS cells of one
-// Spec) at a time as it finishes others; its lanes take 32 cells at a time and walk the records
-// together: one record, the same child headers, neighbouring child rows.
+// Spec) at a time as it finishes others. Per item it first stages the Spec's records and the
+// headers of their children in shared memory, one record per lane, so that the chain record ->
+// child header -> child row costs two round trips per batch of records instead of two per record;
+// then its lanes take 32 cells at a time and walk the staged records together, and the only
+// global loads left in that loop are the child rows.
 struct HotArgs {   // what the two solve phases read, by value: registers instead of the argument block in local memory
   const SpecHdr* hdrs;
   const CandRec* cands;
   const MrlRow* rows;
   MrlRow* temp;
+  MrlRow* base;             // beside every working row: what the unordered phase found for the cell
+  const uint32_t* corner;   // already offset: indexed by Spec id
 };
 __device__ __forceinline__ HotArgs hot_args(const StageArgs& s) {
   HotArgs h;
-  h.hdrs = s.hdrs; h.cands = s.cands; h.rows = s.rows; h.temp = s.temp;
+  h.hdrs = s.hdrs; h.cands = s.cands; h.rows = s.rows; h.temp = s.temp; h.base = s.base; h.corner = s.corner - s.lo;
   return h;
+}
+// A cell with a limit below its Spec's corner has no implementation; no record needs to be read.
+__device__ __forceinline__ bool below_corner(uint32_t corner, uint32_t cpack) {
+  return code_of(cpack, 0) < corner_of(corner, 0) || code_of(cpack, 1) < corner_of(corner, 1) ||
+         code_of(cpack, 2) < corner_of(corner, 2) || code_of(cpack, 3) < corner_of(corner, 3);
+}
+
+#ifndef MRL_BATCH
+#define MRL_BATCH 16
+#endif
+constexpr int kBatch = MRL_BATCH;   // records staged at a time
+struct StagedRec {           // a record with what the row lookups of its children need
+  uint4 rec;                 // action | kind << 16 | nchild << 24, imm, level | thr << 8 | peak << 16, units
+  uint4 mask[3];
+  unsigned long long base[3];
+  unsigned long long pad;
+};
+static_assert(sizeof(StagedRec) == 96, "staged record");
+
+// A staged record at one limits point; eval_candidate with the record and the child headers
+// already at hand. All children are finished, so the rows come from the table on the read-only path.
+__device__ __forceinline__ void eval_staged(const StagedRec& s, const MrlRow* __restrict__ rows, uint32_t ci,
+                                            uint32_t cpack, uint32_t bm0, uint32_t bm1, uint32_t bm2, uint32_t bm3,
+                                            Best& best, Tally& tally) {
+  const uint4 a = s.rec;
+  const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;   // the same in all lanes
+  const uint32_t imm = a.y;
+  const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu, pcode = (a.z >> 16) & 0xFFu;
+  const uint32_t units = a.w;
+  const uint32_t lv = code_of(cpack, level);
+  tally.cands++;
+  uint32_t k_main, k_peaks, k_tail;
+  if (kind == MRL_CK_LEAF) {
+    if (lv < thr) return;
+    k_main = imm;
+    k_peaks = pcode << peak_shift(level);
+    k_tail = (1u << 16) | action;
+  } else {
+    uint32_t c0 = bm0, c1 = bm1, c2 = bm2, c3 = bm3;
+    const uint32_t sh = peak_shift(level);
+    if (kind == MRL_CK_MOVE) {
+      if (lv < thr) return;
+      if (imm > best.main) return;   // a Move costs at least its own base cost
+      const uint32_t cb = below(child_code(level, lv, units));
+      c0 = (level == 0) ? cb : c0;
+      c1 = (level == 1) ? cb : c1;
+      c2 = (level == 2) ? cb : c2;
+      c3 = (level == 3) ? cb : c3;
+    }
+    const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(row_of(rows, rows, s.mask[0], s.base[0], c0, c1, c2, c3)));
+    uint4 r1 = r0, r2 = r0;
+    if (nchild > 1) r1 = __ldg(reinterpret_cast<const uint4*>(row_of(rows, rows, s.mask[1], s.base[1], c0, c1, c2, c3)));
+    if (nchild > 2) r2 = __ldg(reinterpret_cast<const uint4*>(row_of(rows, rows, s.mask[2], s.base[2], c0, c1, c2, c3)));
+    tally.lookups += nchild;
+    if (r0.z == MRL_UNSAT || r1.z == MRL_UNSAT || r2.z == MRL_UNSAT) return;
+    uint32_t depth;
+    if (kind == MRL_CK_LOOP) {
+      k_main = sat_mul(r0.x, imm);
+      k_peaks = r0.y;
+      depth = 1u;
+    } else {
+      k_main = (kind == MRL_CK_MOVE) ? sat_add(imm, r0.x) : r0.x;
+      if (nchild > 1) k_main = sat_add(k_main, r1.x);
+      if (nchild > 2) k_main = sat_add(k_main, r2.x);
+      if (k_main > best.main) return;
+      k_peaks = __vmaxu4(__vmaxu4(r0.y, r1.y), r2.y);
+      if (kind == MRL_CK_MOVE) {
+        const uint32_t cc = (k_peaks >> sh) & 0xFFu;
+        const uint32_t ncode = level < 2 ? units + cc : cache_code_ceil(units + cache_value(cc));
+        k_peaks = (k_peaks & ~(0xFFu << sh)) | (ncode << sh);
+      }
+      depth = min(max(max(r0.z >> 16, r1.z >> 16), r2.z >> 16) + 1u, 255u);
+    }
+    k_tail = (depth << 16) | action;
+  }
+  if (key_less(k_main, k_peaks, k_tail, best)) {
+    best.main = k_main;
+    best.peaks = k_peaks;
+    best.tail = k_tail;
+    best.ci = ci;
+  }
 }
 
 __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items, uint32_t n_items, uint32_t item_cells,
                                          uint32_t* next_item, unsigned long long* block_stats) {
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  __shared__ StagedRec staged_all[kBlock / 32][kBatch];
+  StagedRec* const staged = staged_all[threadIdx.x >> 5];   // this warp's
   Tally tally = {0, 0};
   // every warp starts with the item of its own number; further items are handed out by a counter
   // (no atomics at all when there are fewer items than warps)
@@ -632,28 +736,71 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
     const uint32_t i = it.spec;
     const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
     const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
-    MrlRow* const grid = a.temp + (a.hdrs[i].row_base & ~MRL_TEMP_FLAG);
+    const unsigned long long row0 = a.hdrs[i].row_base & ~MRL_TEMP_FLAG;
+    MrlRow* const grid = a.temp + row0;
+    MrlRow* const found = a.base + row0;
     const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
     const uint32_t cells = n0 * n1 * n2 * n3;
     const uint32_t c_end = min(cells, it.first_cell + item_cells);
-    for (uint32_t c0 = it.first_cell; c0 < c_end; c0 += 32) {
-      const uint32_t cell = c0 + lane;
-      const bool valid = cell < c_end;
-      uint32_t rest = valid ? cell : 0u;
-      const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
-      const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
-      const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
-      const uint32_t k3 = nth_set_bit(m.w, rest);
-      const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
-      const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
-      Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-      for (uint32_t ci = 0; ci < cl.y; ci++) {
-        const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));   // the same for all lanes
-        if (is_late(c)) break;
-        if (valid) eval_candidate<true>(a.hdrs, a.cands, a.rows, a.temp, cl.x + ci, c, ci, cpack, bm0, bm1, bm2, bm3, best, tally);
+    const uint32_t corner = a.corner[i];
+    uint32_t b0 = 0;
+    do {
+      // stage the next records (those with a same-stage child come last and end the walk) ...
+      const uint32_t nb = min((uint32_t)kBatch, cl.y - b0);
+      __syncwarp();   // the previous batch has been read by every lane
+      bool late = false;
+      if (lane < nb) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + b0 + lane]));
+        staged[lane].rec = c;
+        late = is_late(c);
       }
-      if (valid) *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
-    }
+      const uint32_t late_lanes = __ballot_sync(0xFFFFFFFFu, late);
+      const uint32_t n_here = late_lanes ? (uint32_t)__ffs(late_lanes) - 1u : nb;
+      __syncwarp();
+      // ... and the headers of their children, one (record, child) per lane
+      for (uint32_t t = lane; t < n_here * 3u; t += 32) {
+        const uint32_t r = t / 3u, j = t - r * 3u;
+        if (j < (staged[r].rec.x >> 24)) {
+          const uint32_t child = __ldg(&a.cands[cl.x + b0 + r].child[j]);
+          staged[r].mask[j] = __ldg(reinterpret_cast<const uint4*>(&a.hdrs[child]));
+          staged[r].base[j] = __ldg(&a.hdrs[child].row_base);
+        }
+      }
+      __syncwarp();
+      for (uint32_t c0 = it.first_cell; c0 < c_end; c0 += 32) {
+        const uint32_t cell = c0 + lane;
+        const bool valid = cell < c_end;
+        uint32_t rest = valid ? cell : 0u;
+        const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
+        const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
+        const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
+        const uint32_t k3 = nth_set_bit(m.w, rest);
+        const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
+        const bool live = valid && !below_corner(corner, cpack);
+        Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+        if (!__any_sync(0xFFFFFFFFu, live)) {
+          if (valid && b0 == 0) {
+            *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+            *reinterpret_cast<uint4*>(found + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+          }
+          continue;
+        }
+        if (b0 && live) {   // what the earlier batches found
+          const uint4 r = *reinterpret_cast<const uint4*>(grid + cell);
+          best.main = r.x; best.peaks = r.y; best.tail = r.z; best.ci = r.w;
+        }
+        const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
+        if (live) {
+          for (uint32_t r = 0; r < n_here; r++) eval_staged(staged[r], a.rows, b0 + r, cpack, bm0, bm1, bm2, bm3, best, tally);
+        }
+        if (valid && (b0 == 0 || live)) {   // the cell, and the copy the relaxation sweeps start from
+          *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+          *reinterpret_cast<uint4*>(found + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
+        }
+      }
+      if (late_lanes) break;
+      b0 += nb;
+    } while (b0 < cl.y);
     if (n_items <= gwarps) break;
     if (lane == 0) w = gwarps + atomicAdd(next_item, 1u);
     w = __shfl_sync(0xFFFFFFFFu, w, 0);
@@ -669,94 +816,197 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
   }
 }
 
-// Pass step 4b, one diagonal: the candidates with a same-stage child, one thread per listed cell,
-// on top of what phase_early left in the cell. Every cell such a candidate reads lies on a lower
-// diagonal. The records come dearest first and are walked from the end, so the cheapest Move is
-// tried first and a Move whose base cost alone exceeds the cell's optimum ends the walk.
-__device__ __noinline__ void phase_combine(const HotArgs a, const CellRef* list, uint32_t n_cells, uint32_t* next_cell,
-                                           unsigned long long* block_stats) {
+// Whole-row accesses to working rows that other warps may be writing at the same time: one
+// 128-bit access each, so a reader sees a row either before or after an update, never a mix.
+__device__ __forceinline__ uint4 ld_row_shared(const MrlRow* p) {
+  unsigned long long lo, hi;
+  asm volatile("{\n\t.reg .b128 q;\n\tld.relaxed.gpu.global.b128 q, [%2];\n\tmov.b128 {%0, %1}, q;\n\t}"
+               : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
+  return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+}
+__device__ __forceinline__ void st_row_shared(MrlRow* p, const uint4 v) {
+  const unsigned long long lo = v.x | ((unsigned long long)v.y << 32), hi = v.z | ((unsigned long long)v.w << 32);
+  asm volatile("{\n\t.reg .b128 q;\n\tmov.b128 q, {%1, %2};\n\tst.relaxed.gpu.global.b128 [%0], q;\n\t}"
+               :: "l"(p), "l"(lo), "l"(hi) : "memory");
+}
+
+// A staged record with a same-stage child at one limits point. Children of the stage being solved
+// live in the working rows and may improve while this runs; finished children are read-only.
+__device__ __forceinline__ void eval_staged_late(const StagedRec& s, const MrlRow* __restrict__ rows, const MrlRow* temp,
+                                                 uint32_t ci, uint32_t cpack, uint32_t bm0, uint32_t bm1, uint32_t bm2,
+                                                 uint32_t bm3, Best& best, Tally& tally) {
+  const uint4 a = s.rec;
+  const uint32_t action = a.x & 0xFFFFu, kind = (a.x >> 16) & 0xFFu, nchild = a.x >> 24;   // the same in all lanes
+  const uint32_t imm = a.y;
+  const uint32_t level = a.z & 0xFFu, thr = (a.z >> 8) & 0xFFu;
+  const uint32_t units = a.w;
+  const uint32_t lv = code_of(cpack, level);
+  tally.cands++;
+  uint32_t c0 = bm0, c1 = bm1, c2 = bm2, c3 = bm3;
+  const uint32_t sh = peak_shift(level);
+  if (kind == MRL_CK_MOVE) {
+    if (lv < thr) return;
+    if (imm > best.main) return;   // a Move costs at least its own base cost
+    const uint32_t cb = below(child_code(level, lv, units));
+    c0 = (level == 0) ? cb : c0;
+    c1 = (level == 1) ? cb : c1;
+    c2 = (level == 2) ? cb : c2;
+    c3 = (level == 3) ? cb : c3;
+  }
+  uint4 r[3];
+#pragma unroll
+  for (int j = 0; j < 3; j++) {
+    if ((uint32_t)j < nchild) {
+      const unsigned long long base = s.base[j];
+      const MrlRow* const p = row_of(rows, temp, s.mask[j], base, c0, c1, c2, c3);
+      r[j] = (base & MRL_TEMP_FLAG) ? ld_row_shared(p) : __ldg(reinterpret_cast<const uint4*>(p));
+    } else {
+      r[j] = r[0];
+    }
+  }
+  tally.lookups += nchild;
+  if (r[0].z == MRL_UNSAT || r[1].z == MRL_UNSAT || r[2].z == MRL_UNSAT) return;
+  uint32_t k_main, k_peaks, depth;
+  if (kind == MRL_CK_LOOP) {
+    k_main = sat_mul(r[0].x, imm);
+    k_peaks = r[0].y;
+    depth = 1u;
+  } else {
+    k_main = (kind == MRL_CK_MOVE) ? sat_add(imm, r[0].x) : r[0].x;
+    if (nchild > 1) k_main = sat_add(k_main, r[1].x);
+    if (nchild > 2) k_main = sat_add(k_main, r[2].x);
+    if (k_main > best.main) return;
+    k_peaks = __vmaxu4(__vmaxu4(r[0].y, r[1].y), r[2].y);
+    if (kind == MRL_CK_MOVE) {
+      const uint32_t cc = (k_peaks >> sh) & 0xFFu;
+      const uint32_t ncode = level < 2 ? units + cc : cache_code_ceil(units + cache_value(cc));
+      k_peaks = (k_peaks & ~(0xFFu << sh)) | (ncode << sh);
+    }
+    depth = min(max(max(r[0].z >> 16, r[1].z >> 16), r[2].z >> 16) + 1u, 255u);
+  }
+  const uint32_t k_tail = (depth << 16) | action;
+  if (key_less(k_main, k_peaks, k_tail, best)) {
+    best.main = k_main;
+    best.peaks = k_peaks;
+    best.tail = k_tail;
+    best.ci = ci;
+  }
+}
+
+// Pass step 4b, one relaxation sweep: the candidates with a child in the Spec's own stage (relayout
+// Moves). Such a child is read at limits reduced by what the Move allocates, so the dependencies
+// between cells form no cycle and the system "cell = best of its candidates at its children's
+// values" has exactly one solution. A sweep recomputes every cell from what phase_early found for
+// it (kept in the base rows) and all its same-stage records at the children's current values, in
+// place, while other warps read and write their own cells; a cell whose children all hold their
+// final values gets its final value, so every sweep settles at least one more level of the
+// dependency order, and the pass is finished after a sweep that changed nothing anywhere. (Keeping
+// the better of the old and the new value instead of recomputing would be wrong: a child that
+// improves can make the parent's peaks or depth worse.) From the second sweep on a Spec is looked
+// at again only if one of its same-stage children changed since the sweep before last began
+// (stamp = number of the last sweep that changed any cell of a Spec).
+// The records come dearest first and are staged from the end, so the cheapest Move is tried first.
+__device__ __forceinline__ void stage_late_batch(const HotArgs& a, StagedRec* staged, uint32_t last_rec, uint32_t n_here,
+                                                 uint32_t lane) {
+  __syncwarp();   // the previous batch has been read by every lane
+  if (lane < n_here) staged[lane].rec = __ldg(reinterpret_cast<const uint4*>(&a.cands[last_rec - lane]));
+  __syncwarp();
+  for (uint32_t t = lane; t < n_here * 3u; t += 32) {
+    const uint32_t r = t / 3u, j = t - r * 3u;
+    if (j < (staged[r].rec.x >> 24)) {
+      const uint32_t child = __ldg(&a.cands[last_rec - r].child[j]);
+      staged[r].mask[j] = *reinterpret_cast<const uint4*>(&a.hdrs[child]);   // same-stage headers: written earlier in this launch
+      staged[r].base[j] = a.hdrs[child].row_base;
+    }
+  }
+  __syncwarp();
+}
+
+__device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, uint32_t n_items, uint32_t item_cells,
+                                        uint32_t* next_item, uint32_t lo, uint32_t* stamp /* by position in the stage */,
+                                        uint32_t sweep, bool first_sweep, uint32_t* changed,
+                                        unsigned long long* block_stats) {
+  __shared__ StagedRec staged_all[kBlock / 32][kBatch];
+  StagedRec* const staged = staged_all[threadIdx.x >> 5];   // this warp's
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t gwarps = gridDim.x * (kBlock / 32);
-  const uint32_t gwarp = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
   Tally tally = {0, 0};
-  if (n_cells <= gwarps * 4u) {
-    // A small diagonal lasts as long as one cell's chain of dependent loads: 8 lanes share a cell,
-    // each takes every 8th record of the walk, and the group min-reduces with shuffles.
-    const uint32_t t = gwarp * 4u + (lane >> 3), sub = lane & 7u;
-    const bool valid = t < n_cells;
-    Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
-    MrlRow* out = nullptr;
-    uint32_t was = MRL_UNSAT;
-    if (valid) {
-      const CellRef ref = list[t];
-      const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[ref.spec].cand_off);
-      const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[ref.spec]);
-      MrlRow* const grid = a.temp + (a.hdrs[ref.spec].row_base & ~MRL_TEMP_FLAG);
-      const uint32_t bm0 = below(code_of(ref.cpack, 0)), bm1 = below(code_of(ref.cpack, 1)),
-                     bm2 = below(code_of(ref.cpack, 2)), bm3 = below(code_of(ref.cpack, 3));
-      const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-      const uint32_t i0 = __popc(m.x & bm0) - 1, i1 = __popc(m.y & bm1) - 1, i2 = __popc(m.z & bm2) - 1,
-                     i3 = __popc(m.w & bm3) - 1;
-      out = grid + (((i3 * n2 + i2) * n1 + i1) * n0 + i0);
-      const uint4 r = *reinterpret_cast<const uint4*>(out);
-      best.main = r.x; best.peaks = r.y; best.tail = r.z; best.ci = r.w;
-      was = r.w;
-      for (uint32_t back = sub; back < cl.y; back += 8) {
-        const uint32_t ci = cl.y - 1 - back;
-        const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
-        if (!is_late(c) || c.y > best.main) break;   // later steps of this lane's walk are dearer still, or not late
-        eval_candidate<false>(a.hdrs, a.cands, a.rows, a.temp, cl.x + ci, c, ci, ref.cpack, bm0, bm1, bm2, bm3, best, tally);
-      }
+  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_items;) {
+    const WorkItem it = items[w];
+    const uint32_t i = it.spec;
+    const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+    // the records with a same-stage child are the last ones
+    uint32_t n_late = 0;
+    for (uint32_t k = 0; k < cl.y; k += 32) {
+      const bool late = k + lane < cl.y && ((__ldg(&reinterpret_cast<const uint32_t*>(&a.cands[cl.x + cl.y - 1 - k - lane])[2]) >> 24) & 1u);
+      const uint32_t not_late = ~__ballot_sync(0xFFFFFFFFu, late);
+      const uint32_t run = not_late ? (uint32_t)__ffs(not_late) - 1u : 32u;
+      n_late += run;
+      if (run < 32) break;
     }
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-      Best other;
-      other.main = __shfl_xor_sync(0xFFFFFFFFu, best.main, o);
-      other.peaks = __shfl_xor_sync(0xFFFFFFFFu, best.peaks, o);
-      other.tail = __shfl_xor_sync(0xFFFFFFFFu, best.tail, o);
-      other.ci = __shfl_xor_sync(0xFFFFFFFFu, best.ci, o);
-      if (key_less(other.main, other.peaks, other.tail, best)) best = other;
-    }
-    if (valid && sub == 0 && best.ci != was) *reinterpret_cast<uint4*>(out) = make_uint4(best.main, best.peaks, best.tail, best.ci);
-  } else {
-    // Cells a warp takes at a time: an even share of the diagonal in whole warp-wide steps, at most
-    // 64. Every warp starts with the piece of its own number; what a large diagonal has beyond
-    // that is handed out by a counter.
-    const uint32_t grab = min(64u, max(32u, ((n_cells + gwarps - 1) / gwarps + 31u) & ~31u));
-    const bool more = (unsigned long long)gwarps * grab < n_cells;
-    for (uint32_t g0 = gwarp * grab; g0 < n_cells;) {
-      const uint32_t g1 = min(n_cells, g0 + grab);
-      for (uint32_t t = g0 + lane; t < g1; t += 32) {
-        const CellRef ref = list[t];
-        const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[ref.spec].cand_off);
-        if (cl.y == 0) continue;
-        uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + cl.y - 1]));
-        if (!is_late(c)) continue;   // nothing in this Spec depends on the stage itself
-        const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[ref.spec]);
-        MrlRow* const grid = a.temp + (a.hdrs[ref.spec].row_base & ~MRL_TEMP_FLAG);   // Specs being solved live in the working rows
-        const uint32_t bm0 = below(code_of(ref.cpack, 0)), bm1 = below(code_of(ref.cpack, 1)),
-                       bm2 = below(code_of(ref.cpack, 2)), bm3 = below(code_of(ref.cpack, 3));
-        // the cell's place in its Spec's working grid: slot = breakpoints at or below the code, minus one
-        const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
-        const uint32_t i0 = __popc(m.x & bm0) - 1, i1 = __popc(m.y & bm1) - 1, i2 = __popc(m.z & bm2) - 1,
-                       i3 = __popc(m.w & bm3) - 1;
-        const uint32_t cell = ((i3 * n2 + i2) * n1 + i1) * n0 + i0;
-        const uint4 r = *reinterpret_cast<const uint4*>(grid + cell);
-        Best best = {r.x, r.y, r.z, r.w};
-        for (uint32_t ci = cl.y - 1;;) {
-          if (c.y > best.main) break;   // base cost of this Move and of every one before it in the records
-          eval_candidate<false>(a.hdrs, a.cands, a.rows, a.temp, cl.x + ci, c, ci, ref.cpack, bm0, bm1, bm2, bm3, best, tally);
-          if (ci == 0) break;
-          ci--;
-          c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
-          if (!is_late(c)) break;
+    bool fresh = first_sweep && n_late;   // some same-stage child changed lately
+    if (n_late && !first_sweep) {
+      for (uint32_t t = lane; t < n_late * 3u; t += 32) {
+        const uint32_t r = t / 3u, j = t - r * 3u;
+        const CandRec* const rec = &a.cands[cl.x + cl.y - 1 - r];
+        if (j < (__ldg(reinterpret_cast<const uint32_t*>(rec)) >> 24)) {
+          const uint32_t child = __ldg(&rec->child[j]);
+          if (child >= lo && stamp[child - lo] + 1u >= sweep) fresh = true;
         }
-        if (best.ci != r.w) *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
       }
-      if (!more) break;
-      if (lane == 0) g0 = gwarps * grab + atomicAdd(next_cell, grab);
-      g0 = __shfl_sync(0xFFFFFFFFu, g0, 0);
+      fresh = __any_sync(0xFFFFFFFFu, fresh);
     }
+    if (fresh) {
+      const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+      const unsigned long long row0 = a.hdrs[i].row_base & ~MRL_TEMP_FLAG;
+      MrlRow* const grid = a.temp + row0;
+      const MrlRow* const found = a.base + row0;
+      const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
+      const uint32_t c_end = min(n0 * n1 * n2 * n3, it.first_cell + item_cells);
+      const uint32_t corner = a.corner[i];
+      const bool single = n_late <= (uint32_t)kBatch;   // all records staged once for the whole item
+      if (single) stage_late_batch(a, staged, cl.x + cl.y - 1, n_late, lane);
+      bool changed_any = false;
+      for (uint32_t c0 = it.first_cell; c0 < c_end; c0 += 32) {
+        const uint32_t cell = c0 + lane;
+        const bool valid = cell < c_end;
+        uint32_t rest = valid ? cell : 0u;
+        const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
+        const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
+        const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
+        const uint32_t k3 = nth_set_bit(m.w, rest);
+        const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
+        const bool live = valid && !below_corner(corner, cpack);
+        if (!__any_sync(0xFFFFFFFFu, live)) continue;
+        Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+        if (live) {
+          const uint4 f = *reinterpret_cast<const uint4*>(found + cell);
+          best.main = f.x; best.peaks = f.y; best.tail = f.z; best.ci = f.w;
+        }
+        const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
+        for (uint32_t b = 0; b < n_late; b += kBatch) {
+          const uint32_t n_here = min((uint32_t)kBatch, n_late - b);
+          if (!single) stage_late_batch(a, staged, cl.x + cl.y - 1 - b, n_here, lane);
+          if (live)
+            for (uint32_t r = 0; r < n_here; r++)
+              eval_staged_late(staged[r], a.rows, a.temp, cl.y - 1 - b - r, cpack, bm0, bm1, bm2, bm3, best, tally);
+        }
+        if (live) {
+          const uint4 was = *reinterpret_cast<const uint4*>(grid + cell);   // only this warp writes the cell in this sweep
+          if (best.main != was.x || best.peaks != was.y || best.tail != was.z) {
+            st_row_shared(grid + cell, make_uint4(best.main, best.peaks, best.tail, best.ci));
+            changed_any = true;
+          }
+        }
+      }
+      if (__any_sync(0xFFFFFFFFu, changed_any) && lane == 0) {
+        stamp[i - lo] = sweep;
+        *changed = sweep;
+      }
+    }
+    if (n_items <= gwarps) break;
+    if (lane == 0) w = gwarps + atomicAdd(next_item, 1u);
+    w = __shfl_sync(0xFFFFFFFFu, w, 0);
   }
   uint32_t tc = tally.cands, tl = tally.lookups;
   for (int o = 16; o > 0; o >>= 1) {
@@ -943,23 +1193,27 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
       ctl->spread_epoch = 0;
       ctl->temp_top = 0;
       ctl->all_cells = 0;
+      ctl->sweep_next[0] = ctl->sweep_next[1] = 0;
+      ctl->late_changed = 0;
     }
+    for (uint32_t i = gtid; i < a.hi - a.lo; i += gthreads) a.stamp[i] = 0;
     if (a.mine)
       for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) a.rmask[i] = make_uint4(0, 0, 0, 0);   // other ranks' Specs: zero until the exchange
     for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) a.dirty[i] = 0;
+    phase_minsat(a, gtid, gthreads);
     GRID_SYNC();
-    uint32_t epoch = 0;
-    unsigned long long combine_ns = 0, early_ns = 0;
+    uint32_t epoch = 0, sweep = 0, sweep_before = 0;
+    unsigned long long combine_ns = 0, early_ns = 0, n_sweeps = 0;
     bool failed = false;
     for (int pass = 0;; pass++) {
       if (pass >= kMaxPasses) { failed = true; if (gtid == 0) { ctl->failed_stage = a.stage; ctl->error |= MRL_ERR_PASSES; } break; }
       // masks: the first pass knows nothing about same-stage children and seeds their breakpoints
       // one hop deep with their own first masks (a third fewer passes for a tenth more cells);
       // later passes add the real breakpoints the previous passes found in them.
-      phase_derive(a, gtid, gthreads, pass == 0, pass == 0 ? 0 : 1, pass == 0);
+      phase_derive(a, gtid, gthreads, pass == 0, pass == 0 ? 0 : 1, pass == 0, pass == 0);
       GRID_SYNC();
       if (pass == 0) {
-        phase_derive(a, gtid, gthreads, 0, 1, 0);
+        phase_derive(a, gtid, gthreads, 0, 1, 0, 1);
         GRID_SYNC();
       } else {
         // close the marks under "has a marked same-stage child"
@@ -979,7 +1233,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
       const uint32_t item_cells = (uint32_t)min((unsigned long long)MRL_ITEM_CELLS, max(32ull, ((cells + gwarps - 1) / gwarps + 31ull) & ~31ull));
       const unsigned long long max_items = cells / item_cells + (a.hi - a.lo);
       if (cells == 0) break;   // nothing left to solve: every working grid is consistent
-      if (temp_top + cells > a.temp_cap || warps > a.chunk_cap || max_items > a.item_cap || cells > a.cell_cap ||
+      if (temp_top + cells > a.temp_cap || warps > a.chunk_cap || max_items > a.item_cap ||
           cells >= 0xFFFFFFF0ull || warps >= 0xFFFFFFF0ull) {
         failed = true;
         if (gtid == 0) {
@@ -988,39 +1242,37 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
           ctl->need_temp = temp_top + cells;
           ctl->need_chunks = warps;
           ctl->need_items = max_items;
-          ctl->need_cells = cells;
         }
         break;
       }
       phase_place(a, temp_top, item_cells);
-      for (uint32_t k = gtid; k < MRL_MAX_DIAG; k += gthreads) a.diag->count[k] = 0;
       GRID_SYNC();
       const uint32_t n_chunks = (uint32_t)warps;
-      phase_histogram(a, n_chunks);
-      GRID_SYNC();
-      if (gtid == 0) diag_layout(a.diag);
-      GRID_SYNC();
+      const uint32_t n_items = ctl->item_cursor;
       unsigned long long t0 = 0;
       if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-      phase_scatter(a, n_chunks);
-      phase_early(hot_args(a), a.items, ctl->item_cursor, item_cells, &ctl->item_next, block_stats);
+      phase_early(hot_args(a), a.items, n_items, item_cells, &ctl->item_next, block_stats);
       GRID_SYNC();
       if (gtid == 0) {
         unsigned long long t1;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
         early_ns += t1 - t0;
       }
-      const uint32_t n_occ = a.diag->n_occupied;
-      for (uint32_t q = 0; q < n_occ; q++) {
-        const uint32_t d = a.diag->order[q];
-        phase_combine(hot_args(a), a.cells + a.diag->base[d], a.diag->count[d], &a.diag->work[d], block_stats);
+      for (bool first_sweep = true;; first_sweep = false) {
+        sweep++;
+        if (gtid == 0) ctl->sweep_next[(sweep + 1) & 1] = 0;   // the other counter is idle during this sweep
+        phase_late(hot_args(a), a.items, n_items, item_cells, &ctl->sweep_next[sweep & 1], a.lo, a.stamp, sweep, first_sweep,
+                   &ctl->late_changed, block_stats);
         GRID_SYNC();
+        if (ctl->late_changed != sweep) break;   // nothing improved anywhere: the stage's cells are consistent
       }
       if (gtid == 0) {
         unsigned long long t1;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
         combine_ns += t1 - t0;
+        n_sweeps += sweep - sweep_before;
       }
+      sweep_before = sweep;
       phase_real_masks(a, n_chunks);
       for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads)
         if (a.dirty[i] == 2) a.dirty[i] = 0;
@@ -1039,7 +1291,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
       atomicAdd(&ctl->st_cands, block_stats[0]);
       atomicAdd(&ctl->st_lookups, block_stats[1]);
     }
-    if (gtid == 0) { ctl->st_combine_ns += combine_ns; ctl->st_early_ns += early_ns; }
+    if (gtid == 0) { ctl->st_combine_ns += combine_ns; ctl->st_early_ns += early_ns; ctl->st_sweeps += n_sweeps; }
     if (failed) {
       if (gtid == 0) ctl->st_syncs += syncs;
       return;   // uniform
@@ -1203,14 +1455,14 @@ void DeviceFill::free_(void* p) {
 
 void DeviceFill::release() {
   wait_upload();
-  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_); free_(d_cells_);
-  free_(d_diag_); free_(d_dirty_);
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr;
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_minsat_); free_(d_corner_); free_(d_stamp_); free_(d_rows_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_);
+  free_(d_dirty_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr; d_minsat_ = nullptr; d_corner_ = nullptr; d_stamp_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctl_ = nullptr;
-  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
+  d_stage_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
-  row_cap_ = temp_cap_ = chunk_cap_ = item_cap_ = cell_cap_ = 0;
+  row_cap_ = temp_cap_ = chunk_cap_ = item_cap_ = 0;
   buf_off_ = 0;
   cands_present_ = false;
   if (h_ctl_ && h_ctl_ != &ctl_pageable_) cudaFreeHost(h_ctl_);
@@ -1288,12 +1540,12 @@ int DeviceFill::wait_upload() { return wait_cands_(~uint64_t(0) >> 1); }
 int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaSetDevice(device_));
   wait_upload();   // of an earlier plan
-  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_rows_);
-  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_); free_(d_cells_);
-  free_(d_diag_); free_(d_dirty_);
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr;
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_minsat_); free_(d_corner_); free_(d_stamp_); free_(d_rows_);
+  free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_);
+  free_(d_dirty_);
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr; d_minsat_ = nullptr; d_corner_ = nullptr; d_stamp_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctl_ = nullptr;
-  d_stage_ = nullptr; d_cells_ = nullptr; d_diag_ = nullptr; d_dirty_ = nullptr;
+  d_stage_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
   buf_off_ = 0;
   cands_present_ = false;
@@ -1302,47 +1554,49 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   for (const Stage& st : plan.stages) max_stage_ = std::max(max_stage_, st.spec_hi - st.spec_lo);
   int rc;
   if ((rc = alloc_((void**)&d_ctl_, 512))) return rc;
-  if ((rc = alloc_((void**)&d_diag_, sizeof(DiagTable)))) return rc;
   if ((rc = alloc_((void**)&d_hdrs_, plan.hdrs.size() * sizeof(SpecHdr)))) return rc;
   if ((rc = alloc_((void**)&d_cands_, plan.cands.size() * sizeof(CandRec)))) return rc;
   if ((rc = alloc_((void**)&d_rmask_, plan.hdrs.size() * sizeof(uint4)))) return rc;
   if ((rc = alloc_((void**)&d_dirty_, plan.hdrs.size()))) return rc;
+  if ((rc = alloc_((void**)&d_minsat_, plan.hdrs.size() * sizeof(uint32_t)))) return rc;
+  if ((rc = alloc_((void**)&d_corner_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
+  if ((rc = alloc_((void**)&d_stamp_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
   if (!plan.mine.empty() && (rc = alloc_((void**)&d_mine_, plan.mine.size()))) return rc;
   if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
   if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage_ / kBlock + 1) * sizeof(unsigned long long)))) return rc;
   if (fixed_) {
-    // Everything left is split once: lookup staging, chunks, cell list, working rows and final rows.
+    // Everything left is split once: lookup staging, chunks, work items, working rows and final rows.
     stage_bytes_ = 64 << 10;
     if ((rc = alloc_(&d_stage_, stage_bytes_))) return rc;
     const size_t left = buf_bytes_ > align256(buf_off_) + 2048 ? buf_bytes_ - align256(buf_off_) - 2048 : 0;
-    // per working cell: 16 bytes of row, 8 of cell list, under 1 of chunks and work items; the
-    // rest is the table
+    // per working cell: two rows of 16 bytes (the cell and what the unordered phase found for it),
+    // under 1 byte of chunks and work items; the rest is the table
     chunk_cap_ = left / 64 / sizeof(Chunk);
     item_cap_ = left / 64 / sizeof(WorkItem);
-    temp_cap_ = left * 14 / 32 / sizeof(MrlRow);
-    cell_cap_ = left * 7 / 32 / sizeof(CellRef);
-    row_cap_ = (left - 2 * (left / 64) - left * 14 / 32 - left * 7 / 32) / sizeof(MrlRow);
-    if (item_cap_ < cell_cap_ / 32 + max_stage_ + 1) return too_large_();
+    temp_cap_ = left * 10 / 32 / (2 * sizeof(MrlRow));
+    row_cap_ = (left - 2 * (left / 64) - left * 10 / 32) / sizeof(MrlRow);
+    if (item_cap_ < temp_cap_ / 32 + max_stage_ + 1) return too_large_();
     if (chunk_cap_ == 0 || row_cap_ == 0) return too_large_();
     h_ctl_ = &ctl_pageable_;
   } else {
-    // Starting sizes from what fills of this kind ended with (about 40 table rows per Spec and 700
-    // working cells per Spec of the largest stage at size 8), within a share of the free memory
-    // each. A stage that needs more reports what it needs and is run again with larger buffers.
+    // Starting sizes from what fills of this kind ended with (about 45 table rows per Spec; 1000
+    // working cells per Spec of the largest stage, of which a rank of a sharded fill sees its
+    // share), each within a part of the free memory. The table gets the largest
+    // part: enlarging it later needs the old and the new copy at once. A stage that needs more than
+    // these reports what it needs and is run again with larger buffers.
     size_t free_b = 0, total_b = 0;
     CK(cudaMemGetInfo(&free_b, &total_b));
-    const uint64_t share = free_b / 5;
-    chunk_cap_ = std::max<uint64_t>(1u << 16, (uint64_t)max_stage_ * 32);
-    temp_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage_ * 1000, share / sizeof(MrlRow)));
-    cell_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)max_stage_ * 600, share / sizeof(CellRef)));
-    row_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)n_specs_ * 40, share / sizeof(MrlRow)));
-    item_cap_ = cell_cap_ / 32 + max_stage_ + 1;   // a work item holds at least 32 cells, and every Spec at most one partial item
+    const uint64_t shard = std::max<uint32_t>(1, plan.world);
+    const uint64_t stage_part = ((uint64_t)max_stage_ * 3 / 2 + shard - 1) / shard;   // Specs of the largest stage a rank solves, with slack
+    chunk_cap_ = std::max<uint64_t>(1u << 16, stage_part * 32);
+    temp_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>(stage_part * 1000, free_b / 4 / (2 * sizeof(MrlRow))));
+    row_cap_ = std::max<uint64_t>(1u << 20, std::min<uint64_t>((uint64_t)n_specs_ * 48, free_b / 2 / sizeof(MrlRow)));
+    item_cap_ = temp_cap_ / 32 + max_stage_ + 1;   // a work item holds at least 32 cells, and every Spec at most one partial item
     if (!h_ctl_) CK(cudaHostAlloc((void**)&h_ctl_, sizeof(FillCtl), cudaHostAllocDefault));
   }
   if ((rc = alloc_((void**)&d_chunks_, chunk_cap_ * sizeof(Chunk)))) return rc;
   if ((rc = alloc_((void**)&d_items_, item_cap_ * sizeof(WorkItem)))) return rc;
-  if ((rc = alloc_((void**)&d_temp_, temp_cap_ * sizeof(MrlRow)))) return rc;
-  if ((rc = alloc_((void**)&d_cells_, cell_cap_ * sizeof(CellRef)))) return rc;
+  if ((rc = alloc_((void**)&d_temp_, temp_cap_ * 2 * sizeof(MrlRow)))) return rc;   // the cells, then what the unordered phase found for them
   if ((rc = alloc_((void**)&d_rows_, row_cap_ * sizeof(MrlRow)))) return rc;
   h2d_bytes_ = plan.hdrs.size() * sizeof(SpecHdr) + (skip_cands ? 0 : plan.cands.size() * sizeof(CandRec)) + plan.mine.size();
   CK(cudaMemsetAsync(d_ctl_, 0, 512, stream_));
@@ -1466,10 +1720,9 @@ int DeviceFill::grow_after_error_(uint32_t bits) {
   };
   int rc;
   if (bits & MRL_ERR_WORKING) {
-    if ((rc = regrow((void**)&d_temp_, &temp_cap_, h_ctl_->need_temp, sizeof(MrlRow)))) return rc;
+    if ((rc = regrow((void**)&d_temp_, &temp_cap_, h_ctl_->need_temp, 2 * sizeof(MrlRow)))) return rc;
     if ((rc = regrow((void**)&d_chunks_, &chunk_cap_, h_ctl_->need_chunks, sizeof(Chunk)))) return rc;
     if ((rc = regrow((void**)&d_items_, &item_cap_, h_ctl_->need_items, sizeof(WorkItem)))) return rc;
-    if ((rc = regrow((void**)&d_cells_, &cell_cap_, h_ctl_->need_cells, sizeof(CellRef)))) return rc;
   }
   if (bits & MRL_ERR_TABLE) {
     const uint64_t need = h_ctl_->need_rows;
@@ -1518,10 +1771,11 @@ int DeviceFill::launch_solve_(const Plan& plan, uint32_t si, bool place_too) {
   }
   StageArgs a;
   a.hdrs = d_hdrs_; a.cands = d_cands_; a.rmask = d_rmask_; a.mine = d_mine_; a.dirty = d_dirty_;
-  a.chunks = d_chunks_; a.items = d_items_; a.cells = d_cells_; a.diag = d_diag_; a.rows = d_rows_; a.temp = d_temp_;
-  a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.ctl = d_ctl_;
+  a.chunks = d_chunks_; a.items = d_items_; a.rows = d_rows_; a.temp = d_temp_; a.base = d_temp_ + temp_cap_;
+  a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.minsat = d_minsat_; a.corner = d_corner_; a.stamp = d_stamp_; a.ctl = d_ctl_;
   a.lo = st.spec_lo; a.hi = st.spec_hi; a.top_pack = plan.top_pack(); a.stage = si;
-  a.temp_cap = temp_cap_; a.chunk_cap = chunk_cap_; a.item_cap = item_cap_; a.cell_cap = cell_cap_; a.row_cap = row_cap_;
+  a.prev_lo = si ? plan.stages[si - 1].spec_lo : 0; a.prev_hi = si ? plan.stages[si - 1].spec_hi : 0;
+  a.temp_cap = temp_cap_; a.chunk_cap = chunk_cap_; a.item_cap = item_cap_; a.row_cap = row_cap_;
   a.solve = 1;
   a.place = place_too ? 1 : 0;
   // Small stages run on fewer blocks: a grid-wide barrier costs less, and there is no work for more.
@@ -1539,10 +1793,11 @@ int DeviceFill::launch_place_(const Plan& plan, uint32_t si) {
   if (n == 0) return 0;
   StageArgs a;
   a.hdrs = d_hdrs_; a.cands = d_cands_; a.rmask = d_rmask_; a.mine = d_mine_; a.dirty = d_dirty_;
-  a.chunks = d_chunks_; a.items = d_items_; a.cells = d_cells_; a.diag = d_diag_; a.rows = d_rows_; a.temp = d_temp_;
-  a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.ctl = d_ctl_;
+  a.chunks = d_chunks_; a.items = d_items_; a.rows = d_rows_; a.temp = d_temp_; a.base = d_temp_ + temp_cap_;
+  a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.minsat = d_minsat_; a.corner = d_corner_; a.stamp = d_stamp_; a.ctl = d_ctl_;
   a.lo = st.spec_lo; a.hi = st.spec_hi; a.top_pack = plan.top_pack(); a.stage = si;
-  a.temp_cap = temp_cap_; a.chunk_cap = chunk_cap_; a.item_cap = item_cap_; a.cell_cap = cell_cap_; a.row_cap = row_cap_;
+  a.prev_lo = si ? plan.stages[si - 1].spec_lo : 0; a.prev_hi = si ? plan.stages[si - 1].spec_hi : 0;
+  a.temp_cap = temp_cap_; a.chunk_cap = chunk_cap_; a.item_cap = item_cap_; a.row_cap = row_cap_;
   a.solve = 0;
   a.place = 1;
   const uint64_t want = ((uint64_t)n + kBlock - 1) / kBlock;
@@ -1587,8 +1842,8 @@ int DeviceFill::place_stage(const Plan& plan, uint32_t si, void** rows_ptr, uint
     const uint32_t bits = h_ctl_->error;
     if (bits & MRL_ERR_WORKING) {
       snprintf(err_, sizeof(err_), "stage %u needs larger working buffers than a sharded fill starts with "
-               "(%llu working rows, %llu cells); fill once unsharded, or with fewer Specs per stage", si,
-               (unsigned long long)h_ctl_->need_temp, (unsigned long long)h_ctl_->need_cells);
+               "(%llu working rows); fill once unsharded, or with fewer Specs per stage", si,
+               (unsigned long long)h_ctl_->need_temp);
       return -6;
     }
     if (bits & ~(uint32_t)MRL_ERR_TABLE) {
@@ -1615,6 +1870,7 @@ void DeviceFill::take_stats_() {
   stats_.alg_bytes = c.st_final_bytes;
   stats_.passes = c.st_passes;
   stats_.grid_syncs = c.st_syncs;
+  stats_.sweeps = c.st_sweeps;
   stats_.combine_ms = (float)(c.st_combine_ns * 1e-6);
   stats_.early_ms = (float)(c.st_early_ns * 1e-6);
 }

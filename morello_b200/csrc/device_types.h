@@ -60,20 +60,6 @@ struct Chunk {
   uint32_t col_start;
 };
 
-// Per limits diagonal (sum of the four codes, < 128) of the pass being solved: how many working
-// cells lie on it, where their descriptors start in the cell list, and the occupied diagonals in
-// ascending order.
-#define MRL_MAX_DIAG 128
-struct DiagTable {
-  uint32_t count[MRL_MAX_DIAG];
-  uint32_t cursor[MRL_MAX_DIAG];
-  unsigned long long base[MRL_MAX_DIAG];
-  uint32_t order[MRL_MAX_DIAG];
-  uint32_t work[MRL_MAX_DIAG];    // how many of a diagonal's cells have been handed to a warp
-  uint32_t n_occupied;
-  uint32_t pad[3];
-};
-
 // A piece of one Spec's working grid for the unordered solve phase: consecutive cells from
 // first_cell on, at most MRL_ITEM_CELLS of them (a pass picks the size). Warps take items as they
 // finish others.
@@ -83,17 +69,10 @@ struct WorkItem {
   uint32_t first_cell;
 };
 
-// One working cell: Spec id and the cell's limits as lattice codes, one per byte (RF in byte 0
-// .. GL in byte 3). Its place in the Spec's working grid follows from the masks by popcounts.
-struct CellRef {
-  uint32_t spec;
-  uint32_t cpack;
-};
-
 // Error bits a fill kernel can raise (sticky until the host clears them).
 enum {
   MRL_ERR_CHILD = 1,      // a candidate record names a Spec id outside the plan
-  MRL_ERR_WORKING = 2,    // a working buffer (rows, chunks, cell list) is too small
+  MRL_ERR_WORKING = 2,    // a working buffer (rows, chunks, work items) is too small
   MRL_ERR_TABLE = 4,      // the row table is too small
   MRL_ERR_PASSES = 8,     // a stage did not reach a consistent limits grid
 };
@@ -110,13 +89,16 @@ struct FillCtl {
   uint32_t item_cursor;
   uint32_t item_next;                // next work item to hand out
   uint32_t spread_epoch;             // closure of the re-solve marks: last round that marked a Spec
+  uint32_t sweep_next[2];            // work hand-out of the relaxation sweeps, alternating
+  uint32_t late_changed;             // last relaxation sweep that improved a cell
+  uint32_t pad0;
   // -- one stage
   unsigned long long temp_top;       // working rows handed out so far in this stage
   unsigned long long all_cells;      // working cells of all the stage's Specs under the final masks
   // -- sticky over a fill
   uint32_t error;                    // MRL_ERR_* bits
   uint32_t failed_stage;             // first stage that raised one
-  unsigned long long need_temp, need_chunks, need_items, need_cells, need_rows;   // what it would have taken
+  unsigned long long need_temp, need_chunks, need_items, need_rows;   // what it would have taken
   unsigned long long final_top;      // rows of the finished table
   unsigned long long stage_first_row, stage_rows;   // the last placed stage's slice of the table
   // -- statistics of a fill
@@ -128,6 +110,7 @@ struct FillCtl {
   unsigned long long st_early_ns;    // of which the unordered phase (with the cell listing)
   unsigned long long st_final_bytes; // algorithmic bytes of the finished rows (see fill.hpp)
   unsigned long long st_syncs;       // grid-wide barriers executed
+  unsigned long long st_sweeps;      // relaxation sweeps, all passes
   // -- scratch of verify and checksum
   unsigned long long scratch[4];
 };

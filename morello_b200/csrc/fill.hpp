@@ -21,6 +21,7 @@ struct FillStats {
   uint64_t alg_bytes = 0;
   uint64_t passes = 0;          // solve passes over all stages
   uint64_t launches = 0;        // kernel launches
+  uint64_t sweeps = 0;          // relaxation sweeps of the candidates with a same-stage child
   uint64_t grid_syncs = 0;      // grid-wide barriers inside the stage kernels
   float fill_ms = 0;            // device time of the whole fill (CUDA events on the launch stream)
   float combine_ms = 0;         // device time inside the solve phases (device timer)
@@ -103,12 +104,13 @@ class DeviceFill {
   uint4* d_rmask_ = nullptr;
   uint8_t* d_mine_ = nullptr;
   uint8_t* d_dirty_ = nullptr;   // by Spec id: to be solved (again) in the coming pass
+  uint32_t* d_minsat_ = nullptr; // by Spec id: lower corner of the satisfiable region
+  uint32_t* d_stamp_ = nullptr;  // by position in the stage being solved: last relaxation sweep that improved the Spec
+  uint32_t* d_corner_ = nullptr; // by position in the stage being solved: where its working grids are clipped
   Chunk* d_chunks_ = nullptr;
   WorkItem* d_items_ = nullptr;  // pieces of working grids for the unordered solve phase
-  CellRef* d_cells_ = nullptr;   // working cells of the pass, listed diagonal by diagonal
-  DiagTable* d_diag_ = nullptr;
   MrlRow* d_rows_ = nullptr;     // the table
-  MrlRow* d_temp_ = nullptr;     // working grids of the stage being solved
+  MrlRow* d_temp_ = nullptr;     // working grids of the stage being solved (temp_cap_ rows), then as many rows for what the unordered phase found
   uint32_t* d_fcount_ = nullptr;
   unsigned long long* d_block_sums_ = nullptr;
   FillCtl* d_ctl_ = nullptr;
@@ -117,7 +119,7 @@ class DeviceFill {
   FillCtl* h_ctl_ = nullptr;     // pinned, or &ctl_pageable_ when nothing may be allocated
   FillCtl ctl_pageable_;
   uint32_t n_specs_ = 0, max_stage_ = 1;
-  uint64_t row_cap_ = 0, temp_cap_ = 0, chunk_cap_ = 0, item_cap_ = 0, cell_cap_ = 0;
+  uint64_t row_cap_ = 0, temp_cap_ = 0, chunk_cap_ = 0, item_cap_ = 0;
   uint64_t h2d_bytes_ = 0;
   uint64_t n_cand_bytes_ = 0;
   bool cands_present_ = false;   // the device candidate records are complete and checked

@@ -1,5 +1,6 @@
 // Host-side planner of the database fill. See plan.hpp.
 #include "plan.hpp"
+#include <malloc.h>
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -213,7 +214,10 @@ std::vector<LogicalSpec> precompute_goals(u32 size, Through through, const std::
   size_t total = 0;
   for (auto& v : per_task) total += v.size();
   goals.reserve(total);
-  for (auto& v : per_task) goals.insert(goals.end(), v.begin(), v.end());
+  for (auto& v : per_task) {
+    goals.insert(goals.end(), v.begin(), v.end());
+    std::vector<LogicalSpec>().swap(v);
+  }
   return goals;
 }
 
@@ -686,51 +690,64 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
   plan.cands.reset(ncand);
   {
+    // Written in the order the Specs were discovered - the order their temporary records were
+    // allocated in - and each Spec's temporary records are released as soon as they are copied. A
+    // large job does this in slices and hands the freed pages back to the system after each, so
+    // that the final arrays grow as the temporaries shrink instead of on top of them.
     std::vector<u64> kids_t(1, 0);
-    parallel_for(n, n_threads, [&](size_t i, int) {
-      const TempSpec& ts = temp[order[i]];
-      u64 kids = 0;
-      {
-        const u32 id = pos_a[i];
-        plan.specs[id] = ts.ls;
-        SpecHdr& h = plan.hdrs[id];
-        memset(&h, 0, sizeof(h));
-        u64 off = offs[id];
-        h.cand_off = (u32)off;
-        h.ncand = (u32)ts.cands.size();
-        for (CandRec r : ts.cands) {
-          for (int j = 0; j < r.nchild; j++) r.child[j] = id_a[r.child[j]];
-          kids += r.nchild;
-          plan.cands[off++] = r;
+    const u32 n_slices = n > (8u << 20) ? 24 : 1;
+    for (u32 sl = 0; sl < n_slices; sl++) {
+      const u32 t_lo = (u32)((u64)n * sl / n_slices), t_hi = (u32)((u64)n * (sl + 1) / n_slices);
+      parallel_for(t_hi - t_lo, n_threads, [&](size_t k, int) {
+        const u32 t = t_lo + (u32)k;
+        TempSpec& ts = temp[t];
+        u64 kids = 0;
+        {
+          const u32 id = id_a[t];
+          plan.specs[id] = ts.ls;
+          SpecHdr& h = plan.hdrs[id];
+          memset(&h, 0, sizeof(h));
+          u64 off = offs[id];
+          h.cand_off = (u32)off;
+          h.ncand = (u32)ts.cands.size();
+          for (CandRec r : ts.cands) {
+            for (int j = 0; j < r.nchild; j++) r.child[j] = id_a[r.child[j]];
+            kids += r.nchild;
+            plan.cands[off++] = r;
+          }
         }
-      }
-      if (twin) {
-        const u32 id = pos_b[i];
-        LogicalSpec sb = ts.ls;
-        sb.dtype = dt_b;
-        plan.specs[id] = sb;
-        SpecHdr& h = plan.hdrs[id];
-        memset(&h, 0, sizeof(h));
-        u64 off = offs[id];
-        h.cand_off = (u32)off;
-        h.ncand = (u32)(offs[id + 1] - offs[id]);
-        // its own leaf kernels, numbered from where the leaf section starts ...
-        const u32 leaf_end_b = ts.twin_leaf_end;
-        for (const CandRec& r : ts.twin_leaf) plan.cands[off++] = r;
-        // ... then the first dtype's other records; what is numbered after the leaf section
-        // (ToAccum, splits) moves by the difference in applicable kernels
-        const int shift = (int)leaf_end_b - (int)ts.leaf_end;
-        for (CandRec r : ts.cands) {
-          if (r.kind == MRL_CK_LEAF) continue;
-          if (r.kind == MRL_CK_BLOCK || (r.kind == MRL_CK_LOOP && r.action >= ts.leaf_end)) r.action = (u16)((int)r.action + shift);
-          for (int j = 0; j < r.nchild; j++) r.child[j] = id_b[r.child[j]];
-          kids += r.nchild;
-          plan.cands[off++] = r;
+        if (twin) {
+          const u32 id = id_b[t];
+          LogicalSpec sb = ts.ls;
+          sb.dtype = dt_b;
+          plan.specs[id] = sb;
+          SpecHdr& h = plan.hdrs[id];
+          memset(&h, 0, sizeof(h));
+          u64 off = offs[id];
+          h.cand_off = (u32)off;
+          h.ncand = (u32)(offs[id + 1] - offs[id]);
+          // its own leaf kernels, numbered from where the leaf section starts ...
+          const u32 leaf_end_b = ts.twin_leaf_end;
+          for (const CandRec& r : ts.twin_leaf) plan.cands[off++] = r;
+          // ... then the first dtype's other records; what is numbered after the leaf section
+          // (ToAccum, splits) moves by the difference in applicable kernels
+          const int shift = (int)leaf_end_b - (int)ts.leaf_end;
+          for (CandRec r : ts.cands) {
+            if (r.kind == MRL_CK_LEAF) continue;
+            if (r.kind == MRL_CK_BLOCK || (r.kind == MRL_CK_LOOP && r.action >= ts.leaf_end)) r.action = (u16)((int)r.action + shift);
+            for (int j = 0; j < r.nchild; j++) r.child[j] = id_b[r.child[j]];
+            kids += r.nchild;
+            plan.cands[off++] = r;
+          }
+          if (off != offs[id + 1]) throw ModelError("planner: twin record count mismatch");
         }
-        if (off != offs[id + 1]) throw ModelError("planner: twin record count mismatch");
-      }
-      __atomic_fetch_add(&kids_t[0], kids, __ATOMIC_RELAXED);
-    });
+        std::vector<CandRec>().swap(ts.cands);
+        std::vector<CandRec>().swap(ts.twin_leaf);
+        std::string().swap(ts.key);
+        __atomic_fetch_add(&kids_t[0], kids, __ATOMIC_RELAXED);
+      });
+      if (n_slices > 1) malloc_trim(0);
+    }
     plan.stats.n_children += kids_t[0];
   }
   // The temporary Specs are taken apart by a few threads of their own while the rest of the
