@@ -367,7 +367,8 @@ struct StageArgs {
   WorkItem* items;
   MrlRow* rows;
   MrlRow* temp;
-  MrlRow* base;                   // as many rows again: what the unordered phase found for each working cell
+  MrlRow* base;                   // as many rows again: the grids of the unordered phase
+  SpecHdr* ehdr;                  // by position in the stage: masks and first row (in base) of the Spec's grid of the unordered phase
   uint32_t* fcount;
   unsigned long long* block_sums;
   uint32_t* minsat;               // by Spec id: lower corner of the satisfiable region (see phase_minsat)
@@ -420,105 +421,132 @@ __device__ __noinline__ void phase_minsat(const StageArgs& a, uint32_t gtid, uin
   }
 }
 
-// Pass step 1: per Spec of the stage, the masks its working grid needs. child_source says what
-// is known about same-stage children: 0 = nothing (first pass: they are ignored), 1 = the
-// breakpoints in rmask (found real by the previous pass; or, when seeding, the children's own
-// first working masks). A Spec whose masks grew is marked for solving. seed_copy: also copy the
-// new masks to rmask (so that a following phase can read them as the children's breakpoints).
-__device__ __noinline__ void phase_derive(const StageArgs& a, uint32_t gtid, uint32_t gthreads, int first, int child_source,
-                                          int seed_copy, int pass0) {
+// Step 0: the corner of every Spec of the stage, per memory the minimum over its candidates of
+// what each needs at least (its threshold; its children's corners, shifted by what a Move
+// takes). Two rounds: the first knows nothing about same-stage children (bound zero) and leaves
+// its result in minsat, the second reads those for same-stage children and writes the array the
+// grids are clipped with, so that no thread reads what another writes.
+__device__ __noinline__ void phase_corner(const StageArgs& a, uint32_t gtid, uint32_t gthreads, int round) {
   for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
     if (!computed_here(a, i)) continue;
-    const uint4 old = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
     const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
-    uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
-    // lower corner of the Spec's satisfiable region: per memory the minimum over its candidates of
-    // what each needs at least (its threshold; its children's corners, shifted by what a Move takes)
     uint32_t l0 = MRL_NEVER, l1 = MRL_NEVER, l2 = MRL_NEVER, l3 = MRL_NEVER;
     for (uint32_t ci = 0; ci < cl.y; ci++) {
       const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
       const uint32_t kind = (c.x >> 16) & 0xFFu, nchild = c.x >> 24;
       const uint32_t level = c.z & 0xFFu, thr = (c.z >> 8) & 0xFFu, units = c.w;
-      if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
       uint32_t q0 = 0, q1 = 0, q2 = 0, q3 = 0;   // this candidate's corner
       if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) {
         q0 = level == 0 ? thr : 0u; q1 = level == 1 ? thr : 0u; q2 = level == 2 ? thr : 0u; q3 = level == 3 ? thr : 0u;
       }
-      if (kind == MRL_CK_LEAF) {
-        l0 = min(l0, q0); l1 = min(l1, q1); l2 = min(l2, q2); l3 = min(l3, q3);
-        continue;
-      }
-      const uint4 b = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]) + 1);
       bool never = false;
-      for (uint32_t j = 0; j < nchild; j++) {
-        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
-        // a finished child's exact corner; a same-stage child's bound so far (zero before the first round)
-        const uint32_t cp = (child < a.lo || !first) ? a.minsat[child] : 0u;
-        uint32_t e0 = corner_of(cp, 0), e1 = corner_of(cp, 1), e2 = corner_of(cp, 2), e3 = corner_of(cp, 3);
-        if (e0 == MRL_NEVER || e1 == MRL_NEVER || e2 == MRL_NEVER || e3 == MRL_NEVER) { never = true; break; }
-        if (kind == MRL_CK_MOVE) {
-          const uint32_t e = sel4(e0, e1, e2, e3, level);
-          uint32_t sh = 0;
-          if (e) {
-            const uint32_t bit = shift_mask(1u << e, level, units, code_of(a.top_pack, level));
-            if (!bit) { never = true; break; }
-            sh = __ffs(bit) - 1;
+      if (kind != MRL_CK_LEAF) {
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]) + 1);
+        for (uint32_t j = 0; j < nchild; j++) {
+          const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+          // a finished child's exact corner; a same-stage child's bound from the first round
+          const uint32_t cp = (child < a.lo || round) ? a.minsat[child] : 0u;
+          uint32_t e0 = corner_of(cp, 0), e1 = corner_of(cp, 1), e2 = corner_of(cp, 2), e3 = corner_of(cp, 3);
+          if (e0 == MRL_NEVER) { never = true; break; }
+          if (kind == MRL_CK_MOVE) {
+            const uint32_t e = sel4(e0, e1, e2, e3, level);
+            uint32_t sh = 0;
+            if (e) {
+              const uint32_t bit = shift_mask(1u << e, level, units, code_of(a.top_pack, level));
+              if (!bit) { never = true; break; }
+              sh = __ffs(bit) - 1;
+            }
+            e0 = level == 0 ? sh : e0; e1 = level == 1 ? sh : e1; e2 = level == 2 ? sh : e2; e3 = level == 3 ? sh : e3;
           }
-          e0 = level == 0 ? sh : e0; e1 = level == 1 ? sh : e1; e2 = level == 2 ? sh : e2; e3 = level == 3 ? sh : e3;
+          q0 = max(q0, e0); q1 = max(q1, e1); q2 = max(q2, e2); q3 = max(q3, e3);
         }
-        q0 = max(q0, e0); q1 = max(q1, e1); q2 = max(q2, e2); q3 = max(q3, e3);
       }
       if (!never) { l0 = min(l0, q0); l1 = min(l1, q1); l2 = min(l2, q2); l3 = min(l3, q3); }
-      for (uint32_t j = 0; j < nchild; j++) {
-        const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
-        uint4 cm;
-        if (child < a.lo) cm = *reinterpret_cast<const uint4*>(&a.hdrs[child]);   // finished stage: final masks
-        else if (child_source == 0) continue;
-        else cm = a.rmask[child];
-        if (kind == MRL_CK_MOVE) {
-          const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(a.top_pack, level));
-          r0 |= (level == 0) ? s : cm.x;
-          r1 |= (level == 1) ? s : cm.y;
-          r2 |= (level == 2) ? s : cm.z;
-          r3 |= (level == 3) ? s : cm.w;
-        } else {
-          r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
-        }
-      }
     }
-    uint4 nm = first ? make_uint4(r0, r1, r2, r3) : make_uint4(old.x | r0, old.y | r1, old.z | r2, old.w | r3);
-    // Clip the grid at the corner: below it everything is unsatisfiable, so one cell [0, corner)
-    // per memory is enough. The corner is settled in the first pass (its two rounds let a bound
-    // travel two relayouts deep) and kept afterwards, so that grids only ever grow.
-    uint32_t corner;
-    if (pass0) {
-      const uint32_t t0 = code_of(a.top_pack, 0), t1 = code_of(a.top_pack, 1), t2 = code_of(a.top_pack, 2), t3 = code_of(a.top_pack, 3);
-      if (l0 > t0 || l1 > t1 || l2 > t2 || l3 > t3) l0 = l1 = l2 = l3 = MRL_NEVER;   // no limits inside the lattice reach it
-      corner = l0 | (l1 << 5) | (l2 << 10) | (l3 << 15);
-      // the first round's bound is what the second round reads for same-stage children; the
-      // second round's goes to an array of its own, so that no thread reads what another writes
-      if (first) a.minsat[i] = corner;
-      a.corner[i - a.lo] = corner;
+    const uint32_t t0 = code_of(a.top_pack, 0), t1 = code_of(a.top_pack, 1), t2 = code_of(a.top_pack, 2), t3 = code_of(a.top_pack, 3);
+    if (l0 > t0 || l1 > t1 || l2 > t2 || l3 > t3) l0 = l1 = l2 = l3 = MRL_NEVER;   // no limits inside the lattice reach it
+    const uint32_t corner = l0 | (l1 << 5) | (l2 << 10) | (l3 << 15);
+    if (round == 0) a.minsat[i] = corner;
+    a.corner[i - a.lo] = corner;
+  }
+}
+
+// Clips a grid at the corner: below it everything is unsatisfiable, so one cell [0, corner) per
+// memory is enough.
+__device__ __forceinline__ uint4 clip_at_corner(uint4 nm, uint32_t corner) {
+  const uint32_t k0 = corner_of(corner, 0), k1 = corner_of(corner, 1), k2 = corner_of(corner, 2), k3 = corner_of(corner, 3);
+  if (k0 == MRL_NEVER) return make_uint4(1u, 1u, 1u, 1u);   // unsatisfiable at every limit: a single cell
+  if (k0) nm.x = (nm.x & ~((1u << k0) - 1u)) | 1u | (1u << k0);
+  if (k1) nm.y = (nm.y & ~((1u << k1) - 1u)) | 1u | (1u << k1);
+  if (k2) nm.z = (nm.z & ~((1u << k2) - 1u)) | 1u | (1u << k2);
+  if (k3) nm.w = (nm.w & ~((1u << k3) - 1u)) | 1u | (1u << k3);
+  return nm;
+}
+
+// ORs into r the breakpoints one record puts into its Spec's grid: its own threshold, and its
+// children's breakpoints (for a Move, shifted in the memory it allocates in). Children of
+// finished stages contribute their final masks, same-stage children what rmask holds for them.
+__device__ __forceinline__ void record_breakpoints(const StageArgs& a, uint32_t rec, const uint4 c, uint32_t& r0, uint32_t& r1,
+                                                   uint32_t& r2, uint32_t& r3) {
+  const uint32_t kind = (c.x >> 16) & 0xFFu, nchild = c.x >> 24;
+  const uint32_t level = c.z & 0xFFu, thr = (c.z >> 8) & 0xFFu, units = c.w;
+  if (kind == MRL_CK_LEAF || kind == MRL_CK_MOVE) or_level(r0, r1, r2, r3, level, 1u << thr);
+  if (kind == MRL_CK_LEAF) return;
+  const uint4 b = __ldg(reinterpret_cast<const uint4*>(&a.cands[rec]) + 1);
+  for (uint32_t j = 0; j < nchild; j++) {
+    const uint32_t child = j == 0 ? b.x : (j == 1 ? b.y : b.z);
+    const uint4 cm = child < a.lo ? *reinterpret_cast<const uint4*>(&a.hdrs[child]) : a.rmask[child];
+    if (kind == MRL_CK_MOVE) {
+      const uint32_t s = shift_mask(sel4(cm.x, cm.y, cm.z, cm.w, level), level, units, code_of(a.top_pack, level));
+      r0 |= (level == 0) ? s : cm.x;
+      r1 |= (level == 1) ? s : cm.y;
+      r2 |= (level == 2) ? s : cm.z;
+      r3 |= (level == 3) ? s : cm.w;
     } else {
-      corner = a.corner[i - a.lo];
+      r0 |= cm.x; r1 |= cm.y; r2 |= cm.z; r3 |= cm.w;
     }
-    {
-      const uint32_t k0 = corner_of(corner, 0), k1 = corner_of(corner, 1), k2 = corner_of(corner, 2), k3 = corner_of(corner, 3);
-      if (k0 == MRL_NEVER) {
-        nm = make_uint4(1u, 1u, 1u, 1u);   // unsatisfiable at every limit: a single cell
-      } else {
-        if (k0) nm.x = (nm.x & ~((1u << k0) - 1u)) | 1u | (1u << k0);
-        if (k1) nm.y = (nm.y & ~((1u << k1) - 1u)) | 1u | (1u << k1);
-        if (k2) nm.z = (nm.z & ~((1u << k2) - 1u)) | 1u | (1u << k2);
-        if (k3) nm.w = (nm.w & ~((1u << k3) - 1u)) | 1u | (1u << k3);
-      }
+  }
+}
+
+// Step 1: per Spec of the stage the grid of the unordered phase: the breakpoints of the records
+// whose children all lie in finished stages (they come first). Nothing of it depends on the
+// stage itself, so it is derived, and solved, once.
+__device__ __noinline__ void phase_derive_early(const StageArgs& a, uint32_t gtid, uint32_t gthreads) {
+  for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
+    if (!computed_here(a, i)) continue;
+    const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+    uint32_t r0 = 1, r1 = 1, r2 = 1, r3 = 1;
+    for (uint32_t ci = 0; ci < cl.y; ci++) {
+      const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+      if ((c.z >> 24) & 1u) break;   // records with a same-stage child come last
+      record_breakpoints(a, cl.x + ci, c, r0, r1, r2, r3);
     }
-    const bool changed = first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w;
-    if (changed) {
+    *reinterpret_cast<uint4*>(&a.ehdr[i - a.lo]) = clip_at_corner(make_uint4(r0, r1, r2, r3), a.corner[i - a.lo]);
+  }
+}
+
+// Pass step 1: per Spec of the stage the grid the records with a same-stage child are solved on:
+// the real breakpoints of what the unordered phase found (first pass: they are in rmask), the
+// breakpoints of those records, and for their same-stage children the breakpoints in rmask -
+// first pass: of what the unordered phase found for the child; later passes: found real by the
+// pass before. Grids only grow; a Spec whose masks grew is marked for solving.
+__device__ __noinline__ void phase_derive_late(const StageArgs& a, uint32_t gtid, uint32_t gthreads, int first) {
+  for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
+    if (!computed_here(a, i)) continue;
+    const uint4 old = first ? a.rmask[i] : *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+    const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
+    uint32_t r0 = old.x, r1 = old.y, r2 = old.z, r3 = old.w;
+    for (uint32_t back = 0; back < cl.y; back++) {
+      const uint32_t ci = cl.y - 1 - back;
+      const uint4 c = __ldg(reinterpret_cast<const uint4*>(&a.cands[cl.x + ci]));
+      if (!((c.z >> 24) & 1u)) break;
+      record_breakpoints(a, cl.x + ci, c, r0, r1, r2, r3);
+    }
+    const uint4 nm = clip_at_corner(make_uint4(r0, r1, r2, r3), a.corner[i - a.lo]);
+    if (first || nm.x != old.x || nm.y != old.y || nm.z != old.z || nm.w != old.w) {
       *reinterpret_cast<uint4*>(&a.hdrs[i]) = nm;
       a.dirty[i] = 1;
     }
-    if (seed_copy) a.rmask[i] = nm;
   }
 }
 
@@ -546,43 +574,38 @@ __device__ __noinline__ void phase_spread(const StageArgs& a, uint32_t gtid, uin
   }
 }
 
-// Totals of what the coming solve takes (marked Specs only) and the working cells of the whole stage.
-__device__ __noinline__ void phase_totals(const StageArgs& a, uint32_t gtid, uint32_t gthreads) {
-  unsigned long long cells = 0, warps = 0, all_cells = 0;
+// Totals of what the coming solve takes: the grids of the unordered phase of all the stage's
+// Specs (early), or the grids of the marked Specs (else).
+__device__ __noinline__ void phase_totals(const StageArgs& a, uint32_t gtid, uint32_t gthreads, bool early) {
+  unsigned long long cells = 0, warps = 0;
   for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads) {
-    if (!computed_here(a, i)) continue;
-    const Grid g = grid_of(*reinterpret_cast<const uint4*>(&a.hdrs[i]));
-    all_cells += g.cells;
-    if (a.dirty[i]) {
-      cells += g.cells;
-      warps += g.warps;
-    }
+    if (!computed_here(a, i) || !(early || a.dirty[i])) continue;
+    const Grid g = grid_of(*reinterpret_cast<const uint4*>(early ? &a.ehdr[i - a.lo] : &a.hdrs[i]));
+    cells += g.cells;
+    warps += g.warps;
   }
   for (int o = 16; o > 0; o >>= 1) {
     cells += __shfl_xor_sync(0xFFFFFFFFu, cells, o);
     warps += __shfl_xor_sync(0xFFFFFFFFu, warps, o);
-    all_cells += __shfl_xor_sync(0xFFFFFFFFu, all_cells, o);
   }
-  if ((threadIdx.x & 31) == 0) {
-    if (cells) {
-      atomicAdd(&a.ctl->cells, cells);
-      atomicAdd(&a.ctl->warps, warps);
-    }
-    if (all_cells) atomicAdd(&a.ctl->all_cells, all_cells);
+  if ((threadIdx.x & 31) == 0 && cells) {
+    atomicAdd(&a.ctl->cells, cells);
+    atomicAdd(&a.ctl->warps, warps);
   }
 }
 
-// Pass step 2: gives every marked Spec of the stage fresh working rows (from temp_top up; Specs
-// that are not solved again keep theirs) and its chunks, and resets its real-breakpoint masks.
-// Capacities were checked against the pass totals before.
-__device__ __noinline__ void phase_place(const StageArgs& a, unsigned long long temp_top, uint32_t item_cells) {
+// Gives every Spec of the stage the rows of its grid of the unordered phase (early: in the base
+// rows, from row 0), or every marked Spec fresh working rows (from temp_top up; Specs that are not
+// solved again keep theirs), with its work items and chunks, and resets its real-breakpoint
+// masks. Capacities were checked against the totals before.
+__device__ __noinline__ void phase_place(const StageArgs& a, unsigned long long temp_top, uint32_t item_cells, bool early) {
   __shared__ unsigned long long row0, chunk0, item0;
   for (uint32_t base = a.lo + blockIdx.x * kBlock; base < a.hi; base += gridDim.x * kBlock) {
     const uint32_t i = base + threadIdx.x;
-    const bool active = i < a.hi && computed_here(a, i) && a.dirty[i] == 1;
+    const bool active = i < a.hi && computed_here(a, i) && (early || a.dirty[i] == 1);
     Grid g;
     g.cells = 0; g.warps = 0; g.F = 0;
-    if (active) g = grid_of(*reinterpret_cast<const uint4*>(&a.hdrs[i]));
+    if (active) g = grid_of(*reinterpret_cast<const uint4*>(early ? &a.ehdr[i - a.lo] : &a.hdrs[i]));
     const uint32_t n_items = (uint32_t)((g.cells + item_cells - 1) / item_cells);
     unsigned long long tot_cells, tot_warps, tot_items;
     const unsigned long long my_row = block_excl_scan(g.cells, &tot_cells);
@@ -602,9 +625,13 @@ __device__ __noinline__ void phase_place(const StageArgs& a, unsigned long long 
         it.first_cell = w * item_cells;
         a.items[item0 + my_item + w] = it;
       }
-      a.hdrs[i].row_base = (temp_top + row0 + my_row) | MRL_TEMP_FLAG;
+      if (early) {
+        a.ehdr[i - a.lo].row_base = row0 + my_row;
+      } else {
+        a.hdrs[i].row_base = (temp_top + row0 + my_row) | MRL_TEMP_FLAG;
+        a.dirty[i] = 2;   // solved by this pass
+      }
       a.rmask[i] = make_uint4(1u, 1u, 1u, 1u);
-      a.dirty[i] = 2;   // solved by this pass
       for (uint32_t w = 0; w < g.warps; w++) {
         Chunk c;
         c.spec = i;
@@ -620,8 +647,8 @@ __device__ __noinline__ void phase_place(const StageArgs& a, unsigned long long 
 // it and stores these records after all others, dearest first.
 __device__ __forceinline__ bool is_late(const uint4 a) { return (a.z >> 24) & 1u; }
 
-// Pass step 4a: the candidates whose children all lie in earlier stages, for every cell of every
-// Spec being solved. No order is needed. A warp takes a work item (up to MRL_ITEM_CELLS cells of one
+// Step 2: the candidates whose children all lie in earlier stages, for every cell of every
+// Spec's grid of the unordered phase. No order is needed. A warp takes a work item (up to MRL_ITEM_CELLS cells of one
 // Spec) at a time as it finishes others. Per item it first stages the Spec's records and the
 // headers of their children in shared memory, one record per lane, so that the chain record ->
 // child header -> child row costs two round trips per batch of records instead of two per record;
@@ -632,12 +659,13 @@ struct HotArgs {   // what the two solve phases read, by value: registers instea
   const CandRec* cands;
   const MrlRow* rows;
   MrlRow* temp;
-  MrlRow* base;             // beside every working row: what the unordered phase found for the cell
+  MrlRow* base;             // the grids of the unordered phase
+  const SpecHdr* ehdr;      // their masks and first rows; already offset: indexed by Spec id
   const uint32_t* corner;   // already offset: indexed by Spec id
 };
 __device__ __forceinline__ HotArgs hot_args(const StageArgs& s) {
   HotArgs h;
-  h.hdrs = s.hdrs; h.cands = s.cands; h.rows = s.rows; h.temp = s.temp; h.base = s.base; h.corner = s.corner - s.lo;
+  h.hdrs = s.hdrs; h.cands = s.cands; h.rows = s.rows; h.temp = s.temp; h.base = s.base; h.ehdr = s.ehdr - s.lo; h.corner = s.corner - s.lo;
   return h;
 }
 // A cell with a limit below its Spec's corner has no implementation; no record needs to be read.
@@ -734,11 +762,9 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
   for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_items;) {
     const WorkItem it = items[w];
     const uint32_t i = it.spec;
-    const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+    const uint4 m = *reinterpret_cast<const uint4*>(&a.ehdr[i]);
     const uint2 cl = *reinterpret_cast<const uint2*>(&a.hdrs[i].cand_off);
-    const unsigned long long row0 = a.hdrs[i].row_base & ~MRL_TEMP_FLAG;
-    MrlRow* const grid = a.temp + row0;
-    MrlRow* const found = a.base + row0;
+    MrlRow* const grid = a.base + a.ehdr[i].row_base;
     const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
     const uint32_t cells = n0 * n1 * n2 * n3;
     const uint32_t c_end = min(cells, it.first_cell + item_cells);
@@ -779,10 +805,7 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
         const bool live = valid && !below_corner(corner, cpack);
         Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
         if (!__any_sync(0xFFFFFFFFu, live)) {
-          if (valid && b0 == 0) {
-            *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
-            *reinterpret_cast<uint4*>(found + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
-          }
+          if (valid && b0 == 0) *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
           continue;
         }
         if (b0 && live) {   // what the earlier batches found
@@ -793,10 +816,8 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
         if (live) {
           for (uint32_t r = 0; r < n_here; r++) eval_staged(staged[r], a.rows, b0 + r, cpack, bm0, bm1, bm2, bm3, best, tally);
         }
-        if (valid && (b0 == 0 || live)) {   // the cell, and the copy the relaxation sweeps start from
+        if (valid && (b0 == 0 || live))
           *reinterpret_cast<uint4*>(grid + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
-          *reinterpret_cast<uint4*>(found + cell) = make_uint4(best.main, best.peaks, best.tail, best.ci);
-        }
       }
       if (late_lanes) break;
       b0 += nb;
@@ -896,8 +917,8 @@ __device__ __forceinline__ void eval_staged_late(const StagedRec& s, const MrlRo
 // Pass step 4b, one relaxation sweep: the candidates with a child in the Spec's own stage (relayout
 // Moves). Such a child is read at limits reduced by what the Move allocates, so the dependencies
 // between cells form no cycle and the system "cell = best of its candidates at its children's
-// values" has exactly one solution. A sweep recomputes every cell from what phase_early found for
-// it (kept in the base rows) and all its same-stage records at the children's current values, in
+// values" has exactly one solution. A sweep recomputes every cell from what phase_early found at
+// its limits (in the base rows) and all its same-stage records at the children's current values, in
 // place, while other warps read and write their own cells; a cell whose children all hold their
 // final values gets its final value, so every sweep settles at least one more level of the
 // dependency order, and the pass is finished after a sweep that changed nothing anywhere. (Keeping
@@ -920,6 +941,36 @@ __device__ __forceinline__ void stage_late_batch(const HotArgs& a, StagedRec* st
     }
   }
   __syncwarp();
+}
+
+// Pass step 3: every cell of the grids placed by this pass starts from what the unordered phase
+// found at the cell's limits. For a Spec without same-stage records that is its final value.
+__device__ __noinline__ void phase_late_init(const HotArgs a, const WorkItem* items, uint32_t n_items, uint32_t item_cells,
+                                             uint32_t* next_item) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_items;) {
+    const WorkItem it = items[w];
+    const uint32_t i = it.spec;
+    const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
+    MrlRow* const grid = a.temp + (a.hdrs[i].row_base & ~MRL_TEMP_FLAG);
+    const uint4 em = *reinterpret_cast<const uint4*>(&a.ehdr[i]);
+    const unsigned long long ebase = a.ehdr[i].row_base;
+    const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
+    const uint32_t c_end = min(n0 * n1 * n2 * n3, it.first_cell + item_cells);
+    for (uint32_t cell = it.first_cell + lane; cell < c_end; cell += 32) {
+      uint32_t rest = cell;
+      const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
+      const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
+      const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
+      const uint32_t k3 = nth_set_bit(m.w, rest);
+      *reinterpret_cast<uint4*>(grid + cell) =
+          *reinterpret_cast<const uint4*>(row_of(a.base, a.base, em, ebase, below(k0), below(k1), below(k2), below(k3)));
+    }
+    if (n_items <= gwarps) break;
+    if (lane == 0) w = gwarps + atomicAdd(next_item, 1u);
+    w = __shfl_sync(0xFFFFFFFFu, w, 0);
+  }
 }
 
 __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, uint32_t n_items, uint32_t item_cells,
@@ -958,9 +1009,9 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
     }
     if (fresh) {
       const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
-      const unsigned long long row0 = a.hdrs[i].row_base & ~MRL_TEMP_FLAG;
-      MrlRow* const grid = a.temp + row0;
-      const MrlRow* const found = a.base + row0;
+      MrlRow* const grid = a.temp + (a.hdrs[i].row_base & ~MRL_TEMP_FLAG);
+      const uint4 em = *reinterpret_cast<const uint4*>(&a.ehdr[i]);   // where the unordered phase left its result
+      const unsigned long long ebase = a.ehdr[i].row_base;
       const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
       const uint32_t c_end = min(n0 * n1 * n2 * n3, it.first_cell + item_cells);
       const uint32_t corner = a.corner[i];
@@ -979,11 +1030,11 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
         const bool live = valid && !below_corner(corner, cpack);
         if (!__any_sync(0xFFFFFFFFu, live)) continue;
         Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
+        const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
         if (live) {
-          const uint4 f = *reinterpret_cast<const uint4*>(found + cell);
+          const uint4 f = *reinterpret_cast<const uint4*>(row_of(a.base, a.base, em, ebase, bm0, bm1, bm2, bm3));
           best.main = f.x; best.peaks = f.y; best.tail = f.z; best.ci = f.w;
         }
-        const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
         for (uint32_t b = 0; b < n_late; b += kBatch) {
           const uint32_t n_here = min((uint32_t)kBatch, n_late - b);
           if (!single) stage_late_batch(a, staged, cl.x + cl.y - 1 - b, n_here, lane);
@@ -1021,15 +1072,18 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
 
 // Pass step 5: which breakpoints of the working grids are real. A breakpoint (memory k, code c)
 // is real when some cell starting at c differs from its neighbour one slot lower in k.
-__device__ __noinline__ void phase_real_masks(const StageArgs& a, uint32_t n_chunks) {
+// early: of the grids of the unordered phase (in the base rows), else of the working grids.
+__device__ __noinline__ void phase_real_masks(const StageArgs& a, uint32_t n_chunks, bool early) {
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t gwarps = gridDim.x * (kBlock / 32);
+  const SpecHdr* const H = early ? a.ehdr - a.lo : a.hdrs;
+  const MrlRow* const R = early ? a.base : a.temp;
   for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < n_chunks; w += gwarps) {
     const Chunk ch = a.chunks[w];
-    const Column c = decode_column(a.hdrs, ch, lane);
+    const Column c = decode_column(H, ch, lane);
     uint32_t bits[4] = {0, 0, 0, 0};
     if (c.valid) {
-      const unsigned long long base = a.hdrs[ch.spec].row_base & ~MRL_TEMP_FLAG;
+      const unsigned long long base = H[ch.spec].row_base & ~MRL_TEMP_FLAG;
       const uint32_t st[4] = {1u, c.nn[0], c.nn[0] * c.nn[1], c.nn[0] * c.nn[1] * c.nn[2]};
       const uint32_t mF = sel4(c.mm[0], c.mm[1], c.mm[2], c.mm[3], c.F);
       const uint32_t nF = sel4(c.nn[0], c.nn[1], c.nn[2], c.nn[3], c.F);
@@ -1043,11 +1097,11 @@ __device__ __noinline__ void phase_real_masks(const StageArgs& a, uint32_t n_chu
         const uint32_t codeF = __ffs(mrest) - 1;
         mrest &= mrest - 1;
         const unsigned long long r_at = base + off0 + (unsigned long long)s * stF;
-        const uint4 r = *reinterpret_cast<const uint4*>(a.temp + r_at);
+        const uint4 r = *reinterpret_cast<const uint4*>(R + r_at);
 #pragma unroll
         for (int k = 0; k < 4; k++) {
           if ((uint32_t)k == c.F || c.idx[k] == 0) continue;
-          const uint4 nb = *reinterpret_cast<const uint4*>(a.temp + r_at - st[k]);
+          const uint4 nb = *reinterpret_cast<const uint4*>(R + r_at - st[k]);
           if (nb.x != r.x || nb.y != r.y || nb.z != r.z) bits[k] |= 1u << c.code[k];
         }
         if (s > 0 && (prev.x != r.x || prev.y != r.y || prev.z != r.z)) fbits |= 1u << codeF;
@@ -1192,7 +1246,6 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
       ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
       ctl->spread_epoch = 0;
       ctl->temp_top = 0;
-      ctl->all_cells = 0;
       ctl->sweep_next[0] = ctl->sweep_next[1] = 0;
       ctl->late_changed = 0;
     }
@@ -1205,17 +1258,60 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
     uint32_t epoch = 0, sweep = 0, sweep_before = 0;
     unsigned long long combine_ns = 0, early_ns = 0, n_sweeps = 0;
     bool failed = false;
-    for (int pass = 0;; pass++) {
-      if (pass >= kMaxPasses) { failed = true; if (gtid == 0) { ctl->failed_stage = a.stage; ctl->error |= MRL_ERR_PASSES; } break; }
-      // masks: the first pass knows nothing about same-stage children and seeds their breakpoints
-      // one hop deep with their own first masks (a third fewer passes for a tenth more cells);
-      // later passes add the real breakpoints the previous passes found in them.
-      phase_derive(a, gtid, gthreads, pass == 0, pass == 0 ? 0 : 1, pass == 0, pass == 0);
-      GRID_SYNC();
-      if (pass == 0) {
-        phase_derive(a, gtid, gthreads, 0, 1, 0, 1);
+    const uint32_t gwarps = gridDim.x * (kBlock / 32);
+    // ---- once per stage: the corners, then the candidates whose children are all finished, on grids of their own
+    phase_corner(a, gtid, gthreads, 0);
+    GRID_SYNC();
+    phase_corner(a, gtid, gthreads, 1);
+    GRID_SYNC();
+    phase_derive_early(a, gtid, gthreads);
+    GRID_SYNC();
+    phase_totals(a, gtid, gthreads, true);
+    GRID_SYNC();
+    {
+      const unsigned long long cells = ctl->cells, warps = ctl->warps;
+      // Work items: an even share of the cells per warp, in whole warp-wide steps, at most
+      // MRL_ITEM_CELLS; every Spec adds at most one partial item.
+      const uint32_t item_cells = (uint32_t)min((unsigned long long)MRL_ITEM_CELLS, max(32ull, ((cells + gwarps - 1) / gwarps + 31ull) & ~31ull));
+      const unsigned long long max_items = cells / item_cells + (a.hi - a.lo);
+      if (cells > a.temp_cap || warps > a.chunk_cap || max_items > a.item_cap || cells >= 0xFFFFFFF0ull || warps >= 0xFFFFFFF0ull) {
+        failed = true;
+        if (gtid == 0) {
+          ctl->failed_stage = a.stage;
+          ctl->error |= MRL_ERR_WORKING;
+          ctl->need_temp = cells;
+          ctl->need_chunks = warps;
+          ctl->need_items = max_items;
+        }
+      } else if (cells) {
+        phase_place(a, 0, item_cells, true);
         GRID_SYNC();
-      } else {
+        const uint32_t n_items = ctl->item_cursor;
+        unsigned long long t0 = 0;
+        if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        phase_early(hot_args(a), a.items, n_items, item_cells, &ctl->item_next, block_stats);
+        GRID_SYNC();
+        if (gtid == 0) {
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+          early_ns += t1 - t0;
+          combine_ns += t1 - t0;
+        }
+        phase_real_masks(a, (uint32_t)warps, true);   // into rmask: what the first pass seeds the working grids with
+        if (gtid == 0) {
+          ctl->st_cells += cells;
+          ctl->cells = ctl->warps = ctl->row_cursor = 0;
+          ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
+        }
+        GRID_SYNC();
+      }
+    }
+    // ---- passes: the candidates with a same-stage child, until every working grid is consistent
+    for (int pass = 0; !failed; pass++) {
+      if (pass >= kMaxPasses) { failed = true; if (gtid == 0) { ctl->failed_stage = a.stage; ctl->error |= MRL_ERR_PASSES; } break; }
+      phase_derive_late(a, gtid, gthreads, pass == 0);
+      GRID_SYNC();
+      if (pass > 0) {
         // close the marks under "has a marked same-stage child"
         for (;;) {
           epoch++;
@@ -1224,12 +1320,9 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
           if (ctl->spread_epoch != epoch) break;
         }
       }
-      phase_totals(a, gtid, gthreads);
+      phase_totals(a, gtid, gthreads, false);
       GRID_SYNC();
       const unsigned long long cells = ctl->cells, warps = ctl->warps, temp_top = ctl->temp_top;
-      // Work items of the unordered phase: an even share of the pass's cells per warp, in whole
-      // warp-wide steps, at most MRL_ITEM_CELLS; every Spec adds at most one partial item.
-      const uint32_t gwarps = gridDim.x * (kBlock / 32);
       const uint32_t item_cells = (uint32_t)min((unsigned long long)MRL_ITEM_CELLS, max(32ull, ((cells + gwarps - 1) / gwarps + 31ull) & ~31ull));
       const unsigned long long max_items = cells / item_cells + (a.hi - a.lo);
       if (cells == 0) break;   // nothing left to solve: every working grid is consistent
@@ -1245,26 +1338,21 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
         }
         break;
       }
-      phase_place(a, temp_top, item_cells);
+      phase_place(a, temp_top, item_cells, false);
       GRID_SYNC();
       const uint32_t n_chunks = (uint32_t)warps;
       const uint32_t n_items = ctl->item_cursor;
       unsigned long long t0 = 0;
       if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-      phase_early(hot_args(a), a.items, n_items, item_cells, &ctl->item_next, block_stats);
+      phase_late_init(hot_args(a), a.items, n_items, item_cells, &ctl->item_next);
       GRID_SYNC();
-      if (gtid == 0) {
-        unsigned long long t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        early_ns += t1 - t0;
-      }
       for (bool first_sweep = true;; first_sweep = false) {
         sweep++;
         if (gtid == 0) ctl->sweep_next[(sweep + 1) & 1] = 0;   // the other counter is idle during this sweep
         phase_late(hot_args(a), a.items, n_items, item_cells, &ctl->sweep_next[sweep & 1], a.lo, a.stamp, sweep, first_sweep,
                    &ctl->late_changed, block_stats);
         GRID_SYNC();
-        if (ctl->late_changed != sweep) break;   // nothing improved anywhere: the stage's cells are consistent
+        if (ctl->late_changed != sweep) break;   // nothing changed anywhere: the stage's cells are consistent
       }
       if (gtid == 0) {
         unsigned long long t1;
@@ -1273,7 +1361,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
         n_sweeps += sweep - sweep_before;
       }
       sweep_before = sweep;
-      phase_real_masks(a, n_chunks);
+      phase_real_masks(a, n_chunks, false);
       for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads)
         if (a.dirty[i] == 2) a.dirty[i] = 0;
       if (gtid == 0) {
@@ -1282,7 +1370,6 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
         ctl->st_passes += 1;
         ctl->cells = ctl->warps = ctl->row_cursor = 0;
         ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
-        ctl->all_cells = 0;
       }
       GRID_SYNC();
     }
@@ -1455,10 +1542,10 @@ void DeviceFill::free_(void* p) {
 
 void DeviceFill::release() {
   wait_upload();
-  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_minsat_); free_(d_corner_); free_(d_stamp_); free_(d_rows_);
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_minsat_); free_(d_corner_); free_(d_stamp_); free_(d_ehdr_); free_(d_rows_);
   free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_);
   free_(d_dirty_);
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr; d_minsat_ = nullptr; d_corner_ = nullptr; d_stamp_ = nullptr;
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr; d_minsat_ = nullptr; d_corner_ = nullptr; d_stamp_ = nullptr; d_ehdr_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctl_ = nullptr;
   d_stage_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
@@ -1540,10 +1627,10 @@ int DeviceFill::wait_upload() { return wait_cands_(~uint64_t(0) >> 1); }
 int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   CK(cudaSetDevice(device_));
   wait_upload();   // of an earlier plan
-  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_minsat_); free_(d_corner_); free_(d_stamp_); free_(d_rows_);
+  free_(d_hdrs_); free_(d_cands_); free_(d_rmask_); free_(d_mine_); free_(d_chunks_); free_(d_items_); free_(d_minsat_); free_(d_corner_); free_(d_stamp_); free_(d_ehdr_); free_(d_rows_);
   free_(d_temp_); free_(d_fcount_); free_(d_block_sums_); free_(d_ctl_); free_(d_stage_);
   free_(d_dirty_);
-  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr; d_minsat_ = nullptr; d_corner_ = nullptr; d_stamp_ = nullptr;
+  d_hdrs_ = nullptr; d_cands_ = nullptr; d_rmask_ = nullptr; d_mine_ = nullptr; d_chunks_ = nullptr; d_items_ = nullptr; d_minsat_ = nullptr; d_corner_ = nullptr; d_stamp_ = nullptr; d_ehdr_ = nullptr;
   d_rows_ = nullptr; d_temp_ = nullptr; d_fcount_ = nullptr; d_block_sums_ = nullptr; d_ctl_ = nullptr;
   d_stage_ = nullptr; d_dirty_ = nullptr;
   stage_bytes_ = 0;
@@ -1561,6 +1648,7 @@ int DeviceFill::upload(const Plan& plan, bool skip_cands) {
   if ((rc = alloc_((void**)&d_minsat_, plan.hdrs.size() * sizeof(uint32_t)))) return rc;
   if ((rc = alloc_((void**)&d_corner_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
   if ((rc = alloc_((void**)&d_stamp_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
+  if ((rc = alloc_((void**)&d_ehdr_, (size_t)max_stage_ * sizeof(SpecHdr)))) return rc;
   if (!plan.mine.empty() && (rc = alloc_((void**)&d_mine_, plan.mine.size()))) return rc;
   if ((rc = alloc_((void**)&d_fcount_, (size_t)max_stage_ * sizeof(uint32_t)))) return rc;
   if ((rc = alloc_((void**)&d_block_sums_, ((size_t)max_stage_ / kBlock + 1) * sizeof(unsigned long long)))) return rc;
@@ -1771,7 +1859,7 @@ int DeviceFill::launch_solve_(const Plan& plan, uint32_t si, bool place_too) {
   }
   StageArgs a;
   a.hdrs = d_hdrs_; a.cands = d_cands_; a.rmask = d_rmask_; a.mine = d_mine_; a.dirty = d_dirty_;
-  a.chunks = d_chunks_; a.items = d_items_; a.rows = d_rows_; a.temp = d_temp_; a.base = d_temp_ + temp_cap_;
+  a.chunks = d_chunks_; a.items = d_items_; a.rows = d_rows_; a.temp = d_temp_; a.base = d_temp_ + temp_cap_; a.ehdr = d_ehdr_;
   a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.minsat = d_minsat_; a.corner = d_corner_; a.stamp = d_stamp_; a.ctl = d_ctl_;
   a.lo = st.spec_lo; a.hi = st.spec_hi; a.top_pack = plan.top_pack(); a.stage = si;
   a.prev_lo = si ? plan.stages[si - 1].spec_lo : 0; a.prev_hi = si ? plan.stages[si - 1].spec_hi : 0;
@@ -1793,7 +1881,7 @@ int DeviceFill::launch_place_(const Plan& plan, uint32_t si) {
   if (n == 0) return 0;
   StageArgs a;
   a.hdrs = d_hdrs_; a.cands = d_cands_; a.rmask = d_rmask_; a.mine = d_mine_; a.dirty = d_dirty_;
-  a.chunks = d_chunks_; a.items = d_items_; a.rows = d_rows_; a.temp = d_temp_; a.base = d_temp_ + temp_cap_;
+  a.chunks = d_chunks_; a.items = d_items_; a.rows = d_rows_; a.temp = d_temp_; a.base = d_temp_ + temp_cap_; a.ehdr = d_ehdr_;
   a.fcount = d_fcount_; a.block_sums = d_block_sums_; a.minsat = d_minsat_; a.corner = d_corner_; a.stamp = d_stamp_; a.ctl = d_ctl_;
   a.lo = st.spec_lo; a.hi = st.spec_hi; a.top_pack = plan.top_pack(); a.stage = si;
   a.prev_lo = si ? plan.stages[si - 1].spec_lo : 0; a.prev_hi = si ? plan.stages[si - 1].spec_hi : 0;

@@ -94,7 +94,6 @@ struct FillCtl {
   uint32_t pad0;
   // -- one stage
   unsigned long long temp_top;       // working rows handed out so far in this stage
-  unsigned long long all_cells;      // working cells of all the stage's Specs under the final masks
   // -- sticky over a fill
   uint32_t error;                    // MRL_ERR_* bits
   uint32_t failed_stage;             // first stage that raised one

@@ -105,12 +105,13 @@ class DeviceFill {
   uint8_t* d_mine_ = nullptr;
   uint8_t* d_dirty_ = nullptr;   // by Spec id: to be solved (again) in the coming pass
   uint32_t* d_minsat_ = nullptr; // by Spec id: lower corner of the satisfiable region
+  SpecHdr* d_ehdr_ = nullptr;    // by position in the stage being solved: the Spec's grid of the unordered phase
   uint32_t* d_stamp_ = nullptr;  // by position in the stage being solved: last relaxation sweep that improved the Spec
   uint32_t* d_corner_ = nullptr; // by position in the stage being solved: where its working grids are clipped
   Chunk* d_chunks_ = nullptr;
   WorkItem* d_items_ = nullptr;  // pieces of working grids for the unordered solve phase
   MrlRow* d_rows_ = nullptr;     // the table
-  MrlRow* d_temp_ = nullptr;     // working grids of the stage being solved (temp_cap_ rows), then as many rows for what the unordered phase found
+  MrlRow* d_temp_ = nullptr;     // working grids of the stage being solved (temp_cap_ rows), then as many rows for the grids of the unordered phase
   uint32_t* d_fcount_ = nullptr;
   unsigned long long* d_block_sums_ = nullptr;
   FillCtl* d_ctl_ = nullptr;
