@@ -58,6 +58,14 @@ typedef struct mrl_stats {
   double combine_ms;           /* of which inside the solve phases (device timer) */
   double early_ms;             /* of which the phase that needs no order: candidates whose children lie in earlier stages */
   uint64_t n_sweeps;           /* relaxation sweeps over the candidates with a same-stage child, all passes */
+  double plan_goal_seconds;    /* of plan_seconds: enumerating the goal Specs */
+  double plan_discover_seconds;/* of plan_seconds: closure of the goals and their candidate records */
+  double plan_layout_seconds;  /* of plan_seconds: stage order, final ids, record array */
+  uint64_t n_cells_unordered;  /* of n_cells_solved: cells of the grids of the unordered phase */
+  uint64_t n_candidates_swept; /* of n_candidates_evaluated: by the relaxation sweeps */
+  uint64_t n_items_swept;      /* work items (pieces of one Spec's working grid) the sweeps evaluated */
+  double phase_ms[8];          /* device time of the last fill by part of the stage kernels: setup, unordered phase, its real
+                                * breakpoints, per-pass setup, cell initialisation, first sweeps, later sweeps, real breakpoints */
 } mrl_stats;
 
 /* One row of the device table as mrl_export_all hands it out: main cost; peak memory as lattice

@@ -69,6 +69,10 @@ void copy_fill_stats(mrl_ctx* ctx) {
   ctx->stats.combine_ms = fs.combine_ms;
   ctx->stats.early_ms = fs.early_ms;
   ctx->stats.n_sweeps = fs.sweeps;
+  ctx->stats.n_cells_unordered = fs.early_cells;
+  ctx->stats.n_candidates_swept = fs.late_cands;
+  ctx->stats.n_items_swept = fs.late_items;
+  for (int k = 0; k < 8; k++) ctx->stats.phase_ms[k] = fs.phase_ms[k];
 }
 
 // Upload + fill of the planned tables.
@@ -103,6 +107,8 @@ int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals, int mirror_dty
   ctx->stats.n_candidates = ps.n_cands;
   ctx->stats.n_stages = ps.n_stages;
   ctx->stats.plan_seconds = now_s() - t0;
+  ctx->stats.plan_discover_seconds = ps.seconds_discover;
+  ctx->stats.plan_layout_seconds = ps.seconds_layout;
   return 0;
 }
 
@@ -239,8 +245,10 @@ int mrl_plan_precompute(mrl_ctx* ctx, uint32_t size, int through, int dtype_mask
       mirror = DT_F32;
     }
     std::vector<LogicalSpec> goals = precompute_goals(size, (Through)through, dts, ctx->n_threads);
+    const double t_goals = now_s() - t0;
     int rc = set_plan(ctx, goals, mirror);
     ctx->stats.plan_seconds = now_s() - t0;
+    ctx->stats.plan_goal_seconds = t_goals;
     return rc;
   } catch (const std::exception& e) {
     return fail(ctx, -1, e.what());

@@ -1008,6 +1008,7 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
       fresh = __any_sync(0xFFFFFFFFu, fresh);
     }
     if (fresh) {
+      if (lane == 0) atomicAdd(&block_stats[4], 1ull);
       const uint4 m = *reinterpret_cast<const uint4*>(&a.hdrs[i]);
       MrlRow* const grid = a.temp + (a.hdrs[i].row_base & ~MRL_TEMP_FLAG);
       const uint4 em = *reinterpret_cast<const uint4*>(&a.ehdr[i]);   // where the unordered phase left its result
@@ -1065,8 +1066,8 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
     tl += __shfl_xor_sync(0xFFFFFFFFu, tl, o);
   }
   if (lane == 0 && (tc | tl)) {
-    atomicAdd(&block_stats[0], (unsigned long long)tc);
-    atomicAdd(&block_stats[1], (unsigned long long)tl);
+    atomicAdd(&block_stats[2], (unsigned long long)tc);
+    atomicAdd(&block_stats[3], (unsigned long long)tl);
   }
 }
 
@@ -1237,8 +1238,8 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
   uint32_t syncs = 0;
 #define GRID_SYNC() do { grid.sync(); syncs++; } while (0)
   if (ctl->error) return;   // an earlier stage failed: the host repairs and resumes (uniform: nothing writes it before the first barrier)
-  __shared__ unsigned long long block_stats[2];   // candidates evaluated, rows gathered
-  if (threadIdx.x < 2) block_stats[threadIdx.x] = 0;
+  __shared__ unsigned long long block_stats[5];   // candidates evaluated and rows gathered by the unordered phase; by the sweeps; items the sweeps evaluated
+  if (threadIdx.x < 5) block_stats[threadIdx.x] = 0;
   __syncthreads();
   if (a.solve) {
     if (gtid == 0) {
@@ -1256,7 +1257,11 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
     phase_minsat(a, gtid, gthreads);
     GRID_SYNC();
     uint32_t epoch = 0, sweep = 0, sweep_before = 0;
-    unsigned long long combine_ns = 0, early_ns = 0, n_sweeps = 0;
+    unsigned long long n_sweeps = 0, t_last = 0;
+    if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_last));
+    // device time since the last mark goes to part ph (thread 0 only; after a barrier)
+#define MARK(ph) do { if (gtid == 0) { unsigned long long t_now; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_now)); \
+                                       ctl->st_phase_ns[ph] += t_now - t_last; t_last = t_now; } } while (0)
     bool failed = false;
     const uint32_t gwarps = gridDim.x * (kBlock / 32);
     // ---- once per stage: the corners, then the candidates whose children are all finished, on grids of their own
@@ -1286,24 +1291,20 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
       } else if (cells) {
         phase_place(a, 0, item_cells, true);
         GRID_SYNC();
+        MARK(MRL_PH_SETUP);
         const uint32_t n_items = ctl->item_cursor;
-        unsigned long long t0 = 0;
-        if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
         phase_early(hot_args(a), a.items, n_items, item_cells, &ctl->item_next, block_stats);
         GRID_SYNC();
-        if (gtid == 0) {
-          unsigned long long t1;
-          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-          early_ns += t1 - t0;
-          combine_ns += t1 - t0;
-        }
+        MARK(MRL_PH_EARLY);
         phase_real_masks(a, (uint32_t)warps, true);   // into rmask: what the first pass seeds the working grids with
         if (gtid == 0) {
           ctl->st_cells += cells;
+          ctl->st_early_cells += cells;
           ctl->cells = ctl->warps = ctl->row_cursor = 0;
           ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
         }
         GRID_SYNC();
+        MARK(MRL_PH_EARLY_MASKS);
       }
     }
     // ---- passes: the candidates with a same-stage child, until every working grid is consistent
@@ -1340,26 +1341,22 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
       }
       phase_place(a, temp_top, item_cells, false);
       GRID_SYNC();
+      MARK(MRL_PH_PASS_SETUP);
       const uint32_t n_chunks = (uint32_t)warps;
       const uint32_t n_items = ctl->item_cursor;
-      unsigned long long t0 = 0;
-      if (gtid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
       phase_late_init(hot_args(a), a.items, n_items, item_cells, &ctl->item_next);
       GRID_SYNC();
+      MARK(MRL_PH_INIT);
       for (bool first_sweep = true;; first_sweep = false) {
         sweep++;
         if (gtid == 0) ctl->sweep_next[(sweep + 1) & 1] = 0;   // the other counter is idle during this sweep
         phase_late(hot_args(a), a.items, n_items, item_cells, &ctl->sweep_next[sweep & 1], a.lo, a.stamp, sweep, first_sweep,
                    &ctl->late_changed, block_stats);
         GRID_SYNC();
+        MARK(first_sweep ? MRL_PH_SWEEP_FIRST : MRL_PH_SWEEP_MORE);
         if (ctl->late_changed != sweep) break;   // nothing changed anywhere: the stage's cells are consistent
       }
-      if (gtid == 0) {
-        unsigned long long t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        combine_ns += t1 - t0;
-        n_sweeps += sweep - sweep_before;
-      }
+      n_sweeps += sweep - sweep_before;
       sweep_before = sweep;
       phase_real_masks(a, n_chunks, false);
       for (uint32_t i = a.lo + gtid; i < a.hi; i += gthreads)
@@ -1372,13 +1369,18 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
         ctl->chunk_cursor = ctl->item_cursor = ctl->item_next = 0;
       }
       GRID_SYNC();
+      MARK(MRL_PH_PASS_MASKS);
     }
+    MARK(MRL_PH_PASS_SETUP);   // of a pass that found nothing left to solve
+#undef MARK
     __syncthreads();
-    if (threadIdx.x == 0 && (block_stats[0] | block_stats[1])) {
-      atomicAdd(&ctl->st_cands, block_stats[0]);
-      atomicAdd(&ctl->st_lookups, block_stats[1]);
+    if (threadIdx.x == 0 && (block_stats[0] | block_stats[1] | block_stats[2] | block_stats[4])) {
+      atomicAdd(&ctl->st_cands, block_stats[0] + block_stats[2]);
+      atomicAdd(&ctl->st_lookups, block_stats[1] + block_stats[3]);
+      atomicAdd(&ctl->st_late_cands, block_stats[2]);
+      atomicAdd(&ctl->st_late_items, block_stats[4]);
     }
-    if (gtid == 0) { ctl->st_combine_ns += combine_ns; ctl->st_early_ns += early_ns; ctl->st_sweeps += n_sweeps; }
+    if (gtid == 0) ctl->st_sweeps += n_sweeps;
     if (failed) {
       if (gtid == 0) ctl->st_syncs += syncs;
       return;   // uniform
@@ -1959,8 +1961,12 @@ void DeviceFill::take_stats_() {
   stats_.passes = c.st_passes;
   stats_.grid_syncs = c.st_syncs;
   stats_.sweeps = c.st_sweeps;
-  stats_.combine_ms = (float)(c.st_combine_ns * 1e-6);
-  stats_.early_ms = (float)(c.st_early_ns * 1e-6);
+  stats_.early_cells = c.st_early_cells;
+  stats_.late_cands = c.st_late_cands;
+  stats_.late_items = c.st_late_items;
+  for (int k = 0; k < 8; k++) stats_.phase_ms[k] = (float)(c.st_phase_ns[k] * 1e-6);
+  stats_.early_ms = stats_.phase_ms[MRL_PH_EARLY];
+  stats_.combine_ms = stats_.early_ms + stats_.phase_ms[MRL_PH_INIT] + stats_.phase_ms[MRL_PH_SWEEP_FIRST] + stats_.phase_ms[MRL_PH_SWEEP_MORE];
 }
 
 int DeviceFill::end_fill() {

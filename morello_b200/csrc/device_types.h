@@ -77,6 +77,18 @@ enum {
   MRL_ERR_PASSES = 8,     // a stage did not reach a consistent limits grid
 };
 
+// Parts of a stage kernel whose device time is accounted separately.
+enum {
+  MRL_PH_SETUP = 0,       // corners, grids of the unordered phase, their placement
+  MRL_PH_EARLY = 1,       // the unordered phase
+  MRL_PH_EARLY_MASKS = 2, // real breakpoints of its result
+  MRL_PH_PASS_SETUP = 3,  // per pass: working grids, marks, placement
+  MRL_PH_INIT = 4,        // per pass: cells start from the unordered phase's result
+  MRL_PH_SWEEP_FIRST = 5, // per pass: the first relaxation sweep
+  MRL_PH_SWEEP_MORE = 6,  // per pass: the sweeps after it
+  MRL_PH_PASS_MASKS = 7,  // per pass: real breakpoints of the working grids
+};
+
 // Control block of a fill, in device memory. The stage kernels read their sizes and cursors
 // here and leave the host nothing to decide between launches; the host reads it once per fill
 // (once per stage when the fill is sharded).
@@ -105,11 +117,13 @@ struct FillCtl {
   unsigned long long st_cands;       // candidate records evaluated
   unsigned long long st_lookups;     // child rows gathered
   unsigned long long st_passes;
-  unsigned long long st_combine_ns;  // device time inside the solve phases (globaltimer)
-  unsigned long long st_early_ns;    // of which the unordered phase (with the cell listing)
   unsigned long long st_final_bytes; // algorithmic bytes of the finished rows (see fill.hpp)
   unsigned long long st_syncs;       // grid-wide barriers executed
   unsigned long long st_sweeps;      // relaxation sweeps, all passes
+  unsigned long long st_early_cells; // of st_cells: cells of the grids of the unordered phase
+  unsigned long long st_late_cands;  // of st_cands: evaluated by the sweeps
+  unsigned long long st_late_items;  // work items the sweeps evaluated
+  unsigned long long st_phase_ns[8]; // device time by part of the stage kernel (see MRL_PH_*)
   // -- scratch of verify and checksum
   unsigned long long scratch[4];
 };

@@ -21,11 +21,15 @@ struct FillStats {
   uint64_t alg_bytes = 0;
   uint64_t passes = 0;          // solve passes over all stages
   uint64_t launches = 0;        // kernel launches
+  uint64_t early_cells = 0;     // of cells_solved: cells of the grids of the unordered phase
+  uint64_t late_cands = 0;      // of cands_evaluated: by the relaxation sweeps
+  uint64_t late_items = 0;      // work items the sweeps evaluated
   uint64_t sweeps = 0;          // relaxation sweeps of the candidates with a same-stage child
   uint64_t grid_syncs = 0;      // grid-wide barriers inside the stage kernels
   float fill_ms = 0;            // device time of the whole fill (CUDA events on the launch stream)
   float combine_ms = 0;         // device time inside the solve phases (device timer)
   float early_ms = 0;           // of which the unordered phase
+  float phase_ms[8] = {};       // device time by part of the stage kernels (MRL_PH_*)
 };
 
 class DeviceFill {

@@ -298,7 +298,9 @@ class SynthesisDatabase:
     def stats(self) -> dict:
         s = L.Stats()
         self._check(self._lib.mrl_get_stats(self._ctx, C.byref(s)))
-        return {name: getattr(s, name) for name, _ in L.Stats._fields_}
+        out = {name: getattr(s, name) for name, _ in L.Stats._fields_}
+        out["phase_ms"] = [float(x) for x in s.phase_ms]
+        return out
 
     def num_specs(self) -> int:
         return int(self._lib.mrl_num_specs(self._ctx))
