@@ -338,6 +338,12 @@ def cuda_arm(args):
                    "candidates_evaluated_per_step_rank0": st["n_candidates_evaluated"],
                    "rows_gathered_per_step_rank0": st["n_rows_gathered"], "grid_syncs_per_step_rank0": st["n_grid_syncs"],
                    "solve_phases_ms_rank0": st["combine_ms"], "unordered_phase_ms_rank0": st["early_ms"],
+                   "relaxation_sweeps_per_step_rank0": st["n_sweeps"],
+                   "cells_of_the_unordered_phase_rank0": st["n_cells_unordered"],
+                   "candidates_evaluated_by_sweeps_rank0": st["n_candidates_swept"],
+                   "kernel_parts_ms_rank0": dict(zip(["setup", "unordered_phase", "its_real_breakpoints", "pass_setup",
+                                                      "cell_init", "first_sweeps", "later_sweeps", "pass_real_breakpoints"],
+                                                     [round(x, 2) for x in st["phase_ms"]])),
                    "l2": ("candidate records and headers %.1f GB + table %.2f GB, larger than L2; L2 also flushed "
                           "between fills" % (plan_gb, table_gb)),
                    "multi_gpu": ("Specs of each stage sharded over %d ranks; masks and rows exchanged per stage over "
@@ -346,6 +352,8 @@ def cuda_arm(args):
         "cells_solved_per_s": sum(cells_by_rank) / (ms_per_step * 1e-3),
         "e2e": {"value": units / e2e_step, "unit": "specs/s", "h2d_bytes_per_step": st2["h2d_bytes"],
                 "d2h_bytes_per_step": st2["d2h_bytes"], "plan_s": st2["plan_seconds"],
+                "plan_parts_s": {"goals": st2["plan_goal_seconds"], "closure_and_records": st2["plan_discover_seconds"],
+                                 "ids_and_record_array": st2["plan_layout_seconds"]},
                 "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "wall_s": e2e_step, "wall_s_runs": e2e_s},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
