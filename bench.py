@@ -362,7 +362,8 @@ def cuda_arm(args):
                      "algorithmic_bytes_how": ("final table rows only: per row 12 B out, 16 B per candidate record of its "
                                                "Spec, 16 B per child of each candidate that fits the row's limits"),
                      "kernel_ms_per_step": kernel_ms, "kernel_launches_per_step": launches // args.steps,
-                     "limiter": "load latency and instruction issue, not DRAM bandwidth (see profiles/)"},
+                     "limiter": ("instruction issue (55-60 % of cycles in the stages that carry the time) and the latency of "
+                                 "dependent loads at 32 resident warps per SM; DRAM at 0.13 of peak (profiles/)")},
         "parity": parity,
         "clocks": clocks,
     }
