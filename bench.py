@@ -308,7 +308,9 @@ def cuda_arm(args):
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         parity["checksum_equal_on_all_ranks"] = bool(torch.equal(mn, mx))
         solo_sum = None
-        if rank == 0:   # the same workload filled by this GPU alone
+        if rank == 0 and SIZE >= 16:
+            parity["equals_single_gpu"] = None   # records, table and working rows of this size do not fit one GPU
+        elif rank == 0:   # the same workload filled by this GPU alone
             solo = m.SynthesisDatabase(device=local_rank)
             solo.precompute(SIZE, through=THROUGH, dtypes=DTYPES)
             solo_sum = solo.checksum()
@@ -321,7 +323,7 @@ def cuda_arm(args):
     hbm_gbs, peak_kind = measured_peaks()
     # the dominant kernel is the stage kernel: every launch of a fill is one, so its time is the fill's
     kernel_ms = ms_per_step
-    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    achieved = alg_bytes / world / (kernel_ms * 1e-3) / 1e9   # per GPU: the bytes of the finished table, split over the ranks
     table_gb = st["n_rows"] * 16 / 1e9
     plan_gb = (st["n_candidates"] * 32 + st["n_specs"] * 48) / 1e9
     line = {
@@ -358,6 +360,7 @@ def cuda_arm(args):
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "stage_kernel",
+                     "scope": "one GPU" if world == 1 else "per GPU (bytes of the whole job / %d ranks)" % world,
                      "algorithmic_bytes_per_step": alg_bytes,
                      "algorithmic_bytes_how": ("final table rows only: per row 12 B out, 16 B per candidate record of its "
                                                "Spec, 16 B per child of each candidate that fits the row's limits"),
@@ -382,9 +385,10 @@ def cuda_arm(args):
             if t and "dram_bytes_per_cell" in t:  # measured DRAM bytes per solved working cell on a small case, scaled to this step (see the file's "how")
                 traffic = t["dram_bytes_per_cell"] * sum(cells_by_rank)
                 line["roofline"]["traffic"] = traffic
-                line["roofline"]["traffic_how"] = "scaled from a small-case ncu capture: profiles/traffic.json"
-                line["roofline"]["dram_GBps"] = traffic / (kernel_ms * 1e-3) / 1e9
-                line["roofline"]["dram_frac_of_peak"] = traffic / (kernel_ms * 1e-3) / 1e9 / hbm_gbs
+                line["roofline"]["traffic_how"] = ("DRAM bytes of one single-GPU fill of this workload (one ncu pass per launch), "
+                                                   "scaled by the working cells solved: profiles/traffic.json")
+                line["roofline"]["dram_GBps"] = traffic / world / (kernel_ms * 1e-3) / 1e9   # per GPU
+                line["roofline"]["dram_frac_of_peak"] = traffic / world / (kernel_ms * 1e-3) / 1e9 / hbm_gbs
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)

@@ -1904,16 +1904,39 @@ int DeviceFill::solve_stage(const Plan& plan, uint32_t si) {
   return launch_solve_(plan, si, false);
 }
 
+static const char* kErrorBits = "(1: candidate record out of range, 2: working buffers too small, 4: row table too small, "
+                                "8: no consistent limits grid)";
+
+// Where the stage's real-breakpoint masks lie (what the ranks exchange before any of them places
+// the stage). The masks must be final before they travel, so this is where a rank learns that its
+// solve ran out of working room: it enlarges its own buffers and solves the stage again; the other
+// ranks wait in the exchange.
 int DeviceFill::stage_masks(const Plan& plan, uint32_t si, void** ptr, uint64_t* bytes) {
   if (si >= plan.stages.size()) { snprintf(err_, sizeof(err_), "stage index out of range"); return -3; }
   const Stage& st = plan.stages[si];
+  if (filling_ && st.spec_hi != st.spec_lo) {
+    int rc;
+    if (read_ctl_() != 0) return -1;
+    if (h_ctl_->error & MRL_ERR_WORKING) {
+      const uint32_t bits = h_ctl_->error;
+      if (bits & ~(uint32_t)(MRL_ERR_WORKING | MRL_ERR_TABLE)) {
+        snprintf(err_, sizeof(err_), "a fill kernel reported error bits 0x%x in stage %u %s", bits, h_ctl_->failed_stage, kErrorBits);
+        return -2;
+      }
+      if ((rc = grow_after_error_(MRL_ERR_WORKING))) return rc;
+      CK(cudaMemsetAsync(&d_ctl_->error, 0, sizeof(uint32_t), stream_));
+      if ((rc = launch_solve_(plan, si, false))) return rc;
+      if (read_ctl_() != 0) return -1;
+      if (h_ctl_->error) {
+        snprintf(err_, sizeof(err_), "stage %u failed again after its working buffers were enlarged (0x%x)", si, h_ctl_->error);
+        return -2;
+      }
+    }
+  }
   if (ptr) *ptr = d_rmask_ + st.spec_lo;
   if (bytes) *bytes = (uint64_t)(st.spec_hi - st.spec_lo) * sizeof(uint4);
   return 0;
 }
-
-static const char* kErrorBits = "(1: candidate record out of range, 2: working buffers too small, 4: row table too small, "
-                                "8: no consistent limits grid)";
 
 // Appends the stage's compacted grids to the table and reports where they went (the slice other
 // ranks need), which costs the one synchronisation of the stage. A stage that ran out of room is
