@@ -150,14 +150,16 @@ def reference_arm(args):
         return
     cores = os.cpu_count() or 1
     times, last = [], None
+    # each step is one bounded sample; the samples are sized so that the whole run stays within five minutes
+    budget = min(args.cpu_budget, max(3.0, 300.0 / max(1, args.steps)))
     for i in range((0 if SIZE > 2 else args.warmup) + args.steps):
-        rep, o = run_oracle(cores, args.cpu_budget)
+        rep, o = run_oracle(cores, budget)
         o.close()
         if SIZE > 2 or i >= args.warmup:
             times.append(rep["seconds"])
             last = rep
     per_step = sum(times) / len(times)
-    base = cpu_baseline_object(last, cores, args.cpu_budget)
+    base = cpu_baseline_object(last, cores, budget)
     line = {
         "impl": "reference", "metric": "specs_resolved_per_s", "value": base["value"], "unit": "specs/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,

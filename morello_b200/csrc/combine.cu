@@ -60,6 +60,7 @@ constexpr int kBlock = 128;      // threads per block of every kernel here
 #endif
 constexpr int kMinBlocks = MRL_MIN_BLOCKS;   // resident blocks per SM the stage kernel is compiled for
 constexpr int kMaxPasses = 128;
+constexpr int kMaxSweeps = 256;   // per pass; a dependency chain is shorter than the 70 diagonals of the limits lattice
 
 __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
   uint32_t s = a + b;
@@ -1372,7 +1373,13 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageAr
         GRID_SYNC();
         MARK(first_sweep ? MRL_PH_SWEEP_FIRST : MRL_PH_SWEEP_MORE);
         if (ctl->late_changed != sweep) break;   // nothing changed anywhere: the stage's cells are consistent
+        if (sweep - sweep_before >= (uint32_t)kMaxSweeps) {   // more sweeps than the limits lattice has diagonals: give up rather than spin
+          failed = true;
+          if (gtid == 0) { ctl->failed_stage = a.stage; ctl->error |= MRL_ERR_PASSES; }
+          break;
+        }
       }
+      if (failed) break;
       n_sweeps += sweep - sweep_before;
       sweep_before = sweep;
       phase_real_masks(a, n_chunks, false);
