@@ -358,7 +358,8 @@ def cuda_arm(args):
                 "d2h_bytes_per_step": st2["d2h_bytes"], "plan_s": st2["plan_seconds"],
                 "plan_parts_s": {"goals": st2["plan_goal_seconds"], "closure_and_records": st2["plan_discover_seconds"],
                                  "ids_and_record_array": st2["plan_layout_seconds"]},
-                "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "wall_s": e2e_step, "wall_s_runs": e2e_s},
+                "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "buffer_growths": st2["n_buffer_growths"],
+                "wall_s": e2e_step, "wall_s_runs": e2e_s},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "stage_kernel",

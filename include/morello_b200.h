@@ -64,6 +64,7 @@ typedef struct mrl_stats {
   uint64_t n_cells_unordered;  /* of n_cells_solved: cells of the grids of the unordered phase */
   uint64_t n_candidates_swept; /* of n_candidates_evaluated: by the relaxation sweeps */
   uint64_t n_items_swept;      /* work items (pieces of one Spec's working grid) the sweeps evaluated */
+  uint64_t n_buffer_growths;   /* times the last fill had to enlarge a device buffer and solve a stage again */
   double phase_ms[8];          /* device time of the last fill by part of the stage kernels: setup, unordered phase, its real
                                 * breakpoints, per-pass setup, cell initialisation, first sweeps, later sweeps, real breakpoints */
 } mrl_stats;

@@ -72,6 +72,7 @@ void copy_fill_stats(mrl_ctx* ctx) {
   ctx->stats.n_cells_unordered = fs.early_cells;
   ctx->stats.n_candidates_swept = fs.late_cands;
   ctx->stats.n_items_swept = fs.late_items;
+  ctx->stats.n_buffer_growths = fs.growths;
   for (int k = 0; k < 8; k++) ctx->stats.phase_ms[k] = fs.phase_ms[k];
 }
 

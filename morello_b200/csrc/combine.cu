@@ -1820,6 +1820,7 @@ int DeviceFill::read_ctl_() {
 // hold nothing worth keeping between stages; the rows placed so far move along.
 int DeviceFill::grow_after_error_(uint32_t bits) {
   if (fixed_) return too_large_();
+  stats_.growths++;
   CK(cudaStreamSynchronize(stream_));
   auto regrow = [&](void** p, uint64_t* cap, uint64_t need, size_t elem) -> int {
     if (need <= *cap) return 0;

@@ -24,6 +24,7 @@ struct FillStats {
   uint64_t early_cells = 0;     // of cells_solved: cells of the grids of the unordered phase
   uint64_t late_cands = 0;      // of cands_evaluated: by the relaxation sweeps
   uint64_t late_items = 0;      // work items the sweeps evaluated
+  uint64_t growths = 0;         // times a buffer had to be enlarged (the stage that asked is solved again)
   uint64_t sweeps = 0;          // relaxation sweeps of the candidates with a same-stage child
   uint64_t grid_syncs = 0;      // grid-wide barriers inside the stage kernels
   float fill_ms = 0;            // device time of the whole fill (CUDA events on the launch stream)
