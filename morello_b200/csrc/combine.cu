@@ -1,26 +1,33 @@
 // The CUDA side of the synthesis-database fill (sm_100a).
 //
 // Specs are processed stage by stage (plan.hpp). One cooperative launch solves a whole stage
-// on the device, with grid-wide barriers between its phases and nothing for the host to decide:
-//   1. every Spec gets its working limits grid: per memory the lattice codes at which its
-//      result can change - thresholds of its own candidates plus the (shifted) breakpoints of
-//      the finished tables of its children (phase_derive);
-//   2. the Specs to solve get working rows, and the working cells are listed by limits diagonal
-//      (sum of the four codes) (phase_place, phase_histogram, phase_scatter);
-//   3. every working cell is solved. Evaluating a candidate at a cell = feasibility under the
-//      cell's limits, gather of the child rows at the children's limits, combine into a Cost,
-//      lexicographic minimum. Candidates whose children all lie in earlier stages need no order:
-//      a warp takes a Spec, its lanes take 32 cells at a time and walk those candidate records
-//      together, so record and child-header loads are warp-uniform (phase_early). The rest -
-//      relayout Moves, whose body is a Spec of the same stage at strictly lower limits - are
-//      evaluated diagonal by diagonal in ascending order, one thread per listed cell, starting
-//      from the optimum of the first group (phase_combine);
-//   4. breakpoints at which some pair of neighbouring cells differs are real
-//      (phase_real_masks); 1-4 repeat for the Specs whose grid still lacks a breakpoint that a
-//      same-stage child turned out to have, and for the Specs above them;
-//   5. the working grids are compacted to the real breakpoints and appended to the table
+// on the device, with grid-wide barriers between its phases and nothing for the host to decide.
+// A limits grid of a Spec = per memory the lattice codes at which its result can change; a cell
+// = one combination of slots; evaluating a candidate record at a cell = feasibility under the
+// cell's limits, gather of the child rows at the children's limits, combine into a Cost,
+// lexicographic minimum.
+//   0. corners: below its corner a Spec has no implementation at all; every grid of the stage is
+//      clipped there (phase_minsat, phase_corner);
+//   1. once per stage, the records whose children all lie in earlier stages are solved on a grid
+//      of their own - their thresholds plus the (shifted) breakpoints of those children's
+//      finished tables - in no particular order: a warp takes a piece of one Spec's grid, stages
+//      the Spec's records and the headers of their children in shared memory, and its lanes take
+//      32 cells at a time and walk the staged records together (phase_derive_early,
+//      phase_place, phase_early); the real breakpoints of the result are found at once
+//      (phase_real_masks);
+//   2. the rest - relayout Moves, whose body is a Spec of the same stage at strictly lower limits
+//      - is solved on working grids: the real breakpoints of step 1's result, the thresholds of
+//      those records and the shifted breakpoints of their children (phase_derive_late). Every
+//      working cell starts from step 1's result at its limits (phase_late_init) and is recomputed
+//      in place, sweep after sweep, from that and its records at the children's current values,
+//      until a sweep changes nothing (phase_late): the dependencies between cells form no cycle,
+//      so that fixpoint is the direct solve;
+//   3. breakpoints at which some pair of neighbouring cells differs are real
+//      (phase_real_masks); 2-3 repeat for the Specs whose working grid still lacks a breakpoint
+//      that a same-stage child turned out to have, and for the Specs above them (phase_spread);
+//   4. the working grids are compacted to the real breakpoints and appended to the table
 //      (phase_final_count, phase_scan_sums, phase_compact).
-// Step 4's fixpoint is exact: when every Spec's grid contains all thresholds and all shifted
+// Step 3's fixpoint is exact: when every Spec's grid contains all thresholds and all shifted
 // breakpoints of the computed tables of its children, induction over the limits lattice shows
 // every computed cell equals the direct solve at every limit inside it.
 //
@@ -267,8 +274,8 @@ __device__ __forceinline__ Grid grid_of(const uint4 m) {
   Grid g;
   g.nn[0] = __popc(m.x); g.nn[1] = __popc(m.y); g.nn[2] = __popc(m.z); g.nn[3] = __popc(m.w);
   g.cells = (unsigned long long)g.nn[0] * g.nn[1] * g.nn[2] * g.nn[3];
-  // The free memory is the one with the most slots (lowest index on ties): a column then has
-  // a cell on as many diagonals as possible.
+  // The free memory is the one with the most slots (lowest index on ties): the longest columns,
+  // so the fewest chunks.
   g.F = 0;
   uint32_t best = g.nn[0];
 #pragma unroll
@@ -1245,8 +1252,8 @@ __device__ __noinline__ void phase_compact(const StageArgs& a) {
 }
 
 // One stage, start to finish, in one cooperative launch. Every thread of the grid reaches every
-// barrier: what decides the control flow (pass totals, the closure epoch, the occupied
-// diagonals, the error word) is read from device memory after a barrier and written again only
+// barrier: what decides the control flow (totals, the closure epoch, the sweep that last changed
+// a cell, the error word) is read from device memory after a barrier and written again only
 // after a later one, so all threads take the same branches.
 __global__ void __launch_bounds__(kBlock, kMinBlocks) stage_kernel(const StageArgs a) {
   cg::grid_group grid = cg::this_grid();

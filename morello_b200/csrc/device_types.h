@@ -60,7 +60,7 @@ struct Chunk {
   uint32_t col_start;
 };
 
-// A piece of one Spec's working grid for the unordered solve phase: consecutive cells from
+// A piece of one Spec's grid for a solve phase: consecutive cells from
 // first_cell on, at most MRL_ITEM_CELLS of them (a pass picks the size). Warps take items as they
 // finish others.
 #define MRL_ITEM_CELLS 1024u

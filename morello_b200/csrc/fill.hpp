@@ -114,7 +114,7 @@ class DeviceFill {
   uint32_t* d_stamp_ = nullptr;  // by position in the stage being solved: last relaxation sweep that improved the Spec
   uint32_t* d_corner_ = nullptr; // by position in the stage being solved: where its working grids are clipped
   Chunk* d_chunks_ = nullptr;
-  WorkItem* d_items_ = nullptr;  // pieces of working grids for the unordered solve phase
+  WorkItem* d_items_ = nullptr;  // pieces of grids, handed out to warps by the solve phases
   MrlRow* d_rows_ = nullptr;     // the table
   MrlRow* d_temp_ = nullptr;     // working grids of the stage being solved (temp_cap_ rows), then as many rows for the grids of the unordered phase
   uint32_t* d_fcount_ = nullptr;
