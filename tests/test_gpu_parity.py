@@ -182,6 +182,30 @@ def test_size2_tables_satisfy_the_recurrence_at_every_lattice_point(m):
     db.close()
 
 
+def test_refills_are_identical_and_the_statistics_add_up(m):
+    """The relaxation sweeps update cells in place while other warps read them, so how often a
+    Spec is looked at differs from run to run; the table must not. Two fills of one plan give the
+    same rows (checksum) and the same grids; what the kernel reports about itself is consistent."""
+    db = m.SynthesisDatabase()
+    db.plan_precompute(4)
+    db.upload()
+    db.fill()
+    first, st1 = db.checksum(), db.stats()
+    db.fill()
+    second, st2 = db.checksum(), db.stats()
+    assert first == second == 0x2C30E967E6CC225F   # the size-4 tables (pinned against the oracle by the tests above)
+    for st in (st1, st2):
+        assert st["n_rows"] == 3573174
+        assert 0 < st["n_cells_unordered"] < st["n_cells_solved"]
+        assert st["n_sweeps"] >= st["n_passes"] > 0     # every pass ends with a sweep that changes nothing
+        assert 0 < st["n_candidates_swept"] < st["n_candidates_evaluated"]
+        assert 0 < sum(st["phase_ms"]) <= st["fill_ms"] * 1.001
+    assert st2["n_buffer_growths"] == 0 and st2["n_launches"] == st2["n_stages"]   # the buffers fit by now: one launch per stage
+    assert st1["n_rows"] == st2["n_rows"] and st1["n_cells_solved"] == st2["n_cells_solved"] and st1["n_passes"] == st2["n_passes"]
+    assert db.verify(5_000_000, seed=9)[1] == 0
+    db.close()
+
+
 def test_verify_notices_a_corrupted_row(m):
     import torch
     from morello_b200 import sharded
