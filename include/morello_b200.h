@@ -167,7 +167,10 @@ int mrl_fill(mrl_ctx* ctx);
  *   mrl_set_shard, mrl_plan_*, mrl_upload, then per fill: mrl_fill_begin;
  *   for s in stages { mrl_fill_stage_solve(s, &masks, &n); sum masks;
  *                     mrl_fill_stage_place(s, &rows, &n); sum rows }; mrl_fill_end.
- * masks: the limits-grid breakpoints of the stage's Specs; rows: their finished table rows. */
+ * masks: the limits-grid breakpoints of the stage's Specs; rows: their finished table rows.
+ * Both stage calls wait for the stream: mrl_fill_stage_solve until the masks are final (a rank
+ * whose solve ran out of working room enlarges its own buffers and solves the stage again there,
+ * while the others wait in the sum), mrl_fill_stage_place until the size of the row slice is known. */
 int mrl_set_shard(mrl_ctx* ctx, uint32_t rank, uint32_t world);
 /* The ranks of one node share its host cores, so only one of them should plan: it exposes its
  * plan as eight flat host byte ranges (mrl_plan_share), the caller carries the bytes to the other
