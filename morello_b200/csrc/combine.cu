@@ -62,10 +62,7 @@ static_assert(MRL_STATIC_SCRATCH_BYTES == MRL_NOALLOC_MAX_BYTES,
 namespace {
 
 constexpr int kBlock = 128;      // threads per block of every kernel here
-#ifndef MRL_MIN_BLOCKS
-#define MRL_MIN_BLOCKS 8
-#endif
-constexpr int kMinBlocks = MRL_MIN_BLOCKS;   // resident blocks per SM the stage kernel is compiled for
+constexpr int kMinBlocks = 8;   // resident blocks per SM the stage kernel is compiled for
 constexpr int kMaxPasses = 128;
 constexpr int kMaxSweeps = 256;   // per pass; a dependency chain is shorter than the 70 diagonals of the limits lattice
 
@@ -682,10 +679,7 @@ __device__ __forceinline__ bool below_corner(uint32_t corner, uint32_t cpack) {
          code_of(cpack, 2) < corner_of(corner, 2) || code_of(cpack, 3) < corner_of(corner, 3);
 }
 
-#ifndef MRL_BATCH
-#define MRL_BATCH 16
-#endif
-constexpr int kBatch = MRL_BATCH;   // records staged at a time
+constexpr int kBatch = 16;   // records staged at a time
 struct StagedRec {           // a record with what the row lookups of its children need
   uint4 rec;                 // action | kind << 16 | nchild << 24, imm, level | thr << 8 | peak << 16, units
   uint4 mask[3];
