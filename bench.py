@@ -357,7 +357,8 @@ def cuda_arm(args):
         "e2e": {"value": units / e2e_step, "unit": "specs/s", "h2d_bytes_per_step": st2["h2d_bytes"],
                 "d2h_bytes_per_step": st2["d2h_bytes"], "plan_s": st2["plan_seconds"],
                 "plan_parts_s": {"goals": st2["plan_goal_seconds"], "closure_and_records": st2["plan_discover_seconds"],
-                                 "ids_and_record_array": st2["plan_layout_seconds"]},
+                                 "ids_and_record_array": st2["plan_layout_seconds"],
+                                 "of_which_record_array": st2["plan_layout_step_seconds"][3]},
                 "upload_s": st2["upload_seconds"], "fill_ms": st2["fill_ms"], "buffer_growths": st2["n_buffer_growths"],
                 "wall_s": e2e_step, "wall_s_runs": e2e_s},
         "gpu_launches": launches,

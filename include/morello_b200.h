@@ -61,6 +61,8 @@ typedef struct mrl_stats {
   double plan_goal_seconds;    /* of plan_seconds: enumerating the goal Specs */
   double plan_discover_seconds;/* of plan_seconds: closure of the goals and their candidate records */
   double plan_layout_seconds;  /* of plan_seconds: stage order, final ids, record array */
+  double plan_layout_step_seconds[8]; /* of that: key sort, final ids, twin leaf kernels and offsets, record array, id table,
+                                       * stages and families, order and twin checks, release of temporaries */
   uint64_t n_cells_unordered;  /* of n_cells_solved: cells of the grids of the unordered phase */
   uint64_t n_candidates_swept; /* of n_candidates_evaluated: by the relaxation sweeps */
   uint64_t n_items_swept;      /* work items (pieces of one Spec's working grid) the sweeps evaluated */

@@ -23,7 +23,8 @@ class Stats(C.Structure):
                 ("algorithmic_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
                 ("plan_seconds", C.c_double), ("upload_seconds", C.c_double), ("fill_ms", C.c_double),
                 ("combine_ms", C.c_double), ("early_ms", C.c_double), ("n_sweeps", C.c_uint64), ("plan_goal_seconds", C.c_double), ("plan_discover_seconds", C.c_double),
-                ("plan_layout_seconds", C.c_double), ("n_cells_unordered", C.c_uint64),
+                ("plan_layout_seconds", C.c_double), ("plan_layout_step_seconds", C.c_double * 8),
+                ("n_cells_unordered", C.c_uint64),
                 ("n_candidates_swept", C.c_uint64), ("n_items_swept", C.c_uint64), ("n_buffer_growths", C.c_uint64),
                 ("phase_ms", C.c_double * 8)]
 

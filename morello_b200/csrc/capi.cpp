@@ -110,6 +110,7 @@ int set_plan(mrl_ctx* ctx, const std::vector<LogicalSpec>& goals, int mirror_dty
   ctx->stats.plan_seconds = now_s() - t0;
   ctx->stats.plan_discover_seconds = ps.seconds_discover;
   ctx->stats.plan_layout_seconds = ps.seconds_layout;
+  for (int k = 0; k < 8; k++) ctx->stats.plan_layout_step_seconds[k] = ps.seconds_layout_step[k];
   return 0;
 }
 

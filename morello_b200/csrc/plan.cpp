@@ -600,6 +600,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
 
   // ---- 2. final ids: stage-major (phase, log-shape sum, memory-level sum), then key order ----
   double t1 = now_s();
+  double t_step = t1;
+  auto step_done = [&](int k) { const double t = now_s(); plan.stats.seconds_layout_step[k] += t - t_step; t_step = t; };
   std::vector<u32> order(n);
   std::vector<u32> gkey(n);
   parallel_for(n, n_threads, [&](size_t i, int) { gkey[i] = stage_key(temp[(u32)i].ls); });
@@ -634,6 +636,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       });
     for (auto& th : pool) th.join();
   }
+  step_done(0);   // stage keys, buckets, key sort
   // Final ids. Without twins: the sorted position. With twins every stage holds its discovered
   // Specs followed by their twins (the key orders by dtype right after the kind, and dt_a < dt_b):
   // position i of a stage that starts at sorted position lo and has cnt Specs becomes id i + lo,
@@ -666,6 +669,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
       plan.goal_ids[gi] = (twin && goals[gi].dtype == dt_b) ? id_b[plan.goal_ids[gi]] : id_a[plan.goal_ids[gi]];
   }
 
+  step_done(1);   // final ids
   plan.specs.reset(N);
   plan.hdrs.reset(N);
   // candidate records per final id; a twin swaps the leaf records for its own
@@ -689,6 +693,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   const u64 ncand = offs[N];
   if (ncand > 0xFFFFFFFFull) throw ModelError("too many candidate records");
   plan.cands.reset(ncand);
+  step_done(2);   // twin leaf kernels, record offsets
   {
     // Written in the order the Specs were discovered - the order their temporary records were
     // allocated in - and each Spec's temporary records are released as soon as they are copied. A
@@ -750,6 +755,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     }
     plan.stats.n_children += kids_t[0];
   }
+  step_done(3);   // record array
   // The temporary Specs are taken apart by a few threads of their own while the rest of the
   // plan is built; whoever drops the plan's handle last (normally the end of this function)
   // waits for them.
@@ -792,6 +798,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     });
   }
 
+  step_done(4);   // id table
   // stages, and inside them families: maximal runs with equal dtype and shape (ids are
   // key-sorted, and the key starts with kind, dtype, serial flag, rank, shape)
   {
@@ -833,6 +840,7 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     }
   }
 
+  step_done(5);   // stages and families
   // The order the device relies on: a child never lies in a later stage; a child inside its
   // parent's stage belongs to a Move that consumes memory (so it sits at strictly lower limits),
   // to the parent's family and - when the fill is sharded - to the rank that solves the parent.
@@ -903,7 +911,9 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
     if (bad.load() >= 0)
       throw ModelError("planner: records derived for a dtype twin differ from direct tabulation: " + plan.specs[(u32)bad.load()].str());
   }
+  step_done(6);   // owners, order check, twin spot check
   plan.cleanup_.reset();   // waits for the release of the temporaries
+  step_done(7);   // waiting for the temporaries' release
   plan.stats.seconds_layout = now_s() - t1;
 
   plan.stats.n_specs = N;

@@ -78,6 +78,7 @@ struct PlanStats {
   u64 n_stages = 0;
   u64 n_families = 0;
   double seconds_discover = 0, seconds_layout = 0;
+  double seconds_layout_step[8] = {};   // key sort, final ids, twin leaves and offsets, record array, id table, stages and families, checks, release of temporaries
 };
 
 // Specs with the same phase (kind), log-shape sum and memory-level rank (sum over operands of

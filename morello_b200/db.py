@@ -300,6 +300,7 @@ class SynthesisDatabase:
         self._check(self._lib.mrl_get_stats(self._ctx, C.byref(s)))
         out = {name: getattr(s, name) for name, _ in L.Stats._fields_}
         out["phase_ms"] = [float(x) for x in s.phase_ms]
+        out["plan_layout_step_seconds"] = [float(x) for x in s.plan_layout_step_seconds]
         return out
 
     def num_specs(self) -> int:
