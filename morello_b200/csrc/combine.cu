@@ -1033,22 +1033,31 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
       const uint4 em = *reinterpret_cast<const uint4*>(&a.ehdr[i]);   // where the unordered phase left its result
       const unsigned long long ebase = a.ehdr[i].row_base;
       const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z), n3 = __popc(m.w);
-      const uint32_t c_end = min(n0 * n1 * n2 * n3, it.first_cell + item_cells);
+      const uint32_t cells = n0 * n1 * n2 * n3;
       const uint32_t corner = a.corner[i];
+      // Grids are clipped at the corner, so the cells below it are exactly those in slot 0 of a
+      // clipped memory; they stay unsatisfiable and are left out: the lanes walk the live cells
+      // only. The item's share of them: its range of all cells, scaled (the items of a Spec tile
+      // its cells, so the scaled ranges tile the live ones).
+      const uint32_t z0 = corner_of(corner, 0) ? 1u : 0u, z1 = corner_of(corner, 1) ? 1u : 0u, z2 = corner_of(corner, 2) ? 1u : 0u,
+                     z3 = corner_of(corner, 3) ? 1u : 0u;
+      const uint32_t v0 = n0 - z0, v1 = n1 - z1, v2 = n2 - z2, v3 = n3 - z3;
+      const unsigned long long live_cells = (corner_of(corner, 0) == MRL_NEVER) ? 0ull : (unsigned long long)v0 * v1 * v2 * v3;
+      const uint32_t c_hi = min(cells, it.first_cell + item_cells);
+      const uint32_t l_begin = (uint32_t)(live_cells * it.first_cell / cells), l_end = (uint32_t)(live_cells * c_hi / cells);
       const bool single = n_late <= (uint32_t)kBatch;   // all records staged once for the whole item
       if (single) stage_late_batch(a, staged, cl.x + cl.y - 1, n_late, lane);
       bool changed_any = false;
-      for (uint32_t c0 = it.first_cell; c0 < c_end; c0 += 32) {
-        const uint32_t cell = c0 + lane;
-        const bool valid = cell < c_end;
-        uint32_t rest = valid ? cell : 0u;
-        const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
-        const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
-        const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
-        const uint32_t k3 = nth_set_bit(m.w, rest);
+      for (uint32_t c0 = l_begin; c0 < l_end; c0 += 32) {
+        const bool live = c0 + lane < l_end;
+        uint32_t rest = live ? c0 + lane : l_begin;
+        const uint32_t s0 = rest % v0 + z0; rest /= v0;
+        const uint32_t s1 = rest % v1 + z1; rest /= v1;
+        const uint32_t s2 = rest % v2 + z2;
+        const uint32_t s3 = rest / v2 + z3;
+        const uint32_t cell = ((s3 * n2 + s2) * n1 + s1) * n0 + s0;
+        const uint32_t k0 = nth_set_bit(m.x, s0), k1 = nth_set_bit(m.y, s1), k2 = nth_set_bit(m.z, s2), k3 = nth_set_bit(m.w, s3);
         const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
-        const bool live = valid && !below_corner(corner, cpack);
-        if (!__any_sync(0xFFFFFFFFu, live)) continue;
         Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
         const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
         if (live) {
