@@ -683,28 +683,29 @@ constexpr int kBatch = 16;   // records staged at a time
 struct StagedRec {           // a record with what the row lookups of its children need
   uint4 rec;                 // action | kind << 16 | nchild << 24, imm, level | thr << 8 | peak << 16, units
   uint4 mask[3];
-  unsigned long long base[3];
+  const MrlRow* grid[3];     // per child: the first row of its grid, in the table or in the working rows
   uint32_t stride[3][3];     // per child: rows per step in memories 1, 2, 3 of its grid
-  uint32_t pad;
+  uint8_t in_temp[4];        // per child: its grid lies in the working rows (it may change during a sweep)
 };
 static_assert(sizeof(StagedRec) == 128, "staged record");
 
 // What the lookups of one child need, into its slot of a staged record.
-__device__ __forceinline__ void stage_child(StagedRec& s, uint32_t j, const uint4 m, unsigned long long base) {
+__device__ __forceinline__ void stage_child(StagedRec& s, uint32_t j, const uint4 m, unsigned long long base, const MrlRow* rows,
+                                            const MrlRow* temp) {
   s.mask[j] = m;
-  s.base[j] = base;
+  s.grid[j] = row_at(rows, temp, base);
+  s.in_temp[j] = (base & MRL_TEMP_FLAG) ? 1 : 0;
   const uint32_t n0 = __popc(m.x), n1 = __popc(m.y), n2 = __popc(m.z);
   s.stride[j][0] = n0;
   s.stride[j][1] = n0 * n1;
   s.stride[j][2] = n0 * n1 * n2;
 }
 // row_of with the child's header and strides at hand.
-__device__ __forceinline__ const MrlRow* staged_row(const StagedRec& s, uint32_t j, const MrlRow* rows, const MrlRow* temp,
-                                                    uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+__device__ __forceinline__ const MrlRow* staged_row(const StagedRec& s, uint32_t j, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
   const uint4 m = s.mask[j];
   const uint32_t i0 = __popc(m.x & b0) - 1, i1 = __popc(m.y & b1) - 1, i2 = __popc(m.z & b2) - 1, i3 = __popc(m.w & b3) - 1;
   const uint32_t off = i3 * s.stride[j][2] + i2 * s.stride[j][1] + i1 * s.stride[j][0] + i0;   // cells per Spec < 2^32
-  return row_at(rows, temp, s.base[j]) + off;
+  return s.grid[j] + off;
 }
 
 // A staged record at one limits point; eval_candidate with the record and the child headers
@@ -737,10 +738,10 @@ __device__ __forceinline__ void eval_staged(const StagedRec& s, const MrlRow* __
       c2 = (level == 2) ? cb : c2;
       c3 = (level == 3) ? cb : c3;
     }
-    const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(staged_row(s, 0, rows, rows, c0, c1, c2, c3)));
+    const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(staged_row(s, 0, c0, c1, c2, c3)));
     uint4 r1 = r0, r2 = r0;
-    if (nchild > 1) r1 = __ldg(reinterpret_cast<const uint4*>(staged_row(s, 1, rows, rows, c0, c1, c2, c3)));
-    if (nchild > 2) r2 = __ldg(reinterpret_cast<const uint4*>(staged_row(s, 2, rows, rows, c0, c1, c2, c3)));
+    if (nchild > 1) r1 = __ldg(reinterpret_cast<const uint4*>(staged_row(s, 1, c0, c1, c2, c3)));
+    if (nchild > 2) r2 = __ldg(reinterpret_cast<const uint4*>(staged_row(s, 2, c0, c1, c2, c3)));
     tally.lookups += nchild;
     if (r0.z == MRL_UNSAT || r1.z == MRL_UNSAT || r2.z == MRL_UNSAT) return;
     uint32_t depth;
@@ -809,7 +810,7 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
         const uint32_t r = t / 3u, j = t - r * 3u;
         if (j < (staged[r].rec.x >> 24)) {
           const uint32_t child = __ldg(&a.cands[cl.x + b0 + r].child[j]);
-          stage_child(staged[r], j, __ldg(reinterpret_cast<const uint4*>(&a.hdrs[child])), __ldg(&a.hdrs[child].row_base));
+          stage_child(staged[r], j, __ldg(reinterpret_cast<const uint4*>(&a.hdrs[child])), __ldg(&a.hdrs[child].row_base), a.rows, a.rows);
         }
       }
       __syncwarp();
@@ -898,9 +899,8 @@ __device__ __forceinline__ void eval_staged_late(const StagedRec& s, const MrlRo
 #pragma unroll
   for (int j = 0; j < 3; j++) {
     if ((uint32_t)j < nchild) {
-      const unsigned long long base = s.base[j];
-      const MrlRow* const p = staged_row(s, j, rows, temp, c0, c1, c2, c3);
-      r[j] = (base & MRL_TEMP_FLAG) ? ld_row_shared(p) : __ldg(reinterpret_cast<const uint4*>(p));
+      const MrlRow* const p = staged_row(s, j, c0, c1, c2, c3);
+      r[j] = s.in_temp[j] ? ld_row_shared(p) : __ldg(reinterpret_cast<const uint4*>(p));
     } else {
       r[j] = r[0];
     }
@@ -956,7 +956,7 @@ __device__ __forceinline__ void stage_late_batch(const HotArgs& a, StagedRec* st
     const uint32_t r = t / 3u, j = t - r * 3u;
     if (j < (staged[r].rec.x >> 24)) {
       const uint32_t child = __ldg(&a.cands[last_rec - r].child[j]);
-      stage_child(staged[r], j, *reinterpret_cast<const uint4*>(&a.hdrs[child]), a.hdrs[child].row_base);   // same-stage headers: written earlier in this launch
+      stage_child(staged[r], j, *reinterpret_cast<const uint4*>(&a.hdrs[child]), a.hdrs[child].row_base, a.rows, a.temp);   // same-stage headers: written earlier in this launch
     }
   }
   __syncwarp();
