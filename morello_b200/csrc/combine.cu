@@ -708,6 +708,20 @@ __device__ __forceinline__ const MrlRow* staged_row(const StagedRec& s, uint32_t
   return s.grid[j] + off;
 }
 
+// The lattice code of every slot of a grid, memory after memory, for the lanes of a warp to look
+// up instead of counting bits (a grid has at most 17 + 17 + 12 + 27 slots).
+constexpr int kMaxSlots = 80;
+__device__ __forceinline__ void stage_slot_codes(uint8_t* codes, const uint4 m, uint32_t n0, uint32_t n1, uint32_t n2, uint32_t n3,
+                                                 uint32_t lane) {
+  __syncwarp();   // the previous item's codes have been read by every lane
+  for (uint32_t t = lane; t < n0 + n1 + n2 + n3; t += 32) {
+    uint32_t mk = m.x, slot = t;
+    if (slot >= n0) { slot -= n0; mk = m.y; if (slot >= n1) { slot -= n1; mk = m.z; if (slot >= n2) { slot -= n2; mk = m.w; } } }
+    codes[t] = (uint8_t)nth_set_bit(mk, slot);
+  }
+  __syncwarp();
+}
+
 // A staged record at one limits point; eval_candidate with the record and the child headers
 // already at hand. All children are finished, so the rows come from the table on the read-only path.
 __device__ __forceinline__ void eval_staged(const StagedRec& s, const MrlRow* __restrict__ rows, uint32_t ci,
@@ -777,7 +791,9 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t gwarps = gridDim.x * (kBlock / 32);
   __shared__ StagedRec staged_all[kBlock / 32][kBatch];
+  __shared__ uint8_t codes_all[kBlock / 32][kMaxSlots];
   StagedRec* const staged = staged_all[threadIdx.x >> 5];   // this warp's
+  uint8_t* const codes = codes_all[threadIdx.x >> 5];
   Tally tally = {0, 0};
   // every warp starts with the item of its own number; further items are handed out by a counter
   // (no atomics at all when there are fewer items than warps)
@@ -791,6 +807,7 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
     const uint32_t cells = n0 * n1 * n2 * n3;
     const uint32_t c_end = min(cells, it.first_cell + item_cells);
     const uint32_t corner = a.corner[i];
+    stage_slot_codes(codes, m, n0, n1, n2, n3, lane);
     uint32_t b0 = 0;
     do {
       // stage the next records (those with a same-stage child come last and end the walk) ...
@@ -818,10 +835,10 @@ __device__ __noinline__ void phase_early(const HotArgs a, const WorkItem* items,
         const uint32_t cell = c0 + lane;
         const bool valid = cell < c_end;
         uint32_t rest = valid ? cell : 0u;
-        const uint32_t k0 = nth_set_bit(m.x, rest % n0); rest /= n0;
-        const uint32_t k1 = nth_set_bit(m.y, rest % n1); rest /= n1;
-        const uint32_t k2 = nth_set_bit(m.z, rest % n2); rest /= n2;
-        const uint32_t k3 = nth_set_bit(m.w, rest);
+        const uint32_t k0 = codes[rest % n0]; rest /= n0;
+        const uint32_t k1 = codes[n0 + rest % n1]; rest /= n1;
+        const uint32_t k2 = codes[n0 + n1 + rest % n2]; rest /= n2;
+        const uint32_t k3 = codes[n0 + n1 + n2 + rest];
         const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
         const bool live = valid && !below_corner(corner, cpack);
         Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
@@ -997,7 +1014,9 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
                                         uint32_t sweep, bool first_sweep, uint32_t* changed,
                                         unsigned long long* block_stats) {
   __shared__ StagedRec staged_all[kBlock / 32][kBatch];
+  __shared__ uint8_t codes_all[kBlock / 32][kMaxSlots];
   StagedRec* const staged = staged_all[threadIdx.x >> 5];   // this warp's
+  uint8_t* const codes = codes_all[threadIdx.x >> 5];
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t gwarps = gridDim.x * (kBlock / 32);
   Tally tally = {0, 0};
@@ -1046,6 +1065,7 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
       const uint32_t c_hi = min(cells, it.first_cell + item_cells);
       const uint32_t l_begin = (uint32_t)(live_cells * it.first_cell / cells), l_end = (uint32_t)(live_cells * c_hi / cells);
       const bool single = n_late <= (uint32_t)kBatch;   // all records staged once for the whole item
+      stage_slot_codes(codes, m, n0, n1, n2, n3, lane);
       if (single) stage_late_batch(a, staged, cl.x + cl.y - 1, n_late, lane);
       bool changed_any = false;
       for (uint32_t c0 = l_begin; c0 < l_end; c0 += 32) {
@@ -1056,7 +1076,7 @@ __device__ __noinline__ void phase_late(const HotArgs a, const WorkItem* items, 
         const uint32_t s2 = rest % v2 + z2;
         const uint32_t s3 = rest / v2 + z3;
         const uint32_t cell = ((s3 * n2 + s2) * n1 + s1) * n0 + s0;
-        const uint32_t k0 = nth_set_bit(m.x, s0), k1 = nth_set_bit(m.y, s1), k2 = nth_set_bit(m.z, s2), k3 = nth_set_bit(m.w, s3);
+        const uint32_t k0 = codes[s0], k1 = codes[n0 + s1], k2 = codes[n0 + n1 + s2], k3 = codes[n0 + n1 + n2 + s3];
         const uint32_t cpack = k0 | (k1 << 8) | (k2 << 16) | (k3 << 24);
         Best best = {MRL_UNSAT, MRL_UNSAT, MRL_UNSAT, MRL_UNSAT};
         const uint32_t bm0 = below(k0), bm1 = below(k1), bm2 = below(k2), bm3 = below(k3);
