@@ -287,8 +287,7 @@ __device__ __forceinline__ Grid grid_of(const uint4 m) {
 // than the Spec's free memory F.
 struct Column {
   uint32_t spec, F;
-  uint32_t mm[4], nn[4], idx[4], code[4];
-  uint32_t others;  // sum of the codes of the fixed memories
+  uint32_t mm[4], nn[4], idx[4];
   bool valid;
 };
 __device__ __forceinline__ Column decode_column(const SpecHdr* hdrs, const Chunk ch, uint32_t lane) {
@@ -298,15 +297,12 @@ __device__ __forceinline__ Column decode_column(const SpecHdr* hdrs, const Chunk
   const uint4 m = *reinterpret_cast<const uint4*>(&hdrs[ch.spec]);
   c.mm[0] = m.x; c.mm[1] = m.y; c.mm[2] = m.z; c.mm[3] = m.w;
   uint32_t rest = (ch.col_start & 0x3FFFFFFFu) + lane;
-  c.others = 0;
 #pragma unroll
   for (int k = 0; k < 4; k++) {
     c.nn[k] = (uint32_t)__popc(c.mm[k]);
     const uint32_t nk = ((uint32_t)k == c.F) ? 1u : c.nn[k];
-    c.idx[k] = rest % nk;
+    c.idx[k] = rest % nk;   // for F: slot 0
     rest /= nk;
-    c.code[k] = nth_set_bit(c.mm[k], c.idx[k]);  // for F: slot 0, code 0
-    c.others += c.code[k];
   }
   c.valid = rest == 0;  // false: column index beyond this Spec's grid
   return c;
@@ -1141,7 +1137,7 @@ __device__ __noinline__ void phase_real_masks(const StageArgs& a, uint32_t n_chu
 #pragma unroll
       for (int k = 0; k < 4; k++) off0 += c.idx[k] * st[k];   // idx[F] is 0
       uint4 prev = make_uint4(0, 0, 0, 0);
-      uint32_t fbits = 0, mrest = mF;
+      uint32_t fbits = 0, mrest = mF, differs = 0;   // differs: memories in which some cell of the column differs from its lower neighbour
       for (uint32_t s = 0; s < nF; s++) {
         const uint32_t codeF = __ffs(mrest) - 1;
         mrest &= mrest - 1;
@@ -1151,14 +1147,16 @@ __device__ __noinline__ void phase_real_masks(const StageArgs& a, uint32_t n_chu
         for (int k = 0; k < 4; k++) {
           if ((uint32_t)k == c.F || c.idx[k] == 0) continue;
           const uint4 nb = *reinterpret_cast<const uint4*>(R + r_at - st[k]);
-          if (nb.x != r.x || nb.y != r.y || nb.z != r.z) bits[k] |= 1u << c.code[k];
+          if (nb.x != r.x || nb.y != r.y || nb.z != r.z) differs |= 1u << k;
         }
         if (s > 0 && (prev.x != r.x || prev.y != r.y || prev.z != r.z)) fbits |= 1u << codeF;
         prev = r;
       }
 #pragma unroll
-      for (int k = 0; k < 4; k++)
+      for (int k = 0; k < 4; k++) {
         if ((uint32_t)k == c.F) bits[k] = fbits;
+        else if ((differs >> k) & 1u) bits[k] = 1u << nth_set_bit(c.mm[k], c.idx[k]);   // the column's slot in that memory starts at a real breakpoint
+      }
     }
 #pragma unroll
     for (int k = 0; k < 4; k++) bits[k] = __reduce_or_sync(0xFFFFFFFFu, bits[k]);
