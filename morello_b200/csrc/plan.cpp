@@ -535,7 +535,8 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
   // Breadth-first: the Specs found in one round (a range of ids) are tabulated in the next.
   for (u32 round_lo = 0, round_hi = next_id.load(); round_lo < round_hi; round_lo = round_hi, round_hi = next_id.load()) {
     struct ChildKey { u64 h; int len; char bytes[LogicalSpec::MAX_KEY]; };
-    struct alignas(128) PerThread { std::vector<Candidate> scratch; std::vector<ChildKey> keys; std::vector<int> key_of; };
+    struct alignas(128) PerThread { std::vector<Candidate> scratch; std::vector<ChildKey> keys; std::vector<int> key_of;
+                                   std::vector<std::pair<u64, u32>> ranks; std::vector<CandRec> sorted; };
     // (the Move memos live across rounds: see move_memos below)
     std::vector<PerThread> per_thread(n_threads);
     parallel_for(round_hi - round_lo, n_threads, [&](size_t fi, int tid) {
@@ -590,8 +591,27 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         ts.n_leaf += r.kind == MRL_CK_LEAF;
         ts.cands.push_back(r);
       }
-      // final record order, while the records are still in cache
-      std::stable_sort(ts.cands.begin(), ts.cands.end(), cand_before);
+      // final record order, while the records are still in cache: a stable sort by rank; a few
+      // tens of records, so by insertion on (rank, position) pairs
+      {
+        std::vector<std::pair<u64, u32>>& rk = per_thread[tid].ranks;
+        const size_t nr = ts.cands.size();
+        if (nr > 96) {
+          std::stable_sort(ts.cands.begin(), ts.cands.end(), cand_before);
+        } else if (nr > 1) {
+          rk.resize(nr);
+          for (size_t k = 0; k < nr; k++) {
+            const std::pair<u64, u32> me(cand_rank(ts.cands[k]), (u32)k);
+            size_t at = k;
+            while (at > 0 && rk[at - 1].first > me.first) { rk[at] = rk[at - 1]; at--; }
+            rk[at] = me;
+          }
+          std::vector<CandRec>& tmp = per_thread[tid].sorted;
+          tmp.resize(nr);
+          for (size_t k = 0; k < nr; k++) tmp[k] = ts.cands[rk[k].second];
+          memcpy(ts.cands.data(), tmp.data(), nr * sizeof(CandRec));
+        }
+      }
     });
   }
   { std::vector<KeyShard>().swap(shards); }
@@ -707,6 +727,12 @@ Plan build_plan(const std::vector<LogicalSpec>& goals, int n_threads, const u64*
         const u32 t = t_lo + (u32)k;
         TempSpec& ts = temp[t];
         u64 kids = 0;
+        // the children's final ids are scattered reads: ask for all of them before any is needed
+        for (const CandRec& r : ts.cands)
+          for (int j = 0; j < r.nchild; j++) {
+            __builtin_prefetch(&id_a[r.child[j]]);
+            if (twin) __builtin_prefetch(&id_b[r.child[j]]);
+          }
         {
           const u32 id = id_a[t];
           plan.specs[id] = ts.ls;
