@@ -28,6 +28,32 @@ def test_python_binding_covers_the_header(built_extension):
     assert sorted(_lib.EXPORTS) == _declared_functions()
 
 
+def test_python_structs_match_the_header(built_extension, tmp_path):
+    """The ctypes mirrors of the header's structs have the sizes and field offsets a C compiler
+    gives them (the statistics struct grows with the kernels; a field added on one side only would
+    shift everything behind it)."""
+    import shutil
+    import subprocess
+    from morello_b200 import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    fields = [name for name, _ in _lib.Stats._fields_]
+    src = tmp_path / "sizes.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "morello_b200.h"', "int main(void) {",
+             '  printf("%zu\\n", sizeof(mrl_stats));']
+    lines += ['  printf("%%zu\\n", offsetof(mrl_stats, %s));' % f for f in fields]
+    lines += ['  printf("%zu %zu\\n", sizeof(mrl_decision), sizeof(mrl_row));', "  return 0;", "}"]
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "sizes"
+    subprocess.run([cc, "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) == C.sizeof(_lib.Stats)
+    for k, f in enumerate(fields):
+        assert int(out[1 + k]) == getattr(_lib.Stats, f).offset, f
+    assert int(out[-2]) == C.sizeof(_lib.Decision) and int(out[-1]) == C.sizeof(_lib.Row)
+
+
 def test_spec_blobs_roundtrip_and_canonicalise(built_extension):
     import morello_b200 as m
     goal = m.simple_spec(m.KIND_MATMUL, m.DTYPE_U32, [1, 2, 2, 2], m.GL)
