@@ -16,6 +16,7 @@
 // (Move solver); morello/src/scheduling/to_accum.rs:12-62; morello/src/scheduling/select.rs:13-56.
 #pragma once
 #include "spec.hpp"
+#include <cstring>
 #include <memory>
 #include <unordered_map>
 
@@ -348,29 +349,46 @@ inline TileResult tile_operand(const TensorSpec& op, const Shape& tile) {
 class MoveMemo {
  public:
   const TileResult& tile(const TensorSpec& op, const Shape& tile_shape) {
-    char kb[8 + 4 * MAX_RANK + 4 + 4 * MAX_PHYS];
-    int p = operand_key(op, false, kb);
-    for (int i = 0; i < tile_shape.n; i++) { kb[p++] = (char)(tile_shape[i] & 0xff); kb[p++] = (char)(tile_shape[i] >> 8); }
-    std::string key(kb, (size_t)p);
+    Key key;
+    int p = operand_key(op, false, key.bytes);
+    for (int i = 0; i < tile_shape.n; i++) { key.bytes[p++] = (char)(tile_shape[i] & 0xff); key.bytes[p++] = (char)(tile_shape[i] >> 8); }
+    key.len = (u8)p;
     auto it = tiles_.find(key);
     if (it != tiles_.end()) return it->second;
-    return tiles_.emplace(std::move(key), tile_operand(op, tile_shape)).first->second;
+    return tiles_.emplace(key, tile_operand(op, tile_shape)).first->second;
   }
   OperandMoves& get(const TensorSpec& op, bool serial_only) {
-    char kb[8 + 2 * MAX_RANK + 4 + 4 * MAX_PHYS];
-    const int p = operand_key(op, serial_only, kb);
-    std::string key(kb, (size_t)p);
+    Key key;
+    key.len = (u8)operand_key(op, serial_only, key.bytes);
     auto it = map_.find(key);
     if (it != map_.end()) return *it->second;
     std::unique_ptr<OperandMoves> om(new OperandMoves());
     operand_moves(op, serial_only, *om);
     OperandMoves& ref = *om;
-    map_.emplace(std::move(key), std::move(om));
+    map_.emplace(key, std::move(om));
     return ref;
   }
   size_t size() const { return map_.size(); }
 
  private:
+  // An operand (and, for tiles, the tile shape) as bytes, held inline: a lookup allocates nothing.
+  struct Key {
+    static constexpr int CAP = 8 + 4 * MAX_RANK + 4 + 4 * MAX_PHYS;
+    char bytes[CAP];
+    u8 len = 0;
+    bool operator==(const Key& o) const { return len == o.len && memcmp(bytes, o.bytes, len) == 0; }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      u64 h = 0x9E3779B97F4A7C15ull ^ k.len;
+      int i = 0;
+      for (; i + 8 <= k.len; i += 8) { u64 w; memcpy(&w, k.bytes + i, 8); h = (h ^ w) * 0xD6E8FEB86659FD93ull; h ^= h >> 32; }
+      u64 w = 0;
+      if (i < k.len) memcpy(&w, k.bytes + i, (size_t)(k.len - i));
+      h = (h ^ w) * 0xD6E8FEB86659FD93ull;
+      return (size_t)(h ^ (h >> 29));
+    }
+  };
   static int operand_key(const TensorSpec& op, bool flag, char* kb) {
     int p = 0;
     kb[p++] = (char)op.dtype; kb[p++] = (char)flag; kb[p++] = (char)op.shape.n; kb[p++] = (char)op.aux.mem;
@@ -382,8 +400,8 @@ class MoveMemo {
     }
     return p;
   }
-  std::unordered_map<std::string, std::unique_ptr<OperandMoves>> map_;
-  std::unordered_map<std::string, TileResult> tiles_;
+  std::unordered_map<Key, std::unique_ptr<OperandMoves>, KeyHash> map_;
+  std::unordered_map<Key, TileResult, KeyHash> tiles_;
 };
 
 // The body Spec of a tile-out or split: `body` comes in with the new spec_shape; every operand's
